@@ -1,0 +1,170 @@
+/*
+ * mtb200 - C ABI of the B200 (sm_100a) dense-contraction path for minitensor.
+ *
+ * This is the boundary a minitensor build binds (Rust `extern "C"` block,
+ * ctypes, cgo ...).  Every function returns an int32 status (0 = OK); the text
+ * of the last failure on the calling thread is at mtb200_last_error().  No
+ * exception, abort or C++ type crosses the boundary.  All data pointers are
+ * DEVICE pointers owned by the caller (from mtb200_alloc or any other CUDA
+ * allocator on the handle's device); matrices are dense row-major.  Work is
+ * enqueued on the handle's stream and is asynchronous until mtb200_sync.
+ * A handle is used from one host thread at a time.
+ *
+ * File/line references name the minitensor source each entry point stands in
+ * for (paths relative to the minitensor repository root).
+ */
+#ifndef MTB200_H_
+#define MTB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MTB200_VERSION 100
+
+/* status codes */
+enum {
+  MTB200_OK = 0,
+  MTB200_ERR_INVALID = 1,      /* bad argument: shape, null pointer, enum out of range   */
+  MTB200_ERR_CUDA = 2,         /* a CUDA runtime / driver call failed                    */
+  MTB200_ERR_NOMEM = 3,        /* device allocation failed                               */
+  MTB200_ERR_UNSUPPORTED = 4,  /* dtype / option not available for this operation        */
+  MTB200_ERR_DEVICE_WAIT = 5,  /* a bounded wait inside a kernel ran out (see mtb200_sync) */
+  MTB200_ERR_BAD_LABEL = 6     /* class index outside [0, C) seen by cross entropy       */
+};
+
+/* element types, numbered like minitensor's DataType (engine/src/tensor/dtype.rs:12-19) */
+enum { MTB200_F32 = 0, MTB200_F64 = 1, MTB200_I32 = 2, MTB200_I64 = 3, MTB200_BOOL = 4 };
+
+/* epilogues fused into mtb200_gemm */
+enum {
+  MTB200_EPI_NONE = 0,
+  MTB200_EPI_RELU = 1,      /* activation::relu      engine/src/operations/activation/softmax.rs:161-203 */
+  MTB200_EPI_GELU_ERF = 2,  /* activation::gelu exact  engine/src/operations/activation/hyperbolic.rs:697-745 */
+  MTB200_EPI_GELU_TANH = 3, /* activation::gelu approximate (same lines)                                  */
+  MTB200_EPI_RELU_BWD = 4   /* ReluBackward: multiply by (aux > 0)  engine/src/autograd/mod/shape.rs:724-816 */
+};
+
+/* f32 arithmetic modes of mtb200_gemm (argument f32_mode, low byte) */
+enum {
+  MTB200_F32_DEFAULT = 0, /* = MTB200_F32_BF16X6                                   */
+  MTB200_F32_BF16X1 = 1,  /* single bf16 product: ~2^-8 relative, for experiments  */
+  MTB200_F32_BF16X3 = 3,  /* three split products: ~2^-16 relative                 */
+  MTB200_F32_BF16X6 = 6,  /* six split products: f32-accurate (default)            */
+  MTB200_F32_BF16X9 = 9   /* all nine split products                               */
+};
+
+typedef struct mtb200_ctx* mtb200_handle;
+
+/* ---- library / handle ---------------------------------------------------- */
+int32_t mtb200_version(void);
+const char* mtb200_last_error(void);
+
+/* Backend::initialize / is_available  (engine/src/backends/mod.rs:21-46,
+ * engine/src/backends/cuda/mod.rs:164-197).  Fails (MTB200_ERR_CUDA) when the
+ * device is absent or is not compute capability 10.x. */
+int32_t mtb200_create(int32_t device_ordinal, mtb200_handle* out);
+int32_t mtb200_destroy(mtb200_handle h);
+/* Enqueue on an existing cudaStream_t / CUstream from now on (NULL = the CUDA
+ * default stream).  A new handle uses a non-blocking stream of its own. */
+int32_t mtb200_set_stream(mtb200_handle h, void* cuda_stream);
+/* CudaBackend::synchronize (engine/src/backends/cuda/mod.rs:153-161); also
+ * reports MTB200_ERR_DEVICE_WAIT if a kernel recorded an expired wait. */
+int32_t mtb200_sync(mtb200_handle h);
+/* Bytes of scratch memory the handle currently holds (operand splits, partial sums). */
+int32_t mtb200_workspace_bytes(mtb200_handle h, size_t* bytes);
+
+/* ---- memory: Backend::allocate / deallocate / copy_from_host / copy_to_host
+ * (engine/src/backends/mod.rs:30-45; CUDA semantics engine/src/backends/cuda/mod.rs:199-317):
+ * zero bytes -> NULL pointer and OK; true device memory, not unified memory. */
+int32_t mtb200_alloc(mtb200_handle h, size_t bytes, void** dptr);
+int32_t mtb200_free(mtb200_handle h, void* dptr, size_t bytes);
+int32_t mtb200_h2d(mtb200_handle h, void* dst_device, const void* src_host, size_t bytes);
+int32_t mtb200_d2h(mtb200_handle h, void* dst_host, const void* src_device, size_t bytes);
+int32_t mtb200_memset_zero(mtb200_handle h, void* dptr, size_t bytes);
+
+/* ---- GEMM: C[b] = epilogue(op(A[b]) * op(B[b]) + bias)
+ *
+ * Stands in for matmul's dtype dispatch matmul_f32/f64/i32/i64
+ * (engine/src/operations/linalg/matmul.rs:376-385, diagonal.rs:400-640), bmm
+ * (matmul.rs:738-763), the two products of MatMulBackward
+ * (engine/src/autograd/mod/core.rs:752-789: dA = dY*B^T is trans_b = 1,
+ * dB = A^T*dY is trans_a = 1, no materialised transpose), DenseLayer::forward
+ * (engine/src/nn/dense_layer.rs:139-169: trans_b = 1 on the [out,in] weight,
+ * bias fused) and the device op CudaOps::matmul (engine/src/backends/cuda/mod.rs:519-578).
+ *
+ * op(A) is M x K: A is row-major [M,K] (trans_a = 0) or [K,M] (trans_a = 1).
+ * op(B) is K x N: B is row-major [K,N] (trans_b = 0) or [N,K] (trans_b = 1).
+ * C is row-major [M,N].  Batch entries are `stride_*` ELEMENTS apart; a stride
+ * of 0 for A or B broadcasts one matrix over the batch (matmul.rs:324-345).
+ * bias: [N] or NULL.  aux: layout of C, read by MTB200_EPI_RELU_BWD, else NULL.
+ * Epilogues other than NONE need a floating dtype.  K == 0 yields
+ * epilogue(bias) (zeros without bias, matmul.rs:373-376).  Integer dtypes wrap
+ * modulo 2^32 / 2^64. */
+int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t trans_b,
+                    int64_t batch, int64_t M, int64_t N, int64_t K,
+                    const void* A, int64_t stride_a, const void* B, int64_t stride_b,
+                    void* C, int64_t stride_c, const void* bias, int32_t epilogue,
+                    const void* aux, int32_t f32_mode);
+
+/* ---- bias gradient: out[n] = sum_m X[m][n]  (f32 / f64)
+ * reduce_gradient_for_broadcasting -> sum over dim 0
+ * (engine/src/autograd/mod/tests.rs:8-68, engine/src/operations/reduction/sum_prod.rs:7-84).
+ * Deterministic: the same input always gives the same bits. */
+int32_t mtb200_colsum(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, const void* X, void* out);
+
+/* ---- activations outside a GEMM (f32 / f64); act uses the MTB200_EPI_* numbers 1..3.
+ * forward: relu / gelu (engine/src/operations/activation/trigonometry.rs:308-344,499-544).
+ * backward: dx = dy * f'; `ref` is the activation OUTPUT for relu and the
+ * activation INPUT for gelu (engine/src/autograd/mod/shape.rs:724-816,
+ * engine/src/autograd/mod/linalg.rs:118-264). */
+int32_t mtb200_act_fwd(mtb200_handle h, int32_t dtype, int32_t act, int64_t n, const void* x, void* y);
+int32_t mtb200_act_bwd(mtb200_handle h, int32_t dtype, int32_t act, int64_t n, const void* ref,
+                       const void* dy, void* dx);
+
+/* ---- cross entropy with class-index targets, reduction "mean" | "sum"
+ * cross_entropy_loss + CrossEntropyLossBackward
+ * (engine/src/operations/loss/regression.rs:178-251,769-862,
+ *  engine/src/autograd/mod/activation.rs:364-427).
+ * logits f32 [B,C]; labels int32 (label_dtype = MTB200_I32) or int64
+ * (MTB200_I64), [B].  loss: 1 float (device).  dlogits: [B,C] or NULL, receives
+ * (softmax - onehot) * (mean ? 1/B : 1) * upstream.  A label outside [0,C) is
+ * reported by the next mtb200_sync as MTB200_ERR_BAD_LABEL. */
+int32_t mtb200_cross_entropy(mtb200_handle h, int64_t B, int64_t C, const float* logits,
+                             const void* labels, int32_t label_dtype, int32_t mean,
+                             float upstream, float* loss, float* dlogits);
+
+/* ---- Adam / AdamW step over one flat f32 buffer
+ * Adam::apply_adam_update without amsgrad (engine/src/optim/adam.rs:245-312).
+ * step is the 1-based step count after the increment (adam.rs:261-266).
+ * grad_scale multiplies the gradient first (1.0 = reference behaviour). */
+int32_t mtb200_adam_step(mtb200_handle h, int64_t n, float* param, const float* grad, float* m,
+                         float* v, double lr, double beta1, double beta2, double eps,
+                         double weight_decay, int32_t decoupled, int64_t step, float grad_scale);
+
+/* ---- conv2d, NCHW input, OIHW weight, f32 (the reference supports nothing
+ * else: engine/src/operations/conv.rs:85-93,202-204).
+ * forward  = conv2d                     engine/src/operations/conv.rs:24-206
+ * bwd_data / bwd_weight / bwd_bias = Conv2dBackward  engine/src/autograd/mod/shape.rs:57-197 */
+int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
+                          int64_t c_out, int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w,
+                          int64_t pad_h, int64_t pad_w, const float* x, const float* w,
+                          const float* bias, float* y, int32_t f32_mode);
+int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t height,
+                               int64_t width, int64_t c_out, int64_t kh, int64_t kw,
+                               int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w,
+                               const float* dy, const float* w, float* dx, int32_t f32_mode);
+int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64_t height,
+                                 int64_t width, int64_t c_out, int64_t kh, int64_t kw,
+                                 int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w,
+                                 const float* dy, const float* x, float* dw, int32_t f32_mode);
+int32_t mtb200_conv2d_bwd_bias(mtb200_handle h, int64_t n, int64_t c_out, int64_t out_h,
+                               int64_t out_w, const float* dy, float* db);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MTB200_H_ */

@@ -1,0 +1,221 @@
+"""Device backend: a thin object over one ``mtb200`` handle.
+
+It plays the role of minitensor's ``CudaBackend`` + ``CudaOps`` pair
+(``engine/src/backends/cuda/mod.rs:164-317,396-655``): it owns the device
+context for one GPU and exposes the operators of the dense-contraction path on
+raw device buffers.  Buffers are ``torch`` CUDA tensors (torch is used for
+device memory and streams only); every computation goes through the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import (EPI_GELU_ERF, EPI_GELU_TANH, EPI_NONE, EPI_RELU, EPI_RELU_BWD, F32, F64, I32,
+                   I64, check)
+
+_DTYPES = {torch.float32: F32, torch.float64: F64, torch.int32: I32, torch.int64: I64}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bool:
+        raise TypeError("Matrix multiplication not supported for boolean tensors")
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None or t.numel() == 0:
+        return None
+    return t.data_ptr()
+
+
+class Backend:
+    """One handle on one CUDA device; work is enqueued on torch's current stream."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("mtb200 needs a CUDA device (B200, sm_100a); none is visible")
+        self.device = torch.device("cuda", device)
+        h = C.c_void_p()
+        check(self.lib.mtb200_create(device, C.byref(h)))
+        self._h = h
+        self.launches = 0  # kernels this backend enqueued (operand splits count)
+        self._bind_stream()
+
+    def _bind_stream(self) -> None:
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        check(self.lib.mtb200_set_stream(self._h, C.c_void_p(s)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.lib.mtb200_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self) -> None:
+        """Wait for the stream and raise if a kernel reported an expired wait or a bad label."""
+        check(self.lib.mtb200_sync(self._h))
+
+    def workspace_bytes(self) -> int:
+        n = C.c_size_t()
+        check(self.lib.mtb200_workspace_bytes(self._h, C.byref(n)))
+        return n.value
+
+    # ------------------------------------------------------------------ GEMM
+    def gemm(self, a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+             bias: Optional[torch.Tensor] = None, epilogue: int = EPI_NONE,
+             aux: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+             f32_mode: int = 0, variant: int = 0) -> torch.Tensor:
+        """``out[b] = epilogue(op(a[b]) @ op(b[b]) + bias)`` for 2-D or 3-D contiguous operands.
+
+        A 2-D operand next to a 3-D one is broadcast over the batch.
+        """
+        if a.dtype != b.dtype:
+            raise TypeError(f"dtype mismatch: {a.dtype} vs {b.dtype}")
+        dt = dtype_code(a)
+        if not (a.is_contiguous() and b.is_contiguous()):
+            raise ValueError("operands must be contiguous")
+        if a.dim() not in (2, 3) or b.dim() not in (2, 3):
+            raise ValueError("operands must be 2-D or 3-D")
+        batch = 1
+        if a.dim() == 3:
+            batch = a.shape[0]
+        if b.dim() == 3:
+            if a.dim() == 3 and b.shape[0] != batch:
+                raise ValueError(f"batch mismatch: {tuple(a.shape)} vs {tuple(b.shape)}")
+            batch = b.shape[0]
+        am, ak = (a.shape[-1], a.shape[-2]) if trans_a else (a.shape[-2], a.shape[-1])
+        bk, bn = (b.shape[-1], b.shape[-2]) if trans_b else (b.shape[-2], b.shape[-1])
+        if ak != bk:
+            raise ValueError(f"shape mismatch: [{am}, {ak}] x [{bk}, {bn}]")
+        m, n, k = am, bn, ak
+        stride_a = a.shape[-1] * a.shape[-2] if a.dim() == 3 else 0
+        stride_b = b.shape[-1] * b.shape[-2] if b.dim() == 3 else 0
+        batched = a.dim() == 3 or b.dim() == 3
+        shape = (batch, m, n) if batched else (m, n)
+        if out is None:
+            out = torch.empty(shape, dtype=a.dtype, device=a.device)
+        elif tuple(out.shape) != shape or out.dtype != a.dtype or not out.is_contiguous():
+            raise ValueError("bad output tensor")
+        self._bind_stream()
+        check(self.lib.mtb200_gemm(self._h, dt, int(trans_a), int(trans_b), batch, m, n, k,
+                                   _ptr(a), stride_a, _ptr(b), stride_b, _ptr(out), m * n,
+                                   _ptr(bias), epilogue, _ptr(aux), (variant << 8) | f32_mode))
+        self.launches += 3 if dt == F32 else 1
+        return out
+
+    # ------------------------------------------------------------------ reductions / elementwise
+    def colsum(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        m, n = x.shape
+        if out is None:
+            out = torch.empty(n, dtype=x.dtype, device=x.device)
+        self._bind_stream()
+        check(self.lib.mtb200_colsum(self._h, dtype_code(x), m, n, _ptr(x), _ptr(out)))
+        self.launches += 2
+        return out
+
+    def act_fwd(self, x: torch.Tensor, act: int) -> torch.Tensor:
+        y = torch.empty_like(x)
+        self._bind_stream()
+        check(self.lib.mtb200_act_fwd(self._h, dtype_code(x), act, x.numel(), _ptr(x), _ptr(y)))
+        self.launches += 1
+        return y
+
+    def act_bwd(self, ref: torch.Tensor, dy: torch.Tensor, act: int) -> torch.Tensor:
+        dx = torch.empty_like(dy)
+        self._bind_stream()
+        check(self.lib.mtb200_act_bwd(self._h, dtype_code(dy), act, dy.numel(), _ptr(ref), _ptr(dy), _ptr(dx)))
+        self.launches += 1
+        return dx
+
+    def cross_entropy(self, logits: torch.Tensor, labels: torch.Tensor, *, mean: bool = True,
+                      upstream: float = 1.0, want_grad: bool = True):
+        """Returns ``(loss[1], dlogits or None)``; labels int32/int64 class indices."""
+        bsz, ncls = logits.shape
+        if labels.dtype not in (torch.int32, torch.int64):
+            raise TypeError("Unsupported target dtype for classification loss")
+        loss = torch.empty(1, dtype=torch.float32, device=logits.device)
+        dl = torch.empty_like(logits) if want_grad else None
+        self._bind_stream()
+        check(self.lib.mtb200_cross_entropy(self._h, bsz, ncls, _ptr(logits), _ptr(labels),
+                                            _DTYPES[labels.dtype], int(mean), float(upstream),
+                                            _ptr(loss), _ptr(dl)))
+        self.launches += 2
+        return loss, dl
+
+    def adam_step(self, p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *,
+                  lr: float, beta1: float, beta2: float, eps: float, weight_decay: float = 0.0,
+                  decoupled: bool = False, step: int = 1, grad_scale: float = 1.0) -> None:
+        self._bind_stream()
+        check(self.lib.mtb200_adam_step(self._h, p.numel(), _ptr(p), _ptr(g), _ptr(m), _ptr(v), lr, beta1,
+                                        beta2, eps, weight_decay, int(decoupled), step, grad_scale))
+        self.launches += 1
+
+    # ------------------------------------------------------------------ conv2d
+    @staticmethod
+    def _geom(xshape, wshape, stride, padding):
+        n, c, h, w = xshape
+        co, ci, kh, kw = wshape
+        return [n, c, h, w, co, kh, kw, stride[0], stride[1], padding[0], padding[1]]
+
+    def conv2d_fwd(self, x, w, bias, stride, padding, f32_mode: int = 0):
+        n, c, h, wd = x.shape
+        co, ci, kh, kw = w.shape
+        oh = (h + 2 * padding[0] - kh) // stride[0] + 1 if stride[0] > 0 else 0
+        ow = (wd + 2 * padding[1] - kw) // stride[1] + 1 if stride[1] > 0 else 0
+        y = torch.empty((n, co, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
+        self._bind_stream()
+        check(self.lib.mtb200_conv2d_fwd(self._h, *self._geom(x.shape, w.shape, stride, padding),
+                                         _ptr(x), _ptr(w), _ptr(bias), _ptr(y), f32_mode))
+        self.launches += 3
+        return y
+
+    def conv2d_bwd_data(self, dy, w, xshape, stride, padding, f32_mode: int = 0):
+        dx = torch.empty(tuple(xshape), dtype=torch.float32, device=dy.device)
+        self._bind_stream()
+        check(self.lib.mtb200_conv2d_bwd_data(self._h, *self._geom(xshape, w.shape, stride, padding),
+                                              _ptr(dy), _ptr(w), _ptr(dx), f32_mode))
+        self.launches += 4
+        return dx
+
+    def conv2d_bwd_weight(self, dy, x, wshape, stride, padding, f32_mode: int = 0):
+        dw = torch.empty(tuple(wshape), dtype=torch.float32, device=dy.device)
+        self._bind_stream()
+        check(self.lib.mtb200_conv2d_bwd_weight(self._h, *self._geom(x.shape, wshape, stride, padding),
+                                                _ptr(dy), _ptr(x), _ptr(dw), f32_mode))
+        self.launches += 4
+        return dw
+
+    def conv2d_bwd_bias(self, dy):
+        n, co, oh, ow = dy.shape
+        db = torch.empty(co, dtype=torch.float32, device=dy.device)
+        self._bind_stream()
+        check(self.lib.mtb200_conv2d_bwd_bias(self._h, n, co, oh, ow, _ptr(dy), _ptr(db)))
+        self.launches += 2
+        return db
+
+
+_default: dict[int, Backend] = {}
+
+
+def get_backend(device: int = 0) -> Backend:
+    """Per-device singleton, like ``get_backend(Device)`` (engine/src/backends/mod.rs:50-64)."""
+    if device not in _default:
+        _default[device] = Backend(device)
+    return _default[device]
+
+
+__all__ = ["Backend", "get_backend", "EPI_NONE", "EPI_RELU", "EPI_GELU_ERF", "EPI_GELU_TANH",
+           "EPI_RELU_BWD"]

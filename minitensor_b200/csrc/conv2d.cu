@@ -1,0 +1,350 @@
+// conv2d (NCHW / OIHW, f32) lowered to the split-bf16 tensor-core GEMM.
+//
+// The reference computes the convolution with direct loops
+// (engine/src/operations/conv.rs:111-157) and its backward with three more
+// (engine/src/autograd/mod/shape.rs:57-197).  Here each of the four results is
+// a GEMM whose operands are gathered straight into the bf16 split planes the
+// GEMM kernel consumes, with the image as the batch entry so the output lands
+// in NCHW without a transpose:
+//   forward   y[n]  [C_out][OH*OW] = W [C_out][C_in*kH*kW]   * patches(x[n])^T  (+ bias per row)
+//   bwd data  dx[n] [C_in][H*W]    = W'[C_in][C_out*kH*kW]   * patches'(dy[n])^T
+//   bwd weight dW [C_out][C_in*kH*kW] = sum over K chunks of dy[C_out][(n,oh,ow)] * patchesT(x)
+//   bwd bias  db[oc] = sum_{n,oh,ow} dy
+#include "mtb200_core.cuh"
+#include "gemm_launch.cuh"
+#include "rowcol_kernels.cuh"
+
+namespace mtb {
+
+struct ConvGeom {
+  int n, c_in, h, w, c_out, kh, kw, sh, sw, ph, pw, oh, ow;
+};
+
+// Gather modes for the patch operand.
+//  PATCH_FWD : row = output pixel (oh,ow), k = (ic,kh,kw), value x[n][ic][oh*s+kh-p][ow*s+kw-p]
+//  PATCH_BWD : row = input pixel (ih,iw),  k = (oc,kh,kw), value dy[n][oc][(ih+p-kh)/s][(iw+p-kw)/s]
+//              when the division is exact and in range
+enum { PATCH_FWD = 0, PATCH_BWD = 1 };
+
+template <int MODE>
+__device__ __forceinline__ float patch_value(const float* __restrict__ img, const ConvGeom& g, int pix, int k) {
+  const int kk = g.kh * g.kw;
+  const int ch = k / kk;
+  const int r = k - ch * kk;
+  const int fh = r / g.kw, fw = r - fh * g.kw;
+  if (MODE == PATCH_FWD) {
+    const int oy = pix / g.ow, ox = pix - oy * g.ow;
+    const int iy = oy * g.sh + fh - g.ph, ix = ox * g.sw + fw - g.pw;
+    if (iy < 0 || ix < 0 || iy >= g.h || ix >= g.w) return 0.0f;
+    return img[(static_cast<long long>(ch) * g.h + iy) * g.w + ix];
+  } else {
+    const int iy = pix / g.w, ix = pix - iy * g.w;
+    const int ty = iy + g.ph - fh, tx = ix + g.pw - fw;
+    if (ty < 0 || tx < 0 || ty % g.sh || tx % g.sw) return 0.0f;
+    const int oy = ty / g.sh, ox = tx / g.sw;
+    if (oy >= g.oh || ox >= g.ow) return 0.0f;
+    return img[(static_cast<long long>(ch) * g.oh + oy) * g.ow + ox];
+  }
+}
+
+// dst[(n*3+s)][pix][k]: 64 pixels x 64 k per block, turned through shared
+// memory (reads run along pixels, writes along k).
+template <int MODE>
+__global__ void __launch_bounds__(256) patch_split_kernel(const float* __restrict__ src, ConvGeom g,
+                                                          int rows, int K, int Kp, long long img_stride,
+                                                          __nv_bfloat16* __restrict__ dst) {
+  __shared__ float tile[64][65];
+  const int n = blockIdx.z;
+  const int r0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+  const float* img = src + n * img_stride;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  for (int kk = ty; kk < 64; kk += 4) {
+    const int k = k0 + kk, r = r0 + tx;
+    tile[kk][tx] = (k < K && r < rows) ? patch_value<MODE>(img, g, r, k) : 0.0f;
+  }
+  __syncthreads();
+  const long long plane = static_cast<long long>(rows) * Kp;
+  for (int it = threadIdx.x; it < 512; it += 256) {
+    const int rr = it >> 3, kc = (it & 7) << 3;
+    const int r = r0 + rr;
+    if (r >= rows || k0 + kc >= Kp) continue;
+    __align__(16) __nv_bfloat16 o0[8], o1[8], o2[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const Split3 t = split3(tile[kc + e][rr]);
+      o0[e] = t.s0; o1[e] = t.s1; o2[e] = t.s2;
+    }
+    __nv_bfloat16* d = dst + (static_cast<long long>(n) * 3) * plane + static_cast<long long>(r) * Kp + k0 + kc;
+    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(o0);
+    *reinterpret_cast<uint4*>(d + plane) = *reinterpret_cast<const uint4*>(o1);
+    *reinterpret_cast<uint4*>(d + 2 * plane) = *reinterpret_cast<const uint4*>(o2);
+  }
+}
+
+// Operands of the weight-gradient GEMM, reduction index k = (n, oh, ow):
+//  WG_DY    : row = oc,          value dy[n][oc][oh][ow]
+//  WG_PATCH : row = (ic,kh,kw),  value x[n][ic][oh*s+kh-p][ow*s+kw-p]
+// dst[s][row][k], k < Kp (zeros past n*OH*OW).  One thread converts 8 k.
+enum { WG_DY = 0, WG_PATCH = 1 };
+template <int MODE>
+__global__ void __launch_bounds__(256) wgrad_split_kernel(const float* __restrict__ src, ConvGeom g,
+                                                          int rows, long long Ktot, long long Kp,
+                                                          __nv_bfloat16* __restrict__ dst) {
+  const long long chunks = Kp >> 3;
+  const long long total = rows * chunks;
+  const int opix = g.oh * g.ow;
+  const long long plane = static_cast<long long>(rows) * Kp;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / chunks);
+    const long long k0 = (i - row * chunks) << 3;
+    int ch = row, fh = 0, fw = 0;
+    if (MODE == WG_PATCH) {
+      const int kk = g.kh * g.kw;
+      ch = row / kk;
+      const int r = row - ch * kk;
+      fh = r / g.kw;
+      fw = r - fh * g.kw;
+    }
+    __align__(16) __nv_bfloat16 o0[8], o1[8], o2[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const long long k = k0 + e;
+      float v = 0.0f;
+      if (k < Ktot) {
+        const int n = static_cast<int>(k / opix);
+        const int pix = static_cast<int>(k - static_cast<long long>(n) * opix);
+        if (MODE == WG_DY) {
+          v = src[(static_cast<long long>(n) * g.c_out + ch) * opix + pix];
+        } else {
+          const int oy = pix / g.ow, ox = pix - oy * g.ow;
+          const int iy = oy * g.sh + fh - g.ph, ix = ox * g.sw + fw - g.pw;
+          if (iy >= 0 && ix >= 0 && iy < g.h && ix < g.w)
+            v = src[((static_cast<long long>(n) * g.c_in + ch) * g.h + iy) * g.w + ix];
+        }
+      }
+      const Split3 t = split3(v);
+      o0[e] = t.s0; o1[e] = t.s1; o2[e] = t.s2;
+    }
+    __nv_bfloat16* d = dst + static_cast<long long>(row) * Kp + k0;
+    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(o0);
+    *reinterpret_cast<uint4*>(d + plane) = *reinterpret_cast<const uint4*>(o1);
+    *reinterpret_cast<uint4*>(d + 2 * plane) = *reinterpret_cast<const uint4*>(o2);
+  }
+}
+
+// w'[ic][oc][kh][kw] = w[oc][ic][kh][kw]
+__global__ void permute_weight_kernel(const float* __restrict__ w, float* __restrict__ wp, int c_out,
+                                      int c_in, int kk) {
+  const long long total = static_cast<long long>(c_out) * c_in * kk;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i % kk);
+    const long long r = i / kk;
+    const int oc = static_cast<int>(r % c_out), ic = static_cast<int>(r / c_out);
+    wp[i] = w[(static_cast<long long>(oc) * c_in + ic) * kk + t];
+  }
+}
+
+// partial[chunk][oc] = sum over the images of the chunk and all pixels of dy[n][oc][.]
+__global__ void __launch_bounds__(256) conv_bias_partial_kernel(const float* __restrict__ dy, int n, int c_out,
+                                                                int opix, int imgs_per_chunk,
+                                                                float* __restrict__ partial) {
+  __shared__ float red[256];
+  const int oc = blockIdx.x, chunk = blockIdx.y;
+  const int n0 = chunk * imgs_per_chunk, n1 = min(n, n0 + imgs_per_chunk);
+  float s = 0.0f;
+  for (int i = n0; i < n1; ++i) {
+    const float* p = dy + (static_cast<long long>(i) * c_out + oc) * opix;
+    for (int k = threadIdx.x; k < opix; k += 256) s += p[k];
+  }
+  red[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o; o >>= 1) {
+    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[static_cast<long long>(chunk) * c_out + oc] = red[0];
+}
+
+static int32_t check_geom(int64_t n, int64_t c_in, int64_t h, int64_t w, int64_t c_out, int64_t kh,
+                          int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, ConvGeom* g) {
+  if (n < 0 || c_in < 0 || h < 0 || w < 0 || c_out < 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0)
+    return fail(MTB200_ERR_INVALID, "conv2d: negative or empty dimension");
+  if (sh <= 0 || sw <= 0) return fail(MTB200_ERR_INVALID, "stride values must be greater than zero");
+  if (kh > h + 2 * ph || kw > w + 2 * pw)
+    return fail(MTB200_ERR_INVALID, "kernel size cannot be larger than padded input");
+  const int64_t oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+  const int64_t lim = INT32_MAX;
+  if (n > 65535 || c_in * kh * kw > lim || c_out * kh * kw > lim || h * w > lim || oh * ow > lim ||
+      c_in * h * w > lim || c_out * oh * ow > lim)
+    return fail(MTB200_ERR_INVALID, "conv2d: dimension exceeds the limits of the device kernels");
+  *g = ConvGeom{int(n), int(c_in), int(h), int(w), int(c_out), int(kh), int(kw), int(sh), int(sw),
+                int(ph), int(pw), int(oh), int(ow)};
+  return MTB200_OK;
+}
+
+}  // namespace mtb
+
+using namespace mtb;
+
+#define MTB_CHECK_HANDLE(h)                                         \
+  if (!(h)) return fail(MTB200_ERR_INVALID, "null handle");         \
+  DeviceGuard guard__((h)->device);                                 \
+  if (!guard__.ok) return fail(MTB200_ERR_CUDA, "cannot make device %d current", (h)->device)
+
+extern "C" {
+
+int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
+                          int64_t c_out, int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w,
+                          int64_t pad_h, int64_t pad_w, const float* x, const float* w, const float* bias,
+                          float* y, int32_t f32_mode) {
+  MTB_CHECK_HANDLE(h);
+  ConvGeom g;
+  int32_t rc = check_geom(n, c_in, height, width, c_out, kh, kw, stride_h, stride_w, pad_h, pad_w, &g);
+  if (rc) return rc;
+  const int opix = g.oh * g.ow;
+  if (g.n == 0 || g.c_out == 0 || opix == 0) return MTB200_OK;
+  if (!y) return fail(MTB200_ERR_INVALID, "null output pointer");
+  const int K = g.c_in * g.kh * g.kw;
+  if (K == 0) return fail(MTB200_ERR_UNSUPPORTED, "conv2d with zero input channels is not supported");
+  if (!x || !w) return fail(MTB200_ERR_INVALID, "null input pointer");
+  const int Kp = padded_k(K);
+  const size_t bytes_w = split_bytes(g.c_out, Kp, 1), bytes_p = split_bytes(opix, Kp, g.n);
+  void* ws = nullptr;
+  rc = workspace_reserve(h, bytes_w + bytes_p, &ws);
+  if (rc) return rc;
+  __nv_bfloat16* sw_ = static_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* sp = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_w);
+  rc = launch_split(h, w, false, g.c_out, K, Kp, 1, 0, sw_, 3);
+  if (rc) return rc;
+  patch_split_kernel<PATCH_FWD><<<dim3((opix + 63) / 64, Kp / 64, g.n), 256, 0, h->stream>>>(
+      x, g, opix, K, Kp, static_cast<long long>(g.c_in) * g.h * g.w, sp);
+  MTB_CUDA(cudaGetLastError());
+  SplitOperand oa{sw_, g.c_out, 0, 1}, ob{sp, opix, g.n > 1, g.n};
+  return run_split_gemm(h, oa, ob, Kp, g.n, g.c_out, opix, y, opix, static_cast<long long>(g.c_out) * opix,
+                        bias, EPI_NONE, nullptr, f32_mode & 0xff, (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
+}
+
+int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
+                               int64_t c_out, int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w,
+                               int64_t pad_h, int64_t pad_w, const float* dy, const float* w, float* dx,
+                               int32_t f32_mode) {
+  MTB_CHECK_HANDLE(h);
+  ConvGeom g;
+  int32_t rc = check_geom(n, c_in, height, width, c_out, kh, kw, stride_h, stride_w, pad_h, pad_w, &g);
+  if (rc) return rc;
+  const int ipix = g.h * g.w;
+  if (g.n == 0 || g.c_in == 0 || ipix == 0) return MTB200_OK;
+  if (!dx) return fail(MTB200_ERR_INVALID, "null output pointer");
+  const int K = g.c_out * g.kh * g.kw;
+  if (K == 0 || g.oh * g.ow == 0) {
+    MTB_CUDA(cudaMemsetAsync(dx, 0, sizeof(float) * g.n * g.c_in * ipix, h->stream));
+    return MTB200_OK;
+  }
+  if (!dy || !w) return fail(MTB200_ERR_INVALID, "null input pointer");
+  const int Kp = padded_k(K);
+  const size_t bytes_w = split_bytes(g.c_in, Kp, 1), bytes_p = split_bytes(ipix, Kp, g.n);
+  const size_t bytes_perm = align_up(sizeof(float) * size_t(g.c_in) * K, 1024);
+  void* ws = nullptr;
+  rc = workspace_reserve(h, bytes_w + bytes_p + bytes_perm, &ws);
+  if (rc) return rc;
+  __nv_bfloat16* sw_ = static_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* sp = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_w);
+  float* wperm = reinterpret_cast<float*>(static_cast<char*>(ws) + bytes_w + bytes_p);
+  const long long wtotal = static_cast<long long>(g.c_in) * K;
+  permute_weight_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
+      w, wperm, g.c_out, g.c_in, g.kh * g.kw);
+  MTB_CUDA(cudaGetLastError());
+  rc = launch_split(h, wperm, false, g.c_in, K, Kp, 1, 0, sw_, 3);
+  if (rc) return rc;
+  patch_split_kernel<PATCH_BWD><<<dim3((ipix + 63) / 64, Kp / 64, g.n), 256, 0, h->stream>>>(
+      dy, g, ipix, K, Kp, static_cast<long long>(g.c_out) * g.oh * g.ow, sp);
+  MTB_CUDA(cudaGetLastError());
+  SplitOperand oa{sw_, g.c_in, 0, 1}, ob{sp, ipix, g.n > 1, g.n};
+  return run_split_gemm(h, oa, ob, Kp, g.n, g.c_in, ipix, dx, ipix, static_cast<long long>(g.c_in) * ipix,
+                        nullptr, EPI_NONE, nullptr, f32_mode & 0xff, (f32_mode >> 8) & 0xff);
+}
+
+int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
+                                 int64_t c_out, int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w,
+                                 int64_t pad_h, int64_t pad_w, const float* dy, const float* x, float* dw,
+                                 int32_t f32_mode) {
+  MTB_CHECK_HANDLE(h);
+  ConvGeom g;
+  int32_t rc = check_geom(n, c_in, height, width, c_out, kh, kw, stride_h, stride_w, pad_h, pad_w, &g);
+  if (rc) return rc;
+  const int rows_b = g.c_in * g.kh * g.kw;
+  if (g.c_out == 0 || rows_b == 0) return MTB200_OK;
+  if (!dw) return fail(MTB200_ERR_INVALID, "null output pointer");
+  const long long Ktot = static_cast<long long>(g.n) * g.oh * g.ow;
+  const size_t out_elems = size_t(g.c_out) * rows_b;
+  if (Ktot == 0) {
+    MTB_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * out_elems, h->stream));
+    return MTB200_OK;
+  }
+  if (!dy || !x) return fail(MTB200_ERR_INVALID, "null input pointer");
+  // split K: enough chunks to occupy the machine, each a whole number of 64-wide K blocks
+  const long long kblocks = (Ktot + 63) / 64;
+  const int tiles = ((g.c_out + 127) / 128) * ((rows_b + 255) / 256);
+  int chunks = int(std::min<long long>(kblocks, std::max(1, (2 * h->sm_count + tiles - 1) / tiles)));
+  const long long kb_per_chunk = (kblocks + chunks - 1) / chunks;
+  chunks = int((kblocks + kb_per_chunk - 1) / kb_per_chunk);
+  const long long Kp = kb_per_chunk * chunks * 64;
+  if (Kp > INT32_MAX) return fail(MTB200_ERR_INVALID, "conv2d weight gradient: reduction length exceeds 2^31");
+  const size_t bytes_a = align_up(size_t(3) * g.c_out * Kp * 2, 1024);
+  const size_t bytes_b = align_up(size_t(3) * rows_b * Kp * 2, 1024);
+  const size_t bytes_part = align_up(sizeof(float) * out_elems * chunks, 1024);
+  void* ws = nullptr;
+  rc = workspace_reserve(h, bytes_a + bytes_b + bytes_part, &ws);
+  if (rc) return rc;
+  __nv_bfloat16* sa = static_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_a);
+  float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + bytes_a + bytes_b);
+  const int gsz = h->sm_count * 16;
+  wgrad_split_kernel<WG_DY><<<gsz, 256, 0, h->stream>>>(dy, g, g.c_out, Ktot, Kp, sa);
+  wgrad_split_kernel<WG_PATCH><<<gsz, 256, 0, h->stream>>>(x, g, rows_b, Ktot, Kp, sb);
+  MTB_CUDA(cudaGetLastError());
+  SplitOperand oa{sa, g.c_out, 0, 1}, ob{sb, rows_b, 0, 1};
+  float* gemm_out = chunks == 1 ? dw : part;
+  rc = run_split_gemm(h, oa, ob, int(Kp), chunks, g.c_out, rows_b, gemm_out, rows_b, (long long)out_elems,
+                      nullptr, EPI_NONE, nullptr, f32_mode & 0xff, (f32_mode >> 8) & 0xff, 0,
+                      /*kb_batch_stride=*/int(kb_per_chunk), /*num_kb (64-wide)=*/int(kb_per_chunk));
+  if (rc) return rc;
+  if (chunks > 1) {
+    colsum_stage2_kernel<float><<<int((out_elems + 255) / 256), 256, 0, h->stream>>>(part, chunks, int(out_elems), dw);
+    MTB_CUDA(cudaGetLastError());
+  }
+  return MTB200_OK;
+}
+
+int32_t mtb200_conv2d_bwd_bias(mtb200_handle h, int64_t n, int64_t c_out, int64_t out_h, int64_t out_w,
+                               const float* dy, float* db) {
+  MTB_CHECK_HANDLE(h);
+  if (n < 0 || c_out < 0 || out_h < 0 || out_w < 0 || out_h * out_w > INT32_MAX || n > INT32_MAX ||
+      c_out > 65535 * 32)
+    return fail(MTB200_ERR_INVALID, "conv2d bias gradient: bad dimension");
+  if (c_out == 0) return MTB200_OK;
+  if (!db) return fail(MTB200_ERR_INVALID, "null output pointer");
+  const int opix = int(out_h * out_w);
+  if (n == 0 || opix == 0) {
+    MTB_CUDA(cudaMemsetAsync(db, 0, sizeof(float) * c_out, h->stream));
+    return MTB200_OK;
+  }
+  if (!dy) return fail(MTB200_ERR_INVALID, "null input pointer");
+  int chunks = int(std::min<int64_t>(n, std::max<int64_t>(1, (4 * h->sm_count) / c_out)));
+  chunks = std::min(chunks, 65535);
+  const int per = int((n + chunks - 1) / chunks);
+  chunks = int((n + per - 1) / per);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, sizeof(float) * size_t(chunks) * c_out, &ws);
+  if (rc) return rc;
+  float* part = static_cast<float*>(ws);
+  conv_bias_partial_kernel<<<dim3(unsigned(c_out), unsigned(chunks)), 256, 0, h->stream>>>(dy, int(n), int(c_out), opix,
+                                                                                         per, part);
+  colsum_stage2_kernel<float><<<int((c_out + 255) / 256), 256, 0, h->stream>>>(part, chunks, int(c_out), db);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+}  // extern "C"

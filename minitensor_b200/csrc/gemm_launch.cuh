@@ -1,0 +1,117 @@
+// Host-side launch of the split-bf16 GEMM: operand preparation into scratch
+// memory, tensor maps, tile-shape choice, kernel launch.
+#pragma once
+#include "mtb200_core.cuh"
+#include "gemm_split_umma.cuh"
+#include "split_bf16.cuh"
+#include <algorithm>
+
+namespace mtb {
+
+// One prepared operand: bf16 split planes [planes = 3*batch][rows][Kp].
+struct SplitOperand {
+  const __nv_bfloat16* base = nullptr;
+  int rows = 0;
+  int batched = 0;  // 0: a single matrix shared by every batch entry
+  int batch = 1;
+};
+
+inline int padded_k(int K) { return (K + 63) / 64 * 64; }
+inline size_t split_bytes(int rows, int Kp, int batch) {
+  return align_up(size_t(3) * batch * rows * Kp * sizeof(__nv_bfloat16), 1024);
+}
+
+// Write the three bf16 planes of a row-major f32 operand.  `trans` = the
+// source is [K][rows] rather than [rows][K].
+inline int32_t launch_split(mtb200_ctx* h, const float* src, bool trans, int rows, int K, int Kp,
+                            int batch, long long bstride, __nv_bfloat16* dst, int nsplit) {
+  if (!trans) {
+    const long long total = static_cast<long long>(rows) * (Kp / 8);
+    const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
+    split_rows_kernel<<<dim3(blocks, 1, batch), 256, 0, h->stream>>>(src, K, bstride, dst, rows, K, Kp, nsplit);
+  } else {
+    split_cols_kernel<<<dim3((rows + 63) / 64, Kp / 64, batch), 256, 0, h->stream>>>(src, rows, bstride, dst,
+                                                                                   rows, K, Kp, nsplit);
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+template <int BN, int BK, int STAGES>
+inline int32_t launch_variant(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp,
+                              GemmArgs g) {
+  using Cfg = GemmCfg<BN, BK, STAGES>;
+  auto kern = gemm_split_umma_kernel<BN, BK, STAGES>;
+  // per-device attribute; setting it on every launch keeps multi-device processes correct
+  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  CUtensorMap ta, tb;
+  int32_t rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(3) * a.batch, BK, Cfg::BM);
+  if (rc) return rc;
+  rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(3) * b.batch, BK, BN);
+  if (rc) return rc;
+  // split-K arguments count 64-wide K blocks; rescale to this variant's block
+  g.num_kb = g.num_kb ? g.num_kb * (64 / BK) : Kp / BK;
+  g.kb_batch_stride *= (64 / BK);
+  const long long tiles = static_cast<long long>((g.M + Cfg::BM - 1) / Cfg::BM) * ((g.N + BN - 1) / BN) * g.batch;
+  const int grid = int(std::min<long long>(tiles, h->sm_count));
+  kern<<<grid, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(ta, tb, g);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+// C[b] = epilogue(A_split[b] * B_split[b]^T + bias) on prepared operands.
+// variant: 0 = choose by N; 1 = 128x256 tile, K block 32; 2 = 128x128, K block 64;
+// 3 = 128x64, K block 64; 4 = 128x128, K block 32.
+inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp,
+                              int batch, int M, int N, float* C, long long ldc, long long strideC,
+                              const float* bias, int epilogue, const float* aux, int mode, int variant,
+                              int bias_per_row = 0, int kb_batch_stride = 0, int num_kb_override = 0) {
+  if (mode == 0) mode = 6;
+  if (mode != 1 && mode != 3 && mode != 6 && mode != 9)
+    return fail(MTB200_ERR_INVALID, "unknown f32 mode %d (use 0, 1, 3, 6 or 9)", mode);
+  GemmArgs g;
+  g.M = M; g.N = N; g.batch = batch;
+  g.C = C; g.ldc = ldc; g.strideC = strideC;
+  g.bias = bias; g.aux = aux; g.epilogue = epilogue; g.mode = mode;
+  g.a_batched = a.batched; g.b_batched = b.batched;
+  g.status = h->status;
+  g.bias_per_row = bias_per_row;
+  g.kb_batch_stride = kb_batch_stride;
+  g.num_kb = num_kb_override;  // 0: the whole padded K
+  if (variant == 0) variant = (N > 128) ? 1 : (N > 64 ? 2 : 3);
+  switch (variant) {
+    case 1: return launch_variant<256, 32, 3>(h, a, b, Kp, g);
+    case 2: return launch_variant<128, 64, 2>(h, a, b, Kp, g);
+    case 3: return launch_variant<64, 64, 3>(h, a, b, Kp, g);
+    case 4: return launch_variant<128, 32, 4>(h, a, b, Kp, g);
+    default: return fail(MTB200_ERR_INVALID, "unknown GEMM tile variant %d", variant);
+  }
+}
+
+// Full f32 GEMM from row-major f32 operands: split both into scratch, multiply.
+inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int batch, int M, int N, int K,
+                              const float* A, long long stride_a, const float* B, long long stride_b,
+                              float* C, long long ldc, long long stride_c, const float* bias,
+                              int epilogue, const float* aux, int mode, int variant) {
+  const int Kp = padded_k(K);
+  const int batch_a = (stride_a == 0 || batch == 1) ? 1 : batch;
+  const int batch_b = (stride_b == 0 || batch == 1) ? 1 : batch;
+  const size_t bytes_a = split_bytes(M, Kp, batch_a), bytes_b = split_bytes(N, Kp, batch_b);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, bytes_a + bytes_b, &ws);
+  if (rc) return rc;
+  __nv_bfloat16* sa = static_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_a);
+  const int eff_mode = mode == 0 ? 6 : mode;
+  const int nsplit = eff_mode == 1 ? 1 : (eff_mode == 3 ? 2 : 3);
+  // op(A) is [M][K]: stored [M][K] when !trans_a (K-major already), [K][M] when trans_a.
+  rc = launch_split(h, A, trans_a, M, K, Kp, batch_a, stride_a, sa, nsplit);
+  if (rc) return rc;
+  // op(B) is [K][N]: the operand the kernel wants is [N][K]; stored so when trans_b.
+  rc = launch_split(h, B, !trans_b, N, K, Kp, batch_b, stride_b, sb, nsplit);
+  if (rc) return rc;
+  SplitOperand oa{sa, M, batch_a > 1, batch_a}, ob{sb, N, batch_b > 1, batch_b};
+  return run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, mode, variant);
+}
+
+}  // namespace mtb

@@ -1,0 +1,460 @@
+// C ABI of the B200 dense-contraction path: handle, memory, GEMM dispatch,
+// column sum, activations, cross entropy, Adam.  conv2d lives in conv2d.cu.
+// Declarations and the reference interfaces they replace: include/mtb200.h.
+#include "mtb200_core.cuh"
+#include "gemm_split_umma.cuh"
+#include "split_bf16.cuh"
+#include "gemm_f64_int.cuh"
+#include "rowcol_kernels.cuh"
+#include "gemm_launch.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <mutex>
+
+namespace mtb {
+
+thread_local std::string g_last_error;
+
+int32_t workspace_reserve(mtb200_ctx* h, size_t bytes, void** out) {
+  if (bytes > h->workspace_bytes) {
+    MTB_CUDA(cudaStreamSynchronize(h->stream));
+    if (h->workspace) {
+      MTB_CUDA(cudaFree(h->workspace));
+      h->workspace = nullptr;
+      h->workspace_bytes = 0;
+    }
+    const size_t want = align_up(bytes + bytes / 8, size_t(1) << 21);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(MTB200_ERR_NOMEM, "scratch allocation of %zu bytes failed: %s", want,
+                  cudaGetErrorString(e));
+    }
+    h->workspace = p;
+    h->workspace_bytes = want;
+  }
+  *out = h->workspace;
+  return MTB200_OK;
+}
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int32_t make_split_tmap(CUtensorMap* out, const void* base, uint64_t Kp, uint64_t rows,
+                        uint64_t planes, uint32_t bk, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[3] = {Kp, rows, planes};
+  const cuuint64_t strides[2] = {Kp * 2, rows * Kp * 2};  // bytes, dims 1 and 2
+  const cuuint32_t box[3] = {bk, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapSwizzle sw = (bk * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for dims {%llu,%llu,%llu} box {%u,%u}",
+                int(r), (unsigned long long)Kp, (unsigned long long)rows, (unsigned long long)planes, bk,
+                box_rows);
+  return MTB200_OK;
+}
+
+static inline int grid_for(long long n, int threads, int sm_count) {
+  long long blocks = (n + threads - 1) / threads;
+  return int(std::max<long long>(1, std::min<long long>(blocks, (long long)sm_count * 16)));
+}
+
+// compiler-rt's integer power (what Rust's f64::powi lowers to): square and multiply.
+static double powi_f64(double a, int b) {
+  const bool recip = b < 0;
+  double r = 1.0;
+  while (true) {
+    if (b & 1) r *= a;
+    b /= 2;
+    if (b == 0) break;
+    a *= a;
+  }
+  return recip ? 1.0 / r : r;
+}
+
+}  // namespace mtb
+
+using namespace mtb;
+
+#define MTB_CHECK_HANDLE(h)                                         \
+  if (!(h)) return fail(MTB200_ERR_INVALID, "null handle");         \
+  DeviceGuard guard__((h)->device);                                 \
+  if (!guard__.ok) return fail(MTB200_ERR_CUDA, "cannot make device %d current", (h)->device)
+
+extern "C" {
+
+int32_t mtb200_version(void) { return MTB200_VERSION; }
+const char* mtb200_last_error(void) { return g_last_error.c_str(); }
+
+int32_t mtb200_create(int32_t device_ordinal, mtb200_handle* out) {
+  if (!out) return fail(MTB200_ERR_INVALID, "null output handle");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return fail(MTB200_ERR_CUDA, "no CUDA device available (%s)",
+                e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  }
+  if (device_ordinal < 0 || device_ordinal >= count)
+    return fail(MTB200_ERR_INVALID, "device ordinal %d out of range [0,%d)", device_ordinal, count);
+  cudaDeviceProp prop;
+  MTB_CUDA(cudaGetDeviceProperties(&prop, device_ordinal));
+  if (prop.major != 10)
+    return fail(MTB200_ERR_CUDA, "device %d is compute capability %d.%d; this library is built for sm_100a only",
+                device_ordinal, prop.major, prop.minor);
+  DeviceGuard guard(device_ordinal);
+  if (!guard.ok) return fail(MTB200_ERR_CUDA, "cannot make device %d current", device_ordinal);
+  mtb200_ctx* h = new mtb200_ctx();
+  h->device = device_ordinal;
+  h->sm_count = prop.multiProcessorCount;
+  e = cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h->status), 2 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(h->status, 0, 2 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&h->status_host), 2 * sizeof(uint32_t));
+  if (e != cudaSuccess) {
+    if (h->status) cudaFree(h->status);
+    if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    delete h;
+    return fail(MTB200_ERR_CUDA, "handle set-up failed: %s", cudaGetErrorString(e));
+  }
+  h->stream = h->own_stream;
+  *out = h;
+  return MTB200_OK;
+}
+
+int32_t mtb200_destroy(mtb200_handle h) {
+  if (!h) return MTB200_OK;
+  DeviceGuard guard(h->device);
+  cudaStreamSynchronize(h->stream);
+  if (h->workspace) cudaFree(h->workspace);
+  if (h->status) cudaFree(h->status);
+  if (h->status_host) cudaFreeHost(h->status_host);
+  if (h->own_stream) cudaStreamDestroy(h->own_stream);
+  delete h;
+  return MTB200_OK;
+}
+
+int32_t mtb200_set_stream(mtb200_handle h, void* cuda_stream) {
+  MTB_CHECK_HANDLE(h);
+  h->stream = static_cast<cudaStream_t>(cuda_stream);
+  return MTB200_OK;
+}
+
+int32_t mtb200_sync(mtb200_handle h) {
+  MTB_CHECK_HANDLE(h);
+  MTB_CUDA(cudaMemcpyAsync(h->status_host, h->status, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                           h->stream));
+  MTB_CUDA(cudaStreamSynchronize(h->stream));
+  const uint32_t wait_code = h->status_host[0], bad_label = h->status_host[1];
+  if (wait_code || bad_label) {
+    MTB_CUDA(cudaMemsetAsync(h->status, 0, 2 * sizeof(uint32_t), h->stream));
+    MTB_CUDA(cudaStreamSynchronize(h->stream));
+    if (wait_code)
+      return fail(MTB200_ERR_DEVICE_WAIT,
+                  "a bounded wait inside a GEMM kernel ran out (role %u, site %u); results are invalid",
+                  wait_code >> 8, wait_code & 0xffu);
+    return fail(MTB200_ERR_BAD_LABEL, "cross entropy saw a class index outside [0, C)");
+  }
+  return MTB200_OK;
+}
+
+int32_t mtb200_workspace_bytes(mtb200_handle h, size_t* bytes) {
+  if (!h || !bytes) return fail(MTB200_ERR_INVALID, "null argument");
+  *bytes = h->workspace_bytes;
+  return MTB200_OK;
+}
+
+int32_t mtb200_alloc(mtb200_handle h, size_t bytes, void** dptr) {
+  MTB_CHECK_HANDLE(h);
+  if (!dptr) return fail(MTB200_ERR_INVALID, "null output pointer");
+  *dptr = nullptr;
+  if (bytes == 0) return MTB200_OK;
+  cudaError_t e = cudaMalloc(dptr, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    *dptr = nullptr;
+    return fail(MTB200_ERR_NOMEM, "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+  }
+  return MTB200_OK;
+}
+
+int32_t mtb200_free(mtb200_handle h, void* dptr, size_t bytes) {
+  MTB_CHECK_HANDLE(h);
+  (void)bytes;
+  if (!dptr) return MTB200_OK;
+  MTB_CUDA(cudaStreamSynchronize(h->stream));
+  MTB_CUDA(cudaFree(dptr));
+  return MTB200_OK;
+}
+
+int32_t mtb200_h2d(mtb200_handle h, void* dst, const void* src, size_t bytes) {
+  MTB_CHECK_HANDLE(h);
+  if (bytes == 0) return MTB200_OK;
+  if (!dst || !src) return fail(MTB200_ERR_INVALID, "null pointer in host-to-device copy");
+  MTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, h->stream));
+  return MTB200_OK;
+}
+
+int32_t mtb200_d2h(mtb200_handle h, void* dst, const void* src, size_t bytes) {
+  MTB_CHECK_HANDLE(h);
+  if (bytes == 0) return MTB200_OK;
+  if (!dst || !src) return fail(MTB200_ERR_INVALID, "null pointer in device-to-host copy");
+  MTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, h->stream));
+  MTB_CUDA(cudaStreamSynchronize(h->stream));
+  return MTB200_OK;
+}
+
+int32_t mtb200_memset_zero(mtb200_handle h, void* dptr, size_t bytes) {
+  MTB_CHECK_HANDLE(h);
+  if (bytes == 0) return MTB200_OK;
+  if (!dptr) return fail(MTB200_ERR_INVALID, "null pointer");
+  MTB_CUDA(cudaMemsetAsync(dptr, 0, bytes, h->stream));
+  return MTB200_OK;
+}
+
+// ------------------------------------------------------------------ GEMM
+static size_t dtype_size(int32_t dt) {
+  switch (dt) {
+    case MTB200_F32: case MTB200_I32: return 4;
+    case MTB200_F64: case MTB200_I64: return 8;
+    default: return 0;
+  }
+}
+
+int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t trans_b, int64_t batch,
+                    int64_t M, int64_t N, int64_t K, const void* A, int64_t stride_a, const void* B,
+                    int64_t stride_b, void* C, int64_t stride_c, const void* bias, int32_t epilogue,
+                    const void* aux, int32_t f32_mode) {
+  MTB_CHECK_HANDLE(h);
+  if (dtype == MTB200_BOOL)
+    return fail(MTB200_ERR_UNSUPPORTED, "Matrix multiplication not supported for boolean tensors");
+  const size_t es = dtype_size(dtype);
+  if (es == 0) return fail(MTB200_ERR_INVALID, "unknown dtype %d", dtype);
+  if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(MTB200_ERR_INVALID, "negative dimension");
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535)
+    return fail(MTB200_ERR_INVALID, "dimension exceeds the 32-bit limit of the device kernels");
+  if (epilogue < 0 || epilogue > MTB200_EPI_RELU_BWD) return fail(MTB200_ERR_INVALID, "unknown epilogue %d", epilogue);
+  const bool is_float = (dtype == MTB200_F32 || dtype == MTB200_F64);
+  if (!is_float && (epilogue != MTB200_EPI_NONE || bias))
+    return fail(MTB200_ERR_UNSUPPORTED, "bias and activation epilogues need a floating dtype");
+  if (epilogue == MTB200_EPI_RELU_BWD && !aux) return fail(MTB200_ERR_INVALID, "RELU_BWD epilogue needs aux");
+  if (batch == 0 || M == 0 || N == 0) return MTB200_OK;  // nothing to write
+  if (!C) return fail(MTB200_ERR_INVALID, "null output pointer");
+  if (K > 0 && (!A || !B)) return fail(MTB200_ERR_INVALID, "null operand pointer");
+  if (stride_c < M * N && batch > 1) return fail(MTB200_ERR_INVALID, "output batch stride overlaps");
+
+  if (K == 0) {
+    // Empty reduction: the reference leaves the zero-initialised output
+    // (matmul.rs:373-376); a fused bias / activation still applies.
+    for (int64_t b = 0; b < batch; ++b) {
+      char* cb = static_cast<char*>(C) + b * stride_c * es;
+      if (dtype == MTB200_F32) {
+        const float* ax = aux ? static_cast<const float*>(aux) + b * stride_c : nullptr;
+        if (epilogue == MTB200_EPI_RELU_BWD) {
+          MTB_CUDA(cudaMemsetAsync(cb, 0, size_t(M) * N * es, h->stream));  // 0 * mask, bias added first
+          if (bias) {
+            bias_act_kernel<float><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+                nullptr, static_cast<const float*>(bias), reinterpret_cast<float*>(cb), M, int(N), N, 0);
+            act_bwd_kernel<float><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+                ax, reinterpret_cast<float*>(cb), reinterpret_cast<float*>(cb), M * N, 1);
+          }
+        } else {
+          bias_act_kernel<float><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+              nullptr, static_cast<const float*>(bias), reinterpret_cast<float*>(cb), M, int(N), N, epilogue);
+        }
+      } else if (dtype == MTB200_F64) {
+        const double* ax = aux ? static_cast<const double*>(aux) + b * stride_c : nullptr;
+        if (epilogue == MTB200_EPI_RELU_BWD) {
+          MTB_CUDA(cudaMemsetAsync(cb, 0, size_t(M) * N * es, h->stream));
+          if (bias) {
+            bias_act_kernel<double><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+                nullptr, static_cast<const double*>(bias), reinterpret_cast<double*>(cb), M, int(N), N, 0);
+            act_bwd_kernel<double><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+                ax, reinterpret_cast<double*>(cb), reinterpret_cast<double*>(cb), M * N, 1);
+          }
+        } else {
+          bias_act_kernel<double><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+              nullptr, static_cast<const double*>(bias), reinterpret_cast<double*>(cb), M, int(N), N, epilogue);
+        }
+      } else {
+        MTB_CUDA(cudaMemsetAsync(cb, 0, size_t(M) * N * es, h->stream));
+      }
+    }
+    MTB_CUDA(cudaGetLastError());
+    return MTB200_OK;
+  }
+
+  if (dtype == MTB200_F32) {
+    const int mode = f32_mode & 0xff, variant = (f32_mode >> 8) & 0xff;
+    return gemm_f32_split(h, trans_a != 0, trans_b != 0, int(batch), int(M), int(N), int(K),
+                          static_cast<const float*>(A), stride_a, static_cast<const float*>(B), stride_b,
+                          static_cast<float*>(C), N, stride_c, static_cast<const float*>(bias), epilogue,
+                          static_cast<const float*>(aux), mode, variant);
+  }
+
+  StridedGemmArgs g;
+  g.M = int(M); g.N = int(N); g.K = int(K); g.batch = int(batch);
+  g.A = A; g.B = B; g.C = C;
+  g.a_si = trans_a ? 1 : K;  g.a_sk = trans_a ? M : 1;  g.a_sb = stride_a;
+  g.b_sk = trans_b ? 1 : N;  g.b_sj = trans_b ? K : 1;  g.b_sb = stride_b;
+  g.ldc = N; g.c_sb = stride_c;
+  g.bias = bias; g.aux = aux; g.epilogue = epilogue;
+  if (dtype == MTB200_F64) {
+    const int smem = 4 * D_BK * D_PITCH * int(sizeof(double));
+    MTB_CUDA(cudaFuncSetAttribute(gemm_f64_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const long long tiles = ((M + D_BM - 1) / D_BM) * ((N + D_BN - 1) / D_BN);
+    gemm_f64_dmma_kernel<<<dim3(unsigned(tiles), unsigned(batch)), 256, smem, h->stream>>>(g);
+  } else if (dtype == MTB200_I32) {
+    const long long tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    gemm_int_kernel<uint32_t, 8, 8><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(g);
+  } else {
+    const long long tiles = ((M + 127) / 128) * ((N + 63) / 64);
+    gemm_int_kernel<unsigned long long, 8, 4><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(g);
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+// ------------------------------------------------------------------ column sum
+int32_t mtb200_colsum(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, const void* X, void* out) {
+  MTB_CHECK_HANDLE(h);
+  if (dtype != MTB200_F32 && dtype != MTB200_F64)
+    return fail(MTB200_ERR_UNSUPPORTED, "column sum supports f32 and f64");
+  if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return fail(MTB200_ERR_INVALID, "bad dimension");
+  if (N == 0) return MTB200_OK;
+  if (!out) return fail(MTB200_ERR_INVALID, "null output pointer");
+  const size_t es = dtype_size(dtype);
+  if (M == 0) {
+    MTB_CUDA(cudaMemsetAsync(out, 0, size_t(N) * es, h->stream));
+    return MTB200_OK;
+  }
+  if (!X) return fail(MTB200_ERR_INVALID, "null input pointer");
+  const int cols_per_block = 8 * int(16 / es);
+  const int col_blocks = int((N + cols_per_block - 1) / cols_per_block);
+  // enough bands to fill the machine a few times over, at least 32 rows each
+  int bands = int(std::min<int64_t>((M + 31) / 32, std::max<int64_t>(1, (int64_t(h->sm_count) * 8) / col_blocks)));
+  bands = std::max(1, std::min(bands, 1024));
+  const int rows_per_band = int((M + bands - 1) / bands);
+  bands = int((M + rows_per_band - 1) / rows_per_band);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, size_t(bands) * N * es, &ws);
+  if (rc) return rc;
+  if (dtype == MTB200_F32) {
+    colsum_stage1_kernel<float><<<dim3(col_blocks, bands), 256, 0, h->stream>>>(
+        static_cast<const float*>(X), N, int(M), int(N), rows_per_band, static_cast<float*>(ws));
+    colsum_stage2_kernel<float><<<int((N + 255) / 256), 256, 0, h->stream>>>(
+        static_cast<const float*>(ws), bands, int(N), static_cast<float*>(out));
+  } else {
+    colsum_stage1_kernel<double><<<dim3(col_blocks, bands), 256, 0, h->stream>>>(
+        static_cast<const double*>(X), N, int(M), int(N), rows_per_band, static_cast<double*>(ws));
+    colsum_stage2_kernel<double><<<int((N + 255) / 256), 256, 0, h->stream>>>(
+        static_cast<const double*>(ws), bands, int(N), static_cast<double*>(out));
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+// ------------------------------------------------------------------ activations
+int32_t mtb200_act_fwd(mtb200_handle h, int32_t dtype, int32_t act, int64_t n, const void* x, void* y) {
+  MTB_CHECK_HANDLE(h);
+  if (act < 1 || act > 3) return fail(MTB200_ERR_INVALID, "unknown activation %d", act);
+  if (n < 0) return fail(MTB200_ERR_INVALID, "negative length");
+  if (n == 0) return MTB200_OK;
+  if (!x || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  if (dtype == MTB200_F32)
+    act_fwd_kernel<float><<<grid_for(n, 256, h->sm_count), 256, 0, h->stream>>>(
+        static_cast<const float*>(x), static_cast<float*>(y), n, act);
+  else if (dtype == MTB200_F64)
+    act_fwd_kernel<double><<<grid_for(n, 256, h->sm_count), 256, 0, h->stream>>>(
+        static_cast<const double*>(x), static_cast<double*>(y), n, act);
+  else
+    return fail(MTB200_ERR_UNSUPPORTED, "activations support f32 and f64");
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+int32_t mtb200_act_bwd(mtb200_handle h, int32_t dtype, int32_t act, int64_t n, const void* ref,
+                       const void* dy, void* dx) {
+  MTB_CHECK_HANDLE(h);
+  if (act < 1 || act > 3) return fail(MTB200_ERR_INVALID, "unknown activation %d", act);
+  if (n < 0) return fail(MTB200_ERR_INVALID, "negative length");
+  if (n == 0) return MTB200_OK;
+  if (!ref || !dy || !dx) return fail(MTB200_ERR_INVALID, "null pointer");
+  if (dtype == MTB200_F32)
+    act_bwd_kernel<float><<<grid_for(n, 256, h->sm_count), 256, 0, h->stream>>>(
+        static_cast<const float*>(ref), static_cast<const float*>(dy), static_cast<float*>(dx), n, act);
+  else if (dtype == MTB200_F64)
+    act_bwd_kernel<double><<<grid_for(n, 256, h->sm_count), 256, 0, h->stream>>>(
+        static_cast<const double*>(ref), static_cast<const double*>(dy), static_cast<double*>(dx), n, act);
+  else
+    return fail(MTB200_ERR_UNSUPPORTED, "activations support f32 and f64");
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+// ------------------------------------------------------------------ cross entropy
+int32_t mtb200_cross_entropy(mtb200_handle h, int64_t B, int64_t C, const float* logits,
+                             const void* labels, int32_t label_dtype, int32_t mean, float upstream,
+                             float* loss, float* dlogits) {
+  MTB_CHECK_HANDLE(h);
+  if (B <= 0 || C <= 0 || B > INT32_MAX || C > INT32_MAX)
+    return fail(MTB200_ERR_INVALID, "cross entropy needs a non-empty [B,C] logits matrix");
+  if (!logits || !labels || !loss) return fail(MTB200_ERR_INVALID, "null pointer");
+  if (label_dtype != MTB200_I32 && label_dtype != MTB200_I64)
+    return fail(MTB200_ERR_UNSUPPORTED, "Unsupported target dtype for classification loss");
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, size_t(B) * sizeof(float), &ws);
+  if (rc) return rc;
+  float* row_loss = static_cast<float*>(ws);
+  const float inv = mean ? float(1.0 / double(B)) : 1.0f;
+  const float gscale = inv * upstream;
+  const int blocks = int((B * 32 + 255) / 256);
+  if (label_dtype == MTB200_I32)
+    cross_entropy_rows_kernel<int32_t><<<blocks, 256, 0, h->stream>>>(
+        logits, static_cast<const int32_t*>(labels), int(B), int(C), gscale, row_loss, dlogits, h->status + 1);
+  else
+    cross_entropy_rows_kernel<long long><<<blocks, 256, 0, h->stream>>>(
+        logits, static_cast<const long long*>(labels), int(B), int(C), gscale, row_loss, dlogits, h->status + 1);
+  loss_reduce_kernel<<<1, 1024, 0, h->stream>>>(row_loss, int(B), inv, loss);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+// ------------------------------------------------------------------ Adam
+int32_t mtb200_adam_step(mtb200_handle h, int64_t n, float* param, const float* grad, float* m,
+                         float* v, double lr, double beta1, double beta2, double eps,
+                         double weight_decay, int32_t decoupled, int64_t step, float grad_scale) {
+  MTB_CHECK_HANDLE(h);
+  if (n < 0) return fail(MTB200_ERR_INVALID, "negative length");
+  if (step < 1 || step > INT32_MAX) return fail(MTB200_ERR_INVALID, "step count must be >= 1");
+  if (n == 0) return MTB200_OK;
+  if (!param || !grad || !m || !v) return fail(MTB200_ERR_INVALID, "null pointer");
+  const double bc1_inv = 1.0 / (1.0 - powi_f64(beta1, int(step)));
+  const double bc2_inv = 1.0 / (1.0 - powi_f64(beta2, int(step)));
+  const int dec = (decoupled && weight_decay != 0.0) ? 1 : 0;
+  adam_kernel<<<grid_for(n, 256, h->sm_count), 256, 0, h->stream>>>(
+      param, grad, m, v, n, float(lr), float(beta1), float(beta2), float(eps), float(weight_decay),
+      float(bc1_inv), float(bc2_inv), dec, grad_scale);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,87 @@
+// Handle, error reporting, scratch memory and tensor-map helpers shared by the
+// C-ABI translation units.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/mtb200.h"
+
+namespace mtb {
+
+extern thread_local std::string g_last_error;
+
+inline int32_t fail(int32_t code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define MTB_CUDA(expr)                                                                    \
+  do {                                                                                    \
+    cudaError_t e__ = (expr);                                                             \
+    if (e__ != cudaSuccess)                                                               \
+      return ::mtb::fail(e__ == cudaErrorMemoryAllocation ? MTB200_ERR_NOMEM : MTB200_ERR_CUDA, \
+                         "%s failed: %s", #expr, cudaGetErrorString(e__));                \
+  } while (0)
+
+}  // namespace mtb
+
+// Device status word layout: [0] expired-wait code of the GEMM kernels,
+// [1] bad-label flag of cross entropy.
+struct mtb200_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
+  uint32_t* status = nullptr;       // device, 2 words
+  uint32_t* status_host = nullptr;  // pinned, 2 words
+};
+
+namespace mtb {
+
+// Make the handle's device current for the duration of a call.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    want = dev;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0 && prev != want) cudaSetDevice(prev);
+  }
+  int want = -1;
+};
+
+// Scratch memory of at least `bytes`, valid for work enqueued on the handle's
+// stream until the next call that asks for more.  Growing synchronises the
+// stream first so no kernel still reads the old block.
+int32_t workspace_reserve(mtb200_ctx* h, size_t bytes, void** out);
+
+// cuTensorMapEncodeTiled looked up through the runtime (no link-time
+// dependency on libcuda, so the library also loads on a machine without a driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_tiled();
+
+// 3-D bf16 tensor map over split planes: dims {Kp, rows, planes}, box {bk, box_rows, 1}.
+int32_t make_split_tmap(CUtensorMap* out, const void* base, uint64_t Kp, uint64_t rows,
+                        uint64_t planes, uint32_t bk, uint32_t box_rows);
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace mtb
