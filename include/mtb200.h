@@ -125,6 +125,13 @@ int32_t mtb200_act_fwd(mtb200_handle h, int32_t dtype, int32_t act, int64_t n, c
 int32_t mtb200_act_bwd(mtb200_handle h, int32_t dtype, int32_t act, int64_t n, const void* ref,
                        const void* dy, void* dx);
 
+/* ---- broadcast bias add with optional activation: y[m][n] = act(x[m][n] + bias[n])
+ * the [M,N] + [N] case of arithmetic::add that DenseLayer uses
+ * (engine/src/operations/arithmetic/kernels.rs:191-334, engine/src/nn/dense_layer.rs:163-166).
+ * act: 0 none or MTB200_EPI_RELU / GELU_ERF / GELU_TANH.  x and y may alias. */
+int32_t mtb200_bias_act(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, const void* x,
+                        const void* bias, int32_t act, void* y);
+
 /* ---- cross entropy with class-index targets, reduction "mean" | "sum"
  * cross_entropy_loss + CrossEntropyLossBackward
  * (engine/src/operations/loss/regression.rs:178-251,769-862,

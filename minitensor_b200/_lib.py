@@ -40,6 +40,7 @@ SIGNATURES = {
     "mtb200_colsum": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
     "mtb200_act_fwd": (_i32, [_vp, _i32, _i32, _i64, _vp, _vp]),
     "mtb200_act_bwd": (_i32, [_vp, _i32, _i32, _i64, _vp, _vp, _vp]),
+    "mtb200_bias_act": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _i32, _vp]),
     "mtb200_cross_entropy": (_i32, [_vp, _i64, _i64, _vp, _vp, _i32, _i32, _f32, _vp, _vp]),
     "mtb200_adam_step": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64, _i32,
                                 _i64, _f32]),

@@ -126,6 +126,16 @@ class Backend:
         self.launches += 2
         return out
 
+    def bias_act(self, x: torch.Tensor, bias: Optional[torch.Tensor], act: int = 0) -> torch.Tensor:
+        """``act(x + bias)`` with ``bias`` broadcast over the rows of the 2-D view of ``x``."""
+        n = x.shape[-1]
+        y = torch.empty_like(x)
+        self._bind_stream()
+        check(self.lib.mtb200_bias_act(self._h, dtype_code(x), x.numel() // max(n, 1), n, _ptr(x), _ptr(bias),
+                                       act, _ptr(y)))
+        self.launches += 1
+        return y
+
     def act_fwd(self, x: torch.Tensor, act: int) -> torch.Tensor:
         y = torch.empty_like(x)
         self._bind_stream()
@@ -154,6 +164,20 @@ class Backend:
                                             _ptr(loss), _ptr(dl)))
         self.launches += 2
         return loss, dl
+
+    def cross_entropy_into(self, logits: torch.Tensor, labels: torch.Tensor, dlogits: torch.Tensor, *,
+                           mean: bool = True, upstream: float = 1.0):
+        """Same as :meth:`cross_entropy` with the gradient written into ``dlogits``."""
+        bsz, ncls = logits.shape
+        if tuple(dlogits.shape) != (bsz, ncls) or dlogits.dtype != torch.float32:
+            raise ValueError("bad gradient buffer")
+        loss = torch.empty(1, dtype=torch.float32, device=logits.device)
+        self._bind_stream()
+        check(self.lib.mtb200_cross_entropy(self._h, bsz, ncls, _ptr(logits), _ptr(labels),
+                                            _DTYPES[labels.dtype], int(mean), float(upstream),
+                                            _ptr(loss), _ptr(dlogits)))
+        self.launches += 2
+        return loss, dlogits
 
     def adam_step(self, p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *,
                   lr: float, beta1: float, beta2: float, eps: float, weight_decay: float = 0.0,

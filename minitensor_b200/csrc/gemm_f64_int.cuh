@@ -8,12 +8,17 @@
 //    (engine/src/operations/linalg/diagonal.rs:495-548): addition and
 //    multiplication modulo 2^32 / 2^64 are associative, so the order of the
 //    partial sums cannot change the answer.
+//  * f32 on the CUDA cores (same kernel, T = float): plain IEEE multiply-add,
+//    run only when an operand of the split-bf16 tensor path held an Inf or
+//    NaN, because Inf times the zero low-order split of a finite value would
+//    turn the reference's Inf results into NaN.
 //
 // Operand addressing is by strides so the same kernels serve the NN / NT / TN
 // / TT forms: element (i, k) of A is A[i*a_si + k*a_sk], element (k, j) of B
 // is B[k*b_sk + j*b_sj].
 #pragma once
 #include <cstdint>
+#include <type_traits>
 
 namespace mtb {
 
@@ -28,6 +33,8 @@ struct StridedGemmArgs {
   const void* bias;            // [N] or nullptr
   const void* aux;             // layout of C, for EPI_RELU_BWD
   int epilogue;
+  const uint32_t* gate;        // optional: the kernel runs only when *gate == gate_value
+  uint32_t gate_value;
 };
 
 __device__ __forceinline__ double apply_epilogue_f64(double x, int epi, double aux) {
@@ -97,7 +104,7 @@ __device__ __forceinline__ void dgemm_stash(double* __restrict__ sm, long long s
   }
 }
 
-__global__ void __launch_bounds__(256, 1) gemm_f64_dmma_kernel(const StridedGemmArgs g) {
+static __global__ void __launch_bounds__(256, 1) gemm_f64_dmma_kernel(const StridedGemmArgs g) {
   extern __shared__ __align__(16) uint8_t dsm_raw[];
   double* As = reinterpret_cast<double*>(dsm_raw);  // [2][D_BK][D_PITCH]
   double* Bs = As + 2 * D_BK * D_PITCH;             // [2][D_BK][D_PITCH]
@@ -181,8 +188,9 @@ __global__ void __launch_bounds__(256, 1) gemm_f64_dmma_kernel(const StridedGemm
 // as 16 x 16; each thread owns a TM x TN register tile made of interleaved
 // groups of 4 so shared-memory reads are 16-byte vectors.
 template <typename T, int TM, int TN>
-__global__ void __launch_bounds__(256) gemm_int_kernel(const StridedGemmArgs g) {
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const StridedGemmArgs g) {
   constexpr int BM = 16 * TM, BN = 16 * TN, BK = 16;
+  if (g.gate && *g.gate != g.gate_value) return;
   constexpr int PA = BM + 4, PB = BN + 4;
   __shared__ T As[BK][PA];
   __shared__ T Bs[BK][PB];
@@ -238,7 +246,17 @@ __global__ void __launch_bounds__(256) gemm_int_kernel(const StridedGemmArgs g) 
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       const int col = tn * BN + (j / 4) * 64 + tx * 4 + (j % 4);
-      if (col < g.N) C[(long long)row * g.ldc + col] = acc[i][j];
+      if (col < g.N) {
+        T x = acc[i][j];
+        if constexpr (std::is_floating_point<T>::value) {  // fused bias / activation
+          if (g.bias) x += static_cast<const T*>(g.bias)[col];
+          const T ax = (g.epilogue == 4)
+                           ? (static_cast<const T*>(g.aux) + b * g.c_sb)[(long long)row * g.ldc + col]
+                           : T(0);
+          x = static_cast<T>(apply_epilogue_f64(x, g.epilogue, ax));
+        }
+        C[(long long)row * g.ldc + col] = x;
+      }
     }
   }
 }

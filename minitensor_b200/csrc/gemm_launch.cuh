@@ -4,6 +4,7 @@
 #include "mtb200_core.cuh"
 #include "gemm_split_umma.cuh"
 #include "split_bf16.cuh"
+#include "gemm_f64_int.cuh"
 #include <algorithm>
 
 namespace mtb {
@@ -24,14 +25,16 @@ inline size_t split_bytes(int rows, int Kp, int batch) {
 // Write the three bf16 planes of a row-major f32 operand.  `trans` = the
 // source is [K][rows] rather than [rows][K].
 inline int32_t launch_split(mtb200_ctx* h, const float* src, bool trans, int rows, int K, int Kp,
-                            int batch, long long bstride, __nv_bfloat16* dst, int nsplit) {
+                            int batch, long long bstride, __nv_bfloat16* dst, int nsplit,
+                            uint32_t* nf_word = nullptr, uint32_t nf_epoch = 0) {
   if (!trans) {
     const long long total = static_cast<long long>(rows) * (Kp / 8);
     const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
-    split_rows_kernel<<<dim3(blocks, 1, batch), 256, 0, h->stream>>>(src, K, bstride, dst, rows, K, Kp, nsplit);
+    split_rows_kernel<<<dim3(blocks, 1, batch), 256, 0, h->stream>>>(src, K, bstride, dst, rows, K, Kp, nsplit,
+                                                                     nf_word, nf_epoch);
   } else {
-    split_cols_kernel<<<dim3((rows + 63) / 64, Kp / 64, batch), 256, 0, h->stream>>>(src, rows, bstride, dst,
-                                                                                   rows, K, Kp, nsplit);
+    split_cols_kernel<<<dim3((rows + 63) / 64, Kp / 64, batch), 256, 0, h->stream>>>(
+        src, rows, bstride, dst, rows, K, Kp, nsplit, nf_word, nf_epoch);
   }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
@@ -105,13 +108,30 @@ inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int bat
   const int eff_mode = mode == 0 ? 6 : mode;
   const int nsplit = eff_mode == 1 ? 1 : (eff_mode == 3 ? 2 : 3);
   // op(A) is [M][K]: stored [M][K] when !trans_a (K-major already), [K][M] when trans_a.
-  rc = launch_split(h, A, trans_a, M, K, Kp, batch_a, stride_a, sa, nsplit);
+  uint32_t* nf_word = h->status + 2;
+  const uint32_t epoch = ++h->epoch;
+  rc = launch_split(h, A, trans_a, M, K, Kp, batch_a, stride_a, sa, nsplit, nf_word, epoch);
   if (rc) return rc;
   // op(B) is [K][N]: the operand the kernel wants is [N][K]; stored so when trans_b.
-  rc = launch_split(h, B, !trans_b, N, K, Kp, batch_b, stride_b, sb, nsplit);
+  rc = launch_split(h, B, !trans_b, N, K, Kp, batch_b, stride_b, sb, nsplit, nf_word, epoch);
   if (rc) return rc;
   SplitOperand oa{sa, M, batch_a > 1, batch_a}, ob{sb, N, batch_b > 1, batch_b};
-  return run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, mode, variant);
+  rc = run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, mode, variant);
+  if (rc) return rc;
+  // Inf / NaN operands: redo the product with IEEE f32 multiply-add.  The kernel
+  // returns at once unless a split kernel of THIS call raised the word.
+  StridedGemmArgs s;
+  s.M = M; s.N = N; s.K = K; s.batch = batch;
+  s.A = A; s.B = B; s.C = C;
+  s.a_si = trans_a ? 1 : K;  s.a_sk = trans_a ? M : 1;  s.a_sb = stride_a;
+  s.b_sk = trans_b ? 1 : N;  s.b_sj = trans_b ? K : 1;  s.b_sb = stride_b;
+  s.ldc = ldc; s.c_sb = stride_c;
+  s.bias = bias; s.aux = aux; s.epilogue = epilogue;
+  s.gate = nf_word; s.gate_value = epoch;
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+  gemm_simt_kernel<float, 8, 8><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(s);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
 }
 
 }  // namespace mtb

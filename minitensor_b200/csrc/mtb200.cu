@@ -126,8 +126,8 @@ int32_t mtb200_create(int32_t device_ordinal, mtb200_handle* out) {
   h->device = device_ordinal;
   h->sm_count = prop.multiProcessorCount;
   e = cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking);
-  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h->status), 2 * sizeof(uint32_t));
-  if (e == cudaSuccess) e = cudaMemset(h->status, 0, 2 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h->status), 4 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(h->status, 0, 4 * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&h->status_host), 2 * sizeof(uint32_t));
   if (e != cudaSuccess) {
     if (h->status) cudaFree(h->status);
@@ -317,6 +317,7 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
   g.b_sk = trans_b ? 1 : N;  g.b_sj = trans_b ? K : 1;  g.b_sb = stride_b;
   g.ldc = N; g.c_sb = stride_c;
   g.bias = bias; g.aux = aux; g.epilogue = epilogue;
+  g.gate = nullptr; g.gate_value = 0;
   if (dtype == MTB200_F64) {
     const int smem = 4 * D_BK * D_PITCH * int(sizeof(double));
     MTB_CUDA(cudaFuncSetAttribute(gemm_f64_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -324,10 +325,10 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
     gemm_f64_dmma_kernel<<<dim3(unsigned(tiles), unsigned(batch)), 256, smem, h->stream>>>(g);
   } else if (dtype == MTB200_I32) {
     const long long tiles = ((M + 127) / 128) * ((N + 127) / 128);
-    gemm_int_kernel<uint32_t, 8, 8><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(g);
+    gemm_simt_kernel<uint32_t, 8, 8><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(g);
   } else {
     const long long tiles = ((M + 127) / 128) * ((N + 63) / 64);
-    gemm_int_kernel<unsigned long long, 8, 4><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(g);
+    gemm_simt_kernel<unsigned long long, 8, 4><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(g);
   }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
@@ -406,6 +407,25 @@ int32_t mtb200_act_bwd(mtb200_handle h, int32_t dtype, int32_t act, int64_t n, c
         static_cast<const double*>(ref), static_cast<const double*>(dy), static_cast<double*>(dx), n, act);
   else
     return fail(MTB200_ERR_UNSUPPORTED, "activations support f32 and f64");
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+int32_t mtb200_bias_act(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, const void* x,
+                        const void* bias, int32_t act, void* y) {
+  MTB_CHECK_HANDLE(h);
+  if (act < 0 || act > 3) return fail(MTB200_ERR_INVALID, "unknown activation %d", act);
+  if (M < 0 || N < 0 || N > INT32_MAX) return fail(MTB200_ERR_INVALID, "bad dimension");
+  if (M == 0 || N == 0) return MTB200_OK;
+  if (!x || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  if (dtype == MTB200_F32)
+    bias_act_kernel<float><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+        static_cast<const float*>(x), static_cast<const float*>(bias), static_cast<float*>(y), M, int(N), N, act);
+  else if (dtype == MTB200_F64)
+    bias_act_kernel<double><<<grid_for(M * N, 256, h->sm_count), 256, 0, h->stream>>>(
+        static_cast<const double*>(x), static_cast<const double*>(bias), static_cast<double*>(y), M, int(N), N, act);
+  else
+    return fail(MTB200_ERR_UNSUPPORTED, "bias add supports f32 and f64");
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
 }

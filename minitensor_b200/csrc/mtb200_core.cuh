@@ -36,7 +36,8 @@ inline int32_t fail(int32_t code, const char* fmt, ...) {
 }  // namespace mtb
 
 // Device status word layout: [0] expired-wait code of the GEMM kernels,
-// [1] bad-label flag of cross entropy.
+// [1] bad-label flag of cross entropy, [2] epoch of the last f32 GEMM whose
+// operands held an Inf or NaN.
 struct mtb200_ctx {
   int device = 0;
   int sm_count = 0;
@@ -44,8 +45,9 @@ struct mtb200_ctx {
   cudaStream_t stream = nullptr;
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
-  uint32_t* status = nullptr;       // device, 2 words
+  uint32_t* status = nullptr;       // device, 4 words
   uint32_t* status_host = nullptr;  // pinned, 2 words
+  uint32_t epoch = 0;               // f32 GEMM call counter (see status[2])
 };
 
 namespace mtb {

@@ -3,7 +3,9 @@
 // remainders x - x0 and x - x0 - x1 are exact in f32).  Output layout, the
 // one the GEMM's tensor maps describe:
 //   dst[(b*3 + s)][r][k]  bf16,  r < R rows, k < Kp (K padded with zeros)
-// i.e. always K-major, whatever the orientation of the source.  The source is
+// i.e. always K-major, whatever the orientation of the source.  A kernel that
+// meets an Inf or NaN raises *nf_word to nf_epoch (the caller's per-GEMM
+// counter) so the GEMM can be redone in plain f32 arithmetic afterwards.  The source is
 // a row-major f32 matrix per batch entry, either [R][K] (trans = 0) or
 // [K][R] (trans = 1); the second form is how the transposes the reference
 // materialises (engine/src/operations/linalg/triangular.rs:8-73) are absorbed.
@@ -16,6 +18,10 @@ namespace mtb {
 struct Split3 {
   __nv_bfloat16 s0, s1, s2;
 };
+
+__device__ __forceinline__ bool is_nonfinite(float x) {
+  return (__float_as_uint(x) & 0x7f800000u) == 0x7f800000u;
+}
 
 __device__ __forceinline__ Split3 split3(float x) {
   Split3 r;
@@ -45,7 +51,7 @@ __device__ __forceinline__ Split3 split3(float x) {
 // k and writes one 16-byte vector per split.
 static __global__ void split_rows_kernel(const float* __restrict__ src, long long ld, long long bstride,
                                   __nv_bfloat16* __restrict__ dst, int R, int K, int Kp,
-                                  int nsplit_out) {
+                                  int nsplit_out, uint32_t* __restrict__ nf_word, uint32_t nf_epoch) {
   const int b = blockIdx.z;
   const int chunks = Kp >> 3;
   const long long total = static_cast<long long>(R) * chunks;
@@ -67,11 +73,14 @@ static __global__ void split_rows_kernel(const float* __restrict__ src, long lon
       for (int e = 0; e < 8; ++e) x[e] = (k0 + e < K) ? p[e] : 0.0f;
     }
     __align__(16) __nv_bfloat16 o0[8], o1[8], o2[8];
+    bool nf = false;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const Split3 t = split3(x[e]);
+      nf |= is_nonfinite(x[e]);
       o0[e] = t.s0; o1[e] = t.s1; o2[e] = t.s2;
     }
+    if (nf && nf_word) atomicMax(nf_word, nf_epoch);
     const long long plane = static_cast<long long>(R) * Kp;
     __nv_bfloat16* d = dst + (static_cast<long long>(b) * 3) * plane + static_cast<long long>(r) * Kp + k0;
     *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(o0);
@@ -85,7 +94,7 @@ static __global__ void split_rows_kernel(const float* __restrict__ src, long lon
 // coalesced.  Block = 256 threads, tile = 64 (k) x 64 (r).
 static __global__ void split_cols_kernel(const float* __restrict__ src, long long ld, long long bstride,
                                   __nv_bfloat16* __restrict__ dst, int R, int K, int Kp,
-                                  int nsplit_out) {
+                                  int nsplit_out, uint32_t* __restrict__ nf_word, uint32_t nf_epoch) {
   __shared__ float tile[64][65];
   const int b = blockIdx.z;
   const int r0 = blockIdx.x * 64;
@@ -107,11 +116,15 @@ static __global__ void split_cols_kernel(const float* __restrict__ src, long lon
     const int r = r0 + rr;
     if (r >= R || k0 + kc >= Kp) continue;
     __align__(16) __nv_bfloat16 o0[8], o1[8], o2[8];
+    bool nf = false;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const Split3 t = split3(tile[kc + e][rr]);
+      const float xv = tile[kc + e][rr];
+      const Split3 t = split3(xv);
+      nf |= is_nonfinite(xv);
       o0[e] = t.s0; o1[e] = t.s1; o2[e] = t.s2;
     }
+    if (nf && nf_word) atomicMax(nf_word, nf_epoch);
     __nv_bfloat16* d = dst + (static_cast<long long>(b) * 3) * plane + static_cast<long long>(r) * Kp + k0 + kc;
     *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(o0);
     if (nsplit_out > 1) *reinterpret_cast<uint4*>(d + plane) = *reinterpret_cast<const uint4*>(o1);

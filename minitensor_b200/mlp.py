@@ -1,0 +1,170 @@
+"""Device-resident MLP training step: DenseLayer -> ReLU -> ... -> DenseLayer,
+CrossEntropyLoss(mean), Adam.
+
+This is the reference's training loop of ``nn.Sequential`` + ``nn.CrossEntropyLoss``
++ ``optim.Adam`` (``engine/src/nn/sequential.rs:74-83``, ``nn/dense_layer.rs:139-169``,
+``operations/loss/regression.rs:178-251``, ``autograd/graph.rs:222-282``,
+``optim/adam.rs:483-514``) laid out for one GPU per process:
+
+* parameters, gradients and Adam moments are four flat f32 buffers in layer
+  order (W [out,in] then b [out] per layer); one Adam launch updates everything;
+* activations and gradient buffers are allocated once;
+* forward   h_{l+1} = relu(h_l W_l^T + b_l)     one GEMM, bias + ReLU in the epilogue
+* backward  db_l = colsum(g), dW_l = g^T h_l     GEMM writes straight into the flat gradient
+            g   <- (g W_l) * (h_l > 0)           one GEMM, ReLU mask in the epilogue
+  (no dX for the first layer: the input does not require grad, ``autograd/mod/core.rs:763``);
+* with ``world_size`` > 1 the batch is sharded by rows, each layer's slice of the
+  flat gradient is all-reduced (sum, NCCL) as soon as it is written, while the
+  remaining backward GEMMs run, and Adam applies ``1/world_size`` so every rank
+  takes the same step on the mean of the per-rank gradients.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ._lib import EPI_NONE, EPI_RELU, EPI_RELU_BWD
+from .backend import Backend, get_backend
+
+
+def mlp_layout(dims: Sequence[int]):
+    """Offsets of every layer's W and b in the flat parameter buffer: (w_off, b_off, total)."""
+    w_off, b_off, total = [], [], 0
+    for l in range(len(dims) - 1):
+        w_off.append(total)
+        total += int(dims[l]) * int(dims[l + 1])
+        b_off.append(total)
+        total += int(dims[l + 1])
+    return w_off, b_off, total
+
+
+def shard_rows(n_rows: int, world_size: int, rank: int):
+    """Row range [lo, hi) of the global batch that ``rank`` trains on (equal shards)."""
+    if n_rows % world_size:
+        raise ValueError(f"global batch {n_rows} is not divisible by world size {world_size}")
+    per = n_rows // world_size
+    return rank * per, (rank + 1) * per
+
+
+def mlp_flops_per_sample(dims: Sequence[int]) -> int:
+    """2*in*out per layer forward, twice that backward, minus the first layer's dX."""
+    fwd = sum(2 * int(dims[l]) * int(dims[l + 1]) for l in range(len(dims) - 1))
+    return 3 * fwd - 2 * int(dims[0]) * int(dims[1])
+
+
+class MLPTrainer:
+    def __init__(self, dims: Sequence[int], batch: int, *, lr: float = 1e-3, beta1: float = 0.9,
+                 beta2: float = 0.999, eps: float = 1e-8, device: int = 0, world_size: int = 1,
+                 seed: int = 0, f32_mode: int = 0, init_params: Optional[np.ndarray] = None):
+        """``batch`` is the number of rows THIS process handles per step."""
+        if len(dims) < 2 or any(d <= 0 for d in dims) or batch <= 0:
+            raise ValueError("dims needs at least two positive entries and batch must be positive")
+        self.dims = [int(d) for d in dims]
+        self.nl = len(dims) - 1
+        self.batch = int(batch)
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+        self.world_size = int(world_size)
+        self.f32_mode = f32_mode
+        self.be: Backend = get_backend(device)
+        dev = self.be.device
+        self.w_off, self.b_off, total = mlp_layout(self.dims)
+        self.n_params = total
+        if init_params is None:
+            # He-uniform weights (bound sqrt(6/fan_in), engine/src/nn/init.rs:471-491), zero biases;
+            # the same seed gives every rank the same replica
+            rng = np.random.default_rng(seed)
+            init_params = np.zeros(total, dtype=np.float32)
+            for l in range(self.nl):
+                fan_in, out_f = self.dims[l], self.dims[l + 1]
+                bound = math.sqrt(6.0 / fan_in)
+                init_params[self.w_off[l]:self.w_off[l] + fan_in * out_f] = rng.uniform(
+                    -bound, bound, fan_in * out_f).astype(np.float32)
+        if init_params.shape != (total,) or init_params.dtype != np.float32:
+            raise ValueError("init_params must be a flat float32 array of all W, b in layer order")
+        self.params = torch.from_numpy(init_params.copy()).to(dev)
+        self.grads = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.m = torch.zeros_like(self.grads)
+        self.v = torch.zeros_like(self.grads)
+        self.step_count = 0
+        self.W = [self.params[self.w_off[l]:self.w_off[l] + self.dims[l] * self.dims[l + 1]].view(
+            self.dims[l + 1], self.dims[l]) for l in range(self.nl)]
+        self.b = [self.params[self.b_off[l]:self.b_off[l] + self.dims[l + 1]] for l in range(self.nl)]
+        self.dW = [self.grads[self.w_off[l]:self.w_off[l] + self.dims[l] * self.dims[l + 1]].view(
+            self.dims[l + 1], self.dims[l]) for l in range(self.nl)]
+        self.db = [self.grads[self.b_off[l]:self.b_off[l] + self.dims[l + 1]] for l in range(self.nl)]
+        B = self.batch
+        self.h = [torch.empty(B, self.dims[l + 1], dtype=torch.float32, device=dev) for l in range(self.nl)]
+        self.g = [torch.empty(B, self.dims[l + 1], dtype=torch.float32, device=dev) for l in range(self.nl)]
+        # double-buffered staging for batches that arrive from host memory
+        self._x_dev = [None, None]
+        self._y_dev = [None, None]
+        self._copy_stream = torch.cuda.Stream(device=dev)
+        self._copy_done = [None, None]
+        self._slot = 0
+
+    # ------------------------------------------------------------------ host batches
+    def prefetch(self, x_host: torch.Tensor, labels_host: torch.Tensor) -> int:
+        """Start the host->device copy of a batch (pinned memory) on the copy stream; returns its slot."""
+        slot = self._slot
+        self._slot ^= 1
+        dev = self.be.device
+        if self._x_dev[slot] is None:
+            self._x_dev[slot] = torch.empty(self.batch, self.dims[0], dtype=torch.float32, device=dev)
+            self._y_dev[slot] = torch.empty(self.batch, dtype=torch.int64, device=dev)
+        # the slot may still be read by the step that used it last
+        self._copy_stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(self._copy_stream):
+            self._x_dev[slot].copy_(x_host, non_blocking=True)
+            self._y_dev[slot].copy_(labels_host, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self._copy_stream)
+        self._copy_done[slot] = ev
+        return slot
+
+    def step_slot(self, slot: int) -> torch.Tensor:
+        torch.cuda.current_stream(self.be.device).wait_event(self._copy_done[slot])
+        return self.step(self._x_dev[slot], self._y_dev[slot])
+
+    # ------------------------------------------------------------------ one step
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        be, a = self.be, x
+        for l in range(self.nl):
+            epi = EPI_RELU if l + 1 < self.nl else EPI_NONE
+            be.gemm(a, self.W[l], trans_b=True, bias=self.b[l], epilogue=epi, out=self.h[l], f32_mode=self.f32_mode)
+            a = self.h[l]
+        return a
+
+    def step(self, x: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """One training step on device-resident ``x [batch, in]`` / ``labels [batch]``; returns the
+        (local-shard mean) loss as a 1-element device tensor."""
+        be = self.be
+        if tuple(x.shape) != (self.batch, self.dims[0]):
+            raise ValueError(f"expected input of shape {(self.batch, self.dims[0])}, got {tuple(x.shape)}")
+        logits = self.forward(x)
+        loss, _ = be.cross_entropy_into(logits, labels, self.g[self.nl - 1])
+        handles = []
+        for l in range(self.nl - 1, -1, -1):
+            g = self.g[l]
+            a_in = x if l == 0 else self.h[l - 1]
+            be.colsum(g, out=self.db[l])
+            be.gemm(g, a_in, trans_a=True, out=self.dW[l], f32_mode=self.f32_mode)          # dW = g^T a
+            if self.world_size > 1:
+                import torch.distributed as dist
+                lo = self.w_off[l]
+                hi = self.b_off[l] + self.dims[l + 1]
+                handles.append(dist.all_reduce(self.grads[lo:hi], op=dist.ReduceOp.SUM, async_op=True))
+            if l > 0:
+                be.gemm(g, self.W[l], epilogue=EPI_RELU_BWD, aux=self.h[l - 1], out=self.g[l - 1],
+                        f32_mode=self.f32_mode)                                            # (g W) * relu'
+        for hnd in handles:
+            hnd.wait()
+        self.step_count += 1
+        be.adam_step(self.params, self.grads, self.m, self.v, lr=self.lr, beta1=self.beta1, beta2=self.beta2,
+                     eps=self.eps, step=self.step_count, grad_scale=1.0 / self.world_size)
+        return loss
+
+    def flops_per_sample(self) -> int:
+        return mlp_flops_per_sample(self.dims)

@@ -1,0 +1,240 @@
+"""Mirror of the ``minitensor.nn`` pieces on the dense-contraction path.
+
+``DenseLayer`` / ``dense_layer`` (``engine/src/nn/dense_layer.rs:24-188``,
+``bindings/src/nn/module.rs:69-94``), ``ReLU`` / ``GELU``
+(``engine/src/nn/activation.rs:88-91,378-390``), ``Sequential``
+(``engine/src/nn/sequential.rs:74-83``), ``Conv2d`` / ``conv2d``
+(``engine/src/nn/conv.rs:24-226``, ``engine/src/operations/conv.rs:24-206``),
+``cross_entropy`` / ``CrossEntropyLoss`` (``engine/src/nn/loss.rs:434-436``,
+``engine/src/operations/loss/regression.rs:178-251``).
+
+What differs from the reference is only where the arithmetic happens: the
+bias add (and a directly following ReLU / GELU inside ``Sequential``) is the
+epilogue of the GEMM kernel, the weight transpose is a descriptor choice, and
+the backward products are launched without materialised transposes.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from ._lib import EPI_GELU_ERF, EPI_GELU_TANH, EPI_NONE, EPI_RELU, EPI_RELU_BWD
+from .tensor import Tensor, _be
+
+_Pair = Union[int, Tuple[int, int]]
+
+
+def _pair(v: _Pair, name: str) -> Tuple[int, int]:
+    """int-or-pair parsing of ``bindings/src/nn/module.rs:96-137``."""
+    if isinstance(v, int):
+        return (v, v)
+    if isinstance(v, (tuple, list)) and len(v) == 2 and all(isinstance(i, int) for i in v):
+        return (int(v[0]), int(v[1]))
+    raise ValueError(f"{name} must be an int or a pair of ints")
+
+
+# ---------------------------------------------------------------------- init
+def _uniform(shape, bound: float, dtype: str, rng: Optional[np.random.Generator]) -> np.ndarray:
+    rng = rng or np.random.default_rng()
+    return rng.uniform(-bound, bound, size=shape).astype(dtype)
+
+
+def xavier_uniform(shape, dtype="float32", rng=None) -> np.ndarray:
+    """bound = sqrt(6 / (fan_in + fan_out)) (``engine/src/nn/init.rs:393-443``)."""
+    fan_in, fan_out = _fans(shape)
+    return _uniform(shape, math.sqrt(6.0 / (fan_in + fan_out)), dtype, rng)
+
+
+def he_uniform(shape, dtype="float32", rng=None) -> np.ndarray:
+    """bound = sqrt(6 / fan_in) (``engine/src/nn/init.rs:471-491``)."""
+    fan_in, _ = _fans(shape)
+    return _uniform(shape, math.sqrt(6.0 / fan_in), dtype, rng)
+
+
+def _fans(shape) -> Tuple[int, int]:
+    # calculate_fan_in_fan_out: dims[1] (x receptive field) in, dims[0] (x receptive field) out
+    recept = int(np.prod(shape[2:])) if len(shape) > 2 else 1
+    return shape[1] * recept, shape[0] * recept
+
+
+# ---------------------------------------------------------------------- dense
+def dense_layer(input: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *, _epilogue: int = EPI_NONE) -> Tensor:
+    """``input @ weight^T + bias`` with ``weight`` stored ``[out_features, in_features]``."""
+    if input.ndim < 2:
+        raise ValueError("DenseLayer expects input with at least 2 dimensions")
+    out_f, in_f = weight.shape
+    if input.shape[-1] != in_f:
+        raise ValueError(f"shape mismatch: expected last dim {in_f}, got {input.shape[-1]}")
+    if input.dtype != weight.dtype or (bias is not None and bias.dtype != weight.dtype):
+        raise TypeError("type mismatch between input, weight and bias")
+    be = _be()
+    x2 = input._buf.reshape(-1, in_f)
+    bbuf = bias._buf if bias is not None else None
+    y2 = be.gemm(x2, weight._buf, trans_b=True, bias=bbuf, epilogue=_epilogue)
+    out_shape = input.shape[:-1] + (out_f,)
+    parents = (input, weight) + ((bias,) if bias is not None else ())
+
+    def bw(g):
+        g2 = g.reshape(-1, out_f).contiguous()
+        if _epilogue == EPI_RELU:
+            g2 = be.act_bwd(y2, g2, EPI_RELU)
+        elif _epilogue in (EPI_GELU_ERF, EPI_GELU_TANH):
+            raise RuntimeError("fused GELU keeps no pre-activation; use the unfused layer for training")
+        gx = be.gemm(g2, weight._buf).reshape(input.shape) if input.requires_grad else None   # dX = dY W
+        gw = be.gemm(g2, x2, trans_a=True) if weight.requires_grad else None                  # dW = dY^T X
+        gb = be.colsum(g2) if (bias is not None and bias.requires_grad) else None
+        return (gx, gw, gb)[: len(parents)]
+
+    return input._result(y2.reshape(out_shape), parents, bw)
+
+
+class Module:
+    def parameters(self) -> List[Tensor]:
+        return []
+
+    def __call__(self, x: Tensor) -> Tensor:
+        return self.forward(x)
+
+
+class DenseLayer(Module):
+    """Weight ``[out, in]`` Xavier-uniform, bias zeros (``dense_layer.rs:47-49``, ``init.rs:503-506``)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, dtype: str = "float32",
+                 rng: Optional[np.random.Generator] = None):
+        if in_features <= 0 or out_features <= 0:
+            raise ValueError("in_features and out_features must be positive")
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = Tensor(xavier_uniform((out_features, in_features), dtype, rng), requires_grad=True)
+        self.bias = Tensor(np.zeros(out_features, dtype=dtype), requires_grad=True) if bias else None
+
+    def forward(self, x: Tensor, _epilogue: int = EPI_NONE) -> Tensor:
+        return dense_layer(x, self.weight, self.bias, _epilogue=_epilogue)
+
+    def parameters(self) -> List[Tensor]:
+        return [self.weight] + ([self.bias] if self.bias is not None else [])
+
+
+class ReLU(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.relu()
+
+
+class GELU(Module):
+    """The layer form uses the tanh approximation (``engine/src/nn/activation.rs:378-390``)."""
+
+    def __init__(self, approximate: str = "tanh"):
+        self.approximate = approximate
+
+    def forward(self, x: Tensor) -> Tensor:
+        return x.gelu(self.approximate)
+
+
+class Sequential(Module):
+    """Runs layers in order; a ``DenseLayer`` directly followed by ``ReLU`` runs as one GEMM
+    with the activation in its epilogue (results equal the unfused pair)."""
+
+    def __init__(self, layers: Sequence[Module], fuse: bool = True):
+        self.layers = list(layers)
+        self.fuse = fuse
+
+    def forward(self, x: Tensor) -> Tensor:
+        i = 0
+        while i < len(self.layers):
+            layer = self.layers[i]
+            nxt = self.layers[i + 1] if i + 1 < len(self.layers) else None
+            if self.fuse and isinstance(layer, DenseLayer) and isinstance(nxt, ReLU):
+                x = layer.forward(x, _epilogue=EPI_RELU)
+                i += 2
+            else:
+                x = layer(x)
+                i += 1
+        return x
+
+    def parameters(self) -> List[Tensor]:
+        return [p for l in self.layers for p in l.parameters()]
+
+
+# ---------------------------------------------------------------------- conv
+def conv2d(input: Tensor, weight: Tensor, bias: Optional[Tensor] = None, stride: _Pair = 1,
+           padding: _Pair = 0) -> Tensor:
+    """NCHW x OIHW convolution, f32 only, with the reference's checks (``conv.rs:32-93``)."""
+    stride, padding = _pair(stride, "stride"), _pair(padding, "padding")
+    if input.ndim != 4:
+        raise ValueError("conv2d expects 4D input tensor [N, C_in, H, W]")
+    if weight.ndim != 4:
+        raise ValueError("conv2d expects 4D weight tensor [C_out, C_in, kH, kW]")
+    n, c, h, w = input.shape
+    co, ci, kh, kw = weight.shape
+    if c != ci:
+        raise ValueError(f"shape mismatch: [{ci}] vs [{c}]")
+    if bias is not None and (bias.ndim != 1 or bias.shape[0] != co):
+        raise ValueError(f"shape mismatch: [{co}] vs {list(bias.shape)}")
+    if stride[0] <= 0 or stride[1] <= 0:
+        raise ValueError("stride values must be greater than zero")
+    if padding[0] < 0 or padding[1] < 0:
+        raise ValueError("padding must be non-negative")
+    if kh > h + 2 * padding[0] or kw > w + 2 * padding[1]:
+        raise ValueError("kernel size cannot be larger than padded input")
+    if input.dtype != "float32" or weight.dtype != "float32" or (bias is not None and bias.dtype != "float32"):
+        raise ValueError("conv2d is implemented only for Float32 tensors")
+    be = _be()
+    y = be.conv2d_fwd(input._buf, weight._buf, bias._buf if bias is not None else None, stride, padding)
+    parents = (input, weight) + ((bias,) if bias is not None else ())
+
+    def bw(g):  # Conv2dBackward (engine/src/autograd/mod/shape.rs:57-197)
+        g = g.contiguous()
+        gx = be.conv2d_bwd_data(g, weight._buf, input.shape, stride, padding) if input.requires_grad else None
+        gw = be.conv2d_bwd_weight(g, input._buf, weight.shape, stride, padding) if weight.requires_grad else None
+        gb = be.conv2d_bwd_bias(g) if (bias is not None and bias.requires_grad) else None
+        return (gx, gw, gb)[: len(parents)]
+
+    return input._result(y, parents, bw)
+
+
+class Conv2d(Module):
+    """He-uniform weight, zero bias (``engine/src/nn/conv.rs:60-74``)."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: _Pair, stride: _Pair = 1,
+                 padding: _Pair = 0, bias: bool = True, rng: Optional[np.random.Generator] = None):
+        kh, kw = _pair(kernel_size, "kernel_size")
+        if in_channels <= 0 or out_channels <= 0 or kh <= 0 or kw <= 0:
+            raise ValueError("channels and kernel size must be positive")
+        self.stride, self.padding = _pair(stride, "stride"), _pair(padding, "padding")
+        self.weight = Tensor(he_uniform((out_channels, in_channels, kh, kw), "float32", rng), requires_grad=True)
+        self.bias = Tensor(np.zeros(out_channels, dtype=np.float32), requires_grad=True) if bias else None
+
+    def forward(self, x: Tensor) -> Tensor:
+        return conv2d(x, self.weight, self.bias, self.stride, self.padding)
+
+    def parameters(self) -> List[Tensor]:
+        return [self.weight] + ([self.bias] if self.bias is not None else [])
+
+
+# ---------------------------------------------------------------------- loss
+def cross_entropy(input: Tensor, target: Tensor, reduction: str = "mean") -> Tensor:
+    """Class-index targets (int32 / int64, shape ``[B]``) against ``[B, C]`` f32 logits."""
+    if reduction not in ("mean", "sum"):
+        if reduction == "none":
+            raise NotImplementedError("reduction 'none' is outside the accelerated path")
+        raise ValueError(f"Invalid reduction mode: {reduction}. Must be 'mean', 'sum', or 'none'")
+    if input.ndim != 2 or target.ndim != 1 or target.shape[0] != input.shape[0]:
+        raise ValueError(f"shape mismatch: {input.shape} vs {target.shape}")
+    if input.dtype != "float32":
+        raise TypeError("cross entropy on this path takes float32 logits")
+    if target.dtype not in ("int32", "int64"):
+        raise TypeError("Unsupported target dtype for classification loss")
+    be = _be()
+    loss, dl = be.cross_entropy(input._buf, target._buf, mean=(reduction == "mean"), want_grad=input.requires_grad)
+    be.sync()  # surfaces an out-of-range class index as IndexError, as the reference does eagerly
+    return input._result(loss.reshape(()), (input,), lambda g: (dl * g.reshape(()),))
+
+
+class CrossEntropyLoss(Module):
+    def __init__(self, reduction: str = "mean"):
+        self.reduction = reduction
+
+    def __call__(self, input: Tensor, target: Tensor) -> Tensor:
+        return cross_entropy(input, target, self.reduction)

@@ -1,0 +1,319 @@
+"""Parity of the device GEMM (through the C ABI) with the CPU oracle and with the reference's
+own known answers.  Tolerances are the ones the path is specified with:
+f32  |delta| <= 1e-4 * ||a_row|| * ||b_col||,  f64  <= 1e-12 of the same norm,  integers bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import fval
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL, F64_TOL = 1e-4, 1e-12
+DT = {"float32": np.float32, "float64": np.float64, "int32": np.int32, "int64": np.int64}
+
+
+def norm_scaled_error(c, ref, a2, b2):
+    """max over outputs of |c - ref| / (||a_row|| * ||b_col||); a2 is [..,M,K], b2 is [..,K,N] (logical)."""
+    na = np.linalg.norm(a2.astype(np.float64), axis=-1)[..., :, None]
+    nb = np.linalg.norm(b2.astype(np.float64), axis=-2)[..., None, :]
+    scale = na * nb
+    scale[scale == 0] = 1.0
+    return float((np.abs(c.astype(np.float64) - ref.astype(np.float64)) / scale).max()) if c.size else 0.0
+
+
+def dev(be, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(be.device)
+
+
+def run_gemm(be, a, b, **kw):
+    out = be.gemm(dev(be, a), dev(be, b), **kw)
+    be.sync()
+    return out.cpu().numpy()
+
+
+# ------------------------------------------------------------------ reference known answers via the Tensor mirror
+def test_reference_known_answers(be, golden):
+    import minitensor_b200.tensor as mt
+    for case in golden["matmul"]:
+        dt = case["dtype"]
+        a = mt.Tensor(np.array(case["a"], dtype=DT[dt]).reshape(case["a_shape"]))
+        b = mt.Tensor(np.array(case["b"], dtype=DT[dt]).reshape(case["b_shape"]))
+        out = a.matmul(b) if len(case["a_shape"]) != 3 else a.bmm(b)
+        assert list(out.shape) == case["out_shape"], case["source"]
+        np.testing.assert_array_equal(out.numpy().ravel(), np.array(case["out"], dtype=DT[dt]), err_msg=case["source"])
+
+
+def test_reference_backward_known_answers(be, golden):
+    import minitensor_b200.tensor as mt
+    for case in golden["matmul_backward_ones"]:
+        a = mt.Tensor(np.array(case["a"], dtype=np.float32).reshape(case["a_shape"]), requires_grad=True)
+        b = mt.Tensor(np.array(case["b"], dtype=np.float32).reshape(case["b_shape"]), requires_grad=True)
+        a.matmul(b).sum().backward()
+        np.testing.assert_array_equal(a.grad.numpy().ravel(), np.array(case["da"], dtype=np.float32))
+        np.testing.assert_array_equal(b.grad.numpy().ravel(), np.array(case["db"], dtype=np.float32))
+
+
+def test_reference_error_cases(be):
+    """tests/ops/test_logic_broadcast_linalg.py:618-708 and engine/src/operations/linalg/triangular.rs:208-336."""
+    import minitensor_b200.tensor as mt
+    with pytest.raises(ValueError):
+        mt.Tensor([[1.0, 2.0]]).matmul(mt.Tensor([[3.0, 4.0, 5.0]]))
+    with pytest.raises(TypeError):
+        mt.Tensor([[1.0, 2.0]], dtype="float32").matmul(mt.Tensor([[3.0], [4.0]], dtype="float64"))
+    with pytest.raises(ValueError):
+        mt.Tensor([[True, False], [False, True]], dtype="bool").matmul(
+            mt.Tensor([[True, True], [False, False]], dtype="bool"))
+    with pytest.raises((ValueError, RuntimeError)):
+        mt.Tensor(2.0).matmul(mt.Tensor(3.0))
+    with pytest.raises(ValueError):
+        mt.Tensor(np.ones((2, 3), np.float32)).bmm(mt.Tensor(np.ones((2, 3, 3), np.float32)))
+    a = mt.Tensor(np.arange(12, dtype=np.float32).reshape(2, 2, 3))
+    b = mt.Tensor(np.arange(18, dtype=np.float32).reshape(3, 3, 2))
+    with pytest.raises(ValueError):
+        a.bmm(b)
+    with pytest.raises(ValueError):
+        a.matmul(b)
+
+
+def test_requires_grad_flags_and_self_matmul(be):
+    """tests/ops/test_logic_broadcast_linalg.py:741-752; tests/tensor/test_tensor_core.py:636-642."""
+    import minitensor_b200.tensor as mt
+    a = mt.Tensor(np.arange(4, dtype=np.float32).reshape(2, 2), requires_grad=True)
+    b = mt.Tensor(np.arange(4, dtype=np.float32).reshape(2, 2), requires_grad=False)
+    a.matmul(b).sum().backward()
+    assert a.grad is not None and b.grad is None
+    x = mt.Tensor(np.array([[1.0, 2.0], [3.0, 4.0]], np.float32), requires_grad=True)
+    (x @ x).sum().backward()
+    xn = x.numpy()
+    ones = np.ones((2, 2), np.float32)
+    np.testing.assert_allclose(x.grad.numpy(), ones @ xn.T + xn.T @ ones)
+
+
+def test_batch_broadcast_and_gradient_reduction(be, orc, rng):
+    """[2,3,4] @ [4,5] and [1,3,4] @ [7,4,5] (matmul.rs:324-345); gradients reduce over the broadcast dims."""
+    import minitensor_b200.tensor as mt
+    for sa, sb in [((2, 3, 4), (4, 5)), ((1, 3, 4), (7, 4, 5))]:
+        an, bn = rng.standard_normal(sa).astype(np.float32), rng.standard_normal(sb).astype(np.float32)
+        a, b = mt.Tensor(an, requires_grad=True), mt.Tensor(bn, requires_grad=True)
+        c = a.matmul(b)
+        ref = np.matmul(an.astype(np.float64), bn.astype(np.float64))
+        np.testing.assert_allclose(c.numpy(), ref, rtol=1e-5, atol=1e-5)
+        c.sum().backward()
+        g = np.ones(ref.shape)
+        ga = np.matmul(g, np.swapaxes(np.broadcast_to(bn, ref.shape[:-2] + bn.shape[-2:]), -1, -2))
+        gb = np.matmul(np.swapaxes(np.broadcast_to(an, ref.shape[:-2] + an.shape[-2:]), -1, -2), g)
+        while ga.ndim > an.ndim:
+            ga = ga.sum(0)
+        if an.shape[0] == 1 and ga.shape[0] != 1:
+            ga = ga.sum(0, keepdims=True)
+        while gb.ndim > bn.ndim:
+            gb = gb.sum(0)
+        np.testing.assert_allclose(a.grad.numpy(), ga, rtol=1e-5, atol=1e-4)
+        np.testing.assert_allclose(b.grad.numpy(), gb, rtol=1e-5, atol=1e-4)
+
+
+def test_inf_nan_propagation(be):
+    """tests/ops/test_logic_broadcast_linalg.py:718-722, plus: Inf times a finite value stays Inf."""
+    a = np.array([[np.inf, np.nan], [1.0, 2.0]], np.float32)
+    b = np.array([[1.0, 2.0], [3.0, 4.0]], np.float32)
+    out = run_gemm(be, a, b)
+    assert np.isnan(out[0]).all()
+    np.testing.assert_array_equal(out[1], [7.0, 10.0])
+    a = np.array([[np.inf, 1.0], [-np.inf, 2.0], [3.0, 4.0]], np.float32)
+    b = np.array([[1.0, -1.0, 0.0], [1.0, 1.0, 1.0]], np.float32)
+    out = run_gemm(be, a, b)
+    with np.errstate(invalid="ignore"):
+        ref = a @ b
+    np.testing.assert_array_equal(np.isnan(out), np.isnan(ref))
+    np.testing.assert_array_equal(out[~np.isnan(ref)], ref[~np.isnan(ref)])
+    # a later clean call is not affected by the earlier non-finite one
+    c = run_gemm(be, np.ones((4, 8), np.float32), np.ones((8, 4), np.float32))
+    np.testing.assert_array_equal(c, np.full((4, 4), 8.0, np.float32))
+
+
+# ------------------------------------------------------------------ f32 parity with the oracle
+SHAPES = [(1, 1, 1), (2, 3, 2), (7, 5, 3), (17, 63, 65), (64, 64, 64), (127, 129, 31), (128, 256, 64),
+          (130, 257, 100), (256, 256, 256), (300, 1000, 777), (32, 10, 128), (32, 128, 784), (1, 513, 1030),
+          (513, 1, 9), (1024, 1024, 1024)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_f32_matches_oracle(be, orc, rng, m, n, k):
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    c = run_gemm(be, a, b)
+    ref = orc.matmul(a, b)                       # reference-order f32
+    wide = orc.matmul_acc_wide(a, b)             # f64-accumulated
+    assert norm_scaled_error(c, ref, a, b) <= F32_TOL
+    assert norm_scaled_error(c, wide, a, b) <= F32_TOL
+    # the default mode is f32-accurate: no worse than a small multiple of the CPU f32 kernel's own error
+    assert norm_scaled_error(c, wide, a, b) <= 4e-6
+
+
+@pytest.mark.parametrize("variant", [1, 2, 3, 4])
+@pytest.mark.parametrize("mode", [3, 6, 9])
+def test_f32_tile_variants_and_modes(be, orc, rng, variant, mode):
+    m, n, k = 257, 300, 193
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    c = run_gemm(be, a, b, f32_mode=mode, variant=variant)
+    assert norm_scaled_error(c, orc.matmul_acc_wide(a, b), a, b) <= (F32_TOL if mode == 3 else 4e-6)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False), (True, True)])
+def test_f32_transposed_operands(be, orc, rng, ta, tb):
+    """The two products of MatMulBackward and the DenseLayer forward use these forms."""
+    m, n, k = 200, 300, 150
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    c = run_gemm(be, a, b, trans_a=ta, trans_b=tb)
+    al, bl = (a.T if ta else a), (b.T if tb else b)
+    assert norm_scaled_error(c, orc.matmul(np.ascontiguousarray(al), np.ascontiguousarray(bl)), al, bl) <= F32_TOL
+
+
+def test_f32_backward_config1(be, orc):
+    """1024^3, N(0,1) entries from seed 7, forward plus backward with an all-ones upstream gradient."""
+    import minitensor_b200.tensor as mt
+    g = np.random.default_rng(7)
+    an = g.standard_normal((1024, 1024)).astype(np.float32)
+    bn = g.standard_normal((1024, 1024)).astype(np.float32)
+    a, b = mt.Tensor(an, requires_grad=True), mt.Tensor(bn, requires_grad=True)
+    c = a.matmul(b)
+    c.sum().backward()
+    dy = np.ones((1024, 1024), np.float32)
+    da, db = orc.matmul_backward(an, bn, dy)
+    assert norm_scaled_error(c.numpy(), orc.matmul(an, bn), an, bn) <= F32_TOL
+    assert norm_scaled_error(a.grad.numpy(), da, dy, bn.T) <= F32_TOL
+    assert norm_scaled_error(b.grad.numpy(), db, an.T, dy) <= F32_TOL
+
+
+def test_bmm_f32(be, orc, rng):
+    a = rng.standard_normal((5, 64, 96)).astype(np.float32)
+    b = rng.standard_normal((5, 96, 80)).astype(np.float32)
+    c = run_gemm(be, a, b)
+    assert norm_scaled_error(c, orc.matmul(a, b), a, b) <= F32_TOL
+    a = rng.standard_normal((64, 128, 128)).astype(np.float32)   # reduced-size stand-in of bmm [64,512,512]
+    b = rng.standard_normal((64, 128, 128)).astype(np.float32)
+    assert norm_scaled_error(run_gemm(be, a, b), orc.matmul(a, b), a, b) <= F32_TOL
+
+
+def test_fused_epilogues_match_unfused_oracle(be, orc, rng):
+    m, n, k = 100, 200, 300
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    z = orc.dense_forward(x, w, bias)
+    y = run_gemm(be, x, w, trans_b=True, bias=dev(be, bias))
+    assert norm_scaled_error(y, z, x, w.T) <= F32_TOL
+    relu_ref, mask = orc.relu(z)
+    y = run_gemm(be, x, w, trans_b=True, bias=dev(be, bias), epilogue=1)
+    assert norm_scaled_error(y, relu_ref, x, w.T) <= F32_TOL
+    for epi, approx in ((2, False), (3, True)):
+        y = run_gemm(be, x, w, trans_b=True, bias=dev(be, bias), epilogue=epi)
+        assert norm_scaled_error(y, orc.gelu(z, approx), x, w.T) <= F32_TOL
+    # ReluBackward fused: (dy @ w2) * (h > 0)
+    h = relu_ref
+    dy = rng.standard_normal((m, 50)).astype(np.float32)
+    w2 = rng.standard_normal((50, n)).astype(np.float32)
+    got = run_gemm(be, dy, w2, epilogue=4, aux=dev(be, h))
+    exp = orc.relu_backward(mask, orc.matmul(dy, w2))
+    assert norm_scaled_error(got, exp, dy, w2) <= F32_TOL
+
+
+def test_zero_sized_and_degenerate(be):
+    for (m, n, k) in [(0, 3, 4), (3, 0, 4), (2, 3, 0)]:
+        c = run_gemm(be, np.zeros((m, k), np.float32), np.zeros((k, n), np.float32))
+        assert c.shape == (m, n) and not c.any()
+    # K == 0 with a fused bias + relu yields relu(bias) in every row
+    bias = np.array([-1.0, 2.0, 0.5], np.float32)
+    c = run_gemm(be, np.zeros((2, 0), np.float32), np.zeros((0, 3), np.float32), bias=dev(be, bias), epilogue=1)
+    np.testing.assert_array_equal(c, np.tile(np.maximum(bias, 0), (2, 1)))
+
+
+def test_deterministic(be, rng):
+    a = dev(be, rng.standard_normal((300, 500)).astype(np.float32))
+    b = dev(be, rng.standard_normal((500, 260)).astype(np.float32))
+    c1 = be.gemm(a, b).clone()
+    c2 = be.gemm(a, b)
+    be.sync()
+    assert torch.equal(c1, c2)
+
+
+# ------------------------------------------------------------------ f64 / integers
+@pytest.mark.parametrize("m,n,k", [(2, 2, 3), (17, 63, 65), (128, 128, 16), (130, 70, 33), (256, 256, 256),
+                                   (300, 200, 1000), (1024, 1024, 1024)])
+def test_f64_matches_oracle(be, orc, rng, m, n, k):
+    a = rng.standard_normal((m, k))
+    b = rng.standard_normal((k, n))
+    c = run_gemm(be, a, b)
+    assert norm_scaled_error(c, orc.matmul(a, b), a, b) <= F64_TOL
+    assert norm_scaled_error(c, orc.matmul_acc_wide(a, b), a, b) <= F64_TOL
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False), (True, True)])
+def test_f64_transposed_and_batched(be, orc, rng, ta, tb):
+    m, n, k = 100, 90, 80
+    a = rng.standard_normal((3, k, m) if ta else (3, m, k))
+    b = rng.standard_normal((3, n, k) if tb else (3, k, n))
+    c = run_gemm(be, a, b, trans_a=ta, trans_b=tb)
+    al = np.ascontiguousarray(np.swapaxes(a, -1, -2) if ta else a)
+    bl = np.ascontiguousarray(np.swapaxes(b, -1, -2) if tb else b)
+    assert norm_scaled_error(c, orc.matmul(al, bl), al, bl) <= F64_TOL
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64])
+@pytest.mark.parametrize("m,n,k", [(2, 2, 3), (17, 63, 65), (130, 70, 33), (256, 256, 256), (1024, 1024, 1024)])
+def test_int_bit_exact(be, orc, rng, dtype, m, n, k):
+    a = rng.integers(-8, 9, (m, k)).astype(dtype)
+    b = rng.integers(-8, 9, (k, n)).astype(dtype)
+    np.testing.assert_array_equal(run_gemm(be, a, b), orc.matmul(a, b))
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64])
+def test_int_wraps_like_release_build(be, orc, rng, dtype):
+    info = np.iinfo(dtype)
+    a = rng.integers(info.min, info.max, (65, 70), dtype=dtype)
+    b = rng.integers(info.min, info.max, (70, 33), dtype=dtype)
+    np.testing.assert_array_equal(run_gemm(be, a, b), orc.matmul(a, b))
+    a3 = rng.integers(-8, 9, (3, 20, 30)).astype(dtype)
+    b3 = rng.integers(-8, 9, (3, 30, 10)).astype(dtype)
+    np.testing.assert_array_equal(run_gemm(be, a3, b3), orc.matmul(a3, b3))
+
+
+# ------------------------------------------------------------------ full-size properties
+def test_large_f32_sampled_rows_and_linearity(be, orc):
+    """4096^3 (the headline size): sampled rows against the f64-accumulated oracle, plus linearity
+    C(A, B1 + B2) = C(A, B1) + C(A, B2) within the same tolerance."""
+    g = torch.Generator(device="cpu").manual_seed(11)
+    n = 4096
+    a = torch.randn(n, n, generator=g)
+    b = torch.randn(n, n, generator=g)
+    ad, bd = a.to(be.device), b.to(be.device)
+    c = be.gemm(ad, bd)
+    be.sync()
+    rows = np.random.default_rng(5).choice(n, 24, replace=False)
+    an, bn = a.numpy(), b.numpy()
+    wide = orc.matmul_acc_wide(np.ascontiguousarray(an[rows]), bn)
+    assert norm_scaled_error(c[rows].cpu().numpy(), wide, an[rows], bn) <= F32_TOL
+    b2 = torch.randn(n, n, generator=g).to(be.device)
+    lhs = be.gemm(ad, bd + b2)
+    rhs = c + be.gemm(ad, b2)
+    be.sync()
+    scale = (ad.double().norm(dim=1)[:, None] * (bd + b2).double().norm(dim=0)[None, :])
+    assert float(((lhs - rhs).double().abs() / scale).max()) <= F32_TOL
+
+
+def test_large_int_modular_identity(be):
+    """i32 4096^3, entries in [-8,8]: sum_j C[i,j] r[j] == sum_l A[i,l] (B r)[l], exact in wrapping arithmetic."""
+    n = 4096
+    g = torch.Generator(device="cpu").manual_seed(3)
+    a = torch.randint(-8, 9, (n, n), generator=g, dtype=torch.int32).to(be.device)
+    b = torch.randint(-8, 9, (n, n), generator=g, dtype=torch.int32).to(be.device)
+    r = torch.randint(-3, 4, (n, 1), generator=g, dtype=torch.int32).to(be.device)
+    c = be.gemm(a, b)
+    lhs = be.gemm(c, r)
+    rhs = be.gemm(a, be.gemm(b, r))
+    be.sync()
+    assert torch.equal(lhs, rhs)
+    assert int(c.abs().max()) <= 64 * n  # |sum| <= 8*8*K: no overflow at these magnitudes

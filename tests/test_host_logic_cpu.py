@@ -1,0 +1,88 @@
+"""Host-side logic that needs no GPU: argument parsing, initialisers, buffer layout, and the
+2-rank data-parallel identity (gloo) the multi-GPU trainer relies on."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from minitensor_b200 import mlp, nn
+
+
+def test_pair_parsing():
+    assert nn._pair(2, "stride") == (2, 2)
+    assert nn._pair((1, 3), "stride") == (1, 3)
+    with pytest.raises(ValueError):
+        nn._pair((1, 2, 3), "stride")
+    with pytest.raises(ValueError):
+        nn._pair("1", "stride")
+
+
+def test_init_bounds_follow_reference():
+    rng = np.random.default_rng(0)
+    w = nn.xavier_uniform((128, 784), rng=rng)          # sqrt(6 / (fan_in + fan_out))
+    assert w.dtype == np.float32 and np.abs(w).max() <= math.sqrt(6.0 / (784 + 128))
+    w = nn.he_uniform((128, 784), rng=rng)              # sqrt(6 / fan_in)
+    assert np.abs(w).max() <= math.sqrt(6.0 / 784) and np.abs(w).max() > 0.9 * math.sqrt(6.0 / 784)
+    w = nn.he_uniform((64, 64, 3, 3), rng=rng)          # conv: fan_in = C_in * kH * kW
+    assert np.abs(w).max() <= math.sqrt(6.0 / 576)
+
+
+def test_flat_layout_and_flops():
+    dims = [8192, 4096, 4096, 4096, 1000]
+    w_off, b_off, total = mlp.mlp_layout(dims)
+    assert total == 71_218_152                      # parameter count of the large MLP config
+    assert w_off[0] == 0 and b_off[0] == 8192 * 4096 and w_off[1] == b_off[0] + 4096
+    assert mlp.mlp_flops_per_sample(dims) == 360_120_320
+    assert mlp.mlp_flops_per_sample([784, 128, 10]) == 3 * 2 * (784 * 128 + 128 * 10) - 2 * 784 * 128
+    assert mlp.shard_rows(65536, 8, 3) == (3 * 8192, 4 * 8192)
+    with pytest.raises(ValueError):
+        mlp.shard_rows(10, 4, 0)
+
+
+def _dp_worker(rank, world, port, dims, x, labels, params, out):
+    import oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    lo, hi = mlp.shard_rows(x.shape[0], world, rank)
+    p = params.copy()
+    m, v = np.zeros_like(p), np.zeros_like(p)
+    # gradients of the local-shard mean loss (the Adam update inside is discarded)
+    _, g = oracle.mlp_train_step(dims, x[lo:hi], labels[lo:hi], p, m, v, 0.0, 0.9, 0.999, 1e-8, 1, want_grads=True)
+    t = torch.from_numpy(g)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)        # what MLPTrainer does per layer slice
+    t *= 1.0 / world                                # what its Adam launch applies as grad_scale
+    if rank == 0:
+        out.put(t.numpy().copy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gradient_average_equals_full_batch():
+    """Row-sharding + all-reduce(sum) / world reproduces the full-batch mean-loss gradient."""
+    import oracle
+    oracle.build()
+    rng = np.random.default_rng(3)
+    dims = [12, 9, 5]
+    x = rng.standard_normal((16, 12)).astype(np.float32)
+    labels = rng.integers(0, 5, 16)
+    _, _, total = mlp.mlp_layout(dims)
+    params = (rng.standard_normal(total) * 0.3).astype(np.float32)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 500)
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, dims, x, labels, params, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    p = params.copy()
+    _, full = oracle.mlp_train_step(dims, x, labels, p, np.zeros_like(p), np.zeros_like(p), 0.0, 0.9, 0.999, 1e-8, 1,
+                                    want_grads=True)
+    np.testing.assert_allclose(got, full, rtol=1e-5, atol=1e-6)

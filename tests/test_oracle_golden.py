@@ -1,0 +1,190 @@
+"""The CPU oracle against the known answers of the reference's own tests, and against
+NumPy on small random inputs (how the reference's Python tests check the same ops)."""
+import math
+
+import numpy as np
+import pytest
+
+from conftest import fval
+
+DT = {"float32": np.float32, "float64": np.float64, "int32": np.int32, "int64": np.int64}
+
+
+def _mm_any_rank(orc, a, b):
+    """The 1-D promotion of matmul (matmul.rs:282-308) around the oracle's core."""
+    a1, b1 = a.ndim == 1, b.ndim == 1
+    a2 = a.reshape(1, -1) if a1 else a
+    b2 = b.reshape(-1, 1) if b1 else b
+    out = orc.matmul(a2, b2)
+    dims = list(out.shape)
+    if b1:
+        dims.pop(len(dims) - 1)
+    if a1:
+        dims.pop(len(dims) - 1 if b1 else len(dims) - 2)
+    return out.reshape(dims)
+
+
+def test_matmul_known_answers(orc, golden):
+    for case in golden["matmul"]:
+        dt = DT[case["dtype"]]
+        a = np.array(case["a"], dtype=dt).reshape(case["a_shape"])
+        b = np.array(case["b"], dtype=dt).reshape(case["b_shape"])
+        out = _mm_any_rank(orc, a, b)
+        assert list(out.shape) == case["out_shape"], case["source"]
+        np.testing.assert_array_equal(out.ravel(), np.array(case["out"], dtype=dt), err_msg=case["source"])
+
+
+def test_matmul_backward_known_answers(orc, golden):
+    for case in golden["matmul_backward_ones"]:
+        a = np.array(case["a"], dtype=np.float32).reshape(case["a_shape"])
+        b = np.array(case["b"], dtype=np.float32).reshape(case["b_shape"])
+        dy = np.ones(a.shape[:-1] + (b.shape[-1],), dtype=np.float32)
+        da, db = orc.matmul_backward(a, b, dy)
+        np.testing.assert_array_equal(da.ravel(), np.array(case["da"], dtype=np.float32), err_msg=case["source"])
+        np.testing.assert_array_equal(db.ravel(), np.array(case["db"], dtype=np.float32), err_msg=case["source"])
+        da_only, none = orc.matmul_backward(a, b, dy, need_b=False)  # requires_grad flags (tests.rs:456-495)
+        assert none is None and da_only is not None
+
+
+def test_conv2d_known_answers(orc, golden):
+    for case in golden["conv2d"]:
+        x = np.array(case["x"], dtype=np.float32).reshape(case["x_shape"])
+        w = np.array(case["w"], dtype=np.float32).reshape(case["w_shape"])
+        bias = None if case["bias"] is None else np.array(case["bias"], dtype=np.float32)
+        y = orc.conv2d(x, w, bias, tuple(case["stride"]), tuple(case["padding"]))
+        assert list(y.shape) == case["out_shape"], case["source"]
+        np.testing.assert_array_equal(y.ravel(), np.array(case["out"], dtype=np.float32), err_msg=case["source"])
+    for case in golden["conv2d_invalid"]:
+        with pytest.raises(ValueError):
+            orc.conv2d(np.zeros(case["x_shape"], np.float32), np.zeros(case["w_shape"], np.float32), None,
+                       tuple(case["stride"]), tuple(case["padding"]))
+
+
+def test_adam_known_answer(orc, golden):
+    for case in golden["adam"]:
+        p = np.array(case["param"], dtype=np.float32)
+        g = np.array(case["grad"], dtype=np.float32)
+        m, v = np.zeros_like(p), np.zeros_like(p)
+        orc.adam_step(p, g, m, v, case["lr"], case["beta1"], case["beta2"], case["eps"], step=1)
+        assert np.all(np.abs(p - case["expected"]) < case["atol"]), case["source"]
+
+
+def test_relu_backward_nan(orc, golden):
+    for case in golden["relu_backward"]:
+        x = np.array([fval(v) for v in case["x"]], dtype=np.float32)
+        go = np.array([fval(v) for v in case["grad_out"]], dtype=np.float32)
+        y, mask = orc.relu(x)
+        gi = orc.relu_backward(mask, go)
+        exp = np.array([fval(v) for v in case["grad_in"]], dtype=np.float32)
+        np.testing.assert_array_equal(np.isnan(gi), np.isnan(exp))
+        np.testing.assert_array_equal(gi[~np.isnan(exp)], exp[~np.isnan(exp)])
+        assert np.isnan(y[1]) and y[0] == 0.0 and y[2] == 1.0  # NaN passes through relu
+
+
+def test_cross_entropy_limits(orc, golden):
+    for case in golden["cross_entropy_limits"]:
+        loss, _ = orc.cross_entropy(np.array(case["logits"], np.float32), np.array(case["label"]))
+        assert math.isinf(loss) and loss > 0, case["source"]
+    # a masked NON-target entry gives NaN (-inf * 0), the reference's quirk (regression.rs:205-210)
+    loss, _ = orc.cross_entropy(np.array([[1000.0, -1000.0]], np.float32), np.array([0]))
+    assert math.isnan(loss)
+    with pytest.raises(IndexError):
+        orc.cross_entropy(np.zeros((2, 3), np.float32), np.array([0, 3]))
+
+
+def test_gelu_formulas(orc, golden):
+    for case in golden["gelu"]:
+        x = np.array(case["x"], dtype=np.float32)
+        approx = case["approximate"] == "tanh"
+        y = orc.gelu(x, approx)
+        g = orc.gelu_backward(x, np.ones_like(x), approx)
+        if approx:
+            k = np.sqrt(np.array(2.0 / np.pi, dtype=x.dtype))
+            inner = k * (x + 0.044715 * x ** 3)
+            exp = 0.5 * x * (1.0 + np.tanh(inner))
+            th = np.tanh(inner)
+            expg = 0.5 * (1.0 + th) + 0.5 * x * (1.0 - th ** 2) * k * (1.0 + 3.0 * 0.044715 * x ** 2)
+        else:
+            erfv = np.array([math.erf(float(v)) for v in (x / np.sqrt(np.float32(2.0)))], dtype=x.dtype)
+            exp = 0.5 * x * (1.0 + erfv)
+            expg = 0.5 * (1.0 + erfv) + x * np.exp(-0.5 * x ** 2) / np.sqrt(np.float32(2.0 * np.pi))
+        np.testing.assert_allclose(y, exp, rtol=case["rtol"], atol=max(case["atol"], 1e-7), err_msg=case["source"])
+        np.testing.assert_allclose(g, expg, rtol=case["rtol"], atol=max(case["atol"], 1e-7), err_msg=case["source"])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.int32, np.int64])
+def test_matmul_vs_numpy_small(orc, rng, dtype):
+    for (bsz, m, k, n) in [(1, 5, 4, 3), (3, 7, 9, 2), (1, 1, 1, 1), (2, 33, 300, 17)]:
+        if np.issubdtype(dtype, np.integer):
+            a = rng.integers(-8, 9, (bsz, m, k)).astype(dtype)
+            b = rng.integers(-8, 9, (bsz, k, n)).astype(dtype)
+            np.testing.assert_array_equal(orc.matmul(a, b), np.matmul(a, b))
+        else:
+            a = rng.standard_normal((bsz, m, k)).astype(dtype)
+            b = rng.standard_normal((bsz, k, n)).astype(dtype)
+            ref = np.matmul(a.astype(np.float64), b.astype(np.float64))
+            np.testing.assert_allclose(orc.matmul(a, b), ref, rtol=1e-4 if dtype == np.float32 else 1e-12,
+                                       atol=1e-4 if dtype == np.float32 else 1e-12)
+
+
+def test_int_matmul_wraps(orc):
+    a = np.full((1, 2), 2 ** 30, dtype=np.int32)
+    b = np.full((2, 1), 4, dtype=np.int32)
+    assert orc.matmul(a, b)[0, 0] == 0  # 2 * 2^32 mod 2^32
+    a64 = np.full((1, 2), 2 ** 62, dtype=np.int64)
+    b64 = np.full((2, 1), 4, dtype=np.int64)
+    assert orc.matmul(a64, b64)[0, 0] == 0
+
+
+def test_conv_backward_finite_difference(orc, rng):
+    """The reference checks conv gradients by finite differences (tests/nn/test_layers.py:160-204)."""
+    for stride, padding in [((1, 1), (0, 0)), ((2, 2), (1, 1)), ((1, 2), (2, 1))]:
+        x = rng.standard_normal((2, 2, 5, 6)).astype(np.float32)
+        w = rng.standard_normal((3, 2, 3, 2)).astype(np.float32)
+        b = rng.standard_normal(3).astype(np.float32)
+        y = orc.conv2d(x, w, b, stride, padding)
+        go = rng.standard_normal(y.shape).astype(np.float32)
+        gx, gw, gb = orc.conv2d_backward(x, w, go, stride, padding)
+        f = lambda xx, ww, bb: float((orc.conv2d(xx, ww, bb, stride, padding).astype(np.float64) * go).sum())
+        eps = 1e-2
+        for arr, grad in ((x, gx), (w, gw), (b, gb)):
+            for idx in [tuple(rng.integers(0, s) for s in arr.shape) for _ in range(4)]:
+                old = arr[idx]
+                arr[idx] = old + eps
+                fp = f(x, w, b)
+                arr[idx] = old - eps
+                fm = f(x, w, b)
+                arr[idx] = old
+                num = (fp - fm) / (2 * eps)
+                assert abs(num - grad[idx]) <= 1e-2 * max(1.0, abs(num))
+
+
+def test_mlp_step_matches_composition(orc, rng):
+    """orc.mlp_train_step equals the composition of the single-op oracles."""
+    dims = [6, 5, 4]
+    bsz = 7
+    x = rng.standard_normal((bsz, dims[0])).astype(np.float32)
+    lab = rng.integers(0, dims[-1], bsz)
+    w1 = rng.standard_normal((5, 6)).astype(np.float32)
+    b1 = rng.standard_normal(5).astype(np.float32)
+    w2 = rng.standard_normal((4, 5)).astype(np.float32)
+    b2 = rng.standard_normal(4).astype(np.float32)
+    params = np.concatenate([w1.ravel(), b1, w2.ravel(), b2]).astype(np.float32)
+    m, v = np.zeros_like(params), np.zeros_like(params)
+    p0 = params.copy()
+    loss, grads = orc.mlp_train_step(dims, x, lab, params, m, v, 1e-3, 0.9, 0.999, 1e-8, 1, want_grads=True)
+    z1 = orc.dense_forward(x, w1, b1)
+    h1, mask = orc.relu(z1)
+    z2 = orc.dense_forward(h1, w2, b2)
+    l2, g2 = orc.cross_entropy(z2, lab)
+    assert loss == pytest.approx(float(l2), rel=0, abs=0)
+    gb2 = orc.sum_dim0(g2)
+    gh1, gw2t = orc.matmul_backward(h1, np.ascontiguousarray(w2.T), g2)
+    gz1 = orc.relu_backward(mask, gh1)
+    gb1 = orc.sum_dim0(gz1)
+    _, gw1t = orc.matmul_backward(x, np.ascontiguousarray(w1.T), gz1, need_a=False)
+    exp = np.concatenate([gw1t.T.ravel(), gb1, gw2t.T.ravel(), gb2])
+    np.testing.assert_array_equal(grads, exp)
+    pe, me, ve = p0.copy(), np.zeros_like(p0), np.zeros_like(p0)
+    orc.adam_step(pe, exp, me, ve, 1e-3, 0.9, 0.999, 1e-8, step=1)
+    np.testing.assert_array_equal(params, pe)

@@ -1,0 +1,135 @@
+"""Column sum (bias gradient), activations, cross entropy and Adam on the device vs the oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import fval
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(be, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(be.device)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("m,n", [(1, 1), (33, 7), (32, 128), (32, 10), (1000, 130), (4096, 515), (65536, 64)])
+def test_colsum_matches_oracle(be, orc, rng, dtype, m, n):
+    x = rng.standard_normal((m, n)).astype(dtype)
+    got = be.colsum(dev(be, x))
+    again = be.colsum(dev(be, x))
+    be.sync()
+    assert torch.equal(got, again)  # deterministic
+    ref = orc.sum_dim0(x)           # ascending-row f32 sum; the reference's own order is rayon-dependent
+    exact = x.astype(np.float64).sum(0)
+    tol = (1e-6 if dtype == np.float32 else 1e-14) * np.abs(x).astype(np.float64).sum(0) + 1e-30
+    assert np.all(np.abs(got.cpu().numpy() - exact) <= tol)
+    assert np.all(np.abs(ref - exact) <= 64 * tol)
+
+
+def test_colsum_empty_rows(be):
+    out = be.colsum(torch.empty((0, 5), dtype=torch.float32, device=be.device))
+    be.sync()
+    assert not out.cpu().numpy().any()
+
+
+def test_relu_forward_backward_known_answer(be, golden):
+    for case in golden["relu_backward"]:
+        x = np.array([fval(v) for v in case["x"]], np.float32)
+        go = np.array([fval(v) for v in case["grad_out"]], np.float32)
+        y = be.act_fwd(dev(be, x), 1)
+        gi = be.act_bwd(y, dev(be, go), 1).cpu().numpy()
+        exp = np.array([fval(v) for v in case["grad_in"]], np.float32)
+        np.testing.assert_array_equal(np.isnan(gi), np.isnan(exp))
+        np.testing.assert_array_equal(gi[~np.isnan(exp)], exp[~np.isnan(exp)])
+        yn = y.cpu().numpy()
+        assert yn[0] == 0 and np.isnan(yn[1]) and yn[2] == 1
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_activations_match_oracle(be, orc, rng, dtype):
+    x = (rng.standard_normal(10007) * 3).astype(dtype)
+    go = rng.standard_normal(10007).astype(dtype)
+    y, mask = orc.relu(x)
+    yd = be.act_fwd(dev(be, x), 1)
+    np.testing.assert_array_equal(yd.cpu().numpy(), y)
+    np.testing.assert_array_equal(be.act_bwd(yd, dev(be, go), 1).cpu().numpy(), orc.relu_backward(mask, go))
+    rtol = 2e-6 if dtype == np.float32 else 1e-13
+    for act, approx in ((2, False), (3, True)):
+        np.testing.assert_allclose(be.act_fwd(dev(be, x), act).cpu().numpy(), orc.gelu(x, approx), rtol=rtol,
+                                   atol=rtol)
+        np.testing.assert_allclose(be.act_bwd(dev(be, x), dev(be, go), act).cpu().numpy(),
+                                   orc.gelu_backward(x, go, approx), rtol=rtol, atol=rtol)
+
+
+def test_gelu_reference_points(be, golden):
+    import minitensor_b200.tensor as mt
+    for case in golden["gelu"]:
+        data = np.array(case["x"], np.float32)
+        t = mt.Tensor(data, requires_grad=True)
+        out = t.gelu(approximate=case["approximate"])
+        out.sum().backward()
+        if case["approximate"] == "tanh":
+            k = np.sqrt(np.array(2.0 / np.pi, dtype=data.dtype))
+            inner = k * (data + 0.044715 * data ** 3)
+            th = np.tanh(inner)
+            exp = 0.5 * data * (1.0 + th)
+            expg = 0.5 * (1.0 + th) + 0.5 * data * (1.0 - th ** 2) * k * (1.0 + 3.0 * 0.044715 * data ** 2)
+        else:
+            erfv = np.array([math.erf(float(v)) for v in (data / np.sqrt(np.float32(2.0)))], dtype=data.dtype)
+            exp = 0.5 * data * (1.0 + erfv)
+            expg = 0.5 * (1.0 + erfv) + data * np.exp(-0.5 * data ** 2) / np.sqrt(np.float32(2.0 * np.pi))
+        np.testing.assert_allclose(out.numpy(), exp, rtol=case["rtol"], atol=max(case["atol"], 1e-7))
+        np.testing.assert_allclose(t.grad.numpy(), expg, rtol=case["rtol"], atol=max(case["atol"], 1e-7))
+
+
+@pytest.mark.parametrize("bsz,ncls", [(32, 10), (7, 33), (100, 1000), (1, 2), (513, 5)])
+@pytest.mark.parametrize("label_dtype", [np.int64, np.int32])
+def test_cross_entropy_matches_oracle(be, orc, rng, bsz, ncls, label_dtype):
+    logits = (rng.standard_normal((bsz, ncls)) * 3).astype(np.float32)
+    labels = rng.integers(0, ncls, bsz).astype(label_dtype)
+    for mean in (True, False):
+        loss, grad = be.cross_entropy(dev(be, logits), dev(be, labels), mean=mean)
+        be.sync()
+        ref_loss, ref_grad = orc.cross_entropy(logits, labels, mean=mean)
+        assert abs(float(loss.item()) - float(ref_loss)) <= 2e-6 * max(1.0, abs(float(ref_loss)))
+        np.testing.assert_allclose(grad.cpu().numpy(), ref_grad, rtol=1e-5, atol=2e-6)  # expf differs by ulps
+
+
+def test_cross_entropy_limits_and_bad_label(be, orc, golden):
+    for case in golden["cross_entropy_limits"]:
+        loss, _ = be.cross_entropy(dev(be, np.array(case["logits"], np.float32)), dev(be, np.array(case["label"])))
+        be.sync()
+        assert math.isinf(loss.item()) and loss.item() > 0
+    loss, _ = be.cross_entropy(dev(be, np.array([[1000.0, -1000.0]], np.float32)), dev(be, np.array([0])))
+    be.sync()
+    assert math.isnan(loss.item())  # the reference's -inf * 0 quirk, kept
+    be.cross_entropy(dev(be, np.zeros((2, 3), np.float32)), dev(be, np.array([0, 3])))
+    with pytest.raises(IndexError):
+        be.sync()
+    be.sync()  # the flag is cleared once reported
+
+
+def test_adam_bit_exact_with_oracle(be, orc, rng, golden):
+    for case in golden["adam"]:
+        p = dev(be, np.array(case["param"], np.float32))
+        g = dev(be, np.array(case["grad"], np.float32))
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        be.adam_step(p, g, m, v, lr=case["lr"], beta1=case["beta1"], beta2=case["beta2"], eps=case["eps"], step=1)
+        assert np.all(np.abs(p.cpu().numpy() - case["expected"]) < case["atol"])
+    n = 100003
+    p0 = rng.standard_normal(n).astype(np.float32)
+    for wd, dec in ((0.0, False), (0.01, False), (0.01, True)):
+        pn, mn, vn = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+        pd, md, vd = dev(be, p0), dev(be, mn), dev(be, vn)
+        for step in (1, 2, 3):
+            g = (rng.standard_normal(n) * 10.0 ** rng.integers(-6, 2, n)).astype(np.float32)
+            orc.adam_step(pn, g, mn, vn, 1e-3, 0.9, 0.999, 1e-8, weight_decay=wd, decoupled=dec, step=step)
+            be.adam_step(pd, dev(be, g), md, vd, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=wd,
+                         decoupled=dec, step=step)
+        be.sync()
+        np.testing.assert_array_equal(pd.cpu().numpy(), pn)
+        np.testing.assert_array_equal(md.cpu().numpy(), mn)
+        np.testing.assert_array_equal(vd.cpu().numpy(), vn)
