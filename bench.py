@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one training step of the large MLP configuration
+(8192 -> 4096 -> 4096 -> 4096 -> 1000 with ReLU, CrossEntropy, Adam, global batch
+65536 f32, N(0,1) inputs, labels uniform in [0,1000), He-uniform weights),
+batch-sharded by rows over N GPUs (one process per GPU, NCCL all-reduce of the
+parameter gradients).  The metric is whole-job training samples per second.
+At N = 1 the same line also carries the f32 4096^3 GEMM rate and the CPU
+baseline.  All inputs are synthetic and seeded; nothing is read from disk.
+
+`--impl reference` times the CPU restatement of the reference's own training
+step (oracle/oracle.cpp, OpenMP over the host cores) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DIMS = [8192, 4096, 4096, 4096, 1000]
+GLOBAL_BATCH = 65536
+METRIC = "mlp_train_samples_per_s"
+UNIT = "samples/s"
+WORKLOAD = "MLP 8192-4096-4096-4096-1000 ReLU + CrossEntropy + Adam, f32, global batch 65536"
+
+
+def _peaks():
+    """Measured peaks of this pool (driver-written file), else the stated fallback."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples taken while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.proc = None
+        self.idx = device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i",
+                 str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=10)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------- CPU side
+def cpu_mlp_samples_per_s(sample_rows: int, steps: int, warmup: int):
+    """Times oracle.mlp_train_step (the reference's step restated for the CPU) on `sample_rows` rows."""
+    import oracle
+    oracle.build()
+    from minitensor_b200.mlp import mlp_layout
+    rng = np.random.default_rng(1)
+    _, _, total = mlp_layout(DIMS)
+    params = np.zeros(total, dtype=np.float32)
+    w_off, b_off, _ = mlp_layout(DIMS)
+    for l in range(len(DIMS) - 1):
+        n = DIMS[l] * DIMS[l + 1]
+        params[w_off[l]:w_off[l] + n] = rng.uniform(-1, 1, n).astype(np.float32) * np.float32(np.sqrt(6.0 / DIMS[l]))
+    m, v = np.zeros_like(params), np.zeros_like(params)
+    x = rng.standard_normal((sample_rows, DIMS[0])).astype(np.float32)
+    labels = rng.integers(0, DIMS[-1], sample_rows)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle.mlp_train_step(DIMS, x, labels, params, m, v, 1e-3, 0.9, 0.999, 1e-8, i + 1)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    per_step = sum(times) / len(times)
+    return sample_rows / per_step, per_step, oracle.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    rows = 2048
+    value, per_step, cores = cpu_mlp_samples_per_s(rows, max(1, args.steps), max(0, min(args.warmup, 1)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": f"{rows} of {GLOBAL_BATCH} rows per step, same layer sizes"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"one reference-ordered training step on {rows} rows (of {GLOBAL_BATCH}); "
+                                   "the reference itself is Rust and cannot be built on this box"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------- GPU side
+def gemm4096(be, torch, peaks):
+    """f32 4096^3 through the public GEMM call: whole call (operand splits + tensor kernel) and the
+    tensor kernel alone, L2 flushed between iterations."""
+    n = 4096
+    g = torch.Generator(device="cpu").manual_seed(7)
+    a = torch.randn(n, n, generator=g).to(be.device)
+    b = torch.randn(n, n, generator=g).to(be.device)
+    out = torch.empty(n, n, device=be.device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=be.device)
+    for _ in range(3):
+        be.gemm(a, b, out=out)
+    torch.cuda.synchronize()
+    be.profile(True)
+    total = 0.0
+    iters = 10
+    for _ in range(iters):
+        flush.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        be.gemm(a, b, out=out)
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    launches, kms, kwork = be.profile_read(0)
+    be.profile(False)
+    ms = total / iters
+    flops = 2.0 * n ** 3
+    peak = peaks["bf16_burst"] / 6.0
+    return {"ms": ms, "tflops": flops / ms / 1e9, "pct_of_peak": 100.0 * flops / ms / 1e9 / peak,
+            "kernel_only_tflops": kwork / kms / 1e9 if kms else None,
+            "kernel_only_pct_of_peak": 100.0 * kwork / kms / 1e9 / peak if kms else None,
+            "peak_tflops": peak, "peak_def": "measured bf16 dense burst / 6 split products per f32 product"}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from minitensor_b200.mlp import MLPTrainer, mlp_flops_per_sample, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(json.dumps({"error": f"--gpus {args.gpus} needs torchrun with {args.gpus} processes"}))
+            return 2
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks = _peaks()
+    lo, hi = shard_rows(GLOBAL_BATCH, world, rank)
+    rows = hi - lo
+    trainer = MLPTrainer(DIMS, rows, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, device=local, world_size=world, seed=0)
+    be = trainer.be
+    dev = be.device
+
+    # synthetic shard, generated on the host (seeded per rank) and staged in pinned memory
+    g = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    host_x = [torch.randn(rows, DIMS[0], generator=g).pin_memory() for _ in range(2)]
+    host_y = [torch.randint(0, DIMS[-1], (rows,), generator=g, dtype=torch.int64).pin_memory() for _ in range(2)]
+    x = host_x[0].to(dev)
+    y = host_y[0].to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident steps (inputs already in HBM)
+    for _ in range(args.warmup):
+        trainer.step(x, y)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    be.profile(True)
+    launches0 = be.launches
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    loss = None
+    for _ in range(args.steps):
+        loss = trainer.step(x, y)
+    e.record()
+    barrier()
+    ms_total = max_over_ranks(s.elapsed_time(e))
+    clocks = sampler.stop() if rank == 0 else None
+    gpu_launches = be.launches - launches0
+    k_launches, k_ms, k_flops = be.profile_read(0)
+    s_launches, s_ms, s_bytes = be.profile_read(1)
+    be.profile(False)
+    be.sync()
+    final_loss = float(loss.item())
+    ms_per_step = ms_total / args.steps
+    value = GLOBAL_BATCH / (ms_per_step * 1e-3)
+
+    # ---- end to end: every step copies its batch from pinned host memory and reads the loss back
+    slot = trainer.prefetch(host_x[0], host_y[0])
+    for i in range(2):
+        nxt = trainer.prefetch(host_x[(i + 1) % 2], host_y[(i + 1) % 2])
+        float(trainer.step_slot(slot).item())
+        slot = nxt
+    barrier()
+    s.record()
+    for i in range(args.steps):
+        nxt = trainer.prefetch(host_x[(i + 1) % 2], host_y[(i + 1) % 2])   # next batch: overlaps this step
+        float(trainer.step_slot(slot).item())                            # loss read back every step
+        slot = nxt
+    e.record()
+    barrier()
+    e2e_ms = max_over_ranks(s.elapsed_time(e)) / args.steps
+    e2e_value = GLOBAL_BATCH / (e2e_ms * 1e-3)
+    h2d = rows * DIMS[0] * 4 + rows * 8
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
+
+    peak_f32 = peaks["bf16_sustained"] / 6.0
+    achieved = k_flops / k_ms / 1e9 if k_ms else None
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "rows_per_gpu": rows,
+                   "parallelism": f"dp{world}", "f32_mode": "bf16x6 split (f32-accurate)",
+                   "l2": "inputs larger than L2 (2.1 GB batch, 1 GB activations per layer)",
+                   "flops_per_sample": mlp_flops_per_sample(DIMS), "final_loss": final_loss},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4, "note": "next batch's host->device copy overlaps the current step"},
+        "gpu_launches": gpu_launches,
+        "roofline": {
+            "kernel": "gemm_split_umma_kernel", "bound": "tensor", "achieved": achieved, "peak": peak_f32,
+            "unit": "TFLOP/s", "frac": (achieved / peak_f32) if achieved else None,
+            "peak_def": f"{peaks['source']} bf16 dense sustained {peaks['bf16_sustained']} TFLOP/s / 6 "
+                        "(six bf16 tensor products per f32 product)",
+            "launches": k_launches, "avg_launch_ms": k_ms / k_launches if k_launches else None,
+            "share_of_step": k_ms / ms_total if ms_total else None,
+            "traffic": None,
+            "split_kernels": {"launches": s_launches, "ms": s_ms, "gbs": s_bytes / s_ms / 1e6 if s_ms else None,
+                              "share_of_step": s_ms / ms_total if ms_total else None},
+        },
+        "step_tflops": mlp_flops_per_sample(DIMS) * value / 1e12,
+    }
+    if world == 1:
+        line["gemm_f32_4096"] = gemm4096(be, torch, peaks)
+        if not args.no_cpu:
+            rows_cpu = 2048
+            v, per_step, cores = cpu_mlp_samples_per_s(rows_cpu, 1, 1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"one reference-ordered training step on {rows_cpu} rows (of "
+                                              f"{GLOBAL_BATCH}), {per_step:.2f} s"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

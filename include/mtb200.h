@@ -74,6 +74,18 @@ int32_t mtb200_set_stream(mtb200_handle h, void* cuda_stream);
 /* CudaBackend::synchronize (engine/src/backends/cuda/mod.rs:153-161); also
  * reports MTB200_ERR_DEVICE_WAIT if a kernel recorded an expired wait. */
 int32_t mtb200_sync(mtb200_handle h);
+/* Per-launch timing, the device-side analogue of the reference's manual
+ * OperationProfiler (engine/src/debug.rs:273-352).  While enabled, every kernel
+ * of the listed classes is bracketed by a CUDA event pair on the handle's
+ * stream.  profile_enable(1) clears earlier records; profile_read synchronises
+ * and returns launches, summed device time and summed algorithmic work of one
+ * class: 0 = split-bf16 tensor-core GEMM kernel (work = 2*M*N*K flops),
+ * 1 = operand split kernels (bytes), 2 = f64 GEMM (flops), 3 = integer GEMM
+ * (ops), 4 = conv gather kernels (bytes). */
+int32_t mtb200_profile_enable(mtb200_handle h, int32_t on);
+int32_t mtb200_profile_read(mtb200_handle h, int32_t kernel_class, int64_t* launches,
+                            double* total_ms, double* total_work);
+
 /* Bytes of scratch memory the handle currently holds (operand splits, partial sums). */
 int32_t mtb200_workspace_bytes(mtb200_handle h, size_t* bytes);
 

@@ -29,6 +29,8 @@ SIGNATURES = {
     "mtb200_destroy": (_i32, [_vp]),
     "mtb200_set_stream": (_i32, [_vp, _vp]),
     "mtb200_sync": (_i32, [_vp]),
+    "mtb200_profile_enable": (_i32, [_vp, _i32]),
+    "mtb200_profile_read": (_i32, [_vp, _i32, C.POINTER(_i64), C.POINTER(_f64), C.POINTER(_f64)]),
     "mtb200_workspace_bytes": (_i32, [_vp, C.POINTER(C.c_size_t)]),
     "mtb200_alloc": (_i32, [_vp, C.c_size_t, C.POINTER(_vp)]),
     "mtb200_free": (_i32, [_vp, _vp, C.c_size_t]),

@@ -68,6 +68,16 @@ class Backend:
         """Wait for the stream and raise if a kernel reported an expired wait or a bad label."""
         check(self.lib.mtb200_sync(self._h))
 
+    def profile(self, on: bool) -> None:
+        """Start (clearing earlier records) or stop per-launch event timing inside the library."""
+        check(self.lib.mtb200_profile_enable(self._h, int(on)))
+
+    def profile_read(self, kernel_class: int = 0):
+        """(launches, total device ms, total algorithmic work) of one kernel class since profile(True)."""
+        n, ms, work = C.c_int64(), C.c_double(), C.c_double()
+        check(self.lib.mtb200_profile_read(self._h, kernel_class, C.byref(n), C.byref(ms), C.byref(work)))
+        return n.value, ms.value, work.value
+
     def workspace_bytes(self) -> int:
         n = C.c_size_t()
         check(self.lib.mtb200_workspace_bytes(self._h, C.byref(n)))
@@ -113,7 +123,7 @@ class Backend:
         check(self.lib.mtb200_gemm(self._h, dt, int(trans_a), int(trans_b), batch, m, n, k,
                                    _ptr(a), stride_a, _ptr(b), stride_b, _ptr(out), m * n,
                                    _ptr(bias), epilogue, _ptr(aux), (variant << 8) | f32_mode))
-        self.launches += 3 if dt == F32 else 1
+        self.launches += 4 if dt == F32 else 1  # two operand splits, GEMM, gated f32 redo
         return out
 
     # ------------------------------------------------------------------ reductions / elementwise

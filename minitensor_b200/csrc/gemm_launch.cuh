@@ -27,6 +27,7 @@ inline size_t split_bytes(int rows, int Kp, int batch) {
 inline int32_t launch_split(mtb200_ctx* h, const float* src, bool trans, int rows, int K, int Kp,
                             int batch, long long bstride, __nv_bfloat16* dst, int nsplit,
                             uint32_t* nf_word = nullptr, uint32_t nf_epoch = 0) {
+  ProfScope prof(h, PROF_SPLIT, double(batch) * rows * (4.0 * K + 2.0 * nsplit * Kp));
   if (!trans) {
     const long long total = static_cast<long long>(rows) * (Kp / 8);
     const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
@@ -57,6 +58,7 @@ inline int32_t launch_variant(mtb200_ctx* h, const SplitOperand& a, const SplitO
   g.kb_batch_stride *= (64 / BK);
   const long long tiles = static_cast<long long>((g.M + Cfg::BM - 1) / Cfg::BM) * ((g.N + BN - 1) / BN) * g.batch;
   const int grid = int(std::min<long long>(tiles, h->sm_count));
+  ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.M * g.N * double(g.num_kb) * BK * g.batch);
   kern<<<grid, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(ta, tb, g);
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;

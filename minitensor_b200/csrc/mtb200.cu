@@ -144,6 +144,10 @@ int32_t mtb200_destroy(mtb200_handle h) {
   if (!h) return MTB200_OK;
   DeviceGuard guard(h->device);
   cudaStreamSynchronize(h->stream);
+  for (auto& r : h->prof) {
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
   if (h->workspace) cudaFree(h->workspace);
   if (h->status) cudaFree(h->status);
   if (h->status_host) cudaFreeHost(h->status_host);
@@ -173,6 +177,37 @@ int32_t mtb200_sync(mtb200_handle h) {
                   wait_code >> 8, wait_code & 0xffu);
     return fail(MTB200_ERR_BAD_LABEL, "cross entropy saw a class index outside [0, C)");
   }
+  return MTB200_OK;
+}
+
+int32_t mtb200_profile_enable(mtb200_handle h, int32_t on) {
+  MTB_CHECK_HANDLE(h);
+  for (auto& r : h->prof) {
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
+  h->prof.clear();
+  h->profiling = on != 0;
+  return MTB200_OK;
+}
+
+int32_t mtb200_profile_read(mtb200_handle h, int32_t kernel_class, int64_t* launches, double* total_ms,
+                            double* total_work) {
+  MTB_CHECK_HANDLE(h);
+  if (kernel_class < 0 || kernel_class >= PROF_NUM) return fail(MTB200_ERR_INVALID, "unknown kernel class %d", kernel_class);
+  if (!launches || !total_ms || !total_work) return fail(MTB200_ERR_INVALID, "null output pointer");
+  MTB_CUDA(cudaStreamSynchronize(h->stream));
+  int64_t n = 0;
+  double ms = 0.0, work = 0.0;
+  for (auto& r : h->prof) {
+    if (r.cls != kernel_class) continue;
+    float t = 0.0f;
+    MTB_CUDA(cudaEventElapsedTime(&t, r.start, r.stop));
+    ms += t;
+    work += r.work;
+    ++n;
+  }
+  *launches = n; *total_ms = ms; *total_work = work;
   return MTB200_OK;
 }
 
@@ -318,6 +353,7 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
   g.ldc = N; g.c_sb = stride_c;
   g.bias = bias; g.aux = aux; g.epilogue = epilogue;
   g.gate = nullptr; g.gate_value = 0;
+  ProfScope prof(h, dtype == MTB200_F64 ? PROF_GEMM_F64 : PROF_GEMM_INT, 2.0 * M * N * K * batch);
   if (dtype == MTB200_F64) {
     const int smem = 4 * D_BK * D_PITCH * int(sizeof(double));
     MTB_CUDA(cudaFuncSetAttribute(gemm_f64_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

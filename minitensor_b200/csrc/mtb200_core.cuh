@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "../../include/mtb200.h"
 
@@ -48,6 +49,10 @@ struct mtb200_ctx {
   uint32_t* status = nullptr;       // device, 4 words
   uint32_t* status_host = nullptr;  // pinned, 2 words
   uint32_t epoch = 0;               // f32 GEMM call counter (see status[2])
+  // optional per-launch timing (mtb200_profile_*): event pairs around kernels
+  struct ProfRec { cudaEvent_t start, stop; double work; int cls; };
+  bool profiling = false;
+  std::vector<ProfRec> prof;
 };
 
 namespace mtb {
@@ -85,5 +90,31 @@ int32_t make_split_tmap(CUtensorMap* out, const void* base, uint64_t Kp, uint64_
                         uint64_t planes, uint32_t bk, uint32_t box_rows);
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Kernel classes of the launch profiler.
+enum ProfClass { PROF_GEMM_UMMA = 0, PROF_SPLIT = 1, PROF_GEMM_F64 = 2, PROF_GEMM_INT = 3, PROF_CONV_GATHER = 4,
+                 PROF_NUM = 5 };
+
+// Brackets the launches made in its scope with a CUDA event pair on the handle's
+// stream when profiling is on; costs nothing otherwise.
+struct ProfScope {
+  mtb200_ctx* h;
+  bool on;
+  cudaEvent_t start = nullptr;
+  double work;
+  int cls;
+  ProfScope(mtb200_ctx* h_, int cls_, double work_) : h(h_), on(h_->profiling), work(work_), cls(cls_) {
+    if (!on) return;
+    if (cudaEventCreate(&start) != cudaSuccess) { on = false; return; }
+    cudaEventRecord(start, h->stream);
+  }
+  ~ProfScope() {
+    if (!on) return;
+    cudaEvent_t stop = nullptr;
+    if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start); return; }
+    cudaEventRecord(stop, h->stream);
+    h->prof.push_back({start, stop, work, cls});
+  }
+};
 
 }  // namespace mtb
