@@ -128,6 +128,30 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
  * Deterministic: the same input always gives the same bits. */
 int32_t mtb200_colsum(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, const void* X, void* out);
 
+/* ---- bias gradient for callers that must not allocate.  (No counterpart in the
+ * reference: its CPU engine sums into a freshly allocated tensor.)
+ * Same result as mtb200_colsum, but the partial sums live in a fixed array
+ * inside the library instead of the handle's growable workspace, so the call
+ * never reaches cudaMalloc / cudaFree (nor their device-wide synchronisation)
+ * and needs no handle: work is enqueued on `cuda_stream` of the CURRENT device.
+ * Meant for callers that run where allocation is off limits: between the
+ * begin and end of a stream capture, inside an application whose own pool
+ * owns all device memory, or in a loop that cannot afford an allocator stall.
+ * Limits and rules:
+ *  - N * sizeof(element) must not exceed MTB200_COLSUM_NOALLOC_SCRATCH_BYTES
+ *    (1,048,576 f32 or 524,288 f64 columns); wider inputs are rejected with
+ *    MTB200_ERR_INVALID.  Every GPU that loads the library holds that array
+ *    until the process exits.
+ *  - The first call on each device looks the array's device address up
+ *    (cudaGetSymbolAddress); make that first call before starting any stream
+ *    capture.
+ *  - All calls share the one array.  Each call overwrites what it reads, so
+ *    stale contents are harmless, but two calls that may run on the GPU at
+ *    the same time (different streams, no ordering between them) race. */
+#define MTB200_COLSUM_NOALLOC_SCRATCH_BYTES (4u << 20)
+int32_t mtb200_colsum_noalloc(void* cuda_stream, int32_t dtype, int64_t M, int64_t N, const void* X,
+                              void* out);
+
 /* ---- activations outside a GEMM (f32 / f64); act uses the MTB200_EPI_* numbers 1..3.
  * forward: relu / gelu (engine/src/operations/activation/trigonometry.rs:308-344,499-544).
  * backward: dx = dy * f'; `ref` is the activation OUTPUT for relu and the

@@ -40,6 +40,7 @@ SIGNATURES = {
     "mtb200_gemm": (_i32, [_vp, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _i64,
                            _vp, _i64, _vp, _i32, _vp, _i32]),
     "mtb200_colsum": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
+    "mtb200_colsum_noalloc": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
     "mtb200_act_fwd": (_i32, [_vp, _i32, _i32, _i64, _vp, _vp]),
     "mtb200_act_bwd": (_i32, [_vp, _i32, _i32, _i64, _vp, _vp, _vp]),
     "mtb200_bias_act": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _i32, _vp]),
