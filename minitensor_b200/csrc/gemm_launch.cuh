@@ -3,6 +3,7 @@
 #pragma once
 #include "mtb200_core.cuh"
 #include "gemm_split_umma.cuh"
+#include "gemm_split_umma2.cuh"
 #include "split_bf16.cuh"
 #include "gemm_f64_int.cuh"
 #include <algorithm>
@@ -64,9 +65,48 @@ inline int32_t launch_variant(mtb200_ctx* h, const SplitOperand& a, const SplitO
   return MTB200_OK;
 }
 
+// Two-CTA kernel: clusters of two CTAs, one 256 x 256 tile per pair at a time.
+template <int BK, int STAGES>
+inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp, GemmArgs g) {
+  using Cfg = Gemm2Cfg<BK, STAGES>;
+  auto kern = gemm_split_umma2_kernel<BK, STAGES>;
+  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  CUtensorMap ta, tb;
+  int32_t rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(3) * a.batch, BK, Cfg::BM);
+  if (rc) return rc;
+  rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(3) * b.batch, BK, Cfg::BNH);
+  if (rc) return rc;
+  g.num_kb = g.num_kb ? g.num_kb * (64 / BK) : Kp / BK;
+  g.kb_batch_stride *= (64 / BK);
+  const long long tiles = static_cast<long long>((g.M + Cfg::TILE_M - 1) / Cfg::TILE_M) *
+                          ((g.N + Cfg::TILE_N - 1) / Cfg::TILE_N) * g.batch;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(Cfg::NUM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = h->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(2 * (h->sm_count / 2));
+  int max_clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0) {
+    cudaGetLastError();
+    max_clusters = h->sm_count / 2;
+  }
+  const int pairs = int(std::min<long long>(tiles, std::min(max_clusters, h->sm_count / 2)));
+  cfg.gridDim = dim3(2 * pairs);
+  ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.M * g.N * double(g.num_kb) * BK * g.batch);
+  MTB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, g));
+  return MTB200_OK;
+}
+
 // C[b] = epilogue(A_split[b] * B_split[b]^T + bias) on prepared operands.
 // variant: 0 = choose by N; 1 = 128x256 tile, K block 32; 2 = 128x128, K block 64;
-// 3 = 128x64, K block 64; 4 = 128x128, K block 32.
+// 3 = 128x64, K block 64; 4 = 128x128, K block 32; 5 / 6 = two-CTA 256x256 pair tile with K block 64 / 32.
 inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp,
                               int batch, int M, int N, float* C, long long ldc, long long strideC,
                               const float* bias, int epilogue, const float* aux, int mode, int variant,
@@ -83,12 +123,15 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
   g.bias_per_row = bias_per_row;
   g.kb_batch_stride = kb_batch_stride;
   g.num_kb = num_kb_override;  // 0: the whole padded K
-  if (variant == 0) variant = (N > 128) ? 1 : (N > 64 ? 2 : 3);
+  // two-CTA pair tiles whenever the output is at least one pair tile tall and wide
+  if (variant == 0) variant = (M > 128 && N > 128) ? 5 : ((N > 128) ? 1 : (N > 64 ? 2 : 3));
   switch (variant) {
     case 1: return launch_variant<256, 32, 3>(h, a, b, Kp, g);
     case 2: return launch_variant<128, 64, 2>(h, a, b, Kp, g);
     case 3: return launch_variant<64, 64, 3>(h, a, b, Kp, g);
     case 4: return launch_variant<128, 32, 4>(h, a, b, Kp, g);
+    case 5: return launch_variant2<64, 2>(h, a, b, Kp, g);
+    case 6: return launch_variant2<32, 4>(h, a, b, Kp, g);
     default: return fail(MTB200_ERR_INVALID, "unknown GEMM tile variant %d", variant);
   }
 }

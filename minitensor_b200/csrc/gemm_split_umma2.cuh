@@ -1,0 +1,270 @@
+// Two-CTA form of the split-bf16 tensor-core GEMM (see gemm_split_umma.cuh for
+// the arithmetic).  Two CTAs of a cluster on neighbouring SMs work on one
+// 256 x 256 output tile with tcgen05.mma.cta_group::2: each CTA stages 128
+// rows of A and 128 of the 256 B columns, the pair's tensor cores exchange
+// the B halves, and each CTA ends up with its 128 x 256 slice of the
+// accumulator in its own tensor memory.  Per SM this halves the B-operand
+// shared-memory reads of the one-CTA 128 x 256 tile (8 KB instead of 12 KB per
+// MMA) and shrinks the ring writes, which is what limited that kernel.
+//
+// Roles per CTA: warp 0 lane 0 = TMA producer for this CTA's halves; warp 1 =
+// TMEM allocation in both CTAs, MMA issue in the leader (cluster rank 0) only;
+// warps 2..5 = epilogue for this CTA's 128 rows.  Barriers:
+//   full[s]      leader only, 2 arrivals (one producer per CTA) + the bytes of
+//                both CTAs' loads (the peer's loads signal the leader's barrier)
+//   empty[s]     one per CTA; the leader's tcgen05.commit arrives on both
+//   acc_full[a]  one per CTA; the leader's tcgen05.commit arrives on both
+//   acc_empty[a] leader only, 8 arrivals (4 epilogue warps of each CTA)
+// No load here uses a cluster broadcast; every CTA fetches its own tiles.
+#pragma once
+#include "gemm_split_umma.cuh"
+
+namespace mtb {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+  return r;
+}
+// arrive (count 1) and add `bytes` to the expected transaction count of a barrier anywhere in the cluster
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_cluster, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar_cluster),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+template <int BK, int STAGES>
+struct Gemm2Cfg {
+  static constexpr int BM = 128;        // rows per CTA
+  static constexpr int BNH = 128;       // B columns staged per CTA
+  static constexpr int TILE_M = 256, TILE_N = 256;
+  static constexpr int ROW_BYTES = BK * 2;
+  static constexpr int A_TILE = BM * ROW_BYTES;
+  static constexpr int B_TILE = BNH * ROW_BYTES;
+  static constexpr int STAGE_BYTES = 3 * A_TILE + 3 * B_TILE;
+  static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
+  static constexpr int NUM_THREADS = 192;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static_assert(ROW_BYTES == 64 || ROW_BYTES == 128, "BK must be 32 or 64");
+};
+
+template <int BK, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                        const GemmArgs g) {
+  using Cfg = Gemm2Cfg<BK, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const uint32_t bars = tiles + STAGES * Cfg::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  const uint32_t abort_addr = tmem_slot + 4u;
+  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(smem_raw + (abort_addr - raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (g.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
+  const int tiles_n = (g.N + Cfg::TILE_N - 1) / Cfg::TILE_N;
+  const int num_tiles = tiles_m * tiles_n * g.batch;
+  const int nsplit = (g.mode == 1) ? 1 : (g.mode == 3 ? 2 : 3);
+  const uint32_t stage_tx = nsplit * (Cfg::A_TILE + Cfg::B_TILE);  // bytes this CTA loads per stage
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 2);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 8);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmapA);
+    prefetch_tmap(&tmapB);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs initialised, TMEM allocated
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int b, tm, tn;
+        tile_coords(t, tiles_m, tiles_n, b, tm, tn);
+        const int za = (g.a_batched ? b : 0) * 3, zb = (g.b_batched ? b : 0) * 3;
+        const int kb0 = b * g.kb_batch_stride;
+        const int row_a = tm * Cfg::TILE_M + int(rank) * Cfg::BM;
+        const int row_b = tn * Cfg::TILE_N + int(rank) * Cfg::BNH;
+        for (int kb = 0; kb < g.num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word)) {
+            *abort_word = 1;
+            atomicMax(g.status, 0x100u | 2u);
+            ok = false;
+            break;
+          }
+          const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
+          mbar_expect_tx_cluster(lead_full, stage_tx);
+          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
+          const uint32_t sb = sa + 3 * Cfg::A_TILE;
+          for (int s = 0; s < nsplit; ++s)
+            tma_load_3d_pair(sa + s * Cfg::A_TILE, &tmapA, lead_full, (kb0 + kb) * BK, row_a, za + s);
+          for (int s = 0; s < nsplit; ++s)
+            tma_load_3d_pair(sb + s * Cfg::B_TILE, &tmapB, lead_full, (kb0 + kb) * BK, row_b, zb + s);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      uint8_t pairs[9];
+      const int npairs = split_pairs(g.mode, pairs);
+      constexpr uint32_t idesc = make_idesc(Cfg::TILE_M, Cfg::TILE_N, 1u, 1u);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_word)) {
+          *abort_word = 1;
+          atomicMax(g.status, 0x200u | 3u);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * Cfg::TILE_N;
+        uint32_t accumulate = 0;
+        for (int kb = 0; kb < g.num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+            *abort_word = 1;
+            atomicMax(g.status, 0x200u | 4u);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
+          const uint32_t sb = sa + 3 * Cfg::A_TILE;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            for (int p = 0; p < npairs; ++p) {
+              const int i = pairs[p] >> 2, j = pairs[p] & 3;
+              const uint64_t da = make_kmajor_desc<Cfg::ROW_BYTES>(sa + i * Cfg::A_TILE + kk * 32);
+              const uint64_t db = make_kmajor_desc<Cfg::ROW_BYTES>(sb + j * Cfg::B_TILE + kk * 32);
+              umma_f16<2>(d_tmem, da, db, idesc, accumulate);
+              accumulate = 1;
+            }
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          umma_commit<2>(empty_bar(stage));
+          umma_commit<2>(map_to_cta(empty_bar(stage), 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit<2>(acc_full_bar(acc));
+        umma_commit<2>(map_to_cta(acc_full_bar(acc), 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) && ((g.ldc & 3) == 0) && ((g.strideC & 3) == 0);
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int b, tm, tn;
+      tile_coords(t, tiles_m, tiles_n, b, tm, tn);
+      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_word)) {
+        *abort_word = 1;
+        if (lane == 0) atomicMax(g.status, 0x300u | 2u);
+        break;
+      }
+      tc_fence_after();
+      const int row = tm * Cfg::TILE_M + int(rank) * Cfg::BM + q * 32 + lane;
+      const bool row_ok = row < g.M;
+      float* crow = g.C + b * g.strideC + static_cast<long long>(row) * g.ldc;
+      const float* arow = g.aux ? g.aux + b * g.strideC + static_cast<long long>(row) * g.ldc : nullptr;
+      const float row_bias = (g.bias && g.bias_per_row && row_ok) ? __ldg(g.bias + row) : 0.0f;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::TILE_N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < Cfg::TILE_N; c0 += 32) {
+        const int col0 = tn * Cfg::TILE_N + c0;
+        if (col0 >= g.N) break;
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c0, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int col = col0 + j;
+            if (col >= g.N) break;
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float x = __uint_as_float(v[j + e]);
+              if (col + e < g.N) {
+                if (g.bias) x += g.bias_per_row ? row_bias : __ldg(g.bias + col + e);
+                const float ax = (g.epilogue == EPI_RELU_BWD) ? arow[col + e] : 0.0f;
+                x = apply_epilogue(x, g.epilogue, ax);
+              }
+              o[e] = x;
+            }
+            if (vec_ok && col + 3 < g.N) {
+              *reinterpret_cast<float4*>(crow + col) = make_float4(o[0], o[1], o[2], o[3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (col + e < g.N) crow[col + e] = o[e];
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(acc_empty_bar(acc), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while the other may still use the pair
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace mtb

@@ -151,7 +151,7 @@ def test_f32_matches_oracle(be, orc, rng, m, n, k):
     assert norm_scaled_error(c, wide, a, b) <= 4e-6
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5, 6])
 @pytest.mark.parametrize("mode", [3, 6, 9])
 def test_f32_tile_variants_and_modes(be, orc, rng, variant, mode):
     m, n, k = 257, 300, 193
