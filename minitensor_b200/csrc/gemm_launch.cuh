@@ -10,12 +10,16 @@
 
 namespace mtb {
 
-// One prepared operand: bf16 split planes [planes = 3*batch][rows][Kp].
+// One prepared operand: bf16 split planes [planes = 3*batch][rows][cols padded to 64].
+// K-major (default): rows index M or N, columns index K (the pad is zero).
+// MN-major: rows index K, columns index M or N (straight split of a [K][MN] matrix).
 struct SplitOperand {
   const __nv_bfloat16* base = nullptr;
   int rows = 0;
   int batched = 0;  // 0: a single matrix shared by every batch entry
   int batch = 1;
+  int mn_major = 0;
+  int cols_p = 0;   // padded column count of the planes (MN-major operands; K-major use Kp)
 };
 
 inline int padded_k(int K) { return (K + 63) / 64 * 64; }
@@ -65,29 +69,36 @@ inline int32_t launch_variant(mtb200_ctx* h, const SplitOperand& a, const SplitO
   return MTB200_OK;
 }
 
-// Two-CTA kernel: clusters of two CTAs, one 256 x 256 tile per pair at a time.
-template <int BK, int STAGES>
-inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp, GemmArgs g) {
-  using Cfg = Gemm2Cfg<BK, STAGES>;
-  auto kern = gemm_split_umma2_kernel<BK, STAGES>;
-  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-  CUtensorMap ta, tb;
-  int32_t rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(3) * a.batch, BK, Cfg::BM);
-  if (rc) return rc;
-  rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(3) * b.batch, BK, Cfg::BNH);
-  if (rc) return rc;
-  g.num_kb = g.num_kb ? g.num_kb * (64 / BK) : Kp / BK;
-  g.kb_batch_stride *= (64 / BK);
-  const long long tiles = static_cast<long long>((g.M + Cfg::TILE_M - 1) / Cfg::TILE_M) *
-                          ((g.N + Cfg::TILE_N - 1) / Cfg::TILE_N) * g.batch;
+// 4-D view {64, k, mn/64, plane} of MN-major planes [plane][k rows][cols_p]; box = 64 x bk x chunks x 1.
+inline int32_t make_split_tmap_mn(CUtensorMap* out, const void* base, uint64_t k_rows, uint64_t cols_p,
+                                  uint64_t planes, uint32_t bk, uint32_t chunks) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {64, k_rows, cols_p / 64, planes};
+  const cuuint64_t strides[3] = {cols_p * 2, 128, k_rows * cols_p * 2};
+  const cuuint32_t box[4] = {64, bk, chunks, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (MN-major) failed (%d) for k %llu cols %llu planes %llu",
+                int(r), (unsigned long long)k_rows, (unsigned long long)cols_p, (unsigned long long)planes);
+  return MTB200_OK;
+}
+
+template <typename Kern>
+inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int threads, long long tiles,
+                                  const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, double work) {
+  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(Cfg::NUM_THREADS);
-  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = h->stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -99,9 +110,46 @@ inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const Split
   }
   const int pairs = int(std::min<long long>(tiles, std::min(max_clusters, h->sm_count / 2)));
   cfg.gridDim = dim3(2 * pairs);
-  ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.M * g.N * double(g.num_kb) * BK * g.batch);
+  ProfScope prof(h, PROF_GEMM_UMMA, work);
   MTB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, g));
   return MTB200_OK;
+}
+
+// Two-CTA kernel: clusters of two CTAs, one 256 x 256 tile per pair at a time.
+// K = logical reduction length; Kp = padded column count of K-major planes.
+template <int BK, int STAGES>
+inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp, GemmArgs g,
+                               int K = 0) {
+  using Cfg = Gemm2Cfg<BK, STAGES>;
+  if (K <= 0) K = Kp;
+  CUtensorMap ta, tb;
+  int32_t rc;
+  if (a.mn_major) rc = make_split_tmap_mn(&ta, a.base, a.rows, a.cols_p, uint64_t(3) * a.batch, BK, Cfg::BM / 64);
+  else            rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(3) * a.batch, BK, Cfg::BM);
+  if (rc) return rc;
+  if (b.mn_major) rc = make_split_tmap_mn(&tb, b.base, b.rows, b.cols_p, uint64_t(3) * b.batch, BK, Cfg::BNH / 64);
+  else            rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(3) * b.batch, BK, Cfg::BNH);
+  if (rc) return rc;
+  g.num_kb = g.num_kb ? g.num_kb * (64 / BK) : (K + BK - 1) / BK;
+  g.kb_batch_stride *= (64 / BK);
+  const long long tiles = static_cast<long long>((g.M + Cfg::TILE_M - 1) / Cfg::TILE_M) *
+                          ((g.N + Cfg::TILE_N - 1) / Cfg::TILE_N) * g.batch;
+  const double work = 2.0 * g.M * g.N * double(g.num_kb) * BK * g.batch;
+  if constexpr (BK == 64) {
+    if (a.mn_major && b.mn_major)
+      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, true>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
+                                tiles, ta, tb, g, work);
+    if (a.mn_major)
+      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, false>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
+                                tiles, ta, tb, g, work);
+    if (b.mn_major)
+      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, true>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
+                                tiles, ta, tb, g, work);
+  } else {
+    if (a.mn_major || b.mn_major) return fail(MTB200_ERR_INVALID, "MN-major operands need the K-block-64 kernel");
+  }
+  return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, false>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
+                            tiles, ta, tb, g, work);
 }
 
 // C[b] = epilogue(A_split[b] * B_split[b]^T + bias) on prepared operands.
@@ -110,7 +158,7 @@ inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const Split
 inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp,
                               int batch, int M, int N, float* C, long long ldc, long long strideC,
                               const float* bias, int epilogue, const float* aux, int mode, int variant,
-                              int bias_per_row = 0, int kb_batch_stride = 0, int num_kb_override = 0) {
+                              int bias_per_row = 0, int kb_batch_stride = 0, int num_kb_override = 0, int K = 0) {
   if (mode == 0) mode = 6;
   if (mode != 1 && mode != 3 && mode != 6 && mode != 9)
     return fail(MTB200_ERR_INVALID, "unknown f32 mode %d (use 0, 1, 3, 6 or 9)", mode);
@@ -125,18 +173,23 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
   g.num_kb = num_kb_override;  // 0: the whole padded K
   // two-CTA pair tiles whenever the output is at least one pair tile tall and wide
   if (variant == 0) variant = (M > 128 && N > 128) ? 5 : ((N > 128) ? 1 : (N > 64 ? 2 : 3));
+  if ((a.mn_major || b.mn_major) && variant != 5)
+    return fail(MTB200_ERR_INVALID, "MN-major operand planes need the two-CTA kernel (variant 5)");
   switch (variant) {
     case 1: return launch_variant<256, 32, 3>(h, a, b, Kp, g);
     case 2: return launch_variant<128, 64, 2>(h, a, b, Kp, g);
     case 3: return launch_variant<64, 64, 3>(h, a, b, Kp, g);
     case 4: return launch_variant<128, 32, 4>(h, a, b, Kp, g);
-    case 5: return launch_variant2<64, 2>(h, a, b, Kp, g);
+    case 5: return launch_variant2<64, 2>(h, a, b, Kp, g, K);
     case 6: return launch_variant2<32, 4>(h, a, b, Kp, g);
     default: return fail(MTB200_ERR_INVALID, "unknown GEMM tile variant %d", variant);
   }
 }
 
 // Full f32 GEMM from row-major f32 operands: split both into scratch, multiply.
+// With the two-CTA kernel every operand is split as it lies in memory (no
+// transposing pass): an operand stored [mn][k] becomes K-major planes, one stored
+// [k][mn] becomes MN-major planes, and the kernel's descriptors do the rest.
 inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int batch, int M, int N, int K,
                               const float* A, long long stride_a, const float* B, long long stride_b,
                               float* C, long long ldc, long long stride_c, const float* bias,
@@ -144,24 +197,39 @@ inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int bat
   const int Kp = padded_k(K);
   const int batch_a = (stride_a == 0 || batch == 1) ? 1 : batch;
   const int batch_b = (stride_b == 0 || batch == 1) ? 1 : batch;
-  const size_t bytes_a = split_bytes(M, Kp, batch_a), bytes_b = split_bytes(N, Kp, batch_b);
+  const int eff_mode = mode == 0 ? 6 : mode;
+  const int nsplit = eff_mode == 1 ? 1 : (eff_mode == 3 ? 2 : 3);
+  if (variant == 0 && M > 128 && N > 128) variant = 5;
+  const bool straight = (variant == 5);
+  // plane geometry: rows x padded cols
+  const int a_rows = (straight && trans_a) ? K : M, a_cols_p = (straight && trans_a) ? padded_k(M) : Kp;
+  const int b_rows = (straight && !trans_b) ? K : N, b_cols_p = (straight && !trans_b) ? padded_k(N) : Kp;
+  const size_t bytes_a = align_up(size_t(3) * batch_a * a_rows * a_cols_p * 2, 1024);
+  const size_t bytes_b = align_up(size_t(3) * batch_b * b_rows * b_cols_p * 2, 1024);
   void* ws = nullptr;
   int32_t rc = workspace_reserve(h, bytes_a + bytes_b, &ws);
   if (rc) return rc;
   __nv_bfloat16* sa = static_cast<__nv_bfloat16*>(ws);
   __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_a);
-  const int eff_mode = mode == 0 ? 6 : mode;
-  const int nsplit = eff_mode == 1 ? 1 : (eff_mode == 3 ? 2 : 3);
-  // op(A) is [M][K]: stored [M][K] when !trans_a (K-major already), [K][M] when trans_a.
   uint32_t* nf_word = h->status + 2;
   const uint32_t epoch = ++h->epoch;
-  rc = launch_split(h, A, trans_a, M, K, Kp, batch_a, stride_a, sa, nsplit, nf_word, epoch);
-  if (rc) return rc;
-  // op(B) is [K][N]: the operand the kernel wants is [N][K]; stored so when trans_b.
-  rc = launch_split(h, B, !trans_b, N, K, Kp, batch_b, stride_b, sb, nsplit, nf_word, epoch);
-  if (rc) return rc;
-  SplitOperand oa{sa, M, batch_a > 1, batch_a}, ob{sb, N, batch_b > 1, batch_b};
-  rc = run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, mode, variant);
+  SplitOperand oa{sa, a_rows, batch_a > 1, batch_a, 0, a_cols_p}, ob{sb, b_rows, batch_b > 1, batch_b, 0, b_cols_p};
+  if (straight) {
+    oa.mn_major = trans_a ? 1 : 0;
+    ob.mn_major = trans_b ? 0 : 1;
+    rc = launch_split(h, A, false, a_rows, trans_a ? M : K, a_cols_p, batch_a, stride_a, sa, nsplit, nf_word, epoch);
+    if (rc) return rc;
+    rc = launch_split(h, B, false, b_rows, trans_b ? K : N, b_cols_p, batch_b, stride_b, sb, nsplit, nf_word, epoch);
+    if (rc) return rc;
+  } else {
+    // op(A) is [M][K]: stored [M][K] when !trans_a (K-major already), [K][M] when trans_a.
+    rc = launch_split(h, A, trans_a, M, K, Kp, batch_a, stride_a, sa, nsplit, nf_word, epoch);
+    if (rc) return rc;
+    // op(B) is [K][N]: the operand the kernel wants is [N][K]; stored so when trans_b.
+    rc = launch_split(h, B, !trans_b, N, K, Kp, batch_b, stride_b, sb, nsplit, nf_word, epoch);
+    if (rc) return rc;
+  }
+  rc = run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, mode, variant, 0, 0, 0, K);
   if (rc) return rc;
   // Inf / NaN operands: redo the product with IEEE f32 multiply-add.  The kernel
   // returns at once unless a split kernel of THIS call raised the word.

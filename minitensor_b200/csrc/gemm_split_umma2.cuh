@@ -60,11 +60,16 @@ struct Gemm2Cfg {
   static_assert(ROW_BYTES == 64 || ROW_BYTES == 128, "BK must be 32 or 64");
 };
 
-template <int BK, int STAGES>
+// A_MN / B_MN: that operand's planes are MN-major ([k][mn] row-major in global
+// memory, mn padded to a multiple of 64) and its tensor map is the 4-D view
+// {64, k, mn / 64, plane}; otherwise K-major planes [mn][k] with the 3-D map.
+// MN-major needs BK = 64 (128-byte swizzle rows of 64 elements).
+template <int BK, int STAGES, bool A_MN = false, bool B_MN = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                         const GemmArgs g) {
   using Cfg = Gemm2Cfg<BK, STAGES>;
+  static_assert(!(A_MN || B_MN) || BK == 64, "MN-major operands need BK = 64");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -135,10 +140,18 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
           mbar_expect_tx_cluster(lead_full, stage_tx);
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + 3 * Cfg::A_TILE;
-          for (int s = 0; s < nsplit; ++s)
-            tma_load_3d_pair(sa + s * Cfg::A_TILE, &tmapA, lead_full, (kb0 + kb) * BK, row_a, za + s);
-          for (int s = 0; s < nsplit; ++s)
-            tma_load_3d_pair(sb + s * Cfg::B_TILE, &tmapB, lead_full, (kb0 + kb) * BK, row_b, zb + s);
+          for (int s = 0; s < nsplit; ++s) {
+            if constexpr (A_MN)
+              tma_load_4d_pair(sa + s * Cfg::A_TILE, &tmapA, lead_full, 0, (kb0 + kb) * BK, row_a >> 6, za + s);
+            else
+              tma_load_3d_pair(sa + s * Cfg::A_TILE, &tmapA, lead_full, (kb0 + kb) * BK, row_a, za + s);
+          }
+          for (int s = 0; s < nsplit; ++s) {
+            if constexpr (B_MN)
+              tma_load_4d_pair(sb + s * Cfg::B_TILE, &tmapB, lead_full, 0, (kb0 + kb) * BK, row_b >> 6, zb + s);
+            else
+              tma_load_3d_pair(sb + s * Cfg::B_TILE, &tmapB, lead_full, (kb0 + kb) * BK, row_b, zb + s);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -148,7 +161,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
     if (lane == 0 && rank == 0) {
       uint8_t pairs[9];
       const int npairs = split_pairs(g.mode, pairs);
-      constexpr uint32_t idesc = make_idesc(Cfg::TILE_M, Cfg::TILE_N, 1u, 1u);
+      constexpr uint32_t idesc = make_idesc(Cfg::TILE_M, Cfg::TILE_N, 1u, 1u, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -175,8 +188,11 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
           for (int kk = 0; kk < BK / 16; ++kk) {
             for (int p = 0; p < npairs; ++p) {
               const int i = pairs[p] >> 2, j = pairs[p] & 3;
-              const uint64_t da = make_kmajor_desc<Cfg::ROW_BYTES>(sa + i * Cfg::A_TILE + kk * 32);
-              const uint64_t db = make_kmajor_desc<Cfg::ROW_BYTES>(sb + j * Cfg::B_TILE + kk * 32);
+              // one MMA covers 16 k: 32 bytes along a K-major row, 16 rows of 128 bytes in an MN-major chunk
+              const uint64_t da = A_MN ? make_mnmajor_desc(sa + i * Cfg::A_TILE + kk * 2048, BK * 128)
+                                       : make_kmajor_desc<Cfg::ROW_BYTES>(sa + i * Cfg::A_TILE + kk * 32);
+              const uint64_t db = B_MN ? make_mnmajor_desc(sb + j * Cfg::B_TILE + kk * 2048, BK * 128)
+                                       : make_kmajor_desc<Cfg::ROW_BYTES>(sb + j * Cfg::B_TILE + kk * 32);
               umma_f16<2>(d_tmem, da, db, idesc, accumulate);
               accumulate = 1;
             }

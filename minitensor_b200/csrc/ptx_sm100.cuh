@@ -125,6 +125,27 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// 4-D form of the pair load (used for MN-major operand planes viewed as
+// {64 elements, k, 64-element chunk, plane}).
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster,
+                                                 int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// 5-D tiled load into this CTA's shared memory (image tensors {c, w, h, n, plane}).
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -258,11 +279,27 @@ __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major operand tile with 128-byte
+// swizzle: the tile is a sequence of chunks of 64 consecutive MN elements;
+// inside a chunk every k is one 128-byte row (k rows packed densely, 8 rows per
+// swizzle repeat -> stride 1024 bytes between 8-row groups); chunks are
+// `chunk_bytes` apart (= rows of k in the tile * 128).  Tile base aligned to 1024.
+__device__ __forceinline__ uint64_t make_mnmajor_desc(uint32_t smem_addr, uint32_t chunk_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((chunk_bytes >> 4) & 0x3FFF) << 16;  // leading byte offset: next 64-element chunk
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset: next group of 8 k rows
+  d |= 1ull << 46;
+  d |= 2ull << 61;                                                // SWIZZLE_128B
+  return d;
+}
+
 // Instruction descriptor: dense, f32 (or s32) accumulator, both operands K-major.
 // fmt: 0 = f16, 1 = bf16 (kind::f16); 1 = signed 8-bit (kind::i8, with c_fmt 2).
+// a_mn / b_mn = 1 marks that operand MN-major (bits 15 / 16).
 __host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n, uint32_t ab_fmt,
-                                                  uint32_t c_fmt) {
-  return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) |
+                                                  uint32_t c_fmt, uint32_t a_mn = 0, uint32_t b_mn = 0) {
+  return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (a_mn << 15) | (b_mn << 16) |
          (static_cast<uint32_t>(umma_n >> 3) << 17) | (static_cast<uint32_t>(umma_m >> 4) << 24);
 }
 
