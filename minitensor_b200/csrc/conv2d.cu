@@ -10,8 +10,17 @@
 //   bwd data  dx[n] [C_in][H*W]    = W'[C_in][C_out*kH*kW]   * patches'(dy[n])^T
 //   bwd weight dW [C_out][C_in*kH*kW] = sum over K chunks of dy[C_out][(n,oh,ow)] * patchesT(x)
 //   bwd bias  db[oc] = sum_{n,oh,ow} dy
+//
+// Stride-1 forward and data gradient run as an IMPLICIT GEMM: the image is
+// split once into channels-last bf16 planes [image*3+split][h][w][c] and the
+// GEMM kernel's TMA producer reads, for every (filter tap, channel block), the
+// shifted window {c block, full rows} of those planes with out-of-range
+// coordinates zero-filled by the hardware: the padding and the im2col matrix
+// never exist in memory.  Other strides and the weight gradient use the
+// gathered-patch (explicit) lowering below.
 #include "mtb200_core.cuh"
 #include "gemm_launch.cuh"
+#include "conv_wgrad_umma.cuh"
 #include "rowcol_kernels.cuh"
 
 namespace mtb {
@@ -167,6 +176,174 @@ __global__ void __launch_bounds__(256) conv_bias_partial_kernel(const float* __r
   if (threadIdx.x == 0) partial[static_cast<long long>(chunk) * c_out + oc] = red[0];
 }
 
+// dst[r][t][cp] (f32, zero for cp >= channels): the A operand of the implicit GEMM.
+//  mode 0 (forward):       r = oc, channel = ic : w[(r*chan + c)*taps + t]
+//  mode 1 (data gradient): r = ic, channel = oc : w[(c*rows + r)*taps + t]
+__global__ void weight_taps_kernel(const float* __restrict__ w, float* __restrict__ dst, int rows, int chan,
+                                   int chan_p, int taps, int mode) {
+  const long long total = static_cast<long long>(rows) * taps * chan_p;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % chan_p);
+    const long long q = i / chan_p;
+    const int t = static_cast<int>(q % taps), r = static_cast<int>(q / taps);
+    float v = 0.0f;
+    if (c < chan)
+      v = mode == 0 ? w[(static_cast<long long>(r) * chan + c) * taps + t]
+                    : w[(static_cast<long long>(c) * rows + r) * taps + t];
+    dst[i] = v;
+  }
+}
+
+// out[n][rows][out_h*out_w] = A[rows][taps*chan_p] * windows(img planes) (+ bias per row), stride 1.
+//  img: f32 NCHW [n][chan][img_h][img_w]; wsrc: OIHW weights; mode as in weight_taps_kernel;
+//  the window of tap (fh,fw) for output pixel (y,x) starts at (y + h0 + sgn*fh, x + w0 + sgn*fw).
+static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, int img_h, int img_w,
+                             const float* wsrc, int rows, int kh, int kw, int mode, int out_h, int out_w,
+                             int w0, int h0, int sgn, const float* bias, float* out, int f32_mode) {
+  constexpr int BK = 32;
+  using Cfg = GemmCfg<256, BK, 3>;
+  const int chan_p = padded_k(chan), taps = kh * kw;
+  const int Kp = taps * chan_p;
+  const int ipix = img_h * img_w, opix = out_h * out_w;
+  const size_t bytes_img = split_bytes(ipix, chan_p, n);
+  const size_t bytes_w = split_bytes(rows, Kp, 1);
+  const size_t bytes_tmp = align_up(sizeof(float) * size_t(rows) * Kp, 1024);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, bytes_img + bytes_w + bytes_tmp, &ws);
+  if (rc) return rc;
+  __nv_bfloat16* p_img = static_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* p_w = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_img);
+  float* wtmp = reinterpret_cast<float*>(static_cast<char*>(ws) + bytes_img + bytes_w);
+  // channels-last planes: per image a [chan][pixels] -> [pixels][chan_p] turning split
+  {
+    ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (4.0 * chan + 6.0 * chan_p));
+    rc = launch_split(h, img, true, ipix, chan, chan_p, n, static_cast<long long>(chan) * ipix, p_img, 3);
+    if (rc) return rc;
+  }
+  const long long wtotal = static_cast<long long>(rows) * Kp;
+  weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
+      wsrc, wtmp, rows, chan, chan_p, taps, mode);
+  MTB_CUDA(cudaGetLastError());
+  rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3);
+  if (rc) return rc;
+
+  int th = std::max(1, 256 / out_w);
+  th = std::min(th, out_h);
+  GemmArgs g = {};
+  g.M = rows; g.N = opix; g.batch = n;
+  g.num_kb = Kp / BK;
+  g.C = out; g.ldc = opix; g.strideC = static_cast<long long>(rows) * opix;
+  g.bias = bias; g.aux = nullptr; g.epilogue = EPI_NONE;
+  g.mode = (f32_mode & 0xff) ? (f32_mode & 0xff) : 6;
+  if (g.mode != 1 && g.mode != 3 && g.mode != 6 && g.mode != 9) return fail(MTB200_ERR_INVALID, "unknown f32 mode");
+  g.a_batched = 0; g.b_batched = 1; g.bias_per_row = 1; g.kb_batch_stride = 0;
+  g.status = h->status;
+  g.cv_th = th; g.cv_n_tile = th * out_w; g.cv_umma_n = (g.cv_n_tile + 15) / 16 * 16;
+  g.cv_kb_per_tap = chan_p / BK; g.cv_kw = kw; g.cv_w0 = w0; g.cv_h0 = h0; g.cv_sgn = sgn;
+
+  CUtensorMap ta, tb;
+  rc = make_split_tmap(&ta, p_w, Kp, rows, 3, BK, Cfg::BM);
+  if (rc) return rc;
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {cuuint64_t(chan_p), cuuint64_t(img_w), cuuint64_t(img_h), cuuint64_t(3) * n};
+  const cuuint64_t strides[3] = {cuuint64_t(chan_p) * 2, cuuint64_t(img_w) * chan_p * 2,
+                                 cuuint64_t(ipix) * chan_p * 2};
+  const cuuint32_t box[4] = {BK, cuuint32_t(out_w), cuuint32_t(th), 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, p_img, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (image planes) failed (%d)", int(r));
+  auto kern = gemm_split_umma_kernel<256, BK, 3, true>;
+  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  const long long tiles = static_cast<long long>((rows + Cfg::BM - 1) / Cfg::BM) * ((out_h + th - 1) / th) * n;
+  const int grid = int(std::min<long long>(tiles, h->sm_count));
+  ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
+  kern<<<grid, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(ta, tb, g);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, int img_w, int img_h, int n,
+                                uint32_t box_c, uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle sw) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {cuuint64_t(chan_p), cuuint64_t(img_w), cuuint64_t(img_h), cuuint64_t(3) * n};
+  const cuuint64_t strides[3] = {cuuint64_t(chan_p) * 2, cuuint64_t(img_w) * chan_p * 2,
+                                 cuuint64_t(img_h) * img_w * chan_p * 2};
+  const cuuint32_t box[4] = {box_c, box_w, box_h, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (image planes) failed (%d)", int(r));
+  return MTB200_OK;
+}
+
+// Stride-1 weight gradient as implicit GEMM (conv_wgrad_umma.cuh).
+static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy, const float* x, float* dw,
+                              int f32_mode) {
+  using Cfg = WgradCfg;
+  const int cop = padded_k(g.c_out), cip = padded_k(g.c_in), taps = g.kh * g.kw;
+  const int opix = g.oh * g.ow, ipix = g.h * g.w;
+  WgradArgs a = {};
+  a.c_out = g.c_out;
+  a.cb_per_tap = cip / 64;
+  a.n_chunks = taps * a.cb_per_tap;
+  a.kw = g.kw; a.pad_h = g.ph; a.pad_w = g.pw;
+  int tw = 1;
+  while (tw < std::min(g.ow, 64)) tw *= 2;
+  a.tw = tw; a.th = 64 / tw;
+  a.wblocks = (g.ow + tw - 1) / tw;
+  a.hblocks = (g.oh + a.th - 1) / a.th;
+  const long long total_kb = static_cast<long long>(g.n) * a.wblocks * a.hblocks;
+  if (total_kb > INT32_MAX) return fail(MTB200_ERR_INVALID, "conv2d weight gradient: too many reduction blocks");
+  a.total_kb = int(total_kb);
+  a.tiles_m = (g.c_out + 127) / 128;
+  a.tiles_n = (a.n_chunks + 1) / 2;
+  const int tiles = a.tiles_m * a.tiles_n;
+  int splits = int(std::min<long long>(total_kb, std::max(1, h->sm_count / tiles)));
+  a.kb_per_split = int((total_kb + splits - 1) / splits);
+  a.splits = int((total_kb + a.kb_per_split - 1) / a.kb_per_split);
+  a.n_total = a.n_chunks * 64;
+  a.mode = (f32_mode & 0xff) ? (f32_mode & 0xff) : 6;
+  if (a.mode != 1 && a.mode != 3 && a.mode != 6 && a.mode != 9) return fail(MTB200_ERR_INVALID, "unknown f32 mode");
+  a.status = h->status;
+  const size_t bytes_dy = split_bytes(opix, cop, g.n), bytes_x = split_bytes(ipix, cip, g.n);
+  const size_t bytes_part = align_up(sizeof(float) * size_t(a.splits) * g.c_out * a.n_total, 1024);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, bytes_dy + bytes_x + bytes_part, &ws);
+  if (rc) return rc;
+  __nv_bfloat16* p_dy = static_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* p_x = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_dy);
+  a.part = reinterpret_cast<float*>(static_cast<char*>(ws) + bytes_dy + bytes_x);
+  {
+    ProfScope prof(h, PROF_CONV_GATHER, double(g.n) * (opix * (4.0 * g.c_out + 6.0 * cop) + ipix * (4.0 * g.c_in + 6.0 * cip)));
+    rc = launch_split(h, dy, true, opix, g.c_out, cop, g.n, static_cast<long long>(g.c_out) * opix, p_dy, 3);
+    if (rc) return rc;
+    rc = launch_split(h, x, true, ipix, g.c_in, cip, g.n, static_cast<long long>(g.c_in) * ipix, p_x, 3);
+    if (rc) return rc;
+  }
+  CUtensorMap tdy, tx;
+  rc = image_plane_tmap(&tdy, p_dy, cop, g.ow, g.oh, g.n, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  MTB_CUDA(cudaFuncSetAttribute(conv_wgrad_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  {
+    ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.c_out * double(opix) * taps * g.c_in * g.n);
+    conv_wgrad_umma_kernel<<<a.splits * tiles, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(tdy, tx, a);
+    MTB_CUDA(cudaGetLastError());
+  }
+  const long long total = static_cast<long long>(g.c_out) * g.c_in * taps;
+  wgrad_reduce_kernel<<<int(std::min<long long>((total + 255) / 256, 4096)), 256, 0, h->stream>>>(
+      a.part, a.splits, g.c_out, g.c_in, cip, taps, dw);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
 static int32_t check_geom(int64_t n, int64_t c_in, int64_t h, int64_t w, int64_t c_out, int64_t kh,
                           int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, ConvGeom* g) {
   if (n < 0 || c_in < 0 || h < 0 || w < 0 || c_out < 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0)
@@ -209,6 +386,10 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
   const int K = g.c_in * g.kh * g.kw;
   if (K == 0) return fail(MTB200_ERR_UNSUPPORTED, "conv2d with zero input channels is not supported");
   if (!x || !w) return fail(MTB200_ERR_INVALID, "null input pointer");
+  const bool force_explicit = ((f32_mode >> 8) & 0xff) == 0xff;  // test hook: gathered-patch lowering
+  if (g.sh == 1 && g.sw == 1 && g.ow <= 256 && !force_explicit)
+    return implicit_conv(h, x, g.n, g.c_in, g.h, g.w, w, g.c_out, g.kh, g.kw, 0, g.oh, g.ow, -g.pw, -g.ph, +1,
+                         bias, y, f32_mode);
   const int Kp = padded_k(K);
   const size_t bytes_w = split_bytes(g.c_out, Kp, 1), bytes_p = split_bytes(opix, Kp, g.n);
   void* ws = nullptr;
@@ -223,7 +404,7 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_out, 0, 1}, ob{sp, opix, g.n > 1, g.n};
   return run_split_gemm(h, oa, ob, Kp, g.n, g.c_out, opix, y, opix, static_cast<long long>(g.c_out) * opix,
-                        bias, EPI_NONE, nullptr, f32_mode & 0xff, (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
+                        bias, EPI_NONE, nullptr, f32_mode & 0xff, force_explicit ? 0 : (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
 }
 
 int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
@@ -243,6 +424,10 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
     return MTB200_OK;
   }
   if (!dy || !w) return fail(MTB200_ERR_INVALID, "null input pointer");
+  const bool force_explicit = ((f32_mode >> 8) & 0xff) == 0xff;
+  if (g.sh == 1 && g.sw == 1 && g.w <= 256 && !force_explicit)
+    return implicit_conv(h, dy, g.n, g.c_out, g.oh, g.ow, w, g.c_in, g.kh, g.kw, 1, g.h, g.w, g.pw, g.ph, -1,
+                         nullptr, dx, f32_mode);
   const int Kp = padded_k(K);
   const size_t bytes_w = split_bytes(g.c_in, Kp, 1), bytes_p = split_bytes(ipix, Kp, g.n);
   const size_t bytes_perm = align_up(sizeof(float) * size_t(g.c_in) * K, 1024);
@@ -263,7 +448,7 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_in, 0, 1}, ob{sp, ipix, g.n > 1, g.n};
   return run_split_gemm(h, oa, ob, Kp, g.n, g.c_in, ipix, dx, ipix, static_cast<long long>(g.c_in) * ipix,
-                        nullptr, EPI_NONE, nullptr, f32_mode & 0xff, (f32_mode >> 8) & 0xff);
+                        nullptr, EPI_NONE, nullptr, f32_mode & 0xff, force_explicit ? 0 : (f32_mode >> 8) & 0xff);
 }
 
 int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
@@ -284,6 +469,7 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
     return MTB200_OK;
   }
   if (!dy || !x) return fail(MTB200_ERR_INVALID, "null input pointer");
+  if (g.sh == 1 && g.sw == 1 && ((f32_mode >> 8) & 0xff) != 0xff) return implicit_wgrad(h, g, dy, x, dw, f32_mode);
   // split K: enough chunks to occupy the machine, each a whole number of 64-wide K blocks
   const long long kblocks = (Ktot + 63) / 64;
   const int tiles = ((g.c_out + 127) / 128) * ((rows_b + 255) / 256);
@@ -308,7 +494,7 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
   SplitOperand oa{sa, g.c_out, 0, 1}, ob{sb, rows_b, 0, 1};
   float* gemm_out = chunks == 1 ? dw : part;
   rc = run_split_gemm(h, oa, ob, int(Kp), chunks, g.c_out, rows_b, gemm_out, rows_b, (long long)out_elems,
-                      nullptr, EPI_NONE, nullptr, f32_mode & 0xff, (f32_mode >> 8) & 0xff, 0,
+                      nullptr, EPI_NONE, nullptr, f32_mode & 0xff, 0, 0,
                       /*kb_batch_stride=*/int(kb_per_chunk), /*num_kb (64-wide)=*/int(kb_per_chunk));
   if (rc) return rc;
   if (chunks > 1) {

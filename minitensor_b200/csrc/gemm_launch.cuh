@@ -162,7 +162,7 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
   if (mode == 0) mode = 6;
   if (mode != 1 && mode != 3 && mode != 6 && mode != 9)
     return fail(MTB200_ERR_INVALID, "unknown f32 mode %d (use 0, 1, 3, 6 or 9)", mode);
-  GemmArgs g;
+  GemmArgs g = {};
   g.M = M; g.N = N; g.batch = batch;
   g.C = C; g.ldc = ldc; g.strideC = strideC;
   g.bias = bias; g.aux = aux; g.epilogue = epilogue; g.mode = mode;

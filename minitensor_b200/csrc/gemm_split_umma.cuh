@@ -49,6 +49,16 @@ struct GemmArgs {
   int bias_per_row;    // 0: bias[N] added along columns; 1: bias[M] added along rows
   int kb_batch_stride; // split-K: batch entry b reduces K blocks [b*stride, b*stride + num_kb)
   uint32_t* status;    // device word; a non-zero value reports a wait that ran out
+  // Implicit-convolution mode (CONV kernels only): the B operand is read straight
+  // from channels-last image planes {c, w, h, image*3+split}; a K block is one
+  // (filter tap, channel block) and an N tile is cv_th full image rows.
+  int cv_n_tile;       // columns per N tile = cv_th * tile width
+  int cv_umma_n;       // MMA N: cv_n_tile rounded up to a multiple of 16
+  int cv_th;           // image rows per N tile
+  int cv_kb_per_tap;   // channel blocks per filter tap
+  int cv_kw;           // filter width (taps per filter row)
+  int cv_w0, cv_h0;    // window origin for tap (0,0): -pad (forward) or +pad (data gradient)
+  int cv_sgn;          // +1 forward (origin + tap), -1 data gradient (origin - tap)
 };
 
 __device__ __forceinline__ float apply_epilogue(float x, int epi, float aux) {
@@ -115,7 +125,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = in_band / rows_in_band;
 }
 
-template <int BN, int BK, int STAGES>
+template <int BN, int BK, int STAGES, bool CONV = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
                        const __grid_constant__ CUtensorMap tmapB, const GemmArgs g) {
@@ -140,11 +150,12 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  const int n_tile = CONV ? g.cv_n_tile : BN;  // output columns per tile
   const int tiles_m = (g.M + BM - 1) / BM;
-  const int tiles_n = (g.N + BN - 1) / BN;
+  const int tiles_n = (g.N + n_tile - 1) / n_tile;
   const int num_tiles = tiles_m * tiles_n * g.batch;
   const int nsplit = (g.mode == 1) ? 1 : (g.mode == 3 ? 2 : 3);
-  const uint32_t stage_tx = nsplit * (Cfg::A_TILE + Cfg::B_TILE);
+  const uint32_t stage_tx = nsplit * (Cfg::A_TILE + (CONV ? n_tile * Cfg::ROW_BYTES : Cfg::B_TILE));
 
   if (threadIdx.x == 0) {
     *abort_word = 0;
@@ -193,8 +204,16 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
           const uint32_t sb = sa + 3 * Cfg::A_TILE;
           for (int s = 0; s < nsplit; ++s)
             tma_load_3d(sa + s * Cfg::A_TILE, &tmapA, full_bar(stage), (kb0 + kb) * BK, tm * BM, za + s);
-          for (int s = 0; s < nsplit; ++s)
-            tma_load_3d(sb + s * Cfg::B_TILE, &tmapB, full_bar(stage), (kb0 + kb) * BK, tn * BN, zb + s);
+          if constexpr (CONV) {
+            const int tap = kb / g.cv_kb_per_tap, cb = kb - tap * g.cv_kb_per_tap;
+            const int fh = tap / g.cv_kw, fw = tap - fh * g.cv_kw;
+            const int w = g.cv_w0 + g.cv_sgn * fw, hh = tn * g.cv_th + g.cv_h0 + g.cv_sgn * fh;
+            for (int s = 0; s < nsplit; ++s)
+              tma_load_4d(sb + s * Cfg::B_TILE, &tmapB, full_bar(stage), cb * BK, w, hh, zb + s);
+          } else {
+            for (int s = 0; s < nsplit; ++s)
+              tma_load_3d(sb + s * Cfg::B_TILE, &tmapB, full_bar(stage), (kb0 + kb) * BK, tn * BN, zb + s);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -204,7 +223,7 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
     if (lane == 0) {
       uint8_t pairs[9];
       const int npairs = split_pairs(g.mode, pairs);
-      constexpr uint32_t idesc = make_idesc(BM, BN, /*bf16*/ 1u, /*f32*/ 1u);
+      const uint32_t idesc = make_idesc(BM, CONV ? g.cv_umma_n : BN, /*bf16*/ 1u, /*f32*/ 1u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -271,9 +290,10 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
       const float row_bias = (g.bias && g.bias_per_row && row_ok) ? __ldg(g.bias + row) : 0.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::ACC_COLS;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = tn * BN + c0;
+      for (int c0 = 0; c0 < n_tile; c0 += 32) {
+        const int col0 = tn * n_tile + c0;
         if (col0 >= g.N) break;  // uniform across the warp
+        const int col_end = min(g.N, (tn + 1) * n_tile);  // a conv tile may end inside a 32-column group
         uint32_t v[32];
         tmem_ld_32x32(t_row + c0, v);
         tmem_ld_wait();
@@ -281,24 +301,24 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             const int col = col0 + j;
-            if (col >= g.N) break;
+            if (col >= col_end) break;
             float o[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               float x = __uint_as_float(v[j + e]);
-              if (col + e < g.N) {
+              if (col + e < col_end) {
                 if (g.bias) x += g.bias_per_row ? row_bias : __ldg(g.bias + col + e);
                 const float ax = (g.epilogue == EPI_RELU_BWD) ? arow[col + e] : 0.0f;
                 x = apply_epilogue(x, g.epilogue, ax);
               }
               o[e] = x;
             }
-            if (vec_ok && col + 3 < g.N) {
+            if (vec_ok && col + 3 < col_end && ((col & 3) == 0)) {
               *reinterpret_cast<float4*>(crow + col) = make_float4(o[0], o[1], o[2], o[3]);
             } else {
 #pragma unroll
               for (int e = 0; e < 4; ++e)
-                if (col + e < g.N) crow[col + e] = o[e];
+                if (col + e < col_end) crow[col + e] = o[e];
             }
           }
         }

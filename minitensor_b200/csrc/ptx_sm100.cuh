@@ -113,6 +113,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// 4-D form (image planes {c, w, h, plane}); w and h may start negative or past the
+// extent, those elements read as zero.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 // Same load issued from either CTA of a cta_group::2 pair: the destination is
 // this CTA's shared memory, the completion bytes are counted on the barrier
 // whose cluster address is `bar_cluster` (normally the leader CTA's barrier).

@@ -103,3 +103,32 @@ def test_full_size_layer_properties(be):
     assert abs(lhs - float(w.double().mul(dw.double()).sum())) <= 1e-5 * abs(lhs) + 1.0
     ref_db = dy.double().sum(dim=(0, 2, 3))
     assert float((db.double() - ref_db).abs().max()) <= 1e-5 * float(dy.abs().double().sum(dim=(0, 2, 3)).max())
+
+
+@pytest.mark.parametrize("geom", [g for g in GEOMS if g[7] == (1, 1)] + [(2, 5, 9, 300, 3, 3, 3, (1, 1), (1, 1)),
+                                                                         (1, 70, 6, 13, 9, 3, 3, (1, 1), (2, 2)),
+                                                                         (3, 2, 20, 5, 4, 2, 4, (1, 1), (0, 3))])
+@pytest.mark.parametrize("lowering", ["implicit", "explicit"])
+def test_both_lowerings_match_oracle(be, orc, rng, geom, lowering):
+    """Stride-1 forward and data gradient exist twice: as implicit GEMM over channels-last planes
+    (default; falls back by itself when a row is wider than 256) and as the gathered-patch lowering
+    (forced here with the variant byte 0xff)."""
+    n, c, h, w, co, kh, kw, stride, padding = geom
+    mode = 0 if lowering == "implicit" else 0xFF00
+    xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wn = (rng.standard_normal((co, c, kh, kw)) * np.sqrt(2.0 / (c * kh * kw))).astype(np.float32)
+    bn = rng.standard_normal(co).astype(np.float32)
+    dev = lambda a: torch.from_numpy(a).to(be.device)
+    y = be.conv2d_fwd(dev(xn), dev(wn), dev(bn), stride, padding, f32_mode=mode)
+    ref = orc.conv2d(xn, wn, bn, stride, padding)
+    go = rng.standard_normal(ref.shape).astype(np.float32)
+    dx = be.conv2d_bwd_data(dev(go), dev(wn), xn.shape, stride, padding, f32_mode=mode)
+    dw = be.conv2d_bwd_weight(dev(go), dev(xn), wn.shape, stride, padding, f32_mode=mode)
+    be.sync()
+    gx, gw, _ = orc.conv2d_backward(xn, wn, go, stride, padding, need_b=False)
+    k_w = n * ref.shape[2] * ref.shape[3]
+    assert np.abs(dw.cpu().numpy() - gw).max() <= F32_TOL * k_w * np.abs(go).max() * np.abs(xn).max()
+    xnorm = np.sqrt(c * kh * kw) * np.abs(xn).max()
+    wnorm = np.linalg.norm(wn.reshape(co, -1), axis=1).max()
+    assert np.abs(y.cpu().numpy() - ref).max() <= F32_TOL * xnorm * wnorm
+    assert np.abs(dx.cpu().numpy() - gx).max() <= F32_TOL * (co * kh * kw) * np.abs(go).max() * np.abs(wn).max()
