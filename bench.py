@@ -307,6 +307,68 @@ def run_ours(args):
     return 0
 
 
+def run_case(args):
+    """Runs one small, fixed workload a few times and prints nothing but a line of timings: the
+    command ncu is pointed at for the per-kernel summaries under profiles/ (sizes above L2 where
+    the kernel is memory-bound, a few GB at most)."""
+    import torch
+    from minitensor_b200.backend import get_backend
+    be = get_backend(0)
+    dev = be.device
+    g = torch.Generator(device="cpu").manual_seed(7)
+    rnd = lambda *shape, dtype=torch.float32: torch.randn(*shape, generator=g, dtype=dtype).to(dev)
+    name = args.case
+    if name == "gemm_f32_4096":
+        a, b = rnd(4096, 4096), rnd(4096, 4096)
+        out = torch.empty(4096, 4096, device=dev)
+        fn = lambda: be.gemm(a, b, out=out)
+    elif name == "gemm_f32_nt_tn":      # the two products of MatMulBackward at 2048
+        a, b, dy = rnd(2048, 2048), rnd(2048, 2048), rnd(2048, 2048)
+        fn = lambda: (be.gemm(dy, b, trans_b=True), be.gemm(a, dy, trans_a=True))
+    elif name == "gemm_f64_2048":
+        a, b = rnd(2048, 2048, dtype=torch.float64), rnd(2048, 2048, dtype=torch.float64)
+        fn = lambda: be.gemm(a, b)
+    elif name == "gemm_i32_2048":
+        a = torch.randint(-8, 9, (2048, 2048), generator=g, dtype=torch.int32).to(dev)
+        b = torch.randint(-8, 9, (2048, 2048), generator=g, dtype=torch.int32).to(dev)
+        fn = lambda: be.gemm(a, b)
+    elif name == "colsum":              # bias gradient of a [65536, 4096] activation gradient (1.07 GB)
+        x = rnd(65536, 4096)
+        fn = lambda: be.colsum(x)
+    elif name == "cross_entropy":       # [65536, 1000] logits (262 MB)
+        x = rnd(65536, 1000)
+        y = torch.randint(0, 1000, (65536,), generator=g).to(dev)
+        fn = lambda: be.cross_entropy(x, y)
+    elif name == "adam":                # 71.2 M parameters (the large MLP): 2.0 GB of traffic
+        n = 71_218_152
+        p, gr = rnd(n), rnd(n)
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        fn = lambda: be.adam_step(p, gr, m, v, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=1)
+    elif name == "dense_small":         # the small MLP's layers: launch / HBM-bound shapes
+        x, w1, b1 = rnd(32, 784), rnd(128, 784), rnd(128)
+        w2, b2 = rnd(10, 128), rnd(10)
+        fn = lambda: be.gemm(be.gemm(x, w1, trans_b=True, bias=b1, epilogue=1), w2, trans_b=True, bias=b2)
+    elif name == "conv":                # the conv config at batch 32 (forward + the three gradients)
+        x, w, b = rnd(32, 64, 56, 56), rnd(64, 64, 3, 3), rnd(64)
+        dy = rnd(32, 64, 56, 56)
+        fn = lambda: (be.conv2d_fwd(x, w, b, (1, 1), (1, 1)), be.conv2d_bwd_data(dy, w, x.shape, (1, 1), (1, 1)),
+                      be.conv2d_bwd_weight(dy, x, w.shape, (1, 1), (1, 1)), be.conv2d_bwd_bias(dy))
+    else:
+        print(json.dumps({"error": f"unknown case {name}"}))
+        return 2
+    times = []
+    for _ in range(args.reps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    be.sync()
+    print(json.dumps({"case": name, "ms": times}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,7 +376,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--case", default=None, help="run one small fixed workload (profiling target) and exit")
+    ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.impl == "reference":
         return run_reference(args)
     args.warmup = max(args.warmup, 3)
