@@ -48,13 +48,18 @@ enum {
   MTB200_EPI_RELU_BWD = 4   /* ReluBackward: multiply by (aux > 0)  engine/src/autograd/mod/shape.rs:724-816 */
 };
 
-/* f32 arithmetic modes of mtb200_gemm (argument f32_mode, low byte) */
+/* f32 arithmetic modes of mtb200_gemm (argument f32_mode, low byte).  Every mode
+ * multiplies on the tensor cores with f32 accumulation; they differ in how an
+ * f32 operand is represented. */
 enum {
-  MTB200_F32_DEFAULT = 0, /* = MTB200_F32_BF16X6                                   */
-  MTB200_F32_BF16X1 = 1,  /* single bf16 product: ~2^-8 relative, for experiments  */
-  MTB200_F32_BF16X3 = 3,  /* three split products: ~2^-16 relative                 */
-  MTB200_F32_BF16X6 = 6,  /* six split products: f32-accurate (default)            */
-  MTB200_F32_BF16X9 = 9   /* all nine split products                               */
+  MTB200_F32_DEFAULT = 0, /* F16X3 when the output is larger than 128 x 128, else BF16X6     */
+  MTB200_F32_BF16X1 = 1,  /* single bf16 product: ~2^-8 relative, for experiments            */
+  MTB200_F32_BF16X3 = 3,  /* two bf16 terms, three products: ~2^-16 relative                 */
+  MTB200_F32_BF16X6 = 6,  /* three bf16 terms (24 bits), six products                        */
+  MTB200_F32_BF16X9 = 9,  /* three bf16 terms, all nine products                             */
+  MTB200_F32_F16X3 = 23   /* two fp16 terms (22 bits) after exact power-of-two row/column
+                           * scaling, three products: the accuracy class of 3xTF32 at half
+                           * its tensor cost; needs M, N > 128                              */
 };
 
 typedef struct mtb200_ctx* mtb200_handle;

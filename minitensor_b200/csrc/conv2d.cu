@@ -238,6 +238,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
   g.mode = (f32_mode & 0xff) ? (f32_mode & 0xff) : 6;
   if (g.mode != 1 && g.mode != 3 && g.mode != 6 && g.mode != 9) return fail(MTB200_ERR_INVALID, "unknown f32 mode");
   g.a_batched = 0; g.b_batched = 1; g.bias_per_row = 1; g.kb_batch_stride = 0;
+  g.planes_per_mat = 3; g.exp_a = nullptr; g.exp_b = nullptr;
   g.status = h->status;
   g.cv_th = th; g.cv_n_tile = th * out_w; g.cv_umma_n = (g.cv_n_tile + 15) / 16 * 16;
   g.cv_kb_per_tap = chan_p / BK; g.cv_kw = kw; g.cv_w0 = w0; g.cv_h0 = h0; g.cv_sgn = sgn;

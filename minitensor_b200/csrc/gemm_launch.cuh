@@ -5,6 +5,7 @@
 #include "gemm_split_umma.cuh"
 #include "gemm_split_umma2.cuh"
 #include "split_bf16.cuh"
+#include "split_f16.cuh"
 #include "gemm_f64_int.cuh"
 #include <algorithm>
 
@@ -20,6 +21,8 @@ struct SplitOperand {
   int batch = 1;
   int mn_major = 0;
   int cols_p = 0;   // padded column count of the planes (MN-major operands; K-major use Kp)
+  int nplanes = 3;  // planes per matrix: 3 (bf16 split) or 2 (fp16 split)
+  const int* expo = nullptr;  // fp16 split: scale exponent per M/N index ([batch][rows or cols])
 };
 
 inline int padded_k(int K) { return (K + 63) / 64 * 64; }
@@ -54,9 +57,9 @@ inline int32_t launch_variant(mtb200_ctx* h, const SplitOperand& a, const SplitO
   // per-device attribute; setting it on every launch keeps multi-device processes correct
   MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
   CUtensorMap ta, tb;
-  int32_t rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(3) * a.batch, BK, Cfg::BM);
+  int32_t rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(a.nplanes) * a.batch, BK, Cfg::BM);
   if (rc) return rc;
-  rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(3) * b.batch, BK, BN);
+  rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(b.nplanes) * b.batch, BK, BN);
   if (rc) return rc;
   // split-K arguments count 64-wide K blocks; rescale to this variant's block
   g.num_kb = g.num_kb ? g.num_kb * (64 / BK) : Kp / BK;
@@ -117,39 +120,41 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
 
 // Two-CTA kernel: clusters of two CTAs, one 256 x 256 tile per pair at a time.
 // K = logical reduction length; Kp = padded column count of K-major planes.
-template <int BK, int STAGES>
+template <int BK, int STAGES, int NP>
 inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp, GemmArgs g,
                                int K = 0) {
-  using Cfg = Gemm2Cfg<BK, STAGES>;
+  using Cfg = Gemm2Cfg<BK, STAGES, NP>;
   if (K <= 0) K = Kp;
+  if (a.nplanes != NP || b.nplanes != NP) return fail(MTB200_ERR_INVALID, "operand planes do not match the GEMM mode");
   CUtensorMap ta, tb;
   int32_t rc;
-  if (a.mn_major) rc = make_split_tmap_mn(&ta, a.base, a.rows, a.cols_p, uint64_t(3) * a.batch, BK, Cfg::BM / 64);
-  else            rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(3) * a.batch, BK, Cfg::BM);
+  if (a.mn_major) rc = make_split_tmap_mn(&ta, a.base, a.rows, a.cols_p, uint64_t(NP) * a.batch, BK, Cfg::BM / 64);
+  else            rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(NP) * a.batch, BK, Cfg::BM);
   if (rc) return rc;
-  if (b.mn_major) rc = make_split_tmap_mn(&tb, b.base, b.rows, b.cols_p, uint64_t(3) * b.batch, BK, Cfg::BNH / 64);
-  else            rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(3) * b.batch, BK, Cfg::BNH);
+  if (b.mn_major) rc = make_split_tmap_mn(&tb, b.base, b.rows, b.cols_p, uint64_t(NP) * b.batch, BK, Cfg::BNH / 64);
+  else            rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(NP) * b.batch, BK, Cfg::BNH);
   if (rc) return rc;
   g.num_kb = g.num_kb ? g.num_kb * (64 / BK) : (K + BK - 1) / BK;
   g.kb_batch_stride *= (64 / BK);
+  g.planes_per_mat = NP;
   const long long tiles = static_cast<long long>((g.M + Cfg::TILE_M - 1) / Cfg::TILE_M) *
                           ((g.N + Cfg::TILE_N - 1) / Cfg::TILE_N) * g.batch;
   const double work = 2.0 * g.M * g.N * double(g.num_kb) * BK * g.batch;
   if constexpr (BK == 64) {
     if (a.mn_major && b.mn_major)
-      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, true>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
-                                tiles, ta, tb, g, work);
+      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, true, NP>, Cfg::SMEM_BYTES,
+                                Cfg::NUM_THREADS, tiles, ta, tb, g, work);
     if (a.mn_major)
-      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, false>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
-                                tiles, ta, tb, g, work);
+      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, false, NP>, Cfg::SMEM_BYTES,
+                                Cfg::NUM_THREADS, tiles, ta, tb, g, work);
     if (b.mn_major)
-      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, true>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
-                                tiles, ta, tb, g, work);
+      return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, true, NP>, Cfg::SMEM_BYTES,
+                                Cfg::NUM_THREADS, tiles, ta, tb, g, work);
   } else {
     if (a.mn_major || b.mn_major) return fail(MTB200_ERR_INVALID, "MN-major operands need the K-block-64 kernel");
   }
-  return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, false>, Cfg::SMEM_BYTES, Cfg::NUM_THREADS,
-                            tiles, ta, tb, g, work);
+  return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, false, NP>, Cfg::SMEM_BYTES,
+                            Cfg::NUM_THREADS, tiles, ta, tb, g, work);
 }
 
 // C[b] = epilogue(A_split[b] * B_split[b]^T + bias) on prepared operands.
@@ -160,30 +165,106 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
                               const float* bias, int epilogue, const float* aux, int mode, int variant,
                               int bias_per_row = 0, int kb_batch_stride = 0, int num_kb_override = 0, int K = 0) {
   if (mode == 0) mode = 6;
-  if (mode != 1 && mode != 3 && mode != 6 && mode != 9)
-    return fail(MTB200_ERR_INVALID, "unknown f32 mode %d (use 0, 1, 3, 6 or 9)", mode);
+  if (mode != 1 && mode != 3 && mode != 6 && mode != 9 && mode != 23)
+    return fail(MTB200_ERR_INVALID, "unknown f32 mode %d (use 0, 1, 3, 6, 9 or 23)", mode);
   GemmArgs g = {};
   g.M = M; g.N = N; g.batch = batch;
   g.C = C; g.ldc = ldc; g.strideC = strideC;
   g.bias = bias; g.aux = aux; g.epilogue = epilogue; g.mode = mode;
   g.a_batched = a.batched; g.b_batched = b.batched;
   g.status = h->status;
+  g.planes_per_mat = a.nplanes;
+  g.exp_a = a.expo; g.exp_b = b.expo;
   g.bias_per_row = bias_per_row;
   g.kb_batch_stride = kb_batch_stride;
   g.num_kb = num_kb_override;  // 0: the whole padded K
   // two-CTA pair tiles whenever the output is at least one pair tile tall and wide
   if (variant == 0) variant = (M > 128 && N > 128) ? 5 : ((N > 128) ? 1 : (N > 64 ? 2 : 3));
-  if ((a.mn_major || b.mn_major) && variant != 5)
-    return fail(MTB200_ERR_INVALID, "MN-major operand planes need the two-CTA kernel (variant 5)");
+  if ((a.mn_major || b.mn_major || mode == 23) && variant != 5)
+    return fail(MTB200_ERR_INVALID, "MN-major planes and the fp16 mode need the two-CTA kernel (variant 5)");
   switch (variant) {
     case 1: return launch_variant<256, 32, 3>(h, a, b, Kp, g);
     case 2: return launch_variant<128, 64, 2>(h, a, b, Kp, g);
     case 3: return launch_variant<64, 64, 3>(h, a, b, Kp, g);
     case 4: return launch_variant<128, 32, 4>(h, a, b, Kp, g);
-    case 5: return launch_variant2<64, 2>(h, a, b, Kp, g, K);
-    case 6: return launch_variant2<32, 4>(h, a, b, Kp, g);
+    case 5: return mode == 23 ? launch_variant2<64, 3, 2>(h, a, b, Kp, g, K) : launch_variant2<64, 2, 3>(h, a, b, Kp, g, K);
+    case 6: return launch_variant2<32, 4, 3>(h, a, b, Kp, g);
     default: return fail(MTB200_ERR_INVALID, "unknown GEMM tile variant %d", variant);
   }
+}
+
+// Scale + split one f32 operand into two fp16 planes and its exponent vector.
+//  k_major: source [mn][k] (scale per row); otherwise source [k][mn] (scale per column).
+inline int32_t launch_split16(mtb200_ctx* h, const float* src, bool k_major, int mn, int K, int batch,
+                              long long bstride, __half* planes, int* expo, uint32_t* nf_word, uint32_t epoch) {
+  if (k_major) {
+    const int Kp = padded_k(K);
+    ProfScope prof(h, PROF_SPLIT, double(batch) * mn * (8.0 * K + 4.0 * Kp));
+    split16_rows_kernel<<<dim3(unsigned(std::min(mn, 65535)), 1, batch), 256, 0, h->stream>>>(
+        src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
+  } else {
+    const int cp = padded_k(mn);
+    ProfScope prof(h, PROF_SPLIT, double(batch) * K * (8.0 * mn + 4.0 * cp));
+    MTB_CUDA(cudaMemsetAsync(expo, 0, sizeof(int) * size_t(batch) * mn, h->stream));
+    const int bands = std::max(1, std::min((K + 63) / 64, (h->sm_count * 8) / std::max(1, (mn + 255) / 256)));
+    const int rows_per_band = (K + bands - 1) / bands;
+    colabsmax_kernel<<<dim3((mn + 255) / 256, (K + rows_per_band - 1) / rows_per_band, batch), 256, 0, h->stream>>>(
+        src, mn, bstride, K, mn, rows_per_band, reinterpret_cast<uint32_t*>(expo), nf_word, epoch);
+    exponent_from_amax_kernel<<<(batch * mn + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<uint32_t*>(expo), expo,
+                                                                          batch * mn);
+    const long long total = static_cast<long long>(K) * (cp / 8);
+    const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
+    split16_cols_scaled_kernel<<<dim3(blocks, 1, batch), 256, 0, h->stream>>>(src, mn, bstride, planes, expo, K, mn, cp);
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+// f32 GEMM in the fp16 two-plane mode (pair-tile kernel only).
+inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int batch, int M, int N, int K,
+                                  const float* A, long long stride_a, const float* B, long long stride_b, float* C,
+                                  long long ldc, long long stride_c, const float* bias, int epilogue,
+                                  const float* aux) {
+  const int Kp = padded_k(K);
+  const int batch_a = (stride_a == 0 || batch == 1) ? 1 : batch;
+  const int batch_b = (stride_b == 0 || batch == 1) ? 1 : batch;
+  const bool a_kmaj = !trans_a, b_kmaj = trans_b;
+  const int a_rows = a_kmaj ? M : K, a_cols_p = a_kmaj ? Kp : padded_k(M);
+  const int b_rows = b_kmaj ? N : K, b_cols_p = b_kmaj ? Kp : padded_k(N);
+  const size_t bytes_a = align_up(size_t(2) * batch_a * a_rows * a_cols_p * 2, 1024);
+  const size_t bytes_b = align_up(size_t(2) * batch_b * b_rows * b_cols_p * 2, 1024);
+  const size_t bytes_ea = align_up(sizeof(int) * size_t(batch_a) * M, 1024);
+  const size_t bytes_eb = align_up(sizeof(int) * size_t(batch_b) * N, 1024);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, bytes_a + bytes_b + bytes_ea + bytes_eb, &ws);
+  if (rc) return rc;
+  char* base = static_cast<char*>(ws);
+  __half* pa = reinterpret_cast<__half*>(base);
+  __half* pb = reinterpret_cast<__half*>(base + bytes_a);
+  int* ea = reinterpret_cast<int*>(base + bytes_a + bytes_b);
+  int* eb = reinterpret_cast<int*>(base + bytes_a + bytes_b + bytes_ea);
+  uint32_t* nf_word = h->status + 2;
+  const uint32_t epoch = ++h->epoch;
+  rc = launch_split16(h, A, a_kmaj, M, K, batch_a, stride_a, pa, ea, nf_word, epoch);
+  if (rc) return rc;
+  rc = launch_split16(h, B, b_kmaj, N, K, batch_b, stride_b, pb, eb, nf_word, epoch);
+  if (rc) return rc;
+  SplitOperand oa{reinterpret_cast<const __nv_bfloat16*>(pa), a_rows, batch_a > 1, batch_a, a_kmaj ? 0 : 1, a_cols_p, 2, ea};
+  SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(pb), b_rows, batch_b > 1, batch_b, b_kmaj ? 0 : 1, b_cols_p, 2, eb};
+  rc = run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, 23, 5, 0, 0, 0, K);
+  if (rc) return rc;
+  StridedGemmArgs s;
+  s.M = M; s.N = N; s.K = K; s.batch = batch;
+  s.A = A; s.B = B; s.C = C;
+  s.a_si = trans_a ? 1 : K;  s.a_sk = trans_a ? M : 1;  s.a_sb = stride_a;
+  s.b_sk = trans_b ? 1 : N;  s.b_sj = trans_b ? K : 1;  s.b_sb = stride_b;
+  s.ldc = ldc; s.c_sb = stride_c;
+  s.bias = bias; s.aux = aux; s.epilogue = epilogue;
+  s.gate = nf_word; s.gate_value = epoch;
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+  gemm_simt_kernel<float, 8, 8><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(s);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
 }
 
 // Full f32 GEMM from row-major f32 operands: split both into scratch, multiply.
@@ -197,9 +278,15 @@ inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int bat
   const int Kp = padded_k(K);
   const int batch_a = (stride_a == 0 || batch == 1) ? 1 : batch;
   const int batch_b = (stride_b == 0 || batch == 1) ? 1 : batch;
-  const int eff_mode = mode == 0 ? 6 : mode;
-  const int nsplit = eff_mode == 1 ? 1 : (eff_mode == 3 ? 2 : 3);
   if (variant == 0 && M > 128 && N > 128) variant = 5;
+  // default arithmetic: the fp16 two-plane mode wherever the pair-tile kernel runs, six bf16 products elsewhere
+  const int eff_mode = mode == 0 ? (variant == 5 ? 23 : 6) : mode;
+  const int nsplit = eff_mode == 1 ? 1 : (eff_mode == 3 ? 2 : 3);
+  if (eff_mode == 23) {
+    if (variant != 5) return fail(MTB200_ERR_UNSUPPORTED, "the fp16 mode runs on the pair-tile kernel (M, N > 128)");
+    return gemm_f32_split_f16(h, trans_a, trans_b, batch, M, N, K, A, stride_a, B, stride_b, C, ldc, stride_c, bias,
+                              epilogue, aux);
+  }
   const bool straight = (variant == 5);
   // plane geometry: rows x padded cols
   const int a_rows = (straight && trans_a) ? K : M, a_cols_p = (straight && trans_a) ? padded_k(M) : Kp;

@@ -43,7 +43,10 @@ struct GemmArgs {
   const float* bias;   // [N] added to every row, or nullptr
   const float* aux;    // same layout as C, read by EPI_RELU_BWD, or nullptr
   int epilogue;
-  int mode;            // 1, 3, 6 or 9 split products
+  int mode;            // 1, 3, 6 or 9 bf16 split products; 23 = fp16 two-plane mode (3 products)
+  int planes_per_mat;  // planes stored per matrix in the operand arrays (3 bf16, 2 fp16)
+  const int* exp_a;    // fp16 mode: per-row scale exponents of A ([batch][M] if A is batched), else nullptr
+  const int* exp_b;    // fp16 mode: per-column scale exponents of B ([batch][N] if B is batched)
   int a_batched;       // 0: one A shared by all batch entries
   int b_batched;
   int bias_per_row;    // 0: bias[N] added along columns; 1: bias[M] added along rows
@@ -83,6 +86,7 @@ __device__ __forceinline__ float apply_epilogue(float x, int epi, float aux) {
 // before the dominant a0*b0 term.  Encoded as (i << 2 | j), i = A split, j = B split.
 __device__ __forceinline__ int split_pairs(int mode, uint8_t (&pairs)[9]) {
   if (mode == 1) { pairs[0] = 0; return 1; }
+  if (mode == 23) { pairs[0] = (0 << 2) | 1; pairs[1] = (1 << 2) | 0; pairs[2] = 0; return 3; }
   if (mode == 3) { pairs[0] = (0 << 2) | 1; pairs[1] = (1 << 2) | 0; pairs[2] = 0; return 3; }
   if (mode == 9) {
     pairs[0] = (2 << 2) | 2; pairs[1] = (1 << 2) | 2; pairs[2] = (2 << 2) | 1;
@@ -189,8 +193,8 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int b, tm, tn;
         tile_coords(t, tiles_m, tiles_n, b, tm, tn);
-        const int za = (g.a_batched ? b : 0) * 3;
-        const int zb = (g.b_batched ? b : 0) * 3;
+        const int za = (g.a_batched ? b : 0) * g.planes_per_mat;
+        const int zb = (g.b_batched ? b : 0) * g.planes_per_mat;
         const int kb0 = b * g.kb_batch_stride;
         for (int kb = 0; kb < g.num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word)) {

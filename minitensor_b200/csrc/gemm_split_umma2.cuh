@@ -45,7 +45,7 @@ __device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
 
-template <int BK, int STAGES>
+template <int BK, int STAGES, int NP = 3>
 struct Gemm2Cfg {
   static constexpr int BM = 128;        // rows per CTA
   static constexpr int BNH = 128;       // B columns staged per CTA
@@ -53,7 +53,7 @@ struct Gemm2Cfg {
   static constexpr int ROW_BYTES = BK * 2;
   static constexpr int A_TILE = BM * ROW_BYTES;
   static constexpr int B_TILE = BNH * ROW_BYTES;
-  static constexpr int STAGE_BYTES = 3 * A_TILE + 3 * B_TILE;
+  static constexpr int STAGE_BYTES = NP * (A_TILE + B_TILE);  // NP planes of each operand per stage
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
   static constexpr int NUM_THREADS = 192;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
@@ -64,11 +64,12 @@ struct Gemm2Cfg {
 // memory, mn padded to a multiple of 64) and its tensor map is the 4-D view
 // {64, k, mn / 64, plane}; otherwise K-major planes [mn][k] with the 3-D map.
 // MN-major needs BK = 64 (128-byte swizzle rows of 64 elements).
-template <int BK, int STAGES, bool A_MN = false, bool B_MN = false>
+// NP = planes per operand held in a stage: 3 (bf16 modes) or 2 (fp16 mode).
+template <int BK, int STAGES, bool A_MN = false, bool B_MN = false, int NP = 3>
 __global__ void __launch_bounds__(192, 1)
 gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                         const GemmArgs g) {
-  using Cfg = Gemm2Cfg<BK, STAGES>;
+  using Cfg = Gemm2Cfg<BK, STAGES, NP>;
   static_assert(!(A_MN || B_MN) || BK == 64, "MN-major operands need BK = 64");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -90,7 +91,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
   const int tiles_m = (g.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
   const int tiles_n = (g.N + Cfg::TILE_N - 1) / Cfg::TILE_N;
   const int num_tiles = tiles_m * tiles_n * g.batch;
-  const int nsplit = (g.mode == 1) ? 1 : (g.mode == 3 ? 2 : 3);
+  const int nsplit = (g.mode == 1) ? 1 : ((g.mode == 3 || g.mode == 23) ? 2 : 3);
   const uint32_t stage_tx = nsplit * (Cfg::A_TILE + Cfg::B_TILE);  // bytes this CTA loads per stage
 
   if (threadIdx.x == 0) {
@@ -125,7 +126,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         int b, tm, tn;
         tile_coords(t, tiles_m, tiles_n, b, tm, tn);
-        const int za = (g.a_batched ? b : 0) * 3, zb = (g.b_batched ? b : 0) * 3;
+        const int za = (g.a_batched ? b : 0) * g.planes_per_mat, zb = (g.b_batched ? b : 0) * g.planes_per_mat;
         const int kb0 = b * g.kb_batch_stride;
         const int row_a = tm * Cfg::TILE_M + int(rank) * Cfg::BM;
         const int row_b = tn * Cfg::TILE_N + int(rank) * Cfg::BNH;
@@ -139,7 +140,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
           const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
           mbar_expect_tx_cluster(lead_full, stage_tx);
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + 3 * Cfg::A_TILE;
+          const uint32_t sb = sa + NP * Cfg::A_TILE;
           for (int s = 0; s < nsplit; ++s) {
             if constexpr (A_MN)
               tma_load_4d_pair(sa + s * Cfg::A_TILE, &tmapA, lead_full, 0, (kb0 + kb) * BK, row_a >> 6, za + s);
@@ -161,7 +162,8 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
     if (lane == 0 && rank == 0) {
       uint8_t pairs[9];
       const int npairs = split_pairs(g.mode, pairs);
-      constexpr uint32_t idesc = make_idesc(Cfg::TILE_M, Cfg::TILE_N, 1u, 1u, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      const uint32_t idesc = make_idesc(Cfg::TILE_M, Cfg::TILE_N, g.mode == 23 ? 0u /*f16*/ : 1u /*bf16*/, 1u,
+                                        A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -183,7 +185,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
           }
           tc_fence_after();
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + 3 * Cfg::A_TILE;
+          const uint32_t sb = sa + NP * Cfg::A_TILE;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
             for (int p = 0; p < npairs; ++p) {
@@ -228,6 +230,9 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
       float* crow = g.C + b * g.strideC + static_cast<long long>(row) * g.ldc;
       const float* arow = g.aux ? g.aux + b * g.strideC + static_cast<long long>(row) * g.ldc : nullptr;
       const float row_bias = (g.bias && g.bias_per_row && row_ok) ? __ldg(g.bias + row) : 0.0f;
+      // fp16 mode: undo the operand scalings, C = acc * 2^(ea[row] + eb[col])
+      const int* eb = g.exp_b ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) : nullptr;
+      const int ea = (g.exp_a && row_ok) ? __ldg(g.exp_a + (g.a_batched ? static_cast<long long>(b) * g.M : 0) + row) : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::TILE_N;
 #pragma unroll 1
       for (int c0 = 0; c0 < Cfg::TILE_N; c0 += 32) {
@@ -246,6 +251,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
             for (int e = 0; e < 4; ++e) {
               float x = __uint_as_float(v[j + e]);
               if (col + e < g.N) {
+                if (eb) x = ldexpf(x, ea + __ldg(eb + col + e));
                 if (g.bias) x += g.bias_per_row ? row_bias : __ldg(g.bias + col + e);
                 const float ax = (g.epilogue == EPI_RELU_BWD) ? arow[col + e] : 0.0f;
                 x = apply_epilogue(x, g.epilogue, ax);

@@ -1,0 +1,169 @@
+// Operand preparation for the fp16 two-plane mode of the tensor-core GEMM.
+//
+// An f32 value a is scaled by a power of two chosen per M (or N) index so that
+// the largest magnitude of that row lands in [2^14, 2^15), and is then written
+// as a0 + a1 with fp16 terms (11 + 11 significand bits; both remainders are
+// exact in f32).  The GEMM multiplies a0b1, a1b0, a0b0 - three fp16 tensor
+// products per f32 product, half the work of the six-product bf16 mode, with
+// the accuracy of a 3xTF32 emulation (which also keeps 22 bits and drops the
+// low x low term) - and the epilogue undoes the two scalings exactly with
+// ldexpf.  Values whose scaled magnitude falls below the fp16 subnormal step
+// lose at most 2^-25 of their row's scaled maximum, i.e. 2^-39 of the row's
+// largest element.
+//
+// Plane layout matches split_bf16.cuh with two planes: dst[(b*2 + s)][row][col],
+// columns padded with zeros to a multiple of 64.  `expo` receives, per scaled
+// index, the integer e with scale = 2^-e.
+//   K-major planes (rows = M/N index):   one scale per ROW   -> split16_rows_kernel
+//   MN-major planes (rows = K index):    one scale per COLUMN -> colabsmax_kernel + split16_cols_scaled_kernel
+#pragma once
+#include <cuda_fp16.h>
+#include <cstdint>
+
+#include "split_bf16.cuh"
+
+namespace mtb {
+
+// e such that max * 2^-e lies in [2^14, 2^15); 0 for max == 0 or non-finite.
+__device__ __forceinline__ int scale_exponent(float amax) {
+  const uint32_t bits = __float_as_uint(amax);
+  if (amax == 0.0f || (bits & 0x7f800000u) == 0x7f800000u) return 0;
+  int ex;
+  frexpf(amax, &ex);  // amax = m * 2^ex, m in [0.5, 1)  ->  amax in [2^(ex-1), 2^ex)
+  return ex - 15;
+}
+
+__device__ __forceinline__ void split2_f16(float x, int e, __half& h0, __half& h1) {
+  if (is_nonfinite(x)) {  // carried as is; the caller has raised the non-finite word
+    h0 = __float2half_rn(x);
+    h1 = __float2half_rn(0.0f);
+    return;
+  }
+  const float v = ldexpf(x, -e);
+  h0 = __float2half_rn(v);
+  h1 = __float2half_rn(v - __half2float(h0));
+}
+
+// One block per row: pass 1 finds the row's largest magnitude, pass 2 (served
+// by L1/L2) scales and splits.  src[b][r][k], row stride ld.
+static __global__ void __launch_bounds__(256)
+split16_rows_kernel(const float* __restrict__ src, long long ld, long long bstride, __half* __restrict__ dst,
+                    int* __restrict__ expo, int R, int K, int Kp, uint32_t* __restrict__ nf_word, uint32_t nf_epoch) {
+  __shared__ float red[8];
+  __shared__ int s_e;
+  const int b = blockIdx.z;
+  const long long plane = static_cast<long long>(R) * Kp;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const float* p = src + b * bstride + static_cast<long long>(r) * ld;
+    const bool vec = ((reinterpret_cast<uintptr_t>(p) & 15) == 0);
+    float amax = 0.0f;
+    bool nf = false;
+    if (vec) {
+      for (int k = threadIdx.x * 4; k + 3 < K; k += 1024) {
+        const float4 u = *reinterpret_cast<const float4*>(p + k);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(u.x), fabsf(u.y)), fmaxf(fabsf(u.z), fabsf(u.w))));
+        nf |= is_nonfinite(u.x) | is_nonfinite(u.y) | is_nonfinite(u.z) | is_nonfinite(u.w);
+      }
+      for (int k = (K & ~3) + threadIdx.x; k < K; k += 256) {
+        amax = fmaxf(amax, fabsf(p[k]));
+        nf |= is_nonfinite(p[k]);
+      }
+    } else {
+      for (int k = threadIdx.x; k < K; k += 256) {
+        amax = fmaxf(amax, fabsf(p[k]));
+        nf |= is_nonfinite(p[k]);
+      }
+    }
+    if (nf && nf_word) atomicMax(nf_word, nf_epoch);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = red[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+      const int e = scale_exponent(m);
+      s_e = e;
+      expo[static_cast<long long>(b) * R + r] = e;
+    }
+    __syncthreads();
+    const int e = s_e;
+    __half* d0 = dst + (static_cast<long long>(b) * 2) * plane + static_cast<long long>(r) * Kp;
+    for (int k0 = threadIdx.x * 8; k0 < Kp; k0 += 2048) {
+      __align__(16) __half o0[8], o1[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float x = (k0 + i < K) ? p[k0 + i] : 0.0f;
+        split2_f16(x, e, o0[i], o1[i]);
+      }
+      *reinterpret_cast<uint4*>(d0 + k0) = *reinterpret_cast<const uint4*>(o0);
+      *reinterpret_cast<uint4*>(d0 + plane + k0) = *reinterpret_cast<const uint4*>(o1);
+    }
+    __syncthreads();
+  }
+}
+
+// amax_bits[b][c] = max over rows of |src[b][r][c]| as raw bits (non-negative floats order like unsigned ints).
+// The vector must be zeroed before the launch.
+static __global__ void __launch_bounds__(256)
+colabsmax_kernel(const float* __restrict__ src, long long ld, long long bstride, int R, int Cc, int rows_per_band,
+                 uint32_t* __restrict__ amax_bits, uint32_t* __restrict__ nf_word, uint32_t nf_epoch) {
+  const int b = blockIdx.z;
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= Cc) return;
+  const int r0 = blockIdx.y * rows_per_band, r1 = min(R, r0 + rows_per_band);
+  const float* p = src + b * bstride + c;
+  float amax = 0.0f;
+  bool nf = false;
+  for (int r = r0; r < r1; ++r) {
+    const float v = p[static_cast<long long>(r) * ld];
+    nf |= is_nonfinite(v);
+    amax = fmaxf(amax, fabsf(v));
+  }
+  if (nf && nf_word) atomicMax(nf_word, nf_epoch);
+  atomicMax(amax_bits + static_cast<long long>(b) * Cc + c, __float_as_uint(amax));
+}
+
+// expo[i] = scale exponent of the magnitude whose bits are amax_bits[i] (in place is fine).
+static __global__ void exponent_from_amax_kernel(const uint32_t* __restrict__ amax_bits, int* __restrict__ expo, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) expo[i] = scale_exponent(__uint_as_float(amax_bits[i]));
+}
+
+// MN-major planes: dst[(b*2+s)][r][c], scale per column c.  One thread converts 8 columns of a row.
+static __global__ void __launch_bounds__(256)
+split16_cols_scaled_kernel(const float* __restrict__ src, long long ld, long long bstride, __half* __restrict__ dst,
+                           const int* __restrict__ expo, int R, int Cc, int Cp) {
+  const int b = blockIdx.z;
+  const int chunks = Cp >> 3;
+  const long long total = static_cast<long long>(R) * chunks;
+  const long long plane = static_cast<long long>(R) * Cp;
+  const float* s = src + b * bstride;
+  const int* ex = expo + static_cast<long long>(b) * Cc;
+  const bool vec = ((reinterpret_cast<uintptr_t>(s) & 15) == 0) && ((ld & 3) == 0);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / chunks);
+    const int c0 = static_cast<int>(i - static_cast<long long>(r) * chunks) << 3;
+    const float* p = s + static_cast<long long>(r) * ld + c0;
+    float x[8];
+    if (vec && c0 + 8 <= Cc) {
+      const float4 u = *reinterpret_cast<const float4*>(p);
+      const float4 w = *reinterpret_cast<const float4*>(p + 4);
+      x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w; x[4] = w.x; x[5] = w.y; x[6] = w.z; x[7] = w.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = (c0 + j < Cc) ? p[j] : 0.0f;
+    }
+    __align__(16) __half o0[8], o1[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) split2_f16(x[j], (c0 + j < Cc) ? ex[c0 + j] : 0, o0[j], o1[j]);
+    __half* d = dst + (static_cast<long long>(b) * 2) * plane + static_cast<long long>(r) * Cp + c0;
+    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(o0);
+    *reinterpret_cast<uint4*>(d + plane) = *reinterpret_cast<const uint4*>(o1);
+  }
+}
+
+}  // namespace mtb

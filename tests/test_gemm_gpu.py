@@ -317,3 +317,61 @@ def test_large_int_modular_identity(be):
     be.sync()
     assert torch.equal(lhs, rhs)
     assert int(c.abs().max()) <= 64 * n  # |sum| <= 8*8*K: no overflow at these magnitudes
+
+
+# ------------------------------------------------------------------ fp16 two-plane mode (the default for large outputs)
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mode", [23, 6])
+def test_f16x3_and_bf16x6_agree_with_oracle_all_orientations(be, orc, rng, ta, tb, mode):
+    m, n, k = 300, 520, 777
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    c = run_gemm(be, a, b, trans_a=ta, trans_b=tb, f32_mode=mode)
+    al = np.ascontiguousarray(a.T if ta else a)
+    bl = np.ascontiguousarray(b.T if tb else b)
+    assert norm_scaled_error(c, orc.matmul_acc_wide(al, bl), al, bl) <= 4e-6
+    assert norm_scaled_error(c, orc.matmul(al, bl), al, bl) <= F32_TOL
+
+
+def test_f16x3_row_and_column_scaling_covers_the_f32_range(be, orc, rng):
+    """Rows of A and columns of B spanning 2^-60 .. 2^60, and a row of subnormals: the per-row / per-column
+    power-of-two scaling keeps every output within the norm-scaled tolerance."""
+    m, n, k = 260, 300, 512
+    a = rng.standard_normal((m, k)).astype(np.float32) * np.exp2(rng.integers(-60, 60, (m, 1))).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32) * np.exp2(rng.integers(-60, 60, (1, n))).astype(np.float32)
+    a[3] = np.float32(1e-41)            # subnormal row
+    a[5] = 0.0                          # zero row
+    b[:, 7] = 0.0
+    wide = orc.matmul_acc_wide(a, b)
+    keep = np.arange(m) != 3
+    for mode in (0, 23):
+        c = run_gemm(be, a, b, f32_mode=mode)
+        assert np.isfinite(c).all()
+        assert norm_scaled_error(c[keep], wide[keep], a[keep], b) <= 4e-6
+        assert not c[5].any() and not c[:, 7].any()
+        # the subnormal row: products with small columns fall below the smallest f32 subnormal, so allow
+        # one subnormal step (2^-149) on top of the norm-scaled bound
+        scale3 = np.linalg.norm(a[3].astype(np.float64)) * np.linalg.norm(b.astype(np.float64), axis=0)
+        assert np.all(np.abs(c[3].astype(np.float64) - wide[3]) <= 4e-6 * scale3 + 2.0 ** -149)
+    # wide range INSIDE a row: small elements lose at most 2^-39 of the row maximum
+    a2 = rng.standard_normal((m, k)).astype(np.float32) * np.exp2(rng.integers(-20, 20, (m, k))).astype(np.float32)
+    c = run_gemm(be, a2, b, f32_mode=23)
+    assert norm_scaled_error(c, orc.matmul_acc_wide(a2, b), a2, b) <= 4e-6
+
+
+def test_f16x3_batched_and_epilogue(be, orc, rng):
+    a = rng.standard_normal((3, 200, 150)).astype(np.float32)
+    b = rng.standard_normal((3, 150, 300)).astype(np.float32)
+    c = run_gemm(be, a, b, f32_mode=23)
+    assert norm_scaled_error(c, orc.matmul(a, b), a, b) <= F32_TOL
+    w = rng.standard_normal((150, 300)).astype(np.float32)          # one B broadcast over the batch
+    c = run_gemm(be, a, w, f32_mode=23)
+    assert norm_scaled_error(c, orc.matmul(a, np.broadcast_to(w, (3, 150, 300)).copy()), a, w) <= F32_TOL
+    x = rng.standard_normal((260, 300)).astype(np.float32)
+    wt = rng.standard_normal((200, 300)).astype(np.float32)
+    bias = rng.standard_normal(200).astype(np.float32)
+    y = run_gemm(be, x, wt, trans_b=True, bias=dev(be, bias), epilogue=1, f32_mode=23)
+    ref, _ = orc.relu(orc.dense_forward(x, wt, bias))
+    assert norm_scaled_error(y, ref, x, wt.T) <= F32_TOL
+    with pytest.raises(ValueError):                                  # the mode needs the pair-tile kernel
+        run_gemm(be, x[:64], wt, trans_b=True, f32_mode=23)
