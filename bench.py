@@ -49,18 +49,25 @@ def _peaks():
 class ClockSampler:
     """nvidia-smi clock / throttle samples taken while the timed region runs."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device_index: int):
         self.proc = None
         self.idx = device_index
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
                  str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -74,17 +81,27 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
+        import datetime
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 8:
+            if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[2]), float(f[3]), float(f[4]), f[5:9]))
             except ValueError:
                 continue
-            for n, v in zip(names, f[4:8]):
+        # samples taken while the timed region ran (the sampler starts before the warm-up steps); if the
+        # region was shorter than the sampling period, fall back to the nearest samples under load
+        inside = [r for r in rows if self.t0 is not None and self.t0 - 0.05 <= r[0] <= self.t1 + 0.05]
+        if not inside and rows and self.t0 is not None:
+            inside = sorted(rows, key=lambda r: abs(r[0] - 0.5 * (self.t0 + self.t1)))[:2]
+        for ts, c, m, p, flags in (inside or rows):
+            sm.append(c); mx.append(m); power.append(p)
+            for n, v in zip(names, flags):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
@@ -193,6 +210,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = _peaks()
     lo, hi = shard_rows(GLOBAL_BATCH, world, rank)
@@ -221,12 +240,13 @@ def run_ours(args):
         return float(t.item())
 
     # ---- device-resident steps (inputs already in HBM)
-    for _ in range(args.warmup):
-        trainer.step(x, y)
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        trainer.step(x, y)
+    barrier()
+    sampler.mark_begin()
     be.profile(True)
     launches0 = be.launches
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -236,6 +256,7 @@ def run_ours(args):
         loss = trainer.step(x, y)
     e.record()
     barrier()
+    sampler.mark_end()
     ms_total = max_over_ranks(s.elapsed_time(e))
     clocks = sampler.stop() if rank == 0 else None
     gpu_launches = be.launches - launches0
