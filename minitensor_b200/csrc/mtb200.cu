@@ -7,6 +7,7 @@
 #include "gemm_f64_int.cuh"
 #include "rowcol_kernels.cuh"
 #include "gemm_launch.cuh"
+#include "gemm_i32_limb.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -87,6 +88,72 @@ static double powi_f64(double a, int b) {
     a *= a;
   }
   return recip ? 1.0 / r : r;
+}
+
+}  // namespace mtb
+
+namespace mtb {
+
+// int32 GEMM on the integer tensor cores (gemm_i32_limb.cuh): byte-limb planes of both operands in
+// scratch, then one launch per K chunk of at most 8192.
+static int32_t gemm_i32_limb(mtb200_ctx* h, bool trans_a, bool trans_b, int batch, int M, int N, int K,
+                             const int32_t* A, long long stride_a, const int32_t* B, long long stride_b,
+                             int32_t* C, long long stride_c) {
+  using Cfg = I32LimbCfg;
+  const int Kp = (K + 63) / 64 * 64;
+  const int batch_a = (stride_a == 0 || batch == 1) ? 1 : batch;
+  const int batch_b = (stride_b == 0 || batch == 1) ? 1 : batch;
+  const size_t bytes_a = align_up(size_t(4) * batch_a * M * Kp, 1024), bytes_b = align_up(size_t(4) * batch_b * N * Kp, 1024);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, bytes_a + bytes_b, &ws);
+  if (rc) return rc;
+  uint8_t* pa = static_cast<uint8_t*>(ws);
+  uint8_t* pb = pa + bytes_a;
+  uint32_t* wide_word = h->status + 3;
+  const uint32_t epoch = ++h->epoch;
+  {
+    ProfScope prof(h, PROF_SPLIT, 8.0 * (double(batch_a) * M + double(batch_b) * N) * K);
+    // op(A) is [M][K]: source [M][K] or, transposed, [K][M];  op(B)^T is [N][K]: source [K][N] needs the turn
+    limb_split_kernel<<<dim3((M + 63) / 64, Kp / 64, batch_a), 256, 0, h->stream>>>(
+        A, trans_a ? M : K, stride_a, trans_a ? 1 : 0, pa, M, K, Kp, wide_word, epoch);
+    limb_split_kernel<<<dim3((N + 63) / 64, Kp / 64, batch_b), 256, 0, h->stream>>>(
+        B, trans_b ? K : N, stride_b, trans_b ? 0 : 1, pb, N, K, Kp, wide_word, epoch);
+    MTB_CUDA(cudaGetLastError());
+  }
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap ta, tb;
+  auto make = [&](CUtensorMap* out, void* base, int rows, int planes) -> int32_t {
+    const cuuint64_t dims[3] = {cuuint64_t(Kp), cuuint64_t(rows), cuuint64_t(planes)};
+    const cuuint64_t strides[2] = {cuuint64_t(Kp), cuuint64_t(rows) * Kp};
+    const cuuint32_t box[3] = {Cfg::BKB, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MTB200_OK : fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (limb planes) failed (%d)", int(r));
+  };
+  rc = make(&ta, pa, M, 4 * batch_a);
+  if (rc) return rc;
+  rc = make(&tb, pb, N, 4 * batch_b);
+  if (rc) return rc;
+  MTB_CUDA(cudaFuncSetAttribute(gemm_i32_limb_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  I32LimbArgs g = {};
+  g.M = M; g.N = N; g.batch = batch;
+  g.C = reinterpret_cast<uint32_t*>(C); g.strideC = stride_c;
+  g.a_batched = batch_a > 1; g.b_batched = batch_b > 1;
+  g.wide_word = wide_word; g.wide_epoch = epoch; g.status = h->status;
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128) * batch;
+  const int grid = int(std::min<long long>(tiles, h->sm_count));
+  const int total_kb = Kp / 64, chunk_kb = 8192 / 64;
+  for (int kb0 = 0; kb0 < total_kb; kb0 += chunk_kb) {
+    g.kb0 = kb0;
+    g.num_kb = std::min(chunk_kb, total_kb - kb0);
+    g.accumulate = kb0 > 0;
+    ProfScope prof(h, PROF_GEMM_INT, 2.0 * M * N * double(g.num_kb) * 64 * batch);
+    gemm_i32_limb_umma_kernel<<<grid, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(ta, tb, g);
+    MTB_CUDA(cudaGetLastError());
+  }
+  return MTB200_OK;
 }
 
 }  // namespace mtb
@@ -345,6 +412,15 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
                           static_cast<const float*>(aux), mode, variant);
   }
 
+  // int32: the tensor-core limb path once the product is large enough to amortise the limb split
+  // (f32_mode variant byte 0xfe forces the CUDA-core kernel, 0xfd forces the tensor path)
+  if (dtype == MTB200_I32) {
+    const int variant = (f32_mode >> 8) & 0xff;
+    const bool big = double(M) * double(N) * double(K) >= double(1 << 24) && K >= 64;
+    if ((big && variant != 0xfe) || variant == 0xfd)
+      return gemm_i32_limb(h, trans_a != 0, trans_b != 0, int(batch), int(M), int(N), int(K), static_cast<const int32_t*>(A),
+                           stride_a, static_cast<const int32_t*>(B), stride_b, static_cast<int32_t*>(C), stride_c);
+  }
   StridedGemmArgs g;
   g.M = int(M); g.N = int(N); g.K = int(K); g.batch = int(batch);
   g.A = A; g.B = B; g.C = C;

@@ -38,7 +38,8 @@ inline int32_t fail(int32_t code, const char* fmt, ...) {
 
 // Device status word layout: [0] expired-wait code of the GEMM kernels,
 // [1] bad-label flag of cross entropy, [2] epoch of the last f32 GEMM whose
-// operands held an Inf or NaN.
+// operands held an Inf or NaN, [3] epoch of the last int32 GEMM with an operand
+// element outside the int8 range.
 struct mtb200_ctx {
   int device = 0;
   int sm_count = 0;

@@ -375,3 +375,37 @@ def test_f16x3_batched_and_epilogue(be, orc, rng):
     assert norm_scaled_error(y, ref, x, wt.T) <= F32_TOL
     with pytest.raises(ValueError):                                  # the mode needs the pair-tile kernel
         run_gemm(be, x[:64], wt, trans_b=True, f32_mode=23)
+
+
+# ------------------------------------------------------------------ int32 on the integer tensor cores (byte limbs)
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (130, 70, 33), (128, 128, 64), (300, 260, 1000), (64, 200, 9000)])
+@pytest.mark.parametrize("full_range", [False, True])
+def test_i32_limb_path_bit_exact(be, orc, rng, m, n, k, full_range):
+    """The tensor-core limb kernel (forced with variant byte 0xfd) and the CUDA-core kernel (0xfe) both equal the
+    reference's wrapping triple loop, for small entries (one signed-byte product) and for the full int32 range
+    (ten unsigned limb products, reductions longer than 8192 chained)."""
+    info = np.iinfo(np.int32)
+    lo, hi = (info.min, info.max) if full_range else (-8, 9)
+    a = rng.integers(lo, hi, (m, k), dtype=np.int64).astype(np.int32)
+    b = rng.integers(lo, hi, (k, n), dtype=np.int64).astype(np.int32)
+    ref = orc.matmul(a, b)
+    np.testing.assert_array_equal(run_gemm(be, a, b, variant=0xFD), ref)
+    np.testing.assert_array_equal(run_gemm(be, a, b, variant=0xFE), ref)
+
+
+def test_i32_limb_path_transposed_batched_and_mixed_range(be, orc, rng):
+    a = rng.integers(-2 ** 31, 2 ** 31, (3, 80, 65), dtype=np.int64).astype(np.int32)     # [b][K][M]
+    b = rng.integers(-8, 9, (3, 90, 80), dtype=np.int64).astype(np.int32)                 # [b][N][K]: small, A is wide
+    got = run_gemm(be, a, b, trans_a=True, trans_b=True, variant=0xFD)
+    ref = orc.matmul(np.ascontiguousarray(np.swapaxes(a, -1, -2)), np.ascontiguousarray(np.swapaxes(b, -1, -2)))
+    np.testing.assert_array_equal(got, ref)
+    # a wide call followed by a narrow one: the per-call range flag does not leak
+    s1 = rng.integers(-8, 9, (140, 70), dtype=np.int64).astype(np.int32)
+    s2 = rng.integers(-8, 9, (70, 150), dtype=np.int64).astype(np.int32)
+    np.testing.assert_array_equal(run_gemm(be, s1, s2, variant=0xFD), s1 @ s2)
+    # boundary of the signed-byte range
+    e1 = np.full((130, 64), -128, np.int32)
+    e2 = np.full((64, 130), 127, np.int32)
+    np.testing.assert_array_equal(run_gemm(be, e1, e2, variant=0xFD), e1 @ e2)
+    e1[0, 0] = 128
+    np.testing.assert_array_equal(run_gemm(be, e1, e2, variant=0xFD), e1 @ e2)
