@@ -97,6 +97,90 @@ __device__ __forceinline__ int split_pairs(int mode, uint8_t (&pairs)[9]) {
   pairs[3] = (0 << 2) | 1; pairs[4] = (1 << 2) | 0; pairs[5] = 0; return 6;
 }
 
+// Epilogue of one warp for one accumulator: 32 rows (one per lane in tensor memory) x `ncols`
+// columns.  tcgen05.ld hands every lane CW consecutive columns of ITS row, which written to
+// global memory directly would make each store instruction touch 32 different rows (32 partial
+// lines).  The values therefore go through a small shared-memory tile [32][CW + 1] and come back
+// with 32 / (CW / 4) rows per instruction, each row segment a contiguous run of float4 stores.
+// Scale (fp16 mode), bias, activation and ReLU mask are applied on the way out.
+//   stage      : this warp's [32][CW + 1] floats of shared memory
+//   t_row      : TMEM address of (first lane of this warp, first column of the accumulator)
+//   row0       : global row of lane 0;  col_base / col_end: global column range of the tile
+template <int CW>
+__device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* stage, uint32_t t_row, int b, int row0,
+                                                   int col_base, int col_end, int lane, bool vec_ok) {
+  constexpr int LPR = CW / 4;        // lanes per row when reading back
+  constexpr int RPI = 32 / LPR;      // rows per store instruction
+  constexpr int PITCH = CW + 1;
+  const int my_row = row0 + lane;
+  const bool my_row_ok = my_row < g.M;
+  const float row_bias_own = (g.bias && g.bias_per_row && my_row_ok) ? __ldg(g.bias + my_row) : 0.0f;
+  const int* eb = g.exp_b ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) : nullptr;
+  const int ea_own =
+      (g.exp_a && my_row_ok) ? __ldg(g.exp_a + (g.a_batched ? static_cast<long long>(b) * g.M : 0) + my_row) : 0;
+  float* cbase = g.C + b * g.strideC;
+  const float* abase = g.aux ? g.aux + b * g.strideC : nullptr;
+  const int cq = (lane % LPR) * 4, rsub = lane / LPR;
+#pragma unroll 1
+  for (int c0 = col_base; c0 < col_end; c0 += CW) {
+    uint32_t v[CW];
+    if constexpr (CW == 32) tmem_ld_32x32(t_row + (c0 - col_base), v);
+    else tmem_ld_32x16(t_row + (c0 - col_base), v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < CW; ++j) stage[lane * PITCH + j] = __uint_as_float(v[j]);
+    __syncwarp();
+    const int col = c0 + cq;
+    float cb[4];
+    int ce[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool ok = col + e < col_end;
+      cb[e] = (g.bias && !g.bias_per_row && ok) ? __ldg(g.bias + col + e) : 0.0f;
+      ce[e] = (eb && ok) ? __ldg(eb + col + e) : 0;
+    }
+#pragma unroll
+    for (int it = 0; it < LPR; ++it) {
+      const int r = it * RPI + rsub;
+      const int ea_r = __shfl_sync(0xffffffffu, ea_own, r);
+      const float rb = __shfl_sync(0xffffffffu, row_bias_own, r);
+      const int grow = row0 + r;
+      if (grow < g.M && col < col_end) {
+        float* cptr = cbase + static_cast<long long>(grow) * g.ldc + col;
+        const bool full = vec_ok && col + 3 < col_end && ((col & 3) == 0);
+        float ax[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (g.epilogue == EPI_RELU_BWD) {
+          const float* aptr = abase + static_cast<long long>(grow) * g.ldc + col;
+          if (full) {
+            const float4 a4 = *reinterpret_cast<const float4*>(aptr);
+            ax[0] = a4.x; ax[1] = a4.y; ax[2] = a4.z; ax[3] = a4.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < col_end) ax[e] = aptr[e];
+          }
+        }
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float x = stage[r * PITCH + cq + e];
+          if (eb) x = ldexpf(x, ea_r + ce[e]);
+          if (g.bias) x += g.bias_per_row ? rb : cb[e];
+          o[e] = apply_epilogue(x, g.epilogue, ax[e]);
+        }
+        if (full) {
+          *reinterpret_cast<float4*>(cptr) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (col + e < col_end) cptr[e] = o[e];
+        }
+      }
+    }
+    __syncwarp();  // the tile is rewritten by the next column group
+  }
+}
+
 template <int BN, int BK, int STAGES>
 struct GemmCfg {
   static constexpr int BM = 128;
@@ -107,7 +191,10 @@ struct GemmCfg {
   static constexpr int ACC_COLS = BN;                      // f32 columns per accumulator
   static constexpr int TMEM_COLS = 2 * BN;                 // two accumulators (power of two)
   static constexpr int NUM_THREADS = 192;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // epilogue staging: 4 warps x [32][CW + 1] floats; 16-column groups where the ring leaves less room
+  static constexpr int EPI_CW = (STAGES * STAGE_BYTES + 1024 + 256 + 4 * 32 * 33 * 4 <= 232448) ? 32 : 16;
+  static constexpr int EPI_BYTES = 4 * 32 * (EPI_CW + 1) * 4;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
   static_assert(ROW_BYTES == 64 || ROW_BYTES == 128, "BK must be 32 or 64");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM");
@@ -286,47 +373,10 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
         break;
       }
       tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
-      const bool row_ok = row < g.M;
-      float* crow = g.C + b * g.strideC + static_cast<long long>(row) * g.ldc;
-      const float* arow =
-          g.aux ? g.aux + b * g.strideC + static_cast<long long>(row) * g.ldc : nullptr;
-      const float row_bias = (g.bias && g.bias_per_row && row_ok) ? __ldg(g.bias + row) : 0.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::ACC_COLS;
-#pragma unroll 1
-      for (int c0 = 0; c0 < n_tile; c0 += 32) {
-        const int col0 = tn * n_tile + c0;
-        if (col0 >= g.N) break;  // uniform across the warp
-        const int col_end = min(g.N, (tn + 1) * n_tile);  // a conv tile may end inside a 32-column group
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c0, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int col = col0 + j;
-            if (col >= col_end) break;
-            float o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float x = __uint_as_float(v[j + e]);
-              if (col + e < col_end) {
-                if (g.bias) x += g.bias_per_row ? row_bias : __ldg(g.bias + col + e);
-                const float ax = (g.epilogue == EPI_RELU_BWD) ? arow[col + e] : 0.0f;
-                x = apply_epilogue(x, g.epilogue, ax);
-              }
-              o[e] = x;
-            }
-            if (vec_ok && col + 3 < col_end && ((col & 3) == 0)) {
-              *reinterpret_cast<float4*>(crow + col) = make_float4(o[0], o[1], o[2], o[3]);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (col + e < col_end) crow[col + e] = o[e];
-            }
-          }
-        }
-      }
+      float* stage = reinterpret_cast<float*>(smem_raw + (bars + 256u - raw)) + (warp - 2) * 32 * (Cfg::EPI_CW + 1);
+      epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row, b, tm * BM + q * 32, tn * n_tile,
+                                      min(g.N, (tn + 1) * n_tile), lane, vec_ok);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));

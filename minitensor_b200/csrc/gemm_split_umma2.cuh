@@ -44,6 +44,10 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_cluster, uin
 __device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
+// Arrival that orders nothing but the barrier itself (the caller has already fenced what matters).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
 
 template <int BK, int STAGES, int NP = 3>
 struct Gemm2Cfg {
@@ -56,7 +60,10 @@ struct Gemm2Cfg {
   static constexpr int STAGE_BYTES = NP * (A_TILE + B_TILE);  // NP planes of each operand per stage
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
   static constexpr int NUM_THREADS = 192;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int EPI_CW = 32;
+  static constexpr int EPI_BYTES = 4 * 32 * (EPI_CW + 1) * 4;  // epilogue staging, see epilogue_warp_tile
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_BYTES;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
   static_assert(ROW_BYTES == 64 || ROW_BYTES == 128, "BK must be 32 or 64");
 };
 
@@ -225,52 +232,13 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
         break;
       }
       tc_fence_after();
-      const int row = tm * Cfg::TILE_M + int(rank) * Cfg::BM + q * 32 + lane;
-      const bool row_ok = row < g.M;
-      float* crow = g.C + b * g.strideC + static_cast<long long>(row) * g.ldc;
-      const float* arow = g.aux ? g.aux + b * g.strideC + static_cast<long long>(row) * g.ldc : nullptr;
-      const float row_bias = (g.bias && g.bias_per_row && row_ok) ? __ldg(g.bias + row) : 0.0f;
-      // fp16 mode: undo the operand scalings, C = acc * 2^(ea[row] + eb[col])
-      const int* eb = g.exp_b ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) : nullptr;
-      const int ea = (g.exp_a && row_ok) ? __ldg(g.exp_a + (g.a_batched ? static_cast<long long>(b) * g.M : 0) + row) : 0;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::TILE_N;
-#pragma unroll 1
-      for (int c0 = 0; c0 < Cfg::TILE_N; c0 += 32) {
-        const int col0 = tn * Cfg::TILE_N + c0;
-        if (col0 >= g.N) break;
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c0, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int col = col0 + j;
-            if (col >= g.N) break;
-            float o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float x = __uint_as_float(v[j + e]);
-              if (col + e < g.N) {
-                if (eb) x = ldexpf(x, ea + __ldg(eb + col + e));
-                if (g.bias) x += g.bias_per_row ? row_bias : __ldg(g.bias + col + e);
-                const float ax = (g.epilogue == EPI_RELU_BWD) ? arow[col + e] : 0.0f;
-                x = apply_epilogue(x, g.epilogue, ax);
-              }
-              o[e] = x;
-            }
-            if (vec_ok && col + 3 < g.N) {
-              *reinterpret_cast<float4*>(crow + col) = make_float4(o[0], o[1], o[2], o[3]);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (col + e < g.N) crow[col + e] = o[e];
-            }
-          }
-        }
-      }
+      float* stage = reinterpret_cast<float*>(smem_raw + (bars + 256u - raw)) + (warp - 2) * 32 * (Cfg::EPI_CW + 1);
+      epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row, b, tm * Cfg::TILE_M + int(rank) * Cfg::BM + q * 32,
+                                      tn * Cfg::TILE_N, min(g.N, (tn + 1) * Cfg::TILE_N), lane, vec_ok);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(acc_empty_bar(acc), 0));
+      if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(acc_empty_bar(acc), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   }
