@@ -64,6 +64,29 @@ struct GemmArgs {
   int cv_sgn;          // +1 forward (origin + tap), -1 data gradient (origin - tap)
 };
 
+// x * 2^e for any integer e in [-380, 380], as two multiplications by exactly representable powers
+// of two (ldexpf costs ~10x more and sits in the innermost epilogue loop of the fp16 mode).  Exact
+// whenever the result is a normal number or zero; a subnormal result may be off by one subnormal step.
+__device__ __forceinline__ float scale_pow2(float x, int e) {
+  const int e1 = max(-126, min(127, e));
+  const int e2 = max(-126, min(127, e - e1));
+  return x * __int_as_float((e1 + 127) << 23) * __int_as_float((e2 + 127) << 23);
+}
+
+// Compile-time form: the runtime switch below is if-converted by the compiler into "compute every
+// branch, then select", which costs an erff and a tanhf per output element whatever the epilogue.
+template <int EPI>
+__device__ __forceinline__ float apply_epilogue_t(float x, float aux) {
+  if constexpr (EPI == EPI_RELU) return (x != x) ? x : (x > 0.0f ? x : 0.0f);
+  else if constexpr (EPI == EPI_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+  else if constexpr (EPI == EPI_GELU_TANH) {
+    const float c = 0.7978845608028654f;  // sqrt(2/pi)
+    const float x3 = x * x * x;
+    return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x3)));
+  } else if constexpr (EPI == EPI_RELU_BWD) return x * (aux > 0.0f ? 1.0f : 0.0f);
+  else return x;
+}
+
 __device__ __forceinline__ float apply_epilogue(float x, int epi, float aux) {
   switch (epi) {
     case EPI_RELU:
@@ -106,18 +129,19 @@ __device__ __forceinline__ int split_pairs(int mode, uint8_t (&pairs)[9]) {
 //   stage      : this warp's [32][CW + 1] floats of shared memory
 //   t_row      : TMEM address of (first lane of this warp, first column of the accumulator)
 //   row0       : global row of lane 0;  col_base / col_end: global column range of the tile
-template <int CW>
-__device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* stage, uint32_t t_row, int b, int row0,
-                                                   int col_base, int col_end, int lane, bool vec_ok) {
+// EPI and SCALED are compile-time so that only the work an output needs is generated.
+template <int CW, int EPI, bool SCALED>
+__device__ __forceinline__ void epilogue_warp_tile_t(const GemmArgs& g, float* stage, uint32_t t_row, int b, int row0,
+                                                  int col_base, int col_end, int lane, bool vec_ok) {
   constexpr int LPR = CW / 4;        // lanes per row when reading back
   constexpr int RPI = 32 / LPR;      // rows per store instruction
   constexpr int PITCH = CW + 1;
   const int my_row = row0 + lane;
   const bool my_row_ok = my_row < g.M;
   const float row_bias_own = (g.bias && g.bias_per_row && my_row_ok) ? __ldg(g.bias + my_row) : 0.0f;
-  const int* eb = g.exp_b ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) : nullptr;
+  const int* eb = SCALED ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) : nullptr;
   const int ea_own =
-      (g.exp_a && my_row_ok) ? __ldg(g.exp_a + (g.a_batched ? static_cast<long long>(b) * g.M : 0) + my_row) : 0;
+      (SCALED && my_row_ok) ? __ldg(g.exp_a + (g.a_batched ? static_cast<long long>(b) * g.M : 0) + my_row) : 0;
   float* cbase = g.C + b * g.strideC;
   const float* abase = g.aux ? g.aux + b * g.strideC : nullptr;
   const int cq = (lane % LPR) * 4, rsub = lane / LPR;
@@ -137,7 +161,7 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* sta
     for (int e = 0; e < 4; ++e) {
       const bool ok = col + e < col_end;
       cb[e] = (g.bias && !g.bias_per_row && ok) ? __ldg(g.bias + col + e) : 0.0f;
-      ce[e] = (eb && ok) ? __ldg(eb + col + e) : 0;
+      ce[e] = (SCALED && ok) ? __ldg(eb + col + e) : 0;
     }
 #pragma unroll
     for (int it = 0; it < LPR; ++it) {
@@ -149,7 +173,7 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* sta
         float* cptr = cbase + static_cast<long long>(grow) * g.ldc + col;
         const bool full = vec_ok && col + 3 < col_end && ((col & 3) == 0);
         float ax[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (g.epilogue == EPI_RELU_BWD) {
+        if constexpr (EPI == EPI_RELU_BWD) {
           const float* aptr = abase + static_cast<long long>(grow) * g.ldc + col;
           if (full) {
             const float4 a4 = *reinterpret_cast<const float4*>(aptr);
@@ -164,9 +188,9 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* sta
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float x = stage[r * PITCH + cq + e];
-          if (eb) x = ldexpf(x, ea_r + ce[e]);
+          if constexpr (SCALED) x = scale_pow2(x, ea_r + ce[e]);
           if (g.bias) x += g.bias_per_row ? rb : cb[e];
-          o[e] = apply_epilogue(x, g.epilogue, ax[e]);
+          o[e] = apply_epilogue_t<EPI>(x, ax[e]);
         }
         if (full) {
           *reinterpret_cast<float4*>(cptr) = make_float4(o[0], o[1], o[2], o[3]);
@@ -179,6 +203,26 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* sta
     }
     __syncwarp();  // the tile is rewritten by the next column group
   }
+}
+
+template <int CW>
+__device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* stage, uint32_t t_row, int b, int row0,
+                                                   int col_base, int col_end, int lane, bool vec_ok) {
+#define MTB_EPI_CASE(E)                                                                                         \
+  case E:                                                                                                       \
+    if (g.exp_b) epilogue_warp_tile_t<CW, E, true>(g, stage, t_row, b, row0, col_base, col_end, lane, vec_ok);  \
+    else epilogue_warp_tile_t<CW, E, false>(g, stage, t_row, b, row0, col_base, col_end, lane, vec_ok);         \
+    break;
+  switch (g.epilogue) {
+    MTB_EPI_CASE(EPI_RELU)
+    MTB_EPI_CASE(EPI_GELU_ERF)
+    MTB_EPI_CASE(EPI_GELU_TANH)
+    MTB_EPI_CASE(EPI_RELU_BWD)
+    default:
+      if (g.exp_b) epilogue_warp_tile_t<CW, EPI_NONE, true>(g, stage, t_row, b, row0, col_base, col_end, lane, vec_ok);
+      else epilogue_warp_tile_t<CW, EPI_NONE, false>(g, stage, t_row, b, row0, col_base, col_end, lane, vec_ok);
+  }
+#undef MTB_EPI_CASE
 }
 
 template <int BN, int BK, int STAGES>
