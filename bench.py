@@ -352,6 +352,10 @@ def run_case(args):
         a, b = rnd(4096, 4096), rnd(4096, 4096)
         out = torch.empty(4096, 4096, device=dev)
         fn = lambda: be.gemm(a, b, out=out)
+    elif name == "gemm_f32_tall":       # a dense layer's shape at 1/4 of the large MLP's batch: 13.8 waves of tiles
+        a, b = rnd(16384, 4096), rnd(4096, 4096)
+        out = torch.empty(16384, 4096, device=dev)
+        fn = lambda: be.gemm(a, b, trans_b=True, out=out)
     elif name == "gemm_f32_nt_tn":      # the two products of MatMulBackward at 2048
         a, b, dy = rnd(2048, 2048), rnd(2048, 2048), rnd(2048, 2048)
         fn = lambda: (be.gemm(dy, b, trans_b=True), be.gemm(a, dy, trans_a=True))

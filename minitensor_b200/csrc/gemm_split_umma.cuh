@@ -120,6 +120,38 @@ __device__ __forceinline__ int split_pairs(int mode, uint8_t (&pairs)[9]) {
   pairs[3] = (0 << 2) | 1; pairs[4] = (1 << 2) | 0; pairs[5] = 0; return 6;
 }
 
+// The same schedule as a compile-time function of (number of products, position), for issue loops
+// that are unrolled completely: the issuing thread then spends one add per descriptor instead of
+// a table lookup and a descriptor build per product.  3 products serve both two-plane modes.
+__host__ __device__ constexpr int split_pair_at(int npairs, int p) {
+  if (npairs == 1) return 0;
+  if (npairs == 3) return p == 0 ? ((0 << 2) | 1) : (p == 1 ? ((1 << 2) | 0) : 0);
+  if (npairs == 9) {
+    switch (p) {
+      case 0: return (2 << 2) | 2;
+      case 1: return (1 << 2) | 2;
+      case 2: return (2 << 2) | 1;
+      case 3: return (0 << 2) | 2;
+      case 4: return (2 << 2) | 0;
+      case 5: return (1 << 2) | 1;
+      case 6: return (0 << 2) | 1;
+      case 7: return (1 << 2) | 0;
+      default: return 0;
+    }
+  }
+  switch (p) {
+    case 0: return (0 << 2) | 2;
+    case 1: return (2 << 2) | 0;
+    case 2: return (1 << 2) | 1;
+    case 3: return (0 << 2) | 1;
+    case 4: return (1 << 2) | 0;
+    default: return 0;
+  }
+}
+__host__ __device__ constexpr int split_pair_count(int mode) {
+  return mode == 1 ? 1 : ((mode == 3 || mode == 23) ? 3 : (mode == 9 ? 9 : 6));
+}
+
 // Epilogue of one warp for one accumulator: 32 rows (one per lane in tensor memory) x `ncols`
 // columns.  tcgen05.ld hands every lane CW consecutive columns of ITS row, which written to
 // global memory directly would make each store instruction touch 32 different rows (32 partial

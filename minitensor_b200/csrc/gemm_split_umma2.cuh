@@ -17,6 +17,7 @@
 //   acc_empty[a] leader only, 8 arrivals (4 epilogue warps of each CTA)
 // No load here uses a cluster broadcast; every CTA fetches its own tiles.
 #pragma once
+#include <type_traits>
 #include "gemm_split_umma.cuh"
 
 namespace mtb {
@@ -167,54 +168,65 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      uint8_t pairs[9];
-      const int npairs = split_pairs(g.mode, pairs);
       const uint32_t idesc = make_idesc(Cfg::TILE_M, Cfg::TILE_N, g.mode == 23 ? 0u /*f16*/ : 1u /*bf16*/, 1u,
                                         A_MN ? 1u : 0u, B_MN ? 1u : 0u);
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_word)) {
-          *abort_word = 1;
-          atomicMax(g.status, 0x200u | 3u);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * Cfg::TILE_N;
-        uint32_t accumulate = 0;
-        for (int kb = 0; kb < g.num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+      // The whole issue loop, with the product schedule known at compile time: per product the
+      // thread adds a constant to each operand's descriptor and issues the MMA.
+      auto issue_all = [&](auto npairs_tag) {
+        constexpr int NPAIRS = decltype(npairs_tag)::value;
+        // one MMA covers 16 k: 32 bytes along a K-major row, 16 rows of 128 bytes in an MN-major chunk
+        constexpr uint32_t A_KSTEP = A_MN ? 2048u : 32u, B_KSTEP = B_MN ? 2048u : 32u;
+        int stage = 0, acc = 0;
+        uint32_t phase = 0, acc_phase = 0;
+        for (int t = pair; t < num_tiles; t += num_pairs) {
+          if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_word)) {
             *abort_word = 1;
-            atomicMax(g.status, 0x200u | 4u);
-            ok = false;
-            break;
+            atomicMax(g.status, 0x200u | 3u);
+            return;
           }
           tc_fence_after();
-          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + NP * Cfg::A_TILE;
-#pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            for (int p = 0; p < npairs; ++p) {
-              const int i = pairs[p] >> 2, j = pairs[p] & 3;
-              // one MMA covers 16 k: 32 bytes along a K-major row, 16 rows of 128 bytes in an MN-major chunk
-              const uint64_t da = A_MN ? make_mnmajor_desc(sa + i * Cfg::A_TILE + kk * 2048, BK * 128)
-                                       : make_kmajor_desc<Cfg::ROW_BYTES>(sa + i * Cfg::A_TILE + kk * 32);
-              const uint64_t db = B_MN ? make_mnmajor_desc(sb + j * Cfg::B_TILE + kk * 2048, BK * 128)
-                                       : make_kmajor_desc<Cfg::ROW_BYTES>(sb + j * Cfg::B_TILE + kk * 32);
-              umma_f16<2>(d_tmem, da, db, idesc, accumulate);
-              accumulate = 1;
+          const uint32_t d_tmem = tmem_base + acc * Cfg::TILE_N;
+          uint32_t accumulate = 0;
+          for (int kb = 0; kb < g.num_kb; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+              *abort_word = 1;
+              atomicMax(g.status, 0x200u | 4u);
+              return;
             }
+            tc_fence_after();
+            const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
+            const uint32_t sb = sa + NP * Cfg::A_TILE;
+            // descriptors of plane 0, k = 0; the start address sits in the low 14 bits in units of
+            // 16 bytes and shared memory ends below 2^18, so adding an offset never carries out
+            const uint64_t da0 = A_MN ? make_mnmajor_desc(sa, BK * 128) : make_kmajor_desc<Cfg::ROW_BYTES>(sa);
+            const uint64_t db0 = B_MN ? make_mnmajor_desc(sb, BK * 128) : make_kmajor_desc<Cfg::ROW_BYTES>(sb);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+#pragma unroll
+              for (int p = 0; p < NPAIRS; ++p) {
+                const int code = split_pair_at(NPAIRS, p);
+                const uint32_t offa = (code >> 2) * Cfg::A_TILE + kk * A_KSTEP;
+                const uint32_t offb = (code & 3) * Cfg::B_TILE + kk * B_KSTEP;
+                umma_f16<2>(d_tmem, da0 + (offa >> 4), db0 + (offb >> 4), idesc, accumulate);
+                accumulate = 1;
+              }
+            }
+            // the stage is free in both CTAs once these MMAs have read it
+            umma_commit<2>(empty_bar(stage));
+            umma_commit<2>(map_to_cta(empty_bar(stage), 1));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
-          // the stage is free in both CTAs once these MMAs have read it
-          umma_commit<2>(empty_bar(stage));
-          umma_commit<2>(map_to_cta(empty_bar(stage), 1));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          umma_commit<2>(acc_full_bar(acc));
+          umma_commit<2>(map_to_cta(acc_full_bar(acc), 1));
+          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
-        if (!ok) break;
-        umma_commit<2>(acc_full_bar(acc));
-        umma_commit<2>(map_to_cta(acc_full_bar(acc), 1));
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      };
+      const int npairs = split_pair_count(g.mode);
+      if (npairs == 3) issue_all(std::integral_constant<int, 3>{});
+      else if (npairs == 1) issue_all(std::integral_constant<int, 1>{});
+      else if constexpr (NP == 3) {
+        if (npairs == 9) issue_all(std::integral_constant<int, 9>{});
+        else issue_all(std::integral_constant<int, 6>{});
       }
     }
   } else {
