@@ -132,36 +132,45 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
     }
   } else if (warp == 1) {
     if (lane == 0 && has_work) {
-      uint8_t pairs[9];
-      const int npairs = split_pairs(g.mode, pairs);
       constexpr uint32_t idesc = make_idesc(Cfg::BM, Cfg::BN, 1u, 1u, 1u, 1u);  // both operands MN-major
-      int stage = 0;
-      uint32_t phase = 0, accumulate = 0;
-      bool ok = true;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!mbar_wait(full_bar(stage), phase, abort_word)) {
-          *abort_word = 1;
-          atomicMax(g.status, 0x200u | 5u);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-        const uint32_t sb = sa + 3 * Cfg::A_TILE;
-#pragma unroll
-        for (int kk = 0; kk < Cfg::BK / 16; ++kk) {
-          for (int p = 0; p < npairs; ++p) {
-            const int i = pairs[p] >> 2, j = pairs[p] & 3;
-            const uint64_t da = make_mnmajor_desc(sa + i * Cfg::A_TILE + kk * 2048, Cfg::CHUNK);
-            const uint64_t db = make_mnmajor_desc(sb + j * Cfg::B_TILE + kk * 2048, Cfg::CHUNK);
-            umma_f16<1>(tmem_base, da, db, idesc, accumulate);
-            accumulate = 1;
+      // issue loop with the product schedule known at compile time (one add per descriptor)
+      auto issue_all = [&](auto npairs_tag) {
+        constexpr int NPAIRS = decltype(npairs_tag)::value;
+        int stage = 0;
+        uint32_t phase = 0, accumulate = 0;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+            *abort_word = 1;
+            atomicMax(g.status, 0x200u | 5u);
+            return;
           }
+          tc_fence_after();
+          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
+          const uint32_t sb = sa + 3 * Cfg::A_TILE;
+          const uint64_t da0 = make_mnmajor_desc(sa, Cfg::CHUNK);
+          const uint64_t db0 = make_mnmajor_desc(sb, Cfg::CHUNK);
+#pragma unroll
+          for (int kk = 0; kk < Cfg::BK / 16; ++kk) {
+#pragma unroll
+            for (int p = 0; p < NPAIRS; ++p) {
+              const int code = split_pair_at(NPAIRS, p);
+              const uint32_t offa = (code >> 2) * Cfg::A_TILE + kk * 2048;
+              const uint32_t offb = (code & 3) * Cfg::B_TILE + kk * 2048;
+              umma_f16<1>(tmem_base, da0 + (offa >> 4), db0 + (offb >> 4), idesc, accumulate);
+              accumulate = 1;
+            }
+          }
+          umma_commit<1>(empty_bar(stage));
+          if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
         }
-        umma_commit<1>(empty_bar(stage));
-        if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+        umma_commit<1>(acc_full);
+      };
+      switch (split_pair_count(g.mode)) {
+        case 1: issue_all(std::integral_constant<int, 1>{}); break;
+        case 3: issue_all(std::integral_constant<int, 3>{}); break;
+        case 9: issue_all(std::integral_constant<int, 9>{}); break;
+        default: issue_all(std::integral_constant<int, 6>{}); break;
       }
-      if (ok) umma_commit<1>(acc_full);
     }
   } else {
     const int q = warp & 3;

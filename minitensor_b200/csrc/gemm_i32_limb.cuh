@@ -163,44 +163,51 @@ gemm_i32_limb_umma_kernel(const __grid_constant__ CUtensorMap tmapA, const __gri
     if (lane == 0) {
       // kind::i8, s32 accumulate (c format 2); operand format 0 = unsigned, 1 = signed bytes
       const uint32_t idesc = make_idesc(Cfg::BM, Cfg::BN, narrow ? 1u : 0u, 2u);
-      int stage = 0;
-      uint32_t phase = 0, tile_phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(acc_empty, tile_phase ^ 1u, abort_word)) {
-          *abort_word = 1;
-          atomicMax(g.status, 0x200u | 7u);
-          break;
-        }
-        tc_fence_after();
-        uint32_t started = 0;  // bit c set once accumulator c holds a value
-        for (int kb = 0; kb < g.num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+      // issue loop with the limb count known at compile time: one add per descriptor per product
+      auto issue_all = [&](auto nlimb_tag) {
+        constexpr int NLIMB = decltype(nlimb_tag)::value;
+        int stage = 0;
+        uint32_t phase = 0, tile_phase = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+          if (!mbar_wait(acc_empty, tile_phase ^ 1u, abort_word)) {
             *abort_word = 1;
-            atomicMax(g.status, 0x200u | 8u);
-            ok = false;
-            break;
+            atomicMax(g.status, 0x200u | 7u);
+            return;
           }
           tc_fence_after();
-          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + 4 * Cfg::TILE;
+          uint32_t first = 0;  // 0 for the tile's first K block: every accumulator starts from zero there
+          for (int kb = 0; kb < g.num_kb; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+              *abort_word = 1;
+              atomicMax(g.status, 0x200u | 8u);
+              return;
+            }
+            tc_fence_after();
+            const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES, sb = sa + 4 * Cfg::TILE;
+            const uint64_t da0 = make_kmajor_desc<Cfg::BKB>(sa), db0 = make_kmajor_desc<Cfg::BKB>(sb);
 #pragma unroll
-          for (int kk = 0; kk < Cfg::BKB / 32; ++kk) {
-            for (int i = 0; i < nlimb; ++i)
-              for (int j = 0; i + j < nlimb; ++j) {
-                const int c = i + j;
-                const uint64_t da = make_kmajor_desc<Cfg::BKB>(sa + i * Cfg::TILE + kk * 32);
-                const uint64_t db = make_kmajor_desc<Cfg::BKB>(sb + j * Cfg::TILE + kk * 32);
-                umma_i8<1>(tmem_base + c * Cfg::BN, da, db, idesc, (started >> c) & 1u);
-                started |= 1u << c;
-              }
+            for (int kk = 0; kk < Cfg::BKB / 32; ++kk) {
+#pragma unroll
+              for (int i = 0; i < NLIMB; ++i)
+#pragma unroll
+                for (int j = 0; i + j < NLIMB; ++j) {
+                  const int c = i + j;
+                  // accumulator c is first written by (kk = 0, i = 0, j = c)
+                  const uint32_t accumulate = (kk == 0 && i == 0) ? first : 1u;
+                  umma_i8<1>(tmem_base + c * Cfg::BN, da0 + ((i * Cfg::TILE + kk * 32) >> 4),
+                             db0 + ((j * Cfg::TILE + kk * 32) >> 4), idesc, accumulate);
+                }
+            }
+            first = 1u;
+            umma_commit<1>(empty_bar(stage));
+            if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
           }
-          umma_commit<1>(empty_bar(stage));
-          if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+          umma_commit<1>(acc_full);
+          tile_phase ^= 1u;
         }
-        if (!ok) break;
-        umma_commit<1>(acc_full);
-        tile_phase ^= 1u;
-      }
+      };
+      if (nlimb == 1) issue_all(std::integral_constant<int, 1>{});
+      else issue_all(std::integral_constant<int, 4>{});
     }
   } else {
     const int q = warp & 3;

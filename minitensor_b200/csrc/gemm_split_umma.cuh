@@ -20,6 +20,7 @@
 // Two accumulators live in TMEM so the epilogue of tile i overlaps the main
 // loop of tile i+1.
 #pragma once
+#include <type_traits>
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
 
@@ -388,49 +389,58 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      uint8_t pairs[9];
-      const int npairs = split_pairs(g.mode, pairs);
       const uint32_t idesc = make_idesc(BM, CONV ? g.cv_umma_n : BN, /*bf16*/ 1u, /*f32*/ 1u);
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_word)) {
-          *abort_word = 1;
-          atomicMax(g.status, 0x200u | 1u);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_COLS;
-        uint32_t accumulate = 0;
-        for (int kb = 0; kb < g.num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+      // The whole issue loop with the product schedule known at compile time: per product the
+      // thread adds a constant to each operand's descriptor and issues the MMA.
+      auto issue_all = [&](auto npairs_tag) {
+        constexpr int NPAIRS = decltype(npairs_tag)::value;
+        int stage = 0, acc = 0;
+        uint32_t phase = 0, acc_phase = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+          if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_word)) {
             *abort_word = 1;
-            atomicMax(g.status, 0x200u | 2u);
-            ok = false;
-            break;
+            atomicMax(g.status, 0x200u | 1u);
+            return;
           }
           tc_fence_after();
-          const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + 3 * Cfg::A_TILE;
-#pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            for (int p = 0; p < npairs; ++p) {
-              const int i = pairs[p] >> 2, j = pairs[p] & 3;
-              const uint64_t da = make_kmajor_desc<Cfg::ROW_BYTES>(sa + i * Cfg::A_TILE + kk * 32);
-              const uint64_t db = make_kmajor_desc<Cfg::ROW_BYTES>(sb + j * Cfg::B_TILE + kk * 32);
-              umma_f16<1>(d_tmem, da, db, idesc, accumulate);
-              accumulate = 1;
+          const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_COLS;
+          uint32_t accumulate = 0;
+          for (int kb = 0; kb < g.num_kb; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_word)) {
+              *abort_word = 1;
+              atomicMax(g.status, 0x200u | 2u);
+              return;
             }
+            tc_fence_after();
+            const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
+            const uint32_t sb = sa + 3 * Cfg::A_TILE;
+            // descriptors of plane 0, k = 0; the start address sits in the low 14 bits in units of
+            // 16 bytes and shared memory ends below 2^18, so adding an offset never carries out
+            const uint64_t da0 = make_kmajor_desc<Cfg::ROW_BYTES>(sa);
+            const uint64_t db0 = make_kmajor_desc<Cfg::ROW_BYTES>(sb);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+#pragma unroll
+              for (int p = 0; p < NPAIRS; ++p) {
+                const int code = split_pair_at(NPAIRS, p);
+                const uint32_t offa = (code >> 2) * Cfg::A_TILE + kk * 32;
+                const uint32_t offb = (code & 3) * Cfg::B_TILE + kk * 32;
+                umma_f16<1>(d_tmem, da0 + (offa >> 4), db0 + (offb >> 4), idesc, accumulate);
+                accumulate = 1;
+              }
+            }
+            umma_commit<1>(empty_bar(stage));  // stage reusable once these MMAs have read it
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
-          umma_commit<1>(empty_bar(stage));  // stage reusable once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          umma_commit<1>(acc_full_bar(acc));  // accumulator complete
+          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
-        if (!ok) break;
-        umma_commit<1>(acc_full_bar(acc));  // accumulator complete
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      };
+      switch (split_pair_count(g.mode)) {
+        case 1: issue_all(std::integral_constant<int, 1>{}); break;
+        case 3: issue_all(std::integral_constant<int, 3>{}); break;
+        case 9: issue_all(std::integral_constant<int, 9>{}); break;
+        default: issue_all(std::integral_constant<int, 6>{}); break;
       }
     }
   } else {
