@@ -192,7 +192,7 @@ def gemm4096(be, torch, peaks):
             "peak_tflops": peak, "peak_3xtf32_emulated_tflops": peak_3xtf32, "f32_mode": "f16x3",
             "peak_def": "measured 16-bit dense tensor burst (cuBLAS bf16) / 3 products per f32 product; the "
                         "3xTF32-emulated peak is the same burst / 6",
-            "dram_traffic_mb_per_launch": 336.2, "algorithmic_mb_per_launch": 201.3}
+            "dram_traffic_mb_per_launch": 348.6, "algorithmic_mb_per_launch": 201.3}
 
 
 def run_ours(args):
@@ -308,15 +308,19 @@ def run_ours(args):
                 "d2h_bytes_per_step": 4, "note": "next batch's host->device copy overlaps the current step"},
         "gpu_launches": gpu_launches,
         "roofline": {
-            "kernel": "gemm_split_umma_kernel", "bound": "tensor", "achieved": achieved, "peak": peak_f32,
+            "kernel": "gemm_split_umma2_kernel", "bound": "tensor", "achieved": achieved, "peak": peak_f32,
             "unit": "TFLOP/s", "frac": (achieved / peak_f32) if achieved else None,
             "peak_def": f"{peaks['source']} 16-bit dense tensor sustained {peaks['bf16_sustained']} TFLOP/s / 3 "
                         "(three fp16 tensor products per f32 product); a 3xTF32 emulation's roofline is half of this",
             "launches": k_launches, "avg_launch_ms": k_ms / k_launches if k_launches else None,
             "share_of_step": k_ms / ms_total if ms_total else None,
-            # DRAM bytes per launch: ncu cannot capture the step's 3-6 GB GEMMs under the capture size rule;
-            # the 4096^3 capture of the same kernel moved 1.67x its algorithmic bytes (336 MB vs 201 MB)
-            "traffic": None, "traffic_note": "see gemm_f32_4096.dram_traffic_mb_per_launch (ncu, 4096^3 case)",
+            # DRAM bytes per launch: the step's GEMMs hold 3-6 GB each, above the ncu capture size rule, so the
+            # figure is the ncu capture of the same kernel on 16384x4096x4096 (1.511 GB read + written for
+            # 549.8 GFLOP) scaled by the flops of an average launch of this step (traffic per flop is set by the
+            # tile shape and the walk order, which are the same)
+            "traffic": (1.511e9 * (mlp_flops_per_sample(DIMS) * rows / 11) / 549.8e9),
+            "traffic_note": "bytes per average launch, scaled by flops from the ncu capture of the same kernel on "
+                            "16384x4096x4096 (profiles/gemm_split_umma2_f32_4096.md)",
             "split_kernels": {"launches": s_launches, "ms": s_ms, "gbs": s_bytes / s_ms / 1e6 if s_ms else None,
                               "share_of_step": s_ms / ms_total if ms_total else None},
         },
