@@ -216,7 +216,8 @@ def run_ours(args):
     peaks = _peaks()
     lo, hi = shard_rows(GLOBAL_BATCH, world, rank)
     rows = hi - lo
-    trainer = MLPTrainer(DIMS, rows, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, device=local, world_size=world, seed=0)
+    trainer = MLPTrainer(DIMS, rows, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, device=local, world_size=world, seed=0,
+                         fused_dense=not args.per_product)
     be = trainer.be
     dev = be.device
 
@@ -360,6 +361,13 @@ def run_case(args):
         a, b = rnd(16384, 4096), rnd(4096, 4096)
         out = torch.empty(16384, 4096, device=dev)
         fn = lambda: be.gemm(a, b, trans_b=True, out=out)
+    elif name == "dense_pair":          # dense layer forward + backward with shared operand preparation
+        x, w, b, dy = rnd(16384, 4096), rnd(4096, 4096), rnd(4096), rnd(16384, 4096)
+        saved = torch.empty(be.dense_saved_bytes(16384, 4096, 4096), dtype=torch.uint8, device=dev)
+        y, dx = torch.empty(16384, 4096, device=dev), torch.empty(16384, 4096, device=dev)
+        dw, db = torch.empty(4096, 4096, device=dev), torch.empty(4096, device=dev)
+        fn = lambda: (be.dense_forward(x, w, b, 1, out=y, saved=saved),
+                      be.dense_backward(x, w, dy, saved, dx=dx, dx_epilogue=4, dx_aux=x, dw=dw, db=db))
     elif name == "gemm_f32_nt_tn":      # the two products of MatMulBackward at 2048
         a, b, dy = rnd(2048, 2048), rnd(2048, 2048), rnd(2048, 2048)
         fn = lambda: (be.gemm(dy, b, trans_b=True), be.gemm(a, dy, trans_a=True))
@@ -414,6 +422,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--per-product", action="store_true",
+                    help="one GEMM call per product (as the reference's autograd issues them) instead of the dense-layer pair")
     ap.add_argument("--case", default=None, help="run one small fixed workload (profiling target) and exit")
     ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()

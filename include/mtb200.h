@@ -127,6 +127,35 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
                     void* C, int64_t stride_c, const void* bias, int32_t epilogue,
                     const void* aux, int32_t f32_mode);
 
+/* ---- dense layer as one call per direction (f32 / f64)
+ * forward:  y[rows][out] = epilogue(x[rows][in] * W[out][in]^T + bias[out])
+ *           DenseLayer::forward = transpose + matmul + add (engine/src/nn/dense_layer.rs:139-169)
+ * backward: dX[rows][in] = dx_epilogue(dY * W)   (skipped when dX is NULL: input without requires_grad,
+ *                                                 engine/src/autograd/mod/core.rs:763)
+ *           dW[out][in]  = dY^T * x
+ *           db[out]      = column sums of dY      (skipped when db is NULL)
+ *           MatMulBackward (engine/src/autograd/mod/core.rs:743-789), the transpose's backward and the
+ *           broadcast reduction of AddBackward (core.rs:195-223).
+ * Same results as the corresponding mtb200_gemm / mtb200_colsum calls to within the f32 mode's
+ * tolerance.  What the pair adds is shared operand preparation: the forward call leaves the tensor-core
+ * form of x and W (two fp16 planes and one power-of-two exponent per row) in `saved`, a caller-owned
+ * block of mtb200_dense_saved_bytes() bytes from mtb200_alloc, and the backward call multiplies
+ * against those planes as they lie, folding their row scales into dY, whose maxima, column sums and
+ * both plane sets come from two passes over dY.  x, W and `saved` must be unchanged between the two
+ * calls.  `saved` may be NULL (and is ignored when mtb200_dense_saved_bytes reports 0: f64, or a
+ * dimension of 128 or less): both calls then run as plain products.
+ * forward `epilogue`/`aux` as in mtb200_gemm (NONE / RELU / GELU_*); backward `dx_epilogue` is NONE or
+ * RELU_BWD with `dx_aux` = the previous layer's activation output [rows][in]. */
+int32_t mtb200_dense_saved_bytes(int32_t dtype, int64_t rows, int64_t in_features, int64_t out_features,
+                                 size_t* bytes);
+int32_t mtb200_dense_forward(mtb200_handle h, int32_t dtype, int64_t rows, int64_t in_features,
+                             int64_t out_features, const void* x, const void* W, const void* bias,
+                             int32_t epilogue, void* y, void* saved);
+int32_t mtb200_dense_backward(mtb200_handle h, int32_t dtype, int64_t rows, int64_t in_features,
+                              int64_t out_features, const void* x, const void* W, const void* dY,
+                              const void* saved, void* dX, int32_t dx_epilogue, const void* dx_aux,
+                              void* dW, void* db);
+
 /* ---- bias gradient: out[n] = sum_m X[m][n]  (f32 / f64)
  * reduce_gradient_for_broadcasting -> sum over dim 0
  * (engine/src/autograd/mod/tests.rs:8-68, engine/src/operations/reduction/sum_prod.rs:7-84).

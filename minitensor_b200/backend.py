@@ -126,6 +126,53 @@ class Backend:
         self.launches += 4 if dt == F32 else 1  # two operand splits, GEMM, gated f32 redo
         return out
 
+    # ------------------------------------------------------------------ dense layer (shared operand preparation)
+    def dense_saved_bytes(self, rows: int, in_features: int, out_features: int, dtype=torch.float32) -> int:
+        """Bytes of the block ``dense_forward`` leaves for ``dense_backward`` (0: the pair runs as plain products)."""
+        n = C.c_size_t(0)
+        code = dtype_code(torch.empty(0, dtype=dtype))
+        check(self.lib.mtb200_dense_saved_bytes(code, rows, in_features, out_features, C.byref(n)))
+        return int(n.value)
+
+    def dense_forward(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                      epilogue: int = EPI_NONE, out: Optional[torch.Tensor] = None,
+                      saved: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``epilogue(x @ w.T + bias)`` for ``x [rows, in]``, ``w [out, in]``; ``saved`` (uint8, device) receives
+        the prepared operands for ``dense_backward``."""
+        rows, fin = x.shape
+        fout = w.shape[0]
+        if w.shape[1] != fin or x.dtype != w.dtype:
+            raise ValueError(f"shape/dtype mismatch: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}")
+        if out is None:
+            out = torch.empty(rows, fout, dtype=x.dtype, device=x.device)
+        self._bind_stream()
+        check(self.lib.mtb200_dense_forward(self._h, dtype_code(x), rows, fin, fout, _ptr(x), _ptr(w), _ptr(bias),
+                                            epilogue, _ptr(out), _ptr(saved)))
+        self.launches += 5 if saved is not None else 4
+        return out
+
+    def dense_backward(self, x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, saved: Optional[torch.Tensor], *,
+                       dx: Optional[torch.Tensor] = None, need_dx: bool = True, dx_epilogue: int = EPI_NONE,
+                       dx_aux: Optional[torch.Tensor] = None, dw: Optional[torch.Tensor] = None,
+                       db: Optional[torch.Tensor] = None, need_db: bool = True):
+        """Gradients of ``dense_forward``: returns ``(dx or None, dw, db or None)``."""
+        rows, fin = x.shape
+        fout = w.shape[0]
+        if tuple(dy.shape) != (rows, fout):
+            raise ValueError(f"dy must be [{rows}, {fout}], got {tuple(dy.shape)}")
+        if need_dx and dx is None:
+            dx = torch.empty(rows, fin, dtype=x.dtype, device=x.device)
+        if dw is None:
+            dw = torch.empty(fout, fin, dtype=x.dtype, device=x.device)
+        if need_db and db is None:
+            db = torch.empty(fout, dtype=x.dtype, device=x.device)
+        self._bind_stream()
+        check(self.lib.mtb200_dense_backward(self._h, dtype_code(x), rows, fin, fout, _ptr(x), _ptr(w), _ptr(dy),
+                                             _ptr(saved), _ptr(dx) if need_dx else None, dx_epilogue, _ptr(dx_aux),
+                                             _ptr(dw), _ptr(db) if need_db else None))
+        self.launches += (9 if need_dx else 7) if saved is not None else (10 if need_dx else 6)
+        return (dx if need_dx else None), dw, (db if need_db else None)
+
     # ------------------------------------------------------------------ reductions / elementwise
     def colsum(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         m, n = x.shape

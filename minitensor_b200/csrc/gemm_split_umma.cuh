@@ -22,6 +22,7 @@
 #pragma once
 #include <type_traits>
 #include "ptx_sm100.cuh"
+#include "split_bf16.cuh"
 #include <cuda_bf16.h>
 
 namespace mtb {
@@ -64,15 +65,6 @@ struct GemmArgs {
   int cv_w0, cv_h0;    // window origin for tap (0,0): -pad (forward) or +pad (data gradient)
   int cv_sgn;          // +1 forward (origin + tap), -1 data gradient (origin - tap)
 };
-
-// x * 2^e for any integer e in [-380, 380], as two multiplications by exactly representable powers
-// of two (ldexpf costs ~10x more and sits in the innermost epilogue loop of the fp16 mode).  Exact
-// whenever the result is a normal number or zero; a subnormal result may be off by one subnormal step.
-__device__ __forceinline__ float scale_pow2(float x, int e) {
-  const int e1 = max(-126, min(127, e));
-  const int e2 = max(-126, min(127, e - e1));
-  return x * __int_as_float((e1 + 127) << 23) * __int_as_float((e2 + 127) << 23);
-}
 
 // Compile-time form: the runtime switch below is if-converted by the compiler into "compute every
 // branch, then select", which costs an erff and a tanhf per output element whatever the epilogue.

@@ -8,6 +8,7 @@
 #include "rowcol_kernels.cuh"
 #include "gemm_launch.cuh"
 #include "gemm_i32_limb.cuh"
+#include "dense_layer.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -483,6 +484,67 @@ int32_t mtb200_colsum(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, cons
   }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
+}
+
+// ------------------------------------------------------------------ dense layer
+static bool dense_uses_saved(int32_t dtype, int64_t rows, int64_t in, int64_t out) {
+  return dtype == MTB200_F32 && dense_fused_shapes(rows, in, out) && rows <= INT32_MAX && in <= INT32_MAX &&
+         out <= INT32_MAX;
+}
+
+int32_t mtb200_dense_saved_bytes(int32_t dtype, int64_t rows, int64_t in_features, int64_t out_features,
+                                 size_t* bytes) {
+  if (!bytes) return fail(MTB200_ERR_INVALID, "null output pointer");
+  if (dtype != MTB200_F32 && dtype != MTB200_F64) return fail(MTB200_ERR_UNSUPPORTED, "dense layer: dtype must be f32 or f64");
+  if (rows < 0 || in_features < 0 || out_features < 0) return fail(MTB200_ERR_INVALID, "negative dimension");
+  *bytes = dense_uses_saved(dtype, rows, in_features, out_features)
+               ? dense_saved_layout(rows, in_features, out_features).total
+               : 0;
+  return MTB200_OK;
+}
+
+int32_t mtb200_dense_forward(mtb200_handle h, int32_t dtype, int64_t rows, int64_t in_features,
+                             int64_t out_features, const void* x, const void* W, const void* bias,
+                             int32_t epilogue, void* y, void* saved) {
+  MTB_CHECK_HANDLE(h);
+  if (dtype != MTB200_F32 && dtype != MTB200_F64) return fail(MTB200_ERR_UNSUPPORTED, "dense layer: dtype must be f32 or f64");
+  if (epilogue < 0 || epilogue > MTB200_EPI_GELU_TANH)
+    return fail(MTB200_ERR_INVALID, "dense forward epilogue must be NONE, RELU or GELU");
+  if (!saved || !dense_uses_saved(dtype, rows, in_features, out_features))
+    return mtb200_gemm(h, dtype, 0, 1, 1, rows, out_features, in_features, x, 0, W, 0, y, 0, bias, epilogue, nullptr, 0);
+  if (!x || !W || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  return dense_forward_f32(h, int(rows), int(in_features), int(out_features), static_cast<const float*>(x),
+                           static_cast<const float*>(W), static_cast<const float*>(bias), epilogue, nullptr,
+                           static_cast<float*>(y), saved);
+}
+
+int32_t mtb200_dense_backward(mtb200_handle h, int32_t dtype, int64_t rows, int64_t in_features,
+                              int64_t out_features, const void* x, const void* W, const void* dY,
+                              const void* saved, void* dX, int32_t dx_epilogue, const void* dx_aux,
+                              void* dW, void* db) {
+  MTB_CHECK_HANDLE(h);
+  if (dtype != MTB200_F32 && dtype != MTB200_F64) return fail(MTB200_ERR_UNSUPPORTED, "dense layer: dtype must be f32 or f64");
+  if (dx_epilogue != MTB200_EPI_NONE && dx_epilogue != MTB200_EPI_RELU_BWD)
+    return fail(MTB200_ERR_INVALID, "dense backward epilogue must be NONE or RELU_BWD");
+  if (dX && dx_epilogue == MTB200_EPI_RELU_BWD && !dx_aux) return fail(MTB200_ERR_INVALID, "RELU_BWD epilogue needs aux");
+  if (!dW) return fail(MTB200_ERR_INVALID, "null weight-gradient pointer");
+  if (!saved || !dense_uses_saved(dtype, rows, in_features, out_features)) {
+    int32_t rc = mtb200_gemm(h, dtype, 1, 0, 1, out_features, in_features, rows, dY, 0, x, 0, dW, 0, nullptr,
+                             MTB200_EPI_NONE, nullptr, 0);
+    if (rc) return rc;
+    if (dX) {
+      rc = mtb200_gemm(h, dtype, 0, 0, 1, rows, in_features, out_features, dY, 0, W, 0, dX, 0, nullptr, dx_epilogue,
+                       dx_aux, 0);
+      if (rc) return rc;
+    }
+    if (db) return mtb200_colsum(h, dtype, rows, out_features, dY, db);
+    return MTB200_OK;
+  }
+  if (!x || !W || !dY) return fail(MTB200_ERR_INVALID, "null pointer");
+  return dense_backward_f32(h, int(rows), int(in_features), int(out_features), static_cast<const float*>(x),
+                            static_cast<const float*>(W), static_cast<const float*>(dY), saved,
+                            static_cast<float*>(dX), dx_epilogue, static_cast<const float*>(dx_aux),
+                            static_cast<float*>(dW), static_cast<float*>(db));
 }
 
 // ------------------------------------------------------------------ activations

@@ -15,6 +15,16 @@
 
 namespace mtb {
 
+// x * 2^e for any integer e in [-380, 380], as two multiplications by exactly representable powers
+// of two (ldexpf costs ~10x more and sits in the innermost epilogue loop of the fp16 mode).  Exact
+// whenever the result is a normal number or zero; a subnormal result may be off by one subnormal step.
+__device__ __forceinline__ float scale_pow2(float x, int e) {
+  const int e1 = max(-126, min(127, e));
+  const int e2 = max(-126, min(127, e - e1));
+  return x * __int_as_float((e1 + 127) << 23) * __int_as_float((e2 + 127) << 23);
+}
+
+
 struct Split3 {
   __nv_bfloat16 s0, s1, s2;
 };

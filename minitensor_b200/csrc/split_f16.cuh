@@ -6,8 +6,8 @@
 // exact in f32).  The GEMM multiplies a0b1, a1b0, a0b0 - three fp16 tensor
 // products per f32 product, half the work of the six-product bf16 mode, with
 // the accuracy of a 3xTF32 emulation (which also keeps 22 bits and drops the
-// low x low term) - and the epilogue undoes the two scalings exactly with
-// ldexpf.  Values whose scaled magnitude falls below the fp16 subnormal step
+// low x low term) - and the epilogue undoes the two scalings exactly (two
+// multiplications by powers of two).  Values whose scaled magnitude falls below the fp16 subnormal step
 // lose at most 2^-25 of their row's scaled maximum, i.e. 2^-39 of the row's
 // largest element.
 //
@@ -39,7 +39,31 @@ __device__ __forceinline__ void split2_f16(float x, int e, __half& h0, __half& h
     h1 = __float2half_rn(0.0f);
     return;
   }
-  const float v = ldexpf(x, -e);
+  const float v = scale_pow2(x, -e);  // exact: the result is far above the f32 subnormal range or vanishes in fp16 anyway
+  h0 = __float2half_rn(v);
+  h1 = __float2half_rn(v - __half2float(h0));
+}
+
+// The same split with the scaling done on the exponent field: x * 2^s for a normal x is the bit
+// pattern of x with s added to its exponent.  Results below the smallest normal f32 are flushed to
+// zero (they are far below the fp16 planes' resolution); zeros, subnormals, Inf and NaN take the
+// general route.  s is the negated scale exponent.
+__device__ __forceinline__ void split2_f16_shift(float x, int s, __half& h0, __half& h1) {
+  const uint32_t b = __float_as_uint(x);
+  const int e = int((b >> 23) & 0xffu);
+  float v = 0.0f;
+  if (e == 255) {
+    h0 = __float2half_rn(x);
+    h1 = __float2half_rn(0.0f);
+    return;
+  }
+  if (e != 0) {
+    const int ne = e + s;
+    if (ne >= 255) v = scale_pow2(x, s);
+    else if (ne > 0) v = __uint_as_float(b + (static_cast<uint32_t>(s) << 23));
+  } else if ((b << 1) != 0u) {
+    v = scale_pow2(x, s);  // subnormal input
+  }
   h0 = __float2half_rn(v);
   h1 = __float2half_rn(v - __half2float(h0));
 }

@@ -58,8 +58,13 @@ def mlp_flops_per_sample(dims: Sequence[int]) -> int:
 class MLPTrainer:
     def __init__(self, dims: Sequence[int], batch: int, *, lr: float = 1e-3, beta1: float = 0.9,
                  beta2: float = 0.999, eps: float = 1e-8, device: int = 0, world_size: int = 1,
-                 seed: int = 0, f32_mode: int = 0, init_params: Optional[np.ndarray] = None):
-        """``batch`` is the number of rows THIS process handles per step."""
+                 seed: int = 0, f32_mode: int = 0, init_params: Optional[np.ndarray] = None,
+                 fused_dense: Optional[bool] = None):
+        """``batch`` is the number of rows THIS process handles per step.
+
+        ``fused_dense`` (default: on for the default f32 mode) runs every layer through the dense-layer
+        entry points, whose backward re-uses the operands the forward prepared; off, each product is a
+        separate GEMM call as the reference's autograd issues them."""
         if len(dims) < 2 or any(d <= 0 for d in dims) or batch <= 0:
             raise ValueError("dims needs at least two positive entries and batch must be positive")
         self.dims = [int(d) for d in dims]
@@ -68,6 +73,9 @@ class MLPTrainer:
         self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
         self.world_size = int(world_size)
         self.f32_mode = f32_mode
+        self.fused_dense = (f32_mode == 0) if fused_dense is None else bool(fused_dense)
+        if self.fused_dense and f32_mode != 0:
+            raise ValueError("fused_dense uses the default f32 mode")
         self.be: Backend = get_backend(device)
         dev = self.be.device
         self.w_off, self.b_off, total = mlp_layout(self.dims)
@@ -98,6 +106,12 @@ class MLPTrainer:
         B = self.batch
         self.h = [torch.empty(B, self.dims[l + 1], dtype=torch.float32, device=dev) for l in range(self.nl)]
         self.g = [torch.empty(B, self.dims[l + 1], dtype=torch.float32, device=dev) for l in range(self.nl)]
+        self.saved = [None] * self.nl
+        if self.fused_dense:
+            for l in range(self.nl):
+                nbytes = self.be.dense_saved_bytes(B, self.dims[l], self.dims[l + 1])
+                if nbytes:
+                    self.saved[l] = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         # double-buffered staging for batches that arrive from host memory
         self._x_dev = [None, None]
         self._y_dev = [None, None]
@@ -133,7 +147,10 @@ class MLPTrainer:
         be, a = self.be, x
         for l in range(self.nl):
             epi = EPI_RELU if l + 1 < self.nl else EPI_NONE
-            be.gemm(a, self.W[l], trans_b=True, bias=self.b[l], epilogue=epi, out=self.h[l], f32_mode=self.f32_mode)
+            if self.fused_dense:
+                be.dense_forward(a, self.W[l], self.b[l], epi, out=self.h[l], saved=self.saved[l])
+            else:
+                be.gemm(a, self.W[l], trans_b=True, bias=self.b[l], epilogue=epi, out=self.h[l], f32_mode=self.f32_mode)
             a = self.h[l]
         return a
 
@@ -149,14 +166,20 @@ class MLPTrainer:
         for l in range(self.nl - 1, -1, -1):
             g = self.g[l]
             a_in = x if l == 0 else self.h[l - 1]
-            be.colsum(g, out=self.db[l])
-            be.gemm(g, a_in, trans_a=True, out=self.dW[l], f32_mode=self.f32_mode)          # dW = g^T a
+            if self.fused_dense:
+                # db, dW = g^T a and (g W) * relu' from two passes over g and the forward pass's planes
+                be.dense_backward(a_in, self.W[l], g, self.saved[l], need_dx=l > 0, dx=self.g[l - 1] if l > 0 else None,
+                                  dx_epilogue=EPI_RELU_BWD if l > 0 else EPI_NONE, dx_aux=self.h[l - 1] if l > 0 else None,
+                                  dw=self.dW[l], db=self.db[l])
+            else:
+                be.colsum(g, out=self.db[l])
+                be.gemm(g, a_in, trans_a=True, out=self.dW[l], f32_mode=self.f32_mode)      # dW = g^T a
             if self.world_size > 1:
                 import torch.distributed as dist
                 lo = self.w_off[l]
                 hi = self.b_off[l] + self.dims[l + 1]
                 handles.append(dist.all_reduce(self.grads[lo:hi], op=dist.ReduceOp.SUM, async_op=True))
-            if l > 0:
+            if l > 0 and not self.fused_dense:
                 be.gemm(g, self.W[l], epilogue=EPI_RELU_BWD, aux=self.h[l - 1], out=self.g[l - 1],
                         f32_mode=self.f32_mode)                                            # (g W) * relu'
         for hnd in handles:
