@@ -73,7 +73,16 @@ def dense_layer(input: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *,
     be = _be()
     x2 = input._buf.reshape(-1, in_f)
     bbuf = bias._buf if bias is not None else None
-    y2 = be.gemm(x2, weight._buf, trans_b=True, bias=bbuf, epilogue=_epilogue)
+    # training: keep the prepared operands for the backward products (mtb200_dense_forward / _backward)
+    saved = None
+    if weight.requires_grad and x2.is_contiguous():
+        nbytes = be.dense_saved_bytes(x2.shape[0], in_f, out_f, x2.dtype)
+        if nbytes:
+            saved = torch.empty(nbytes, dtype=torch.uint8, device=x2.device)
+    if saved is not None:
+        y2 = be.dense_forward(x2, weight._buf, bbuf, _epilogue, saved=saved)
+    else:
+        y2 = be.gemm(x2, weight._buf, trans_b=True, bias=bbuf, epilogue=_epilogue)
     out_shape = input.shape[:-1] + (out_f,)
     parents = (input, weight) + ((bias,) if bias is not None else ())
 
@@ -83,9 +92,14 @@ def dense_layer(input: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *,
             g2 = be.act_bwd(y2, g2, EPI_RELU)
         elif _epilogue in (EPI_GELU_ERF, EPI_GELU_TANH):
             raise RuntimeError("fused GELU keeps no pre-activation; use the unfused layer for training")
+        want_b = bias is not None and bias.requires_grad
+        if saved is not None:
+            gx, gw, gb = be.dense_backward(x2, weight._buf, g2, saved, need_dx=input.requires_grad, need_db=want_b)
+            gx = gx.reshape(input.shape) if gx is not None else None
+            return (gx, gw, gb)[: len(parents)]
         gx = be.gemm(g2, weight._buf).reshape(input.shape) if input.requires_grad else None   # dX = dY W
         gw = be.gemm(g2, x2, trans_a=True) if weight.requires_grad else None                  # dW = dY^T X
-        gb = be.colsum(g2) if (bias is not None and bias.requires_grad) else None
+        gb = be.colsum(g2) if want_b else None
         return (gx, gw, gb)[: len(parents)]
 
     return input._result(y2.reshape(out_shape), parents, bw)

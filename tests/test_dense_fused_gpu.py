@@ -175,3 +175,22 @@ def test_mlp_trainer_fused_dense_matches_oracle(be, orc):
         scale = np.linalg.norm(x, axis=0).max()
         assert float(np.abs(tr1.grads.cpu().numpy().astype(np.float64) - ref_grads).max()) <= F32_TOL * scale
         assert float((tr1.grads - tr0.grads).abs().max()) <= 1e-5 * scale
+
+
+def test_nn_dense_layer_uses_the_pair_when_training(be, orc, rng):
+    """The host mirror's DenseLayer at a shape the pair serves: forward and all three gradients against the
+    oracle's reference-ordered operators."""
+    import minitensor_b200.nn as nn
+    import minitensor_b200.tensor as mt
+    layer = nn.DenseLayer(200, 260, rng=np.random.default_rng(4))
+    xn = rng.standard_normal((300, 200)).astype(np.float32)
+    x = mt.Tensor(xn, requires_grad=True)
+    y = layer(x)
+    wn, bn = layer.weight.numpy(), layer.bias.numpy()
+    assert nerr(y.numpy(), orc.dense_forward(xn, wn, bn).astype(np.float64), xn, wn.T) <= F32_TOL
+    go = rng.standard_normal((300, 260)).astype(np.float32)
+    y.backward(mt.Tensor(go))
+    gx, gwt = orc.matmul_backward(xn, np.ascontiguousarray(wn.T), go)
+    assert nerr(x.grad.numpy(), gx.astype(np.float64), go, wn) <= F32_TOL
+    assert nerr(layer.weight.grad.numpy(), gwt.T.astype(np.float64), go.T, xn) <= F32_TOL
+    np.testing.assert_allclose(layer.bias.grad.numpy(), orc.sum_dim0(go), rtol=1e-4, atol=1e-4)
