@@ -222,6 +222,53 @@ int32_t mtb200_adam_step(mtb200_handle h, int64_t n, float* param, const float* 
                          float* v, double lr, double beta1, double beta2, double eps,
                          double weight_decay, int32_t decoupled, int64_t step, float grad_scale);
 
+/* ---- cross entropy, general form (f32 logits [B,C])
+ * cross_entropy_loss (engine/src/operations/loss/regression.rs:178-251) with either kind of target it
+ * accepts - class indices [B] (target_dtype MTB200_I32 / MTB200_I64; made one-hot at :769-862) or a
+ * [B,C] float32 probability matrix (target_dtype MTB200_F32) - and its three reductions.
+ * loss: 1 float for SUM / MEAN, B floats for NONE.  dlogits (nullable) receives
+ * (softmax - target) * (MEAN ? 1/B : 1) * upstream * (upstream_rows ? upstream_rows[b] : 1)
+ * (CrossEntropyLossBackward, engine/src/autograd/mod/activation.rs:364-427; upstream_rows is the
+ * per-sample gradient of a NONE loss - the reference multiplies by grad_output through its generic
+ * broadcast, which for a [B] gradient only type-checks when B == C). */
+#define MTB200_REDUCE_SUM 0
+#define MTB200_REDUCE_MEAN 1
+#define MTB200_REDUCE_NONE 2
+int32_t mtb200_cross_entropy_ex(mtb200_handle h, int64_t B, int64_t C, const float* logits,
+                                const void* targets, int32_t target_dtype, int32_t reduction,
+                                float upstream, const float* upstream_rows, float* loss, float* dlogits);
+
+/* ---- SGD step over one flat buffer (f32 / f64), in place
+ * SGD::apply_simple_update / apply_momentum_update (engine/src/optim/sgd.rs:169-296):
+ *   g' = g + weight_decay*p;  momentum > 0: v = momentum*v + (1-dampening)*g',
+ *   p -= lr*(nesterov ? g' + momentum*v : v);  otherwise p -= lr*g' (velocity may be NULL).
+ * Bit-identical to the CPU arithmetic (same operation order, no fused multiply-add). */
+int32_t mtb200_sgd_step(mtb200_handle h, int32_t dtype, int64_t n, void* param, const void* grad,
+                        void* velocity, double lr, double momentum, double dampening,
+                        double weight_decay, int32_t nesterov);
+
+/* ---- RMSprop step (f32 / f64), in place
+ * RMSprop::apply_rmsprop_update (engine/src/optim/rmsprop.rs:187-383):
+ *   g' = g + weight_decay*p;  sq = alpha*sq + (1-alpha)*g'*g';
+ *   grad_avg != NULL (centered): ga = alpha*ga + (1-alpha)*g', denom = sqrt(sq - ga*ga) + eps,
+ *   else denom = sqrt(sq) + eps;  momentum > 0: mb = momentum*mb + lr*g'/denom, p -= mb;
+ *   else p -= lr*g'/denom (momentum_buf may be NULL).  Bit-identical to the CPU arithmetic. */
+int32_t mtb200_rmsprop_step(mtb200_handle h, int32_t dtype, int64_t n, void* param, const void* grad,
+                            void* square_avg, void* momentum_buf, void* grad_avg, double lr,
+                            double alpha, double eps, double weight_decay, double momentum);
+
+/* ---- gradient clipping building blocks (f32 / f64)
+ * GradientUtils::compute_grad_norm_value / clip_grad_norm / clip_grad_value
+ * (engine/src/optim/utils.rs:16-112).
+ * sumsq: *out (one DEVICE double) = [*out +] sum of x[i]^2 accumulated in f64, deterministic; the
+ *        caller takes the square root of the total over all parameters and, when it exceeds
+ *        max_norm, scales every gradient by max_norm / (norm + 1e-6).
+ * scale: x[i] *= (element type)coef.   clamp: x[i] = clamp(x[i], lo, hi), NaN stays NaN. */
+int32_t mtb200_sumsq(mtb200_handle h, int32_t dtype, int64_t n, const void* x, double* out,
+                     int32_t accumulate);
+int32_t mtb200_scale(mtb200_handle h, int32_t dtype, int64_t n, void* x, double coef);
+int32_t mtb200_clamp(mtb200_handle h, int32_t dtype, int64_t n, void* x, double lo, double hi);
+
 /* ---- conv2d, NCHW input, OIHW weight, f32 (the reference supports nothing
  * else: engine/src/operations/conv.rs:85-93,202-204).
  * forward  = conv2d                     engine/src/operations/conv.rs:24-206

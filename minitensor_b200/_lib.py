@@ -48,6 +48,12 @@ SIGNATURES = {
     "mtb200_act_bwd": (_i32, [_vp, _i32, _i32, _i64, _vp, _vp, _vp]),
     "mtb200_bias_act": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _i32, _vp]),
     "mtb200_cross_entropy": (_i32, [_vp, _i64, _i64, _vp, _vp, _i32, _i32, _f32, _vp, _vp]),
+    "mtb200_cross_entropy_ex": (_i32, [_vp, _i64, _i64, _vp, _vp, _i32, _i32, _f32, _vp, _vp, _vp]),
+    "mtb200_sgd_step": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _i32]),
+    "mtb200_rmsprop_step": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64]),
+    "mtb200_sumsq": (_i32, [_vp, _i32, _i64, _vp, _vp, _i32]),
+    "mtb200_scale": (_i32, [_vp, _i32, _i64, _vp, _f64]),
+    "mtb200_clamp": (_i32, [_vp, _i32, _i64, _vp, _f64, _f64]),
     "mtb200_adam_step": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64, _i32,
                                 _i64, _f32]),
     "mtb200_conv2d_fwd": (_i32, [_vp] + [_i64] * 11 + [_vp, _vp, _vp, _vp, _i32]),

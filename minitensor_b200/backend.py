@@ -244,6 +244,74 @@ class Backend:
                                         beta2, eps, weight_decay, int(decoupled), step, grad_scale))
         self.launches += 1
 
+    def cross_entropy_ex(self, logits: torch.Tensor, targets: torch.Tensor, *, reduction: str = "mean",
+                         upstream: float = 1.0, upstream_rows: Optional[torch.Tensor] = None,
+                         want_grad: bool = True):
+        """General cross entropy: ``targets`` are class indices ``[B]`` (int32/int64) or probabilities
+        ``[B, C]`` (float32); ``reduction`` is "sum", "mean" or "none".  Returns ``(loss, dlogits or None)``,
+        the loss a 1-element tensor or ``[B]`` for "none"."""
+        bsz, ncls = logits.shape
+        red = {"sum": 0, "mean": 1, "none": 2}.get(reduction)
+        if red is None:
+            raise ValueError(f"Invalid reduction mode: {reduction}. Must be 'mean', 'sum', or 'none'")
+        if targets.dtype in (torch.int32, torch.int64):
+            if tuple(targets.shape) != (bsz,):
+                raise ValueError(f"shape mismatch: targets {tuple(targets.shape)} for logits {tuple(logits.shape)}")
+        elif targets.dtype == torch.float32:
+            if tuple(targets.shape) != (bsz, ncls):
+                raise ValueError(f"shape mismatch: targets {tuple(targets.shape)} for logits {tuple(logits.shape)}")
+        else:
+            raise TypeError("Unsupported target dtype for classification loss")
+        loss = torch.empty(bsz if red == 2 else 1, dtype=torch.float32, device=logits.device)
+        dl = torch.empty_like(logits) if want_grad else None
+        self._bind_stream()
+        check(self.lib.mtb200_cross_entropy_ex(self._h, bsz, ncls, _ptr(logits), _ptr(targets), _DTYPES[targets.dtype],
+                                               red, float(upstream), _ptr(upstream_rows), _ptr(loss), _ptr(dl)))
+        self.launches += 1 if red == 2 else 2
+        return loss, dl
+
+    def sgd_step(self, p: torch.Tensor, g: torch.Tensor, v: Optional[torch.Tensor] = None, *, lr: float,
+                 momentum: float = 0.0, dampening: float = 0.0, weight_decay: float = 0.0,
+                 nesterov: bool = False) -> None:
+        self._bind_stream()
+        check(self.lib.mtb200_sgd_step(self._h, dtype_code(p), p.numel(), _ptr(p), _ptr(g), _ptr(v), lr, momentum,
+                                       dampening, weight_decay, int(nesterov)))
+        self.launches += 1
+
+    def rmsprop_step(self, p: torch.Tensor, g: torch.Tensor, sq: torch.Tensor, mb: Optional[torch.Tensor] = None,
+                     ga: Optional[torch.Tensor] = None, *, lr: float, alpha: float = 0.99, eps: float = 1e-8,
+                     weight_decay: float = 0.0, momentum: float = 0.0) -> None:
+        self._bind_stream()
+        check(self.lib.mtb200_rmsprop_step(self._h, dtype_code(p), p.numel(), _ptr(p), _ptr(g), _ptr(sq), _ptr(mb),
+                                           _ptr(ga), lr, alpha, eps, weight_decay, momentum))
+        self.launches += 1
+
+    def grad_norm(self, grads) -> float:
+        """L2 norm over a list of f32/f64 tensors, squares accumulated in f64 on the device (one read-back)."""
+        acc = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._bind_stream()
+        for i, g in enumerate(grads):
+            check(self.lib.mtb200_sumsq(self._h, dtype_code(g), g.numel(), _ptr(g), _ptr(acc), int(i > 0)))
+            self.launches += 2
+        return float(acc.item()) ** 0.5
+
+    def clip_grad_norm(self, grads, max_norm: float) -> float:
+        """``GradientUtils::clip_grad_norm``: scales every gradient by max_norm / (norm + 1e-6) when the
+        norm exceeds max_norm; returns the norm before clipping."""
+        total = self.grad_norm(grads)
+        if total > max_norm:
+            coef = max_norm / (total + 1e-6)
+            for g in grads:
+                check(self.lib.mtb200_scale(self._h, dtype_code(g), g.numel(), _ptr(g), coef))
+                self.launches += 1
+        return total
+
+    def clip_grad_value(self, grads, lo: float, hi: float) -> None:
+        self._bind_stream()
+        for g in grads:
+            check(self.lib.mtb200_clamp(self._h, dtype_code(g), g.numel(), _ptr(g), lo, hi))
+            self.launches += 1
+
     # ------------------------------------------------------------------ conv2d
     @staticmethod
     def _geom(xshape, wshape, stride, padding):

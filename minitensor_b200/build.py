@@ -16,7 +16,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 OUT = os.path.join(_HERE, "libmtb200.so")
-SOURCES = ["mtb200.cu", "conv2d.cu", "colsum_static.cu"]
+SOURCES = ["mtb200.cu", "conv2d.cu", "colsum_static.cu", "train_ops.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -228,26 +228,47 @@ class Conv2d(Module):
 
 
 # ---------------------------------------------------------------------- loss
-def cross_entropy(input: Tensor, target: Tensor, reduction: str = "mean") -> Tensor:
-    """Class-index targets (int32 / int64, shape ``[B]``) against ``[B, C]`` f32 logits."""
-    if reduction not in ("mean", "sum"):
-        if reduction == "none":
-            raise NotImplementedError("reduction 'none' is outside the accelerated path")
+def cross_entropy(input: Tensor, target: Tensor, reduction: str = "mean", dim: int = -1) -> Tensor:
+    """``cross_entropy`` of the reference (``engine/src/operations/loss/regression.rs:253-308``): f32 logits with the
+    classes along ``dim``; ``target`` holds class indices (int32 / int64, the logits' shape without ``dim``) or
+    probabilities (float32, the logits' shape); ``reduction`` is "mean", "sum" or "none"."""
+    if reduction not in ("mean", "sum", "none"):
         raise ValueError(f"Invalid reduction mode: {reduction}. Must be 'mean', 'sum', or 'none'")
-    if input.ndim != 2 or target.ndim != 1 or target.shape[0] != input.shape[0]:
-        raise ValueError(f"shape mismatch: {input.shape} vs {target.shape}")
+    nd = input.ndim
+    if nd < 1:
+        raise ValueError("cross entropy expects at least 1-D logits")
+    d = dim + nd if dim < 0 else dim
+    if d < 0 or d >= nd:
+        raise IndexError("dim out of range in cross_entropy")
     if input.dtype != "float32":
         raise TypeError("cross entropy on this path takes float32 logits")
-    if target.dtype not in ("int32", "int64"):
+    if target.dtype not in ("int32", "int64", "float32"):
         raise TypeError("Unsupported target dtype for classification loss")
+    soft = target.dtype == "float32"
+    rest = tuple(s_ for i_, s_ in enumerate(input.shape) if i_ != d)
+    if (soft and target.shape != input.shape) or (not soft and target.shape != rest):
+        raise ValueError(f"shape mismatch: {input.shape} vs {target.shape}")
+    ncls = input.shape[d]
+    # class dimension last, everything else flattened (regression.rs:264-291)
+    x2 = input._buf.movedim(d, -1).reshape(-1, ncls).contiguous()
+    t2 = (target._buf.movedim(d, -1).reshape(-1, ncls) if soft else target._buf.reshape(-1)).contiguous()
     be = _be()
-    loss, dl = be.cross_entropy(input._buf, target._buf, mean=(reduction == "mean"), want_grad=input.requires_grad)
+    loss, dl = be.cross_entropy_ex(x2, t2, reduction=reduction, want_grad=input.requires_grad)
     be.sync()  # surfaces an out-of-range class index as IndexError, as the reference does eagerly
-    return input._result(loss.reshape(()), (input,), lambda g: (dl * g.reshape(()),))
+    moved_shape = tuple(rest) + (ncls,)
+
+    def bw(g):
+        gg = g.reshape(-1, 1) if reduction == "none" else g.reshape(())
+        return ((dl * gg).reshape(moved_shape).movedim(-1, d).contiguous(),)
+
+    out = loss.reshape(rest) if reduction == "none" else loss.reshape(())
+    return input._result(out, (input,), bw)
 
 
 class CrossEntropyLoss(Module):
     def __init__(self, reduction: str = "mean"):
+        if reduction not in ("mean", "sum", "none"):
+            raise ValueError(f"Invalid reduction mode: {reduction}. Must be 'mean', 'sum', or 'none'")
         self.reduction = reduction
 
     def __call__(self, input: Tensor, target: Tensor) -> Tensor:

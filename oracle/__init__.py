@@ -40,6 +40,9 @@ def lib() -> C.CDLL:
         _lib.orc_num_threads.restype = _int
         _lib.orc_conv2d_f32.restype = _int
         _lib.orc_cross_entropy_f32.restype = _int
+        _lib.orc_cross_entropy_ex_f32.restype = _int
+        _lib.orc_sumsq_f32.restype = _f64
+        _lib.orc_sumsq_f64.restype = _f64
     return _lib
 
 
@@ -206,6 +209,69 @@ def cross_entropy(logits, labels, mean: bool = True, upstream: float = 1.0, want
     if rc:
         raise IndexError("class index out of range")
     return loss[0], grad
+
+
+def cross_entropy_ex(logits, targets, reduction: str = "mean", upstream: float = 1.0, upstream_rows=None,
+                     want_grad: bool = True):
+    """General form: ``targets`` are class indices ``[B]`` (integer dtype) or probabilities ``[B, C]`` (float);
+    ``reduction`` in ("sum", "mean", "none").  Returns (loss scalar or ``[B]`` array, grad or None)."""
+    logits = _c(logits, np.float32)
+    bsz, ncls = logits.shape
+    targets = np.asarray(targets)
+    labels = soft = None
+    if targets.dtype.kind in "iu":
+        labels = _c(targets, np.int64)
+    else:
+        soft = _c(targets, np.float32)
+        assert soft.shape == logits.shape
+    red = {"sum": 0, "mean": 1, "none": 2}[reduction]
+    loss = np.zeros(bsz if red == 2 else 1, dtype=np.float32)
+    grad = np.zeros_like(logits) if want_grad else None
+    rows = _c(upstream_rows, np.float32) if upstream_rows is not None else None
+    rc = lib().orc_cross_entropy_ex_f32(_i64(bsz), _i64(ncls), _ptr(logits), _ptr(labels), _ptr(soft), _int(red),
+                                        _f32(upstream), _ptr(rows), _ptr(loss), _ptr(grad))
+    if rc:
+        raise IndexError("class index out of range")
+    return (loss if red == 2 else loss[0]), grad
+
+
+def _sfx(a: np.ndarray) -> str:
+    assert a.dtype in (np.float32, np.float64) and a.flags.c_contiguous
+    return "f32" if a.dtype == np.float32 else "f64"
+
+
+def sgd_step(p, g, v=None, lr=0.01, momentum=0.0, dampening=0.0, weight_decay=0.0, nesterov=False) -> None:
+    """In place on ``p`` (and ``v`` when ``momentum > 0``); float32 or float64 arrays."""
+    g = _c(g, p.dtype)
+    getattr(lib(), "orc_sgd_step_" + _sfx(p))(_i64(p.size), _ptr(p), _ptr(g), _ptr(v), _f64(lr), _f64(momentum),
+                                              _f64(dampening), _f64(weight_decay), _int(int(nesterov)))
+
+
+def rmsprop_step(p, g, sq, mb=None, ga=None, lr=0.01, alpha=0.99, eps=1e-8, weight_decay=0.0, momentum=0.0) -> None:
+    """In place on ``p``, ``sq`` and the optional momentum / centered buffers."""
+    g = _c(g, p.dtype)
+    getattr(lib(), "orc_rmsprop_step_" + _sfx(p))(_i64(p.size), _ptr(p), _ptr(g), _ptr(sq), _ptr(mb), _ptr(ga),
+                                                  _f64(lr), _f64(alpha), _f64(eps), _f64(weight_decay), _f64(momentum))
+
+
+def sumsq(x) -> float:
+    x = np.ascontiguousarray(x)
+    return float(getattr(lib(), "orc_sumsq_" + _sfx(x))(_i64(x.size), _ptr(x)))
+
+
+def clip_grad_norm(grads, max_norm: float) -> float:
+    """GradientUtils::clip_grad_norm over a list of arrays (in place); returns the norm before clipping."""
+    total = float(np.sqrt(sum(sumsq(g) for g in grads)))
+    if total > max_norm:
+        coef = max_norm / (total + 1e-6)
+        for g in grads:
+            getattr(lib(), "orc_scale_" + _sfx(g))(_i64(g.size), _ptr(g), _f64(coef))
+    return total
+
+
+def clip_grad_value(grads, lo: float, hi: float) -> None:
+    for g in grads:
+        getattr(lib(), "orc_clamp_" + _sfx(g))(_i64(g.size), _ptr(g), _f64(lo), _f64(hi))
 
 
 def adam_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay=0.0, decoupled=False, step=1) -> None:

@@ -524,6 +524,176 @@ int orc_cross_entropy_f32(int64_t B, int64_t C, const float* logits, const int64
   return 0;
 }
 
+// cross_entropy_loss in its general form (engine/src/operations/loss/regression.rs:178-251): targets are
+// class indices (one-hot: :769-862) or a [B][C] float matrix used as it is; per-sample loss
+// = -sum_c t[c] * masked_log_softmax[c] (classification.rs:446-450, sum over dim 1 in class order);
+// reduction 0 = sum, 1 = mean, 2 = none (row_loss[B]).  Gradient (engine/src/autograd/mod/activation.rs:364-427):
+// (softmax - t) * (1/B if mean) * upstream, with upstream a scalar times an optional per-sample factor
+// (the reference multiplies by grad_output with its generic broadcast, which for a [B] gradient of a
+// "none" loss only type-checks when B == C; the per-sample factor is the meaning of that product).
+int orc_cross_entropy_ex_f32(int64_t B, int64_t C, const float* logits, const int64_t* labels /*nullable*/,
+                             const float* soft /*nullable*/, int reduction, float upstream,
+                             const float* upstream_rows /*nullable*/, float* loss /*1 or B*/,
+                             float* grad /*nullable*/) {
+  if (labels)
+    for (int64_t i = 0; i < B; ++i)
+      if (labels[i] < 0 || labels[i] >= C) return 1;
+  std::vector<float> per_sample(static_cast<size_t>(B));
+  const float inv_b = static_cast<float>(1.0 / static_cast<double>(B));
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < B; ++i) {
+    const float* x = logits + i * C;
+    float mx = -std::numeric_limits<float>::infinity();
+    for (int64_t c = 0; c < C; ++c)
+      if (x[c] > mx) mx = x[c];
+    std::vector<float> lp(static_cast<size_t>(C));
+    if (std::isinf(mx) && mx < 0) {
+      for (int64_t c = 0; c < C; ++c) lp[c] = -std::numeric_limits<float>::infinity();
+    } else {
+      float s = 0.0f;
+      for (int64_t c = 0; c < C; ++c) s = s + std::exp(x[c] - mx);
+      const float logsum = std::log(s) + mx;
+      for (int64_t c = 0; c < C; ++c) lp[c] = x[c] - logsum;
+    }
+    float row = 0.0f;
+    for (int64_t c = 0; c < C; ++c) {
+      const float sm = std::exp(lp[c]);
+      const float t = labels ? ((c == labels[i]) ? 1.0f : 0.0f) : soft[i * C + c];
+      const float lpm = (sm <= 1e-30f) ? -std::numeric_limits<float>::infinity() : lp[c];
+      row = row + (-(lpm * t));
+      if (grad) {
+        float g = sm - t;
+        if (reduction == 1) g = g * inv_b;
+        g = g * upstream;
+        if (upstream_rows) g = g * upstream_rows[i];
+        grad[i * C + c] = g;
+      }
+    }
+    per_sample[i] = row;
+  }
+  if (reduction == 2) {
+    for (int64_t i = 0; i < B; ++i) loss[i] = per_sample[i];
+    return 0;
+  }
+  float total = 0.0f;
+  for (int64_t i = 0; i < B; ++i) total += per_sample[i];
+  *loss = reduction == 1 ? static_cast<float>(static_cast<double>(total) / static_cast<double>(B)) : total;
+  return 0;
+}
+
+// ------------------------------------------------------------------ SGD, RMSprop, gradient clipping
+// SGD::apply_simple_update / apply_momentum_update (engine/src/optim/sgd.rs:169-296): every constant is
+// cast to the element type first, each operation is rounded separately.
+}  // extern "C"
+template <typename T>
+static void sgd_step(int64_t n, T* p, const T* g, T* v /*nullable*/, double lr_, double momentum_, double damp_,
+                     double wd_, int nesterov) {
+  const T lr = static_cast<T>(lr_), momentum = static_cast<T>(momentum_), damp = static_cast<T>(damp_),
+          wd = static_cast<T>(wd_);
+  const T one_minus_damp = static_cast<T>(1.0) - damp;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    volatile T t;
+    t = wd * p[i];
+    const T grad_val = g[i] + t;
+    if (momentum_ > 0.0) {
+      t = momentum * v[i];
+      T u = one_minus_damp * grad_val;
+      const T vi = t + u;
+      v[i] = vi;
+      T update = vi;
+      if (nesterov) { t = momentum * vi; update = grad_val + t; }
+      t = lr * update;
+      p[i] = p[i] - t;
+    } else {
+      t = lr * grad_val;
+      p[i] = p[i] - t;
+    }
+  }
+}
+extern "C" {
+void orc_sgd_step_f32(int64_t n, float* p, const float* g, float* v, double lr, double momentum, double damp,
+                      double wd, int nesterov) { sgd_step<float>(n, p, g, v, lr, momentum, damp, wd, nesterov); }
+void orc_sgd_step_f64(int64_t n, double* p, const double* g, double* v, double lr, double momentum, double damp,
+                      double wd, int nesterov) { sgd_step<double>(n, p, g, v, lr, momentum, damp, wd, nesterov); }
+
+// RMSprop::apply_rmsprop_update (engine/src/optim/rmsprop.rs:187-383): the four (momentum, centered) variants.
+}  // extern "C"
+template <typename T>
+static void rmsprop_step(int64_t n, T* p, const T* g, T* sq, T* mb /*nullable*/, T* ga /*nullable*/, double lr_,
+                         double alpha_, double eps_, double wd_, double momentum_) {
+  const T lr = static_cast<T>(lr_), alpha = static_cast<T>(alpha_), eps = static_cast<T>(eps_),
+          wd = static_cast<T>(wd_), momentum = static_cast<T>(momentum_);
+  const T oma = static_cast<T>(1.0) - alpha;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    volatile T t;
+    t = wd * p[i];
+    const T gv = g[i] + t;
+    t = alpha * sq[i];
+    T u = oma * gv;
+    u = u * gv;
+    const T sqi = t + u;
+    sq[i] = sqi;
+    T avg = sqi;
+    if (ga) {
+      t = alpha * ga[i];
+      u = oma * gv;
+      const T gai = t + u;
+      ga[i] = gai;
+      t = gai * gai;
+      avg = sqi - t;
+    }
+    const T denom = std::sqrt(avg) + eps;
+    t = lr * gv;
+    const T stepv = t / denom;
+    if (mb) {
+      t = momentum * mb[i];
+      const T mbi = t + stepv;
+      mb[i] = mbi;
+      p[i] = p[i] - mbi;
+    } else {
+      p[i] = p[i] - stepv;
+    }
+  }
+}
+extern "C" {
+void orc_rmsprop_step_f32(int64_t n, float* p, const float* g, float* sq, float* mb, float* ga, double lr,
+                          double alpha, double eps, double wd, double momentum) {
+  rmsprop_step<float>(n, p, g, sq, mb, ga, lr, alpha, eps, wd, momentum);
+}
+void orc_rmsprop_step_f64(int64_t n, double* p, const double* g, double* sq, double* mb, double* ga, double lr,
+                          double alpha, double eps, double wd, double momentum) {
+  rmsprop_step<double>(n, p, g, sq, mb, ga, lr, alpha, eps, wd, momentum);
+}
+
+// GradientUtils (engine/src/optim/utils.rs:16-112): sum of squares in f64 (the reference's order is
+// rayon-dependent; ascending here), scale by a coefficient cast to the element type, clamp (NaN stays NaN).
+double orc_sumsq_f32(int64_t n, const float* x) {
+  double s = 0.0;
+  for (int64_t i = 0; i < n; ++i) s += static_cast<double>(x[i]) * static_cast<double>(x[i]);
+  return s;
+}
+double orc_sumsq_f64(int64_t n, const double* x) {
+  double s = 0.0;
+  for (int64_t i = 0; i < n; ++i) s += x[i] * x[i];
+  return s;
+}
+void orc_scale_f32(int64_t n, float* x, double coef) {
+  const float c = static_cast<float>(coef);
+  for (int64_t i = 0; i < n; ++i) x[i] = x[i] * c;
+}
+void orc_scale_f64(int64_t n, double* x, double coef) {
+  for (int64_t i = 0; i < n; ++i) x[i] = x[i] * coef;
+}
+void orc_clamp_f32(int64_t n, float* x, double lo_, double hi_) {
+  const float lo = static_cast<float>(lo_), hi = static_cast<float>(hi_);
+  for (int64_t i = 0; i < n; ++i) x[i] = x[i] < lo ? lo : (x[i] > hi ? hi : x[i]);
+}
+void orc_clamp_f64(int64_t n, double* x, double lo, double hi) {
+  for (int64_t i = 0; i < n; ++i) x[i] = x[i] < lo ? lo : (x[i] > hi ? hi : x[i]);
+}
+
 // ------------------------------------------------------------------ Adam
 // Adam::apply_adam_update, no amsgrad: engine/src/optim/adam.rs:245-312.
 void orc_adam_step_f32(int64_t n, float* p, const float* g, float* m, float* v, double lr, double beta1,

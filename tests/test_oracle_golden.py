@@ -188,3 +188,62 @@ def test_mlp_step_matches_composition(orc, rng):
     pe, me, ve = p0.copy(), np.zeros_like(p0), np.zeros_like(p0)
     orc.adam_step(pe, exp, me, ve, 1e-3, 0.9, 0.999, 1e-8, step=1)
     np.testing.assert_array_equal(params, pe)
+
+
+# ------------------------------------------------------------------ training-step ops beside the GEMMs
+def test_cross_entropy_general_known_answers(orc, golden):
+    for case in golden["cross_entropy_general"]:
+        logits = np.array(case["logits"], dtype=np.float32)
+        targets = np.array(case["labels"], dtype=np.int64) if "labels" in case else np.array(case["targets"], np.float32)
+        loss, grad = orc.cross_entropy_ex(logits, targets, case["reduction"])
+        if case["loss"] == "inf":
+            assert np.isinf(loss) and loss > 0
+        else:
+            np.testing.assert_allclose(loss, np.array(case["loss"], dtype=np.float64), rtol=1e-5, atol=1e-8)
+    # class indices and their one-hot matrix are the same computation (regression.rs:769-862)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((6, 5)).astype(np.float32)
+    lab = rng.integers(0, 5, 6)
+    onehot = np.eye(5, dtype=np.float32)[lab]
+    for red in ("sum", "mean", "none"):
+        la, ga = orc.cross_entropy_ex(x, lab, red)
+        lb, gb = orc.cross_entropy_ex(x, onehot, red)
+        np.testing.assert_array_equal(la, lb)
+        np.testing.assert_array_equal(ga, gb)
+    l_old, g_old = orc.cross_entropy(x, lab, mean=True)
+    l_new, g_new = orc.cross_entropy_ex(x, lab, "mean")
+    assert l_old == l_new and np.array_equal(g_old, g_new)
+
+
+def test_sgd_rmsprop_clipping_known_answers(orc, golden):
+    for case in golden["sgd"]:
+        dt = np.dtype(case["dtype"])
+        p = np.array(case["param"], dtype=dt)
+        v = np.zeros_like(p) if case["momentum"] > 0 else None
+        orc.sgd_step(p, np.array(case["grad"], dtype=dt), v, case["lr"], case["momentum"], case["dampening"],
+                     case["weight_decay"], case["nesterov"])
+        np.testing.assert_allclose(p, case["expected"], rtol=0, atol=case["atol"])
+    for case in golden["rmsprop"]:
+        p = np.array(case["param"], dtype=np.float32)
+        sq = np.zeros_like(p)
+        mb = np.zeros_like(p) if case["momentum"] > 0 else None
+        ga = np.zeros_like(p) if case["centered"] else None
+        orc.rmsprop_step(p, np.array(case["grad"], dtype=np.float32), sq, mb, ga, case["lr"], case["alpha"], case["eps"],
+                         case["weight_decay"], case["momentum"])
+        assert np.all(p < case["upper_bound"])
+    for case in golden["grad_clipping"]:
+        g = np.array(case["grad"], dtype=np.float32)
+        if case["kind"] == "norm":
+            norm = orc.clip_grad_norm([g], case["max_norm"])
+            assert abs(norm - case["norm"]) < 1e-10 * max(1.0, case["norm"]) + 1e-6
+            if "expected" in case:
+                np.testing.assert_allclose(g, case["expected"], rtol=0, atol=case["atol"])
+            else:
+                assert np.sqrt(orc.sumsq(g)) <= case["norm_after_at_most"]
+        else:
+            orc.clip_grad_value([g], case["min"], case["max"])
+            np.testing.assert_allclose(g, case["expected"], rtol=0, atol=case["atol"])
+    # NaN survives a clamp, as f32::clamp does
+    g = np.array([np.nan, 5.0], dtype=np.float32)
+    orc.clip_grad_value([g], -1.0, 1.0)
+    assert np.isnan(g[0]) and g[1] == 1.0

@@ -1,0 +1,194 @@
+"""SGD, RMSprop, gradient clipping and the general cross entropy through the C ABI against the oracle
+(bit-exact for the optimizers and the clipping arithmetic) and the reference's own known answers."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(be, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(be.device)
+
+
+# ------------------------------------------------------------------ SGD
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("momentum,dampening,nesterov,wd", [(0.0, 0.0, False, 0.0), (0.0, 0.0, False, 0.01),
+                                                            (0.9, 0.0, False, 0.0), (0.9, 0.1, True, 1e-3)])
+def test_sgd_bit_exact_three_steps(be, orc, rng, dtype, momentum, dampening, nesterov, wd):
+    n = 100_003
+    p = rng.standard_normal(n).astype(dtype)
+    v = np.zeros(n, dtype) if momentum > 0 else None
+    pd, vd = dev(be, p), (dev(be, v) if v is not None else None)
+    for _ in range(3):
+        g = rng.standard_normal(n).astype(dtype)
+        orc.sgd_step(p, g, v, 0.05, momentum, dampening, wd, nesterov)
+        be.sgd_step(pd, dev(be, g), vd, lr=0.05, momentum=momentum, dampening=dampening, weight_decay=wd,
+                    nesterov=nesterov)
+    be.sync()
+    np.testing.assert_array_equal(pd.cpu().numpy(), p)
+    if v is not None:
+        np.testing.assert_array_equal(vd.cpu().numpy(), v)
+
+
+def test_sgd_known_answers_and_mirror(be, golden):
+    import minitensor_b200.optim as optim
+    import minitensor_b200.tensor as mt
+    for case in golden["sgd"]:
+        p = mt.Tensor(np.array(case["param"], dtype=case["dtype"]), requires_grad=True)
+        p.grad = mt.Tensor(np.array(case["grad"], dtype=case["dtype"]))
+        opt = optim.SGD([p], lr=case["lr"], momentum=case["momentum"], weight_decay=case["weight_decay"],
+                        dampening=case["dampening"], nesterov=case["nesterov"])
+        opt.step()
+        np.testing.assert_allclose(p.numpy(), case["expected"], rtol=0, atol=case["atol"])
+        assert opt.step_count == 1
+    with pytest.raises(ValueError):
+        optim.SGD([mt.Tensor(np.zeros(3, np.int32))])
+
+
+# ------------------------------------------------------------------ RMSprop
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("momentum,centered,wd", [(0.0, False, 0.0), (0.9, False, 1e-3), (0.0, True, 0.0), (0.9, True, 1e-2)])
+def test_rmsprop_bit_exact_three_steps(be, orc, rng, dtype, momentum, centered, wd):
+    n = 65_537
+    p = rng.standard_normal(n).astype(dtype)
+    sq = np.zeros(n, dtype)
+    mb = np.zeros(n, dtype) if momentum > 0 else None
+    ga = np.zeros(n, dtype) if centered else None
+    pd, sqd = dev(be, p), dev(be, sq)
+    mbd = dev(be, mb) if mb is not None else None
+    gad = dev(be, ga) if ga is not None else None
+    for _ in range(3):
+        g = rng.standard_normal(n).astype(dtype)
+        orc.rmsprop_step(p, g, sq, mb, ga, 0.01, 0.99, 1e-8, wd, momentum)
+        be.rmsprop_step(pd, dev(be, g), sqd, mbd, gad, lr=0.01, alpha=0.99, eps=1e-8, weight_decay=wd, momentum=momentum)
+    be.sync()
+    np.testing.assert_array_equal(pd.cpu().numpy(), p)
+    np.testing.assert_array_equal(sqd.cpu().numpy(), sq)
+    if mb is not None:
+        np.testing.assert_array_equal(mbd.cpu().numpy(), mb)
+    if ga is not None:
+        np.testing.assert_array_equal(gad.cpu().numpy(), ga)
+
+
+def test_rmsprop_known_answers_via_mirror(be, golden):
+    import minitensor_b200.optim as optim
+    import minitensor_b200.tensor as mt
+    for case in golden["rmsprop"]:
+        p = mt.Tensor(np.array(case["param"], dtype=np.float32), requires_grad=True)
+        p.grad = mt.Tensor(np.array(case["grad"], dtype=np.float32))
+        optim.RMSprop([p], lr=case["lr"], alpha=case["alpha"], epsilon=case["eps"], weight_decay=case["weight_decay"],
+                      momentum=case["momentum"], centered=case["centered"]).step()
+        assert np.all(p.numpy() < case["upper_bound"])
+
+
+# ------------------------------------------------------------------ clipping
+def test_grad_clipping_known_answers(be, golden):
+    for case in golden["grad_clipping"]:
+        g = dev(be, np.array(case["grad"], dtype=np.float32))
+        if case["kind"] == "norm":
+            norm = be.clip_grad_norm([g], case["max_norm"])
+            assert abs(norm - case["norm"]) < 1e-6
+            if "expected" in case:
+                np.testing.assert_allclose(g.cpu().numpy(), case["expected"], rtol=0, atol=case["atol"])
+            else:
+                assert be.grad_norm([g]) <= case["norm_after_at_most"]
+        else:
+            be.clip_grad_value([g], case["min"], case["max"])
+            np.testing.assert_allclose(g.cpu().numpy(), case["expected"], rtol=0, atol=case["atol"])
+
+
+def test_grad_norm_and_clipping_against_oracle(be, orc, rng):
+    grads = [rng.standard_normal(1_000_003).astype(np.float32) * 3, rng.standard_normal(4099).astype(np.float64),
+             np.zeros(0, np.float32)]
+    gd = [dev(be, g) for g in grads]
+    ref_norm = float(np.sqrt(sum(orc.sumsq(g) for g in grads)))
+    norm = be.grad_norm(gd)
+    assert abs(norm - ref_norm) <= 1e-12 * ref_norm          # both accumulate in f64; only the order differs
+    assert be.grad_norm(gd) == norm                           # deterministic
+    ref = [g.copy() for g in grads]
+    # scale with the SAME coefficient: the arithmetic itself is bit-exact
+    coef = 10.0 / (norm + 1e-6)
+    total = be.clip_grad_norm(gd, 10.0)
+    assert total == norm
+    np.testing.assert_array_equal(gd[0].cpu().numpy(), ref[0] * np.float32(coef))
+    np.testing.assert_array_equal(gd[1].cpu().numpy(), ref[1] * coef)
+    assert be.clip_grad_norm(gd, 1e9) <= 10.0 + 1e-3          # within the threshold: untouched
+    vals = [g.copy() for g in (a.cpu().numpy() for a in gd[:2])]
+    vals[0][5] = np.nan
+    vd = [dev(be, v) for v in vals]
+    orc.clip_grad_value(vals, -0.01, 0.02)
+    be.clip_grad_value(vd, -0.01, 0.02)
+    np.testing.assert_array_equal(vd[0].cpu().numpy(), vals[0])   # NaN stays NaN
+    np.testing.assert_array_equal(vd[1].cpu().numpy(), vals[1])
+    with pytest.raises(ValueError):
+        be.clip_grad_value(vd, 1.0, -1.0)
+    with pytest.raises(TypeError):
+        be.grad_norm([torch.zeros(4, dtype=torch.int32, device=be.device)])
+
+
+def test_optimizer_clipping_before_step(be):
+    import minitensor_b200.optim as optim
+    import minitensor_b200.tensor as mt
+    p = mt.Tensor(np.ones(3, np.float32), requires_grad=True)
+    p.grad = mt.Tensor(np.full(3, 3.0, np.float32))
+    optim.SGD([p], lr=1.0).with_gradient_clipping(max_norm=1.0).step()
+    # gradient scaled to norm ~1: each component 1/sqrt(3)
+    np.testing.assert_allclose(p.numpy(), 1.0 - 1.0 / np.sqrt(3.0), atol=1e-5)
+    q = mt.Tensor(np.zeros(3, np.float32), requires_grad=True)
+    q.grad = mt.Tensor(np.array([-2.0, 0.5, 2.0], np.float32))
+    optim.SGD([q], lr=1.0).with_gradient_clipping(min_value=-1.0, max_value=1.0).step()
+    np.testing.assert_allclose(q.numpy(), [1.0, -0.5, -1.0], atol=1e-6)
+
+
+# ------------------------------------------------------------------ cross entropy, general form
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("soft", [False, True])
+def test_cross_entropy_general_against_oracle(be, orc, rng, reduction, soft):
+    bsz, ncls = 257, 1000
+    x = (rng.standard_normal((bsz, ncls)) * 3).astype(np.float32)
+    if soft:
+        t = rng.random((bsz, ncls)).astype(np.float32)
+        t /= t.sum(axis=1, keepdims=True)
+    else:
+        t = rng.integers(0, ncls, bsz)
+    rows = rng.standard_normal(bsz).astype(np.float32) if reduction == "none" else None
+    ref_loss, ref_grad = orc.cross_entropy_ex(x, t, reduction, upstream=0.5, upstream_rows=rows)
+    loss, grad = be.cross_entropy_ex(dev(be, x), dev(be, t), reduction=reduction, upstream=0.5,
+                                     upstream_rows=dev(be, rows) if rows is not None else None)
+    be.sync()
+    np.testing.assert_allclose(loss.cpu().numpy().reshape(np.shape(ref_loss)), ref_loss, rtol=2e-5, atol=1e-6)
+    np.testing.assert_allclose(grad.cpu().numpy(), ref_grad, rtol=1e-4, atol=2e-6)
+
+
+def test_cross_entropy_general_known_answers_and_nn_mirror(be, golden):
+    import minitensor_b200.nn as nn
+    import minitensor_b200.tensor as mt
+    for case in golden["cross_entropy_general"]:
+        x = mt.Tensor(np.array(case["logits"], dtype=np.float32), requires_grad=True)
+        t = mt.Tensor(np.array(case["labels"], dtype=np.int64)) if "labels" in case else \
+            mt.Tensor(np.array(case["targets"], dtype=np.float32))
+        loss = nn.cross_entropy(x, t, reduction=case["reduction"])
+        if case["loss"] == "inf":
+            assert np.isinf(loss.numpy()) and loss.numpy() > 0
+        else:
+            np.testing.assert_allclose(loss.numpy(), np.array(case["loss"]), rtol=1e-5, atol=1e-8)
+    # the dim argument: classes along axis 1 of a [2, 3, 4] tensor, per-position losses (regression.rs:253-308)
+    x_np = np.arange(24, dtype=np.float32).reshape(2, 3, 4) * 0.1
+    t_np = np.array([[0, 1, 2, 1], [2, 0, 1, 2]], dtype=np.int64)
+    x = mt.Tensor(x_np, requires_grad=True)
+    loss = nn.cross_entropy(x, mt.Tensor(t_np), reduction="none", dim=1)
+    sh = x_np - x_np.max(axis=1, keepdims=True)
+    sm = np.exp(sh) / np.exp(sh).sum(axis=1, keepdims=True)
+    expected = -np.log(np.take_along_axis(sm, t_np[:, None, :], axis=1).squeeze(1))
+    assert loss.shape == expected.shape
+    np.testing.assert_allclose(loss.numpy(), expected, rtol=1e-5, atol=1e-6)
+    loss.sum().backward()
+    onehot = np.moveaxis(np.eye(3, dtype=np.float32)[t_np], -1, 1)
+    np.testing.assert_allclose(x.grad.numpy(), sm - onehot, rtol=1e-4, atol=1e-6)
+    with pytest.raises(IndexError):
+        nn.cross_entropy(x, mt.Tensor(t_np), dim=3)
+    with pytest.raises(ValueError):
+        nn.cross_entropy(x, mt.Tensor(t_np), reduction="avg")
+    with pytest.raises(IndexError):                                   # class index out of range
+        nn.cross_entropy(mt.Tensor(np.zeros((2, 3), np.float32)), mt.Tensor(np.array([0, 3], np.int64)))
