@@ -132,7 +132,7 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
  *           DenseLayer::forward = transpose + matmul + add (engine/src/nn/dense_layer.rs:139-169)
  * backward: dX[rows][in] = dx_epilogue(dY * W)   (skipped when dX is NULL: input without requires_grad,
  *                                                 engine/src/autograd/mod/core.rs:763)
- *           dW[out][in]  = dY^T * x
+ *           dW[out][in]  = dY^T * x                (skipped when dW is NULL)
  *           db[out]      = column sums of dY      (skipped when db is NULL)
  *           MatMulBackward (engine/src/autograd/mod/core.rs:743-789), the transpose's backward and the
  *           broadcast reduction of AddBackward (core.rs:195-223).

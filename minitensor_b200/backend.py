@@ -153,7 +153,7 @@ class Backend:
 
     def dense_backward(self, x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, saved: Optional[torch.Tensor], *,
                        dx: Optional[torch.Tensor] = None, need_dx: bool = True, dx_epilogue: int = EPI_NONE,
-                       dx_aux: Optional[torch.Tensor] = None, dw: Optional[torch.Tensor] = None,
+                       dx_aux: Optional[torch.Tensor] = None, dw: Optional[torch.Tensor] = None, need_dw: bool = True,
                        db: Optional[torch.Tensor] = None, need_db: bool = True):
         """Gradients of ``dense_forward``: returns ``(dx or None, dw, db or None)``."""
         rows, fin = x.shape
@@ -162,16 +162,17 @@ class Backend:
             raise ValueError(f"dy must be [{rows}, {fout}], got {tuple(dy.shape)}")
         if need_dx and dx is None:
             dx = torch.empty(rows, fin, dtype=x.dtype, device=x.device)
-        if dw is None:
+        if need_dw and dw is None:
             dw = torch.empty(fout, fin, dtype=x.dtype, device=x.device)
         if need_db and db is None:
             db = torch.empty(fout, dtype=x.dtype, device=x.device)
         self._bind_stream()
         check(self.lib.mtb200_dense_backward(self._h, dtype_code(x), rows, fin, fout, _ptr(x), _ptr(w), _ptr(dy),
                                              _ptr(saved), _ptr(dx) if need_dx else None, dx_epilogue, _ptr(dx_aux),
-                                             _ptr(dw), _ptr(db) if need_db else None))
-        self.launches += (9 if need_dx else 7) if saved is not None else (10 if need_dx else 6)
-        return (dx if need_dx else None), dw, (db if need_db else None)
+                                             _ptr(dw) if need_dw else None, _ptr(db) if need_db else None))
+        products = int(need_dx) + int(need_dw)
+        self.launches += (5 + 2 * products) if saved is not None else (4 * products + 2 * int(need_db))
+        return (dx if need_dx else None), (dw if need_dw else None), (db if need_db else None)
 
     # ------------------------------------------------------------------ reductions / elementwise
     def colsum(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

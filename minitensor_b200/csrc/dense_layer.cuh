@@ -164,9 +164,9 @@ static __global__ void keys_to_exponents_kernel(int* __restrict__ keys, int n) {
 
 // Second pass over dY: both plane sets, each [2][M][Np] fp16 (Np = N padded to 64, pad written as zero).
 //   rows_out (ROWS only): dY[r][c] 2^(ew[c] - er[r])   - the K-major A operand of dX = dY W
-//   cols_out:             dY[r][c] 2^(ex[r] - ec[c])   - the MN-major A operand of dW = dY^T x
+//   cols_out (COLS only): dY[r][c] 2^(ex[r] - ec[c])   - the MN-major A operand of dW = dY^T x
 // A thread keeps 8 columns (their exponents in registers) and walks the rows of its band.
-template <bool ROWS>
+template <bool ROWS, bool COLS>
 static __global__ void __launch_bounds__(256)
 dy_split2_kernel(const float* __restrict__ dy, long long ld, int M, int N, int Np, int rows_per_band,
                  const int* __restrict__ ex, const int* __restrict__ ec, const int* __restrict__ ew,
@@ -235,7 +235,8 @@ dy_split2_kernel(const float* __restrict__ dy, long long ld, int M, int N, int N
     const long long off = static_cast<long long>(r) * Np + c0;
     const int xr = ex[r];
     // columns: x * 2^(xr - ce)
-    emit(x, small && abs(xr) <= 63, __int_as_float((127 + max(-63, min(63, xr))) << 23), fce, xr, ce, 1, cols_out, off);
+    if (COLS)
+      emit(x, small && abs(xr) <= 63, __int_as_float((127 + max(-63, min(63, xr))) << 23), fce, xr, ce, 1, cols_out, off);
     if (ROWS) {
       const int rr = er[r];
       // rows: x * 2^(we - rr)
@@ -293,7 +294,7 @@ inline int32_t dense_forward_f32(mtb200_ctx* h, int M, int in, int out, const fl
   return launch_nonfinite_redo(h, false, true, M, out, in, x, W, y, bias, epilogue, aux, epoch);
 }
 
-// dX = epilogue(dY W) (nullable), dW = dY^T x, db = column sums of dY (nullable), from the block a forward
+// dX = epilogue(dY W) (nullable), dW = dY^T x (nullable), db = column sums of dY (nullable), from the block a forward
 // call of the same shapes left in `saved`.  x and W themselves are read only by the Inf / NaN redo.
 inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const float* x, const float* W,
                                   const float* dY, const void* saved, float* dX, int epilogue, const float* aux,
@@ -318,12 +319,13 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
   const size_t bytes_zero = align_up(sizeof(int) * size_t(in), 1024);
   const size_t bytes_part = db ? align_up(sizeof(float) * size_t(bands) * out, 1024) : 0;
   void* ws = nullptr;
-  int32_t rc = workspace_reserve(h, (dX ? 2 : 1) * bytes_planes + bytes_er + bytes_ec + bytes_zero + bytes_part, &ws);
+  const int nsets = (dX ? 1 : 0) + (dW ? 1 : 0);
+  int32_t rc = workspace_reserve(h, nsets * bytes_planes + bytes_er + bytes_ec + bytes_zero + bytes_part, &ws);
   if (rc) return rc;
   char* base = static_cast<char*>(ws);
-  __half* pc = reinterpret_cast<__half*>(base);                                      // column-scaled planes (dW)
-  __half* pr = dX ? reinterpret_cast<__half*>(base + bytes_planes) : nullptr;        // row-scaled planes (dX)
-  char* q = base + (dX ? 2 : 1) * bytes_planes;
+  __half* pc = dW ? reinterpret_cast<__half*>(base) : nullptr;                              // column-scaled planes (dW)
+  __half* pr = dX ? reinterpret_cast<__half*>(base + (dW ? bytes_planes : 0)) : nullptr;   // row-scaled planes (dX)
+  char* q = base + nsets * bytes_planes;
   int* er = reinterpret_cast<int*>(q);
   int* ec = reinterpret_cast<int*>(q + bytes_er);
   int* zero = reinterpret_cast<int*>(q + bytes_er + bytes_ec);
@@ -333,7 +335,7 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
   const uint32_t epoch = ++h->epoch;
   {
     // maxima + column sums: one read of dY; both plane sets: one more read and (one or) two plane writes
-    ProfScope prof(h, PROF_SPLIT, double(M) * (8.0 * out + (dX ? 8.0 : 4.0) * outp));
+    ProfScope prof(h, PROF_SPLIT, double(M) * (8.0 * out + 4.0 * nsets * outp));
     MTB_CUDA(cudaMemsetAsync(er, 0x80, bytes_er + bytes_ec, h->stream));  // every key far below KEY_NONE / 2
     MTB_CUDA(cudaMemsetAsync(zero, 0, bytes_zero, h->stream));
     if (dX)
@@ -350,13 +352,17 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
     const int sp_bands = std::max(1, std::min(M, (h->sm_count * 8 + sp_cols - 1) / sp_cols));
     const int sp_rows = (M + sp_bands - 1) / sp_bands;
     const dim3 sp_grid(sp_cols, (M + sp_rows - 1) / sp_rows);
-    if (dX) dy_split2_kernel<true><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, we, er, pr, pc);
-    else    dy_split2_kernel<false><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, nullptr, nullptr, nullptr, pc);
+    if (dX && dW)
+      dy_split2_kernel<true, true><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, we, er, pr, pc);
+    else if (dX)
+      dy_split2_kernel<true, false><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, we, er, pr, nullptr);
+    else if (dW)
+      dy_split2_kernel<false, true><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, nullptr, nullptr, nullptr, pc);
     MTB_CUDA(cudaGetLastError());
   }
   // dW [out][in] = dY^T x: A = column-scaled dY planes (MN-major, reduction over the batch rows),
   // B = the forward pass's x planes, also MN-major here; their row scales are already inside A.
-  {
+  if (dW) {
     SplitOperand oa{reinterpret_cast<const __nv_bfloat16*>(pc), M, 0, 1, 1, outp, 2, ec};
     SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(xp), M, 0, 1, 1, L.inp, 2, zero};
     rc = run_split_gemm(h, oa, ob, padded_k(M), 1, out, in, dW, in, 0, nullptr, EPI_NONE, nullptr, 23, 5, 0, 0, 0, M);

@@ -527,11 +527,13 @@ int32_t mtb200_dense_backward(mtb200_handle h, int32_t dtype, int64_t rows, int6
   if (dx_epilogue != MTB200_EPI_NONE && dx_epilogue != MTB200_EPI_RELU_BWD)
     return fail(MTB200_ERR_INVALID, "dense backward epilogue must be NONE or RELU_BWD");
   if (dX && dx_epilogue == MTB200_EPI_RELU_BWD && !dx_aux) return fail(MTB200_ERR_INVALID, "RELU_BWD epilogue needs aux");
-  if (!dW) return fail(MTB200_ERR_INVALID, "null weight-gradient pointer");
   if (!saved || !dense_uses_saved(dtype, rows, in_features, out_features)) {
-    int32_t rc = mtb200_gemm(h, dtype, 1, 0, 1, out_features, in_features, rows, dY, 0, x, 0, dW, 0, nullptr,
-                             MTB200_EPI_NONE, nullptr, 0);
-    if (rc) return rc;
+    int32_t rc = MTB200_OK;
+    if (dW) {
+      rc = mtb200_gemm(h, dtype, 1, 0, 1, out_features, in_features, rows, dY, 0, x, 0, dW, 0, nullptr,
+                       MTB200_EPI_NONE, nullptr, 0);
+      if (rc) return rc;
+    }
     if (dX) {
       rc = mtb200_gemm(h, dtype, 0, 0, 1, rows, in_features, out_features, dY, 0, W, 0, dX, 0, nullptr, dx_epilogue,
                        dx_aux, 0);

@@ -59,12 +59,14 @@ class MLPTrainer:
     def __init__(self, dims: Sequence[int], batch: int, *, lr: float = 1e-3, beta1: float = 0.9,
                  beta2: float = 0.999, eps: float = 1e-8, device: int = 0, world_size: int = 1,
                  seed: int = 0, f32_mode: int = 0, init_params: Optional[np.ndarray] = None,
-                 fused_dense: Optional[bool] = None):
+                 fused_dense: Optional[bool] = None, overlap_comm: Optional[bool] = None):
         """``batch`` is the number of rows THIS process handles per step.
 
         ``fused_dense`` (default: on for the default f32 mode) runs every layer through the dense-layer
         entry points, whose backward re-uses the operands the forward prepared; off, each product is a
-        separate GEMM call as the reference's autograd issues them."""
+        separate GEMM call as the reference's autograd issues them.  ``overlap_comm`` (default: on when
+        ``world_size > 1``) selects the backward order that hides the gradient all-reduces and the Adam
+        update behind the products (see ``_backward_overlapped``); the results do not depend on it."""
         if len(dims) < 2 or any(d <= 0 for d in dims) or batch <= 0:
             raise ValueError("dims needs at least two positive entries and batch must be positive")
         self.dims = [int(d) for d in dims]
@@ -76,6 +78,7 @@ class MLPTrainer:
         self.fused_dense = (f32_mode == 0) if fused_dense is None else bool(fused_dense)
         if self.fused_dense and f32_mode != 0:
             raise ValueError("fused_dense uses the default f32 mode")
+        self.overlap_comm = (self.world_size > 1) if overlap_comm is None else bool(overlap_comm)
         self.be: Backend = get_backend(device)
         dev = self.be.device
         self.w_off, self.b_off, total = mlp_layout(self.dims)
@@ -118,6 +121,7 @@ class MLPTrainer:
         self._copy_stream = torch.cuda.Stream(device=dev)
         self._copy_done = [None, None]
         self._slot = 0
+        self._side_stream = None
 
     # ------------------------------------------------------------------ host batches
     def prefetch(self, x_host: torch.Tensor, labels_host: torch.Tensor) -> int:
@@ -162,6 +166,10 @@ class MLPTrainer:
             raise ValueError(f"expected input of shape {(self.batch, self.dims[0])}, got {tuple(x.shape)}")
         logits = self.forward(x)
         loss, _ = be.cross_entropy_into(logits, labels, self.g[self.nl - 1])
+        self.step_count += 1
+        if self.overlap_comm and self.fused_dense:
+            self._backward_overlapped(x)
+            return loss
         handles = []
         for l in range(self.nl - 1, -1, -1):
             g = self.g[l]
@@ -184,10 +192,40 @@ class MLPTrainer:
                         f32_mode=self.f32_mode)                                            # (g W) * relu'
         for hnd in handles:
             hnd.wait()
-        self.step_count += 1
         be.adam_step(self.params, self.grads, self.m, self.v, lr=self.lr, beta1=self.beta1, beta2=self.beta2,
                      eps=self.eps, step=self.step_count, grad_scale=1.0 / self.world_size)
         return loss
+
+    def _backward_overlapped(self, x: torch.Tensor) -> None:
+        """Backward + update for data-parallel runs, ordered so that communication hides behind the products:
+        first the chain of input gradients (no parameter gradient yet), then the parameter gradients from the
+        FIRST layer on - the first layer's is the largest, so its all-reduce starts earliest and the one
+        left exposed at the end is the last layer's small one - and each layer's Adam update on a side
+        stream as soon as its all-reduce has landed (HBM-bound, so it overlaps the tensor-bound products)."""
+        import torch.distributed as dist
+        be = self.be
+        for l in range(self.nl - 1, 0, -1):
+            be.dense_backward(self.h[l - 1], self.W[l], self.g[l], self.saved[l], need_dx=True, dx=self.g[l - 1],
+                              dx_epilogue=EPI_RELU_BWD, dx_aux=self.h[l - 1], need_dw=False, need_db=False)
+        main = torch.cuda.current_stream(be.device)
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=be.device)
+        side = self._side_stream
+        for l in range(self.nl):
+            a_in = x if l == 0 else self.h[l - 1]
+            be.dense_backward(a_in, self.W[l], self.g[l], self.saved[l], need_dx=False, dw=self.dW[l], db=self.db[l])
+            lo, hi = self.w_off[l], self.b_off[l] + self.dims[l + 1]
+            hnd = (dist.all_reduce(self.grads[lo:hi], op=dist.ReduceOp.SUM, async_op=True)
+                   if self.world_size > 1 else None)
+            if hnd is None:
+                side.wait_stream(main)
+            with torch.cuda.stream(side):
+                if hnd is not None:
+                    hnd.wait()   # the side stream waits for the collective, the main stream keeps issuing products
+                be.adam_step(self.params[lo:hi], self.grads[lo:hi], self.m[lo:hi], self.v[lo:hi], lr=self.lr,
+                             beta1=self.beta1, beta2=self.beta2, eps=self.eps, step=self.step_count,
+                             grad_scale=1.0 / self.world_size)
+        main.wait_stream(side)
 
     def flops_per_sample(self) -> int:
         return mlp_flops_per_sample(self.dims)

@@ -194,3 +194,23 @@ def test_nn_dense_layer_uses_the_pair_when_training(be, orc, rng):
     assert nerr(x.grad.numpy(), gx.astype(np.float64), go, wn) <= F32_TOL
     assert nerr(layer.weight.grad.numpy(), gwt.T.astype(np.float64), go.T, xn) <= F32_TOL
     np.testing.assert_allclose(layer.bias.grad.numpy(), orc.sum_dim0(go), rtol=1e-4, atol=1e-4)
+
+
+def test_mlp_trainer_overlapped_schedule_gives_identical_parameters(be):
+    """The multi-GPU backward order (input-gradient chain first, parameter gradients from the first layer on,
+    per-layer Adam on a side stream) on one GPU: same bits as the default order."""
+    from minitensor_b200.mlp import MLPTrainer
+    dims, batch = [200, 260, 192, 150], 320
+    g = np.random.default_rng(12)
+    x = dev(be, g.standard_normal((batch, dims[0])).astype(np.float32))
+    y = torch.from_numpy(g.integers(0, dims[-1], batch)).to(be.device)
+    a = MLPTrainer(dims, batch, seed=3)
+    b = MLPTrainer(dims, batch, seed=3, overlap_comm=True)
+    assert not a.overlap_comm and b.overlap_comm
+    for _ in range(3):
+        la, lb = a.step(x, y), b.step(x, y)
+    be.sync()
+    torch.cuda.synchronize()
+    assert la.item() == lb.item()
+    assert torch.equal(a.grads, b.grads)
+    assert torch.equal(a.params, b.params) and torch.equal(a.m, b.m) and torch.equal(a.v, b.v)
