@@ -269,6 +269,17 @@ int32_t mtb200_sumsq(mtb200_handle h, int32_t dtype, int64_t n, const void* x, d
 int32_t mtb200_scale(mtb200_handle h, int32_t dtype, int64_t n, void* x, double coef);
 int32_t mtb200_clamp(mtb200_handle h, int32_t dtype, int64_t n, void* x, double lo, double hi);
 
+/* ---- the same Adam step with its step count in device memory.  (No counterpart in the reference, whose
+ * optimizer keeps the count on the host.)  For training loops replayed from a CUDA graph: a graph freezes
+ * kernel arguments, so the bias corrections 1/(1 - beta^t) are computed on the device from
+ * *step_counter (one int64 in device memory, 0 before the first step), with the host's own sequence of
+ * f64 products, hence the same bits as mtb200_adam_step(step = t).  advance != 0 increments the
+ * counter before the update (pass it on the first parameter buffer of a step only). */
+int32_t mtb200_adam_step_counted(mtb200_handle h, int64_t n, float* param, const float* grad, float* m,
+                                 float* v, double lr, double beta1, double beta2, double eps,
+                                 double weight_decay, int32_t decoupled, int64_t* step_counter,
+                                 int32_t advance, float grad_scale);
+
 /* ---- conv2d, NCHW input, OIHW weight, f32 (the reference supports nothing
  * else: engine/src/operations/conv.rs:85-93,202-204).
  * forward  = conv2d                     engine/src/operations/conv.rs:24-206

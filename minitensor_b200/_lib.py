@@ -56,6 +56,7 @@ SIGNATURES = {
     "mtb200_clamp": (_i32, [_vp, _i32, _i64, _vp, _f64, _f64]),
     "mtb200_adam_step": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64, _i32,
                                 _i64, _f32]),
+    "mtb200_adam_step_counted": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64, _i32, _vp, _i32, _f32]),
     "mtb200_conv2d_fwd": (_i32, [_vp] + [_i64] * 11 + [_vp, _vp, _vp, _vp, _i32]),
     "mtb200_conv2d_bwd_data": (_i32, [_vp] + [_i64] * 11 + [_vp, _vp, _vp, _i32]),
     "mtb200_conv2d_bwd_weight": (_i32, [_vp] + [_i64] * 11 + [_vp, _vp, _vp, _i32]),

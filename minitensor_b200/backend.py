@@ -313,6 +313,18 @@ class Backend:
             check(self.lib.mtb200_clamp(self._h, dtype_code(g), g.numel(), _ptr(g), lo, hi))
             self.launches += 1
 
+    def adam_step_counted(self, p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *, lr: float,
+                          beta1: float, beta2: float, eps: float, counter: torch.Tensor, advance: bool = True,
+                          weight_decay: float = 0.0, decoupled: bool = False, grad_scale: float = 1.0) -> None:
+        """Adam with the step count in the one-element int64 device tensor ``counter`` (graph-replayable)."""
+        if counter.dtype != torch.int64 or counter.numel() != 1:
+            raise ValueError("counter must be a one-element int64 device tensor")
+        self._bind_stream()
+        check(self.lib.mtb200_adam_step_counted(self._h, p.numel(), _ptr(p), _ptr(g), _ptr(m), _ptr(v), lr, beta1,
+                                                beta2, eps, weight_decay, int(decoupled), _ptr(counter), int(advance),
+                                                grad_scale))
+        self.launches += 2 if advance else 1
+
     # ------------------------------------------------------------------ conv2d
     @staticmethod
     def _geom(xshape, wshape, stride, padding):

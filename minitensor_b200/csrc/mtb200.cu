@@ -653,4 +653,23 @@ int32_t mtb200_adam_step(mtb200_handle h, int64_t n, float* param, const float* 
   return MTB200_OK;
 }
 
+int32_t mtb200_adam_step_counted(mtb200_handle h, int64_t n, float* param, const float* grad, float* m, float* v,
+                                 double lr, double beta1, double beta2, double eps, double weight_decay,
+                                 int32_t decoupled, int64_t* step_counter, int32_t advance, float grad_scale) {
+  MTB_CHECK_HANDLE(h);
+  if (n < 0) return fail(MTB200_ERR_INVALID, "negative length");
+  if (!step_counter) return fail(MTB200_ERR_INVALID, "null step counter");
+  if (advance)
+    counter_add_kernel<<<1, 1, 0, h->stream>>>(reinterpret_cast<long long*>(step_counter), 1);
+  if (n > 0) {
+    if (!param || !grad || !m || !v) return fail(MTB200_ERR_INVALID, "null pointer");
+    const int dec = (decoupled && weight_decay != 0.0) ? 1 : 0;
+    adam_counted_kernel<<<grid_for(n, 256, h->sm_count), 256, 0, h->stream>>>(
+        param, grad, m, v, n, float(lr), beta1, beta2, float(eps), float(weight_decay),
+        reinterpret_cast<const long long*>(step_counter), dec, grad_scale);
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
 }  // extern "C"

@@ -228,30 +228,67 @@ static __global__ void __launch_bounds__(1024) loss_reduce_kernel(const float* _
 //   p -= lr * (m*bc1_inv) / (sqrt(v*bc2_inv) + eps)
 // grad_scale multiplies g first (1 for the reference semantics; 1/world for
 // the mean of per-rank gradients after an all-reduce sum).
+__device__ __forceinline__ void adam_update(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                            float* __restrict__ v, long long i, float lr, float b1, float b2, float omb1,
+                                            float omb2, float eps, float wd, float bc1_inv, float bc2_inv, int decoupled,
+                                            float grad_scale) {
+  float pi = p[i];
+  float gi = g[i];
+  if (grad_scale != 1.0f) gi = __fmul_rn(gi, grad_scale);
+  if (decoupled) {
+    pi = __fsub_rn(pi, __fmul_rn(__fmul_rn(lr, wd), pi));
+  } else {
+    gi = __fadd_rn(gi, __fmul_rn(wd, pi));
+  }
+  const float mi = __fadd_rn(__fmul_rn(b1, m[i]), __fmul_rn(omb1, gi));
+  const float vi = __fadd_rn(__fmul_rn(b2, v[i]), __fmul_rn(__fmul_rn(omb2, gi), gi));
+  m[i] = mi;
+  v[i] = vi;
+  const float mhat = __fmul_rn(mi, bc1_inv);
+  const float vhat = __fmul_rn(vi, bc2_inv);
+  const float denom = __fadd_rn(__fsqrt_rn(vhat), eps);
+  p[i] = __fsub_rn(pi, __fdiv_rn(__fmul_rn(lr, mhat), denom));
+}
+
 static __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g,
                             float* __restrict__ m, float* __restrict__ v, long long n, float lr,
                             float b1, float b2, float eps, float wd, float bc1_inv, float bc2_inv,
                             int decoupled, float grad_scale) {
   const float omb1 = __fsub_rn(1.0f, b1), omb2 = __fsub_rn(1.0f, b2);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float pi = p[i];
-    float gi = g[i];
-    if (grad_scale != 1.0f) gi = __fmul_rn(gi, grad_scale);
-    if (decoupled) {
-      pi = __fsub_rn(pi, __fmul_rn(__fmul_rn(lr, wd), pi));
-    } else {
-      gi = __fadd_rn(gi, __fmul_rn(wd, pi));
-    }
-    const float mi = __fadd_rn(__fmul_rn(b1, m[i]), __fmul_rn(omb1, gi));
-    const float vi = __fadd_rn(__fmul_rn(b2, v[i]), __fmul_rn(__fmul_rn(omb2, gi), gi));
-    m[i] = mi;
-    v[i] = vi;
-    const float mhat = __fmul_rn(mi, bc1_inv);
-    const float vhat = __fmul_rn(vi, bc2_inv);
-    const float denom = __fadd_rn(__fsqrt_rn(vhat), eps);
-    p[i] = __fsub_rn(pi, __fdiv_rn(__fmul_rn(lr, mhat), denom));
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    adam_update(p, g, m, v, i, lr, b1, b2, omb1, omb2, eps, wd, bc1_inv, bc2_inv, decoupled, grad_scale);
+}
+
+// a^b for b >= 1 by square and multiply in f64, the same sequence of products the host computes
+// (what f64::powi lowers to), so the bias corrections match the host's bit for bit.
+__device__ __forceinline__ double powi_dev(double a, long long b) {
+  double r = 1.0;
+  while (true) {
+    if (b & 1) r = __dmul_rn(r, a);
+    b >>= 1;
+    if (b == 0) break;
+    a = __dmul_rn(a, a);
   }
+  return r;
+}
+
+static __global__ void counter_add_kernel(long long* counter, long long delta) { *counter += delta; }
+
+// The same update with the step count read from device memory, so that a loop replayed from a CUDA
+// graph (whose kernel arguments are frozen at capture) still advances its bias corrections.
+static __global__ void adam_counted_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                           float* __restrict__ v, long long n, float lr, double beta1, double beta2,
+                                           float eps, float wd, const long long* __restrict__ step_counter,
+                                           int decoupled, float grad_scale) {
+  const long long step = max(1LL, *step_counter);
+  const float bc1_inv = static_cast<float>(__ddiv_rn(1.0, __dsub_rn(1.0, powi_dev(beta1, step))));
+  const float bc2_inv = static_cast<float>(__ddiv_rn(1.0, __dsub_rn(1.0, powi_dev(beta2, step))));
+  const float b1 = static_cast<float>(beta1), b2 = static_cast<float>(beta2);
+  const float omb1 = __fsub_rn(1.0f, b1), omb2 = __fsub_rn(1.0f, b2);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    adam_update(p, g, m, v, i, lr, b1, b2, omb1, omb2, eps, wd, bc1_inv, bc2_inv, decoupled, grad_scale);
 }
 
 }  // namespace mtb

@@ -122,6 +122,9 @@ class MLPTrainer:
         self._copy_done = [None, None]
         self._slot = 0
         self._side_stream = None
+        self._counted = False
+        self._step_dev = None
+        self._graph = None
 
     # ------------------------------------------------------------------ host batches
     def prefetch(self, x_host: torch.Tensor, labels_host: torch.Tensor) -> int:
@@ -158,6 +161,38 @@ class MLPTrainer:
             a = self.h[l]
         return a
 
+    def capture(self, x: torch.Tensor, labels: torch.Tensor):
+        """Record one training step on the fixed device buffers ``x`` / ``labels`` into a CUDA graph and return
+        ``replay() -> loss``: every later step is one graph launch instead of some forty kernel launches, which
+        is what bounds small models.  New batches are copied INTO ``x`` / ``labels`` before a replay.  At least
+        one eager ``step`` must have run (it sizes the library's scratch memory, which may not grow while a
+        stream is being captured); Adam's step count moves to device memory so replays keep advancing it."""
+        if self.world_size != 1:
+            raise ValueError("capture() records single-GPU steps")
+        if self.step_count < 1:
+            raise RuntimeError("run one eager step() before capture()")
+        if tuple(x.shape) != (self.batch, self.dims[0]):
+            raise ValueError(f"expected input of shape {(self.batch, self.dims[0])}, got {tuple(x.shape)}")
+        dev = self.be.device
+        self._step_dev = torch.full((1,), self.step_count, dtype=torch.int64, device=dev)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        self._counted = True
+        try:
+            with torch.cuda.graph(graph):
+                loss = self.step(x, labels)
+        finally:
+            self._counted = False
+        self.step_count -= 1   # recording ran no kernel
+
+        def replay() -> torch.Tensor:
+            graph.replay()
+            self.step_count += 1
+            return loss
+
+        self._graph = graph    # keeps the recorded buffers alive
+        return replay
+
     def step(self, x: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         """One training step on device-resident ``x [batch, in]`` / ``labels [batch]``; returns the
         (local-shard mean) loss as a 1-element device tensor."""
@@ -192,8 +227,12 @@ class MLPTrainer:
                         f32_mode=self.f32_mode)                                            # (g W) * relu'
         for hnd in handles:
             hnd.wait()
-        be.adam_step(self.params, self.grads, self.m, self.v, lr=self.lr, beta1=self.beta1, beta2=self.beta2,
-                     eps=self.eps, step=self.step_count, grad_scale=1.0 / self.world_size)
+        if self._counted:
+            be.adam_step_counted(self.params, self.grads, self.m, self.v, lr=self.lr, beta1=self.beta1,
+                                 beta2=self.beta2, eps=self.eps, counter=self._step_dev, advance=True)
+        else:
+            be.adam_step(self.params, self.grads, self.m, self.v, lr=self.lr, beta1=self.beta1, beta2=self.beta2,
+                         eps=self.eps, step=self.step_count, grad_scale=1.0 / self.world_size)
         return loss
 
     def _backward_overlapped(self, x: torch.Tensor) -> None:
