@@ -269,6 +269,39 @@ int32_t mtb200_sumsq(mtb200_handle h, int32_t dtype, int64_t n, const void* x, d
 int32_t mtb200_scale(mtb200_handle h, int32_t dtype, int64_t n, void* x, double coef);
 int32_t mtb200_clamp(mtb200_handle h, int32_t dtype, int64_t n, void* x, double lo, double hi);
 
+/* ---- batch normalisation (f32 / f64) on x[N][C][S], S = product of the dimensions after the channel
+ * batch_norm (engine/src/operations/normalization.rs:64-187; layers engine/src/nn/normalization.rs).
+ * forward: statistics per channel over N and S (biased variance) when `training` or when a running
+ *   estimate is NULL, else the running estimates; y = (x - mean) / sqrt(var + eps) * weight + bias
+ *   (weight / bias nullable); while training, running = running*(1-momentum) + batch*momentum.
+ *   save_mean / save_invstd (C elements each, nullable) receive what the backward call needs.
+ * backward: the gradient of that composition, which the reference obtains operator by operator:
+ *   dbias = sum dy, dweight = sum dy*xhat, dx = weight*invstd*(dy - dbias/n - xhat*dweight/n) when the
+ *   forward used batch statistics (batch_stats != 0), weight*invstd*dy otherwise.  Outputs nullable.
+ * Sums are accumulated in f64 in a fixed order (deterministic). */
+int32_t mtb200_batch_norm_fwd(mtb200_handle h, int32_t dtype, int64_t N, int64_t C, int64_t S,
+                              const void* x, const void* weight, const void* bias, void* running_mean,
+                              void* running_var, int32_t training, double momentum, double eps, void* y,
+                              void* save_mean, void* save_invstd);
+int32_t mtb200_batch_norm_bwd(mtb200_handle h, int32_t dtype, int64_t N, int64_t C, int64_t S,
+                              const void* x, const void* dy, const void* weight, const void* save_mean,
+                              const void* save_invstd, int32_t batch_stats, void* dx, void* dweight,
+                              void* dbias);
+
+/* ---- dropout (f32 / f64)
+ * generate_dropout_mask + the element-wise product of Dropout / Dropout2d::forward
+ * (engine/src/nn/dropout.rs:21-92,164-187,258-289).
+ * mask[j] = 1/(1-p) with probability 1-p, else 0 (all ones for p = 0, zeros for p = 1).  The reference
+ * draws from its thread-local StdRng, whose stream cannot be reproduced outside it; here entry j keeps
+ * when the top 24 bits of mix64(seed + (offset + j + 1) * 0x9E3779B97F4A7C15) are below (1-p)*2^24
+ * (mix64 = the splitmix64 finaliser), so a mask is a pure function of (seed, offset, j).
+ * mask_mul: y[i] = x[i] * mask[i / inner] - inner = 1 for Dropout, H*W for Dropout2d (mask [N][C]);
+ * the backward pass is the same call on the upstream gradient. */
+int32_t mtb200_dropout_mask(mtb200_handle h, int32_t dtype, int64_t n, double p, uint64_t seed,
+                            uint64_t offset, void* mask);
+int32_t mtb200_mask_mul(mtb200_handle h, int32_t dtype, int64_t n, int64_t inner, const void* x,
+                        const void* mask, void* y);
+
 /* ---- the same Adam step with its step count in device memory.  (No counterpart in the reference, whose
  * optimizer keeps the count on the host.)  For training loops replayed from a CUDA graph: a graph freezes
  * kernel arguments, so the bias corrections 1/(1 - beta^t) are computed on the device from

@@ -325,6 +325,57 @@ class Backend:
                                                 grad_scale))
         self.launches += 2 if advance else 1
 
+    # ------------------------------------------------------------------ batch norm / dropout
+    @staticmethod
+    def _ncs(x: torch.Tensor):
+        if x.dim() < 2:
+            raise ValueError("batch_norm expects input with at least 2 dimensions")
+        sp = 1
+        for d in x.shape[2:]:
+            sp *= d
+        return x.shape[0], x.shape[1], sp
+
+    def batch_norm_fwd(self, x: torch.Tensor, weight=None, bias=None, running_mean=None, running_var=None, *,
+                       training: bool = True, momentum: float = 0.1, eps: float = 1e-5):
+        """Returns ``(y, save_mean, save_invstd, used_batch_stats)``; running estimates are updated in place."""
+        n, c, sp = self._ncs(x)
+        y = torch.empty_like(x)
+        mean = torch.empty(c, dtype=x.dtype, device=x.device)
+        invstd = torch.empty(c, dtype=x.dtype, device=x.device)
+        self._bind_stream()
+        check(self.lib.mtb200_batch_norm_fwd(self._h, dtype_code(x), n, c, sp, _ptr(x), _ptr(weight), _ptr(bias),
+                                             _ptr(running_mean), _ptr(running_var), int(training), momentum, eps,
+                                             _ptr(y), _ptr(mean), _ptr(invstd)))
+        batch_stats = training or running_mean is None or running_var is None
+        self.launches += 3 if batch_stats else 2
+        return y, mean, invstd, batch_stats
+
+    def batch_norm_bwd(self, x, dy, weight, mean, invstd, *, batch_stats: bool = True, need_dx: bool = True,
+                       need_dw: bool = True, need_db: bool = True):
+        n, c, sp = self._ncs(x)
+        dx = torch.empty_like(x) if need_dx else None
+        dw = torch.empty(c, dtype=x.dtype, device=x.device) if need_dw else None
+        db = torch.empty(c, dtype=x.dtype, device=x.device) if need_db else None
+        self._bind_stream()
+        check(self.lib.mtb200_batch_norm_bwd(self._h, dtype_code(x), n, c, sp, _ptr(x), _ptr(dy), _ptr(weight),
+                                             _ptr(mean), _ptr(invstd), int(batch_stats), _ptr(dx), _ptr(dw), _ptr(db)))
+        self.launches += 3 if need_dx else 2
+        return dx, dw, db
+
+    def dropout_mask(self, n: int, p: float, seed: int, offset: int = 0, dtype=torch.float32) -> torch.Tensor:
+        mask = torch.empty(n, dtype=dtype, device=self.device)
+        self._bind_stream()
+        check(self.lib.mtb200_dropout_mask(self._h, _DTYPES[dtype], n, p, seed, offset, _ptr(mask)))
+        self.launches += 1
+        return mask
+
+    def mask_mul(self, x: torch.Tensor, mask: torch.Tensor, inner: int = 1) -> torch.Tensor:
+        y = torch.empty_like(x)
+        self._bind_stream()
+        check(self.lib.mtb200_mask_mul(self._h, dtype_code(x), x.numel(), inner, _ptr(x), _ptr(mask), _ptr(y)))
+        self.launches += 1
+        return y
+
     # ------------------------------------------------------------------ conv2d
     @staticmethod
     def _geom(xshape, wshape, stride, padding):

@@ -195,6 +195,220 @@ static __global__ void __launch_bounds__(1024) row_loss_reduce_kernel(const floa
   if (threadIdx.x == 0) *loss = red[0] * inv_count;
 }
 
+// ------------------------------------------------------------------ batch norm
+// batch_norm (engine/src/operations/normalization.rs:64-187) on x [N][C][S]: statistics per channel over N and
+// S.  Both reductions of the op are "two sums per channel":
+//   forward : sum (x - k), sum (x - k)^2 with k = the channel's first element (a shift that keeps the variance
+//             formula free of cancellation);  backward: sum dy, sum dy * xhat, xhat = (x - mean) * invstd.
+// They share one kernel pair: per-chunk partial sums in f64 (fixed thread assignment and tree), then a fixed-order
+// fold over the chunks.  MODE 0 = forward, 1 = backward.
+template <typename T, int MODE>
+__device__ __forceinline__ void bn_terms(T xv, T dyv, double a, double b, double& t0, double& t1) {
+  if (MODE == 0) {
+    const double d = static_cast<double>(xv) - a;
+    t0 = d;
+    t1 = d * d;
+  } else {
+    const double xh = (static_cast<double>(xv) - a) * b;
+    t0 = static_cast<double>(dyv);
+    t1 = static_cast<double>(dyv) * xh;
+  }
+}
+
+// General layout (S > 1): block (c, chunk) walks j = n * S + s of its chunk; consecutive threads read
+// consecutive s.  a_c / b_c: MODE 0 unused (k is read from x); MODE 1 mean / invstd per channel.
+template <typename T, int MODE>
+static __global__ void __launch_bounds__(256)
+bn_reduce_general_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ a_c,
+                         const T* __restrict__ b_c, long long N, int C, long long S, long long per_chunk,
+                         double* __restrict__ partial) {
+  __shared__ double r0[256], r1[256];
+  const int c = blockIdx.x, chunk = blockIdx.y;
+  const long long total = N * S;
+  const long long lo = chunk * per_chunk, hi = min(total, lo + per_chunk);
+  const double a = MODE == 0 ? static_cast<double>(x[static_cast<long long>(c) * S]) : static_cast<double>(a_c[c]);
+  const double b = MODE == 0 ? 0.0 : static_cast<double>(b_c[c]);
+  double s0 = 0.0, s1 = 0.0;
+  for (long long j = lo + threadIdx.x; j < hi; j += 256) {
+    const long long n = j / S, i = j - n * S;
+    const long long k = (n * C + c) * S + i;
+    double t0, t1;
+    bn_terms<T, MODE>(x[k], MODE == 1 ? dy[k] : T(0), a, b, t0, t1);
+    s0 += t0;
+    s1 += t1;
+  }
+  r0[threadIdx.x] = s0;
+  r1[threadIdx.x] = s1;
+  __syncthreads();
+  for (int o = 128; o; o >>= 1) {
+    if (threadIdx.x < o) {
+      r0[threadIdx.x] += r0[threadIdx.x + o];
+      r1[threadIdx.x] += r1[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    partial[(static_cast<long long>(chunk) * C + c) * 2 + 0] = r0[0];
+    partial[(static_cast<long long>(chunk) * C + c) * 2 + 1] = r1[0];
+  }
+}
+
+// [N][C] layout (S = 1): block = 32 channels x 8 row lanes over a band of rows; a warp reads 32 consecutive channels.
+template <typename T, int MODE>
+static __global__ void __launch_bounds__(256)
+bn_reduce_cols_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ a_c,
+                      const T* __restrict__ b_c, long long N, int C, long long rows_per_band,
+                      double* __restrict__ partial) {
+  __shared__ double r0[8][33], r1[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  const int band = blockIdx.y;
+  const long long lo = band * rows_per_band, hi = min(N, lo + rows_per_band);
+  double s0 = 0.0, s1 = 0.0;
+  if (c < C) {
+    const double a = MODE == 0 ? static_cast<double>(x[c]) : static_cast<double>(a_c[c]);
+    const double b = MODE == 0 ? 0.0 : static_cast<double>(b_c[c]);
+    for (long long n = lo + ry; n < hi; n += 8) {
+      const long long k = n * C + c;
+      double t0, t1;
+      bn_terms<T, MODE>(x[k], MODE == 1 ? dy[k] : T(0), a, b, t0, t1);
+      s0 += t0;
+      s1 += t1;
+    }
+  }
+  r0[ry][cx] = s0;
+  r1[ry][cx] = s1;
+  __syncthreads();
+  if (ry == 0 && c < C) {
+    double t0 = r0[0][cx], t1 = r1[0][cx];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      t0 += r0[k][cx];
+      t1 += r1[k][cx];
+    }
+    partial[(static_cast<long long>(band) * C + c) * 2 + 0] = t0;
+    partial[(static_cast<long long>(band) * C + c) * 2 + 1] = t1;
+  }
+}
+
+// Forward finalize: mean, biased variance, invstd, running estimates (rm = rm*(1-m) + mean*m, likewise the variance).
+template <typename T>
+static __global__ void bn_finalize_fwd_kernel(const double* __restrict__ partial, int chunks, int C, double count,
+                                              const T* __restrict__ x, long long S, double eps, T* __restrict__ mean_out,
+                                              T* __restrict__ invstd_out, T* __restrict__ rm, T* __restrict__ rv,
+                                              T momentum, T one_minus_momentum) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s0 = 0.0, s1 = 0.0;
+  for (int k = 0; k < chunks; ++k) {
+    s0 += partial[(static_cast<long long>(k) * C + c) * 2 + 0];
+    s1 += partial[(static_cast<long long>(k) * C + c) * 2 + 1];
+  }
+  const double shift = static_cast<double>(x[static_cast<long long>(c) * S]);
+  const double md = s0 / count;
+  const T mean = static_cast<T>(shift + md);
+  const T var = static_cast<T>(fmax(s1 / count - md * md, 0.0));
+  mean_out[c] = mean;
+  invstd_out[c] = T(1) / r_sqrt(r_add(var, static_cast<T>(eps)));
+  if (rm && rv) {
+    rm[c] = r_add(r_mul(rm[c], one_minus_momentum), r_mul(mean, momentum));
+    rv[c] = r_add(r_mul(rv[c], one_minus_momentum), r_mul(var, momentum));
+  }
+}
+// Evaluation with running estimates: mean = rm, invstd = 1 / sqrt(rv + eps).
+template <typename T>
+static __global__ void bn_from_running_kernel(const T* __restrict__ rm, const T* __restrict__ rv, int C, double eps,
+                                              T* __restrict__ mean_out, T* __restrict__ invstd_out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  mean_out[c] = rm[c];
+  invstd_out[c] = T(1) / r_sqrt(r_add(rv[c], static_cast<T>(eps)));
+}
+// Backward finalize: db = sum dy, dw = sum dy*xhat; sums[c] = (db, dw) kept in f64 for the dx pass.
+template <typename T>
+static __global__ void bn_finalize_bwd_kernel(const double* __restrict__ partial, int chunks, int C,
+                                              double* __restrict__ sums, T* __restrict__ dw, T* __restrict__ db) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s0 = 0.0, s1 = 0.0;
+  for (int k = 0; k < chunks; ++k) {
+    s0 += partial[(static_cast<long long>(k) * C + c) * 2 + 0];
+    s1 += partial[(static_cast<long long>(k) * C + c) * 2 + 1];
+  }
+  sums[2 * c] = s0;
+  sums[2 * c + 1] = s1;
+  if (db) db[c] = static_cast<T>(s0);
+  if (dw) dw[c] = static_cast<T>(s1);
+}
+// y = (x - mean) * invstd * w + b
+template <typename T>
+static __global__ void bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ mean, const T* __restrict__ invstd,
+                                       const T* __restrict__ w, const T* __restrict__ b, long long total, int C,
+                                       long long S, T* __restrict__ y) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>((i / S) % C);
+    T o = (x[i] - mean[c]) * invstd[c];
+    if (w) o = o * w[c];
+    if (b) o = o + b[c];
+    y[i] = o;
+  }
+}
+// dx = w*invstd * (dy - db/n - xhat*dw/n)  (batch statistics)  |  w*invstd*dy  (fixed statistics)
+template <typename T>
+static __global__ void bn_dx_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ mean,
+                                    const T* __restrict__ invstd, const T* __restrict__ w,
+                                    const double* __restrict__ sums, double inv_count, int batch_stats,
+                                    long long total, int C, long long S, T* __restrict__ dx) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>((i / S) % C);
+    const double g = (w ? static_cast<double>(w[c]) : 1.0) * static_cast<double>(invstd[c]);
+    double v = static_cast<double>(dy[i]);
+    if (batch_stats) {
+      const double xh = (static_cast<double>(x[i]) - static_cast<double>(mean[c])) * static_cast<double>(invstd[c]);
+      v = v - sums[2 * c] * inv_count - xh * sums[2 * c + 1] * inv_count;
+    }
+    dx[i] = static_cast<T>(g * v);
+  }
+}
+
+// ------------------------------------------------------------------ dropout
+// Mask of generate_dropout_mask (engine/src/nn/dropout.rs:21-92): 1/(1-p) with probability 1-p, else 0.  Entry j
+// keeps when the top 24 bits of mix64(seed + (offset + j + 1) * 0x9E3779B97F4A7C15) are below keep * 2^24 (mix64 =
+// the splitmix64 finaliser): a counter-based stream, so any slice of a mask can be regenerated from (seed, offset).
+// y[i] = x[i] * mask[i / inner]; inner = 1 for Dropout, H*W for Dropout2d (one entry per (sample, channel)).
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  return z ^ (z >> 31);
+}
+template <typename T>
+static __global__ void dropout_mask_kernel(long long n, double keep, unsigned long long seed, unsigned long long offset,
+                                           T* __restrict__ mask) {
+  const T scale = T(1) / static_cast<T>(keep);
+  const unsigned int thresh = static_cast<unsigned int>(keep * 16777216.0);
+  for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    T m;
+    if (keep >= 1.0) m = T(1);
+    else if (keep <= 0.0) m = T(0);
+    else {
+      const unsigned int u = static_cast<unsigned int>(
+          mix64(seed + (offset + static_cast<unsigned long long>(j) + 1ULL) * 0x9E3779B97F4A7C15ULL) >> 40);
+      m = u < thresh ? scale : T(0);
+    }
+    mask[j] = m;
+  }
+}
+template <typename T>
+static __global__ void mask_mul_kernel(const T* __restrict__ x, const T* __restrict__ mask, long long n, long long inner,
+                                       T* __restrict__ y) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    y[i] = r_mul(x[i], mask[inner == 1 ? i : i / inner]);
+}
+
 }  // namespace mtb
 
 using namespace mtb;
@@ -355,6 +569,171 @@ int32_t mtb200_cross_entropy_ex(mtb200_handle h, int64_t B, int64_t C, const flo
     row_loss_reduce_kernel<<<1, 1024, 0, h->stream>>>(row_loss, int(B),
                                                       reduction == MTB200_REDUCE_MEAN ? float(1.0 / double(B)) : 1.0f,
                                                       loss);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+}  // extern "C"
+
+// Launches the two-sums-per-channel reduction (see bn_terms).
+template <typename T, int MODE>
+static int32_t bn_reduce(mtb200_ctx* h, const T* x, const T* dy, const T* a_c, const T* b_c, int64_t N, int64_t C,
+                         int64_t S, double* partial, int chunks, int64_t per_chunk) {
+  if (S == 1)
+    bn_reduce_cols_kernel<T, MODE><<<dim3(unsigned((C + 31) / 32), unsigned(chunks)), 256, 0, h->stream>>>(
+        x, dy, a_c, b_c, N, int(C), per_chunk, partial);
+  else
+    bn_reduce_general_kernel<T, MODE><<<dim3(unsigned(C), unsigned(chunks)), 256, 0, h->stream>>>(
+        x, dy, a_c, b_c, N, int(C), S, per_chunk, partial);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+static void bn_chunking(const mtb200_ctx* h, int64_t N, int64_t C, int64_t S, int* chunks, int64_t* per_chunk) {
+  // enough blocks to fill the machine about four times over, at least 2048 reduced elements per block
+  const int64_t units = S == 1 ? N : N * S;                       // rows (cols kernel) or (n, s) pairs
+  const int64_t blocks_c = S == 1 ? (C + 31) / 32 : C;
+  int64_t want = std::max<int64_t>(1, (int64_t(h->sm_count) * 4) / std::max<int64_t>(1, blocks_c));
+  want = std::min<int64_t>(want, std::max<int64_t>(1, units / (S == 1 ? 64 : 2048)));
+  want = std::min<int64_t>(want, 1024);
+  *per_chunk = (units + want - 1) / want;
+  *chunks = int((units + *per_chunk - 1) / *per_chunk);
+}
+
+template <typename T>
+static int32_t batch_norm_fwd_t(mtb200_ctx* h, int64_t N, int64_t C, int64_t S, const T* x, const T* w, const T* b,
+                                T* rm, T* rv, int training, double momentum, double eps, T* y, T* save_mean,
+                                T* save_invstd) {
+  const bool batch_stats = training || !rm || !rv;
+  int chunks = 1;
+  int64_t per_chunk = 0;
+  bn_chunking(h, N, C, S, &chunks, &per_chunk);
+  const size_t bytes_partial = sizeof(double) * 2 * size_t(chunks) * size_t(C);
+  const size_t bytes_stats = ((sizeof(T) * 2 * size_t(C)) + 15) / 16 * 16;
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, bytes_partial + bytes_stats, &ws);
+  if (rc) return rc;
+  double* partial = static_cast<double*>(ws);
+  T* mean = save_mean ? save_mean : reinterpret_cast<T*>(static_cast<char*>(ws) + bytes_partial);
+  T* invstd = save_invstd ? save_invstd : reinterpret_cast<T*>(static_cast<char*>(ws) + bytes_partial) + C;
+  if (batch_stats) {
+    rc = bn_reduce<T, 0>(h, x, nullptr, nullptr, nullptr, N, C, S, partial, chunks, per_chunk);
+    if (rc) return rc;
+    const bool update = training && rm && rv;
+    bn_finalize_fwd_kernel<T><<<unsigned((C + 255) / 256), 256, 0, h->stream>>>(
+        partial, chunks, int(C), double(N) * double(S), x, S, eps, mean, invstd, update ? rm : nullptr,
+        update ? rv : nullptr, static_cast<T>(momentum), static_cast<T>(1.0 - momentum));
+  } else {
+    bn_from_running_kernel<T><<<unsigned((C + 255) / 256), 256, 0, h->stream>>>(rm, rv, int(C), eps, mean, invstd);
+  }
+  const long long total = N * C * S;
+  bn_apply_kernel<T><<<ew_grid(total, h->sm_count), 256, 0, h->stream>>>(x, mean, invstd, w, b, total, int(C), S, y);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+template <typename T>
+static int32_t batch_norm_bwd_t(mtb200_ctx* h, int64_t N, int64_t C, int64_t S, const T* x, const T* dy, const T* w,
+                                const T* mean, const T* invstd, int batch_stats, T* dx, T* dw, T* db) {
+  int chunks = 1;
+  int64_t per_chunk = 0;
+  bn_chunking(h, N, C, S, &chunks, &per_chunk);
+  const size_t bytes_partial = sizeof(double) * 2 * size_t(chunks) * size_t(C);
+  void* ws = nullptr;
+  int32_t rc = workspace_reserve(h, bytes_partial + sizeof(double) * 2 * size_t(C), &ws);
+  if (rc) return rc;
+  double* partial = static_cast<double*>(ws);
+  double* sums = partial + 2 * size_t(chunks) * size_t(C);
+  rc = bn_reduce<T, 1>(h, x, dy, mean, invstd, N, C, S, partial, chunks, per_chunk);
+  if (rc) return rc;
+  bn_finalize_bwd_kernel<T><<<unsigned((C + 255) / 256), 256, 0, h->stream>>>(partial, chunks, int(C), sums, dw, db);
+  if (dx) {
+    const long long total = N * C * S;
+    bn_dx_kernel<T><<<ew_grid(total, h->sm_count), 256, 0, h->stream>>>(x, dy, mean, invstd, w, sums,
+                                                                        1.0 / (double(N) * double(S)), batch_stats, total,
+                                                                        int(C), S, dx);
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+static int32_t bn_check_dims(int64_t N, int64_t C, int64_t S) {
+  if (N < 0 || C < 0 || S < 0) return fail(MTB200_ERR_INVALID, "negative dimension");
+  if (C > INT32_MAX) return fail(MTB200_ERR_INVALID, "channel count exceeds the 32-bit limit of the device kernels");
+  return MTB200_OK;
+}
+
+extern "C" {
+
+int32_t mtb200_batch_norm_fwd(mtb200_handle h, int32_t dtype, int64_t N, int64_t C, int64_t S, const void* x,
+                              const void* weight, const void* bias, void* running_mean, void* running_var,
+                              int32_t training, double momentum, double eps, void* y, void* save_mean,
+                              void* save_invstd) {
+  MTB_CHECK_HANDLE(h);
+  if (int32_t rc = check_float_dtype(dtype, "batch_norm")) return rc;
+  if (int32_t rc = bn_check_dims(N, C, S)) return rc;
+  if (N == 0 || C == 0 || S == 0) return MTB200_OK;
+  if (!x || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  if (dtype == MTB200_F32)
+    return batch_norm_fwd_t<float>(h, N, C, S, static_cast<const float*>(x), static_cast<const float*>(weight),
+                                   static_cast<const float*>(bias), static_cast<float*>(running_mean),
+                                   static_cast<float*>(running_var), training, momentum, eps, static_cast<float*>(y),
+                                   static_cast<float*>(save_mean), static_cast<float*>(save_invstd));
+  return batch_norm_fwd_t<double>(h, N, C, S, static_cast<const double*>(x), static_cast<const double*>(weight),
+                                  static_cast<const double*>(bias), static_cast<double*>(running_mean),
+                                  static_cast<double*>(running_var), training, momentum, eps, static_cast<double*>(y),
+                                  static_cast<double*>(save_mean), static_cast<double*>(save_invstd));
+}
+
+int32_t mtb200_batch_norm_bwd(mtb200_handle h, int32_t dtype, int64_t N, int64_t C, int64_t S, const void* x,
+                              const void* dy, const void* weight, const void* save_mean, const void* save_invstd,
+                              int32_t batch_stats, void* dx, void* dweight, void* dbias) {
+  MTB_CHECK_HANDLE(h);
+  if (int32_t rc = check_float_dtype(dtype, "batch_norm")) return rc;
+  if (int32_t rc = bn_check_dims(N, C, S)) return rc;
+  if (N == 0 || C == 0 || S == 0) return MTB200_OK;
+  if (!x || !dy || !save_mean || !save_invstd) return fail(MTB200_ERR_INVALID, "null pointer");
+  if (dtype == MTB200_F32)
+    return batch_norm_bwd_t<float>(h, N, C, S, static_cast<const float*>(x), static_cast<const float*>(dy),
+                                   static_cast<const float*>(weight), static_cast<const float*>(save_mean),
+                                   static_cast<const float*>(save_invstd), batch_stats, static_cast<float*>(dx),
+                                   static_cast<float*>(dweight), static_cast<float*>(dbias));
+  return batch_norm_bwd_t<double>(h, N, C, S, static_cast<const double*>(x), static_cast<const double*>(dy),
+                                  static_cast<const double*>(weight), static_cast<const double*>(save_mean),
+                                  static_cast<const double*>(save_invstd), batch_stats, static_cast<double*>(dx),
+                                  static_cast<double*>(dweight), static_cast<double*>(dbias));
+}
+
+int32_t mtb200_dropout_mask(mtb200_handle h, int32_t dtype, int64_t n, double p, uint64_t seed, uint64_t offset,
+                            void* mask) {
+  MTB_CHECK_HANDLE(h);
+  if (int32_t rc = check_float_dtype(dtype, "Dropout mask generation")) return rc;
+  if (!(p >= 0.0 && p <= 1.0)) return fail(MTB200_ERR_INVALID, "dropout probability must be in [0, 1], got %g", p);
+  if (n < 0) return fail(MTB200_ERR_INVALID, "negative length");
+  if (n == 0) return MTB200_OK;
+  if (!mask) return fail(MTB200_ERR_INVALID, "null pointer");
+  const int grid = ew_grid(n, h->sm_count);
+  if (dtype == MTB200_F32)
+    dropout_mask_kernel<float><<<grid, 256, 0, h->stream>>>(n, 1.0 - p, seed, offset, static_cast<float*>(mask));
+  else
+    dropout_mask_kernel<double><<<grid, 256, 0, h->stream>>>(n, 1.0 - p, seed, offset, static_cast<double*>(mask));
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+int32_t mtb200_mask_mul(mtb200_handle h, int32_t dtype, int64_t n, int64_t inner, const void* x, const void* mask,
+                        void* y) {
+  MTB_CHECK_HANDLE(h);
+  if (int32_t rc = check_float_dtype(dtype, "dropout")) return rc;
+  if (n < 0 || inner < 1) return fail(MTB200_ERR_INVALID, "bad length");
+  if (n == 0) return MTB200_OK;
+  if (!x || !mask || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  const int grid = ew_grid(n, h->sm_count);
+  if (dtype == MTB200_F32)
+    mask_mul_kernel<float><<<grid, 256, 0, h->stream>>>(static_cast<const float*>(x), static_cast<const float*>(mask), n,
+                                                        inner, static_cast<float*>(y));
+  else
+    mask_mul_kernel<double><<<grid, 256, 0, h->stream>>>(static_cast<const double*>(x), static_cast<const double*>(mask),
+                                                         n, inner, static_cast<double*>(y));
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
 }

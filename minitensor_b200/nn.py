@@ -171,6 +171,136 @@ class Sequential(Module):
         return [p for l in self.layers for p in l.parameters()]
 
 
+# ---------------------------------------------------------------------- batch norm, dropout
+def batch_norm(input: Tensor, running_mean: Optional[Tensor] = None, running_var: Optional[Tensor] = None,
+               weight: Optional[Tensor] = None, bias: Optional[Tensor] = None, training: bool = False,
+               momentum: float = 0.1, eps: float = 1e-5) -> Tensor:
+    """``batch_norm`` of the reference (``engine/src/operations/normalization.rs:64-187``): channel dimension 1,
+    running estimates updated in place while training."""
+    if input.ndim < 2:
+        raise ValueError("batch_norm expects input with at least 2 dimensions")
+    c = input.shape[1]
+    for t in (weight, bias, running_mean, running_var):
+        if t is not None and (t.ndim != 1 or t.shape[0] != c):
+            raise ValueError(f"shape mismatch: expected [{c}], got {list(t.shape)}")
+    if input.dtype not in ("float32", "float64"):
+        raise TypeError("batch_norm supports float32/float64 tensors")
+    be = _be()
+    x = input._buf.contiguous()
+    wb = weight._buf if weight is not None else None
+    y, mean, invstd, batch_stats = be.batch_norm_fwd(
+        x, wb, bias._buf if bias is not None else None, running_mean._buf if running_mean is not None else None,
+        running_var._buf if running_var is not None else None, training=training, momentum=momentum, eps=eps)
+    parents = (input,) + ((weight,) if weight is not None else ()) + ((bias,) if bias is not None else ())
+
+    def bw(g):
+        dx, dw, db = be.batch_norm_bwd(x, g.contiguous(), wb, mean, invstd, batch_stats=batch_stats,
+                                       need_dx=input.requires_grad,
+                                       need_dw=weight is not None and weight.requires_grad,
+                                       need_db=bias is not None and bias.requires_grad)
+        return (dx,) + ((dw,) if weight is not None else ()) + ((db,) if bias is not None else ())
+
+    return input._result(y, parents, bw)
+
+
+class _BatchNorm(Module):
+    """Weight ones, bias zeros, running mean zeros, running variance ones (``engine/src/nn/normalization.rs``)."""
+    _ndims: Tuple[int, ...] = ()
+
+    def __init__(self, num_features: int, eps: float = 1e-5, momentum: float = 0.1, dtype: str = "float32"):
+        if num_features <= 0:
+            raise ValueError("num_features must be positive")
+        self.num_features, self.eps, self.momentum = num_features, eps, momentum
+        self.weight = Tensor(np.ones(num_features, dtype=dtype), requires_grad=True)
+        self.bias = Tensor(np.zeros(num_features, dtype=dtype), requires_grad=True)
+        self.running_mean = Tensor(np.zeros(num_features, dtype=dtype))
+        self.running_var = Tensor(np.ones(num_features, dtype=dtype))
+        self.training = True
+
+    def train(self):
+        self.training = True
+        return self
+
+    def eval(self):
+        self.training = False
+        return self
+
+    def forward(self, x: Tensor) -> Tensor:
+        if x.ndim not in self._ndims:
+            raise ValueError(f"{type(self).__name__} expects input with {' or '.join(map(str, self._ndims))} dimensions")
+        if x.shape[1] != self.num_features:
+            raise ValueError(f"shape mismatch: expected {self.num_features} features, got {x.shape[1]}")
+        return batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias, self.training,
+                          self.momentum, self.eps)
+
+    def parameters(self) -> List[Tensor]:
+        return [self.weight, self.bias]
+
+
+class BatchNorm1d(_BatchNorm):
+    _ndims = (2, 3)
+
+
+class BatchNorm2d(_BatchNorm):
+    _ndims = (4,)
+
+
+_dropout_calls = [0]
+
+
+def dropout(input: Tensor, p: float = 0.5, training: bool = True, seed: Optional[int] = None, *, _channels: bool = False) -> Tensor:
+    """``Dropout::forward`` (``engine/src/nn/dropout.rs:164-187``): identity when not training or p = 0, zeros for
+    p = 1, otherwise the input times a mask of 0 / 1/(1-p) entries.  ``seed`` fixes the mask; without it every call
+    takes the next stream of the process-wide generator (``manual_seed``)."""
+    if not (0.0 <= p <= 1.0):
+        raise ValueError(f"dropout probability must be between 0 and 1, got {p}")
+    if _channels and input.ndim != 4:
+        raise ValueError("Dropout2d expects 4D input tensor with shape [batch_size, channels, height, width]")
+    if not training or p == 0.0:
+        return input
+    be = _be()
+    if seed is None:
+        _dropout_calls[0] += 1
+        seed = (_global_seed[0] * 0x9E3779B1 + _dropout_calls[0]) & 0xFFFFFFFFFFFFFFFF
+    x = input._buf.contiguous()
+    inner = x.shape[2] * x.shape[3] if _channels else 1
+    mask = be.dropout_mask(x.numel() // inner, p, seed, 0, x.dtype)
+    y = be.mask_mul(x, mask, inner)
+    return input._result(y, (input,), lambda g: (be.mask_mul(g.contiguous(), mask, inner),))
+
+
+_global_seed = [0]
+
+
+def manual_seed(seed: int) -> None:
+    """Seeds the dropout generator of this process (the counterpart of ``mt.manual_seed``)."""
+    _global_seed[0] = int(seed)
+    _dropout_calls[0] = 0
+
+
+class Dropout(Module):
+    def __init__(self, p: float = 0.5):
+        if not (0.0 <= p <= 1.0):
+            raise ValueError(f"dropout probability must be between 0 and 1, got {p}")
+        self.p, self.training = p, True
+
+    def train(self):
+        self.training = True
+        return self
+
+    def eval(self):
+        self.training = False
+        return self
+
+    def forward(self, x: Tensor) -> Tensor:
+        return dropout(x, self.p, self.training)
+
+
+class Dropout2d(Dropout):
+    def forward(self, x: Tensor) -> Tensor:
+        return dropout(x, self.p, self.training, _channels=True)
+
+
 # ---------------------------------------------------------------------- conv
 def conv2d(input: Tensor, weight: Tensor, bias: Optional[Tensor] = None, stride: _Pair = 1,
            padding: _Pair = 0) -> Tensor:

@@ -274,6 +274,49 @@ def clip_grad_value(grads, lo: float, hi: float) -> None:
         getattr(lib(), "orc_clamp_" + _sfx(g))(_i64(g.size), _ptr(g), _f64(lo), _f64(hi))
 
 
+def batch_norm(x, weight=None, bias=None, running_mean=None, running_var=None, training=True, momentum=0.1,
+               eps=1e-5):
+    """``x [N, C, *spatial]`` float32/float64; running estimates are updated in place while training.
+    Returns ``(y, save_mean, save_invstd)``."""
+    x = np.ascontiguousarray(x)
+    sfx = _sfx(x)
+    n, c = x.shape[0], x.shape[1]
+    sp = int(np.prod(x.shape[2:])) if x.ndim > 2 else 1
+    y = np.empty_like(x)
+    mean = np.empty(c, x.dtype)
+    invstd = np.empty(c, x.dtype)
+    w = _c(weight, x.dtype) if weight is not None else None
+    b = _c(bias, x.dtype) if bias is not None else None
+    for r in (running_mean, running_var):
+        assert r is None or (r.dtype == x.dtype and r.flags.c_contiguous)
+    getattr(lib(), "orc_batch_norm_fwd_" + sfx)(_i64(n), _i64(c), _i64(sp), _ptr(x), _ptr(w), _ptr(b),
+                                                _ptr(running_mean), _ptr(running_var), _int(int(training)),
+                                                _f64(momentum), _f64(eps), _ptr(y), _ptr(mean), _ptr(invstd))
+    return y, mean, invstd
+
+
+def batch_norm_backward(x, dy, weight, mean, invstd, batch_stats=True):
+    x = np.ascontiguousarray(x)
+    sfx = _sfx(x)
+    dy = _c(dy, x.dtype)
+    n, c = x.shape[0], x.shape[1]
+    sp = int(np.prod(x.shape[2:])) if x.ndim > 2 else 1
+    dx = np.empty_like(x)
+    dw = np.empty(c, x.dtype)
+    db = np.empty(c, x.dtype)
+    w = _c(weight, x.dtype) if weight is not None else None
+    getattr(lib(), "orc_batch_norm_bwd_" + sfx)(_i64(n), _i64(c), _i64(sp), _ptr(x), _ptr(dy), _ptr(w),
+                                                _ptr(_c(mean, x.dtype)), _ptr(_c(invstd, x.dtype)),
+                                                _int(int(batch_stats)), _ptr(dx), _ptr(dw), _ptr(db))
+    return dx, dw, db
+
+
+def dropout_mask(n: int, p: float, seed: int, offset: int = 0) -> np.ndarray:
+    mask = np.empty(n, np.float32)
+    lib().orc_dropout_mask_f32(_i64(n), _f64(p), C.c_uint64(seed), C.c_uint64(offset), _ptr(mask))
+    return mask
+
+
 def adam_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay=0.0, decoupled=False, step=1) -> None:
     """In place on ``p``, ``m``, ``v`` (contiguous float32 arrays)."""
     for a in (p, m, v):

@@ -694,6 +694,125 @@ void orc_clamp_f64(int64_t n, double* x, double lo, double hi) {
   for (int64_t i = 0; i < n; ++i) x[i] = x[i] < lo ? lo : (x[i] > hi ? hi : x[i]);
 }
 
+// ------------------------------------------------------------------ batch norm, dropout
+}  // extern "C"
+// batch_norm (engine/src/operations/normalization.rs:64-187) on x [N][C][S] (S = product of the trailing
+// dimensions): statistics per channel over N and S, biased variance, y = (x - mean) / sqrt(var + eps) * w + b;
+// batch statistics are used when training or when a running estimate is missing; while training the running
+// estimates become running * (1 - momentum) + batch * momentum.  Sums are accumulated in f64 here (the
+// reference's f32 sums depend on its thread count), element arithmetic in T.
+template <typename T>
+static void batch_norm_fwd(int64_t N, int64_t C, int64_t S, const T* x, const T* w, const T* b, T* rm, T* rv,
+                           int training, double momentum, double eps, T* y, T* save_mean, T* save_invstd) {
+  const bool batch_stats = training || !rm || !rv;
+  const double cnt = static_cast<double>(N) * static_cast<double>(S);
+  for (int64_t c = 0; c < C; ++c) {
+    T mean, var;
+    if (batch_stats) {
+      double s = 0.0;
+      for (int64_t n = 0; n < N; ++n)
+        for (int64_t i = 0; i < S; ++i) s += x[(n * C + c) * S + i];
+      mean = static_cast<T>(s / cnt);
+      double q = 0.0;
+      for (int64_t n = 0; n < N; ++n)
+        for (int64_t i = 0; i < S; ++i) {
+          const T d = x[(n * C + c) * S + i] - mean;
+          q += static_cast<double>(d * d);
+        }
+      var = static_cast<T>(q / cnt);
+    } else {
+      mean = rm[c];
+      var = rv[c];
+    }
+    const T stdv = std::sqrt(var + static_cast<T>(eps));
+    for (int64_t n = 0; n < N; ++n)
+      for (int64_t i = 0; i < S; ++i) {
+        T o = (x[(n * C + c) * S + i] - mean) / stdv;
+        if (w) o = o * w[c];
+        if (b) o = o + b[c];
+        y[(n * C + c) * S + i] = o;
+      }
+    if (save_mean) save_mean[c] = mean;
+    if (save_invstd) save_invstd[c] = static_cast<T>(1) / stdv;
+    if (training && rm && rv) {
+      const T m = static_cast<T>(momentum), om = static_cast<T>(1.0 - momentum);
+      rm[c] = rm[c] * om + mean * m;
+      rv[c] = rv[c] * om + var * m;
+    }
+  }
+}
+// Gradient of the composition above (the reference differentiates it operator by operator): with
+// xh = (x - mean) * invstd, db = sum dy, dw = sum dy * xh, and for batch statistics
+// dx = w * invstd * (dy - db/n - xh * dw/n); with fixed (running) statistics dx = w * invstd * dy.
+template <typename T>
+static void batch_norm_bwd(int64_t N, int64_t C, int64_t S, const T* x, const T* dy, const T* w, const T* mean,
+                           const T* invstd, int batch_stats, T* dx, T* dw, T* db) {
+  const double cnt = static_cast<double>(N) * static_cast<double>(S);
+  for (int64_t c = 0; c < C; ++c) {
+    double sb = 0.0, sw = 0.0;
+    for (int64_t n = 0; n < N; ++n)
+      for (int64_t i = 0; i < S; ++i) {
+        const int64_t k = (n * C + c) * S + i;
+        const double xh = (static_cast<double>(x[k]) - mean[c]) * invstd[c];
+        sb += dy[k];
+        sw += dy[k] * xh;
+      }
+    if (db) db[c] = static_cast<T>(sb);
+    if (dw) dw[c] = static_cast<T>(sw);
+    if (dx) {
+      const double g = (w ? static_cast<double>(w[c]) : 1.0) * invstd[c];
+      for (int64_t n = 0; n < N; ++n)
+        for (int64_t i = 0; i < S; ++i) {
+          const int64_t k = (n * C + c) * S + i;
+          const double xh = (static_cast<double>(x[k]) - mean[c]) * invstd[c];
+          dx[k] = static_cast<T>(batch_stats ? g * (dy[k] - sb / cnt - xh * sw / cnt) : g * dy[k]);
+        }
+    }
+  }
+}
+extern "C" {
+void orc_batch_norm_fwd_f32(int64_t N, int64_t C, int64_t S, const float* x, const float* w, const float* b, float* rm,
+                            float* rv, int training, double momentum, double eps, float* y, float* save_mean,
+                            float* save_invstd) {
+  batch_norm_fwd<float>(N, C, S, x, w, b, rm, rv, training, momentum, eps, y, save_mean, save_invstd);
+}
+void orc_batch_norm_fwd_f64(int64_t N, int64_t C, int64_t S, const double* x, const double* w, const double* b,
+                            double* rm, double* rv, int training, double momentum, double eps, double* y,
+                            double* save_mean, double* save_invstd) {
+  batch_norm_fwd<double>(N, C, S, x, w, b, rm, rv, training, momentum, eps, y, save_mean, save_invstd);
+}
+void orc_batch_norm_bwd_f32(int64_t N, int64_t C, int64_t S, const float* x, const float* dy, const float* w,
+                            const float* mean, const float* invstd, int batch_stats, float* dx, float* dw, float* db) {
+  batch_norm_bwd<float>(N, C, S, x, dy, w, mean, invstd, batch_stats, dx, dw, db);
+}
+void orc_batch_norm_bwd_f64(int64_t N, int64_t C, int64_t S, const double* x, const double* dy, const double* w,
+                            const double* mean, const double* invstd, int batch_stats, double* dx, double* dw,
+                            double* db) {
+  batch_norm_bwd<double>(N, C, S, x, dy, w, mean, invstd, batch_stats, dx, dw, db);
+}
+
+// Dropout mask (engine/src/nn/dropout.rs:21-92): entries are 1/(1-p) with probability 1-p, else 0; p >= 1 gives
+// zeros, p <= 0 ones.  The reference draws from its thread-local StdRng, whose stream cannot be reproduced
+// outside it; this build's generator is counter-based: entry j of a mask with (seed, offset) keeps when the top
+// 24 bits of mix64(seed + (offset + j + 1) * 0x9E3779B97F4A7C15) are below keep * 2^24, mix64 being the
+// splitmix64 finaliser.
+static inline uint64_t mix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  return z ^ (z >> 31);
+}
+void orc_dropout_mask_f32(int64_t n, double p, uint64_t seed, uint64_t offset, float* mask) {
+  const double keep = 1.0 - p;
+  const float scale = 1.0f / static_cast<float>(keep);
+  const uint32_t thresh = static_cast<uint32_t>(keep * 16777216.0);
+  for (int64_t j = 0; j < n; ++j) {
+    if (keep >= 1.0) { mask[j] = 1.0f; continue; }
+    if (keep <= 0.0) { mask[j] = 0.0f; continue; }
+    const uint32_t u = static_cast<uint32_t>(mix64(seed + (offset + static_cast<uint64_t>(j) + 1) * 0x9E3779B97F4A7C15ULL) >> 40);
+    mask[j] = u < thresh ? scale : 0.0f;
+  }
+}
+
 // ------------------------------------------------------------------ Adam
 // Adam::apply_adam_update, no amsgrad: engine/src/optim/adam.rs:245-312.
 void orc_adam_step_f32(int64_t n, float* p, const float* g, float* m, float* v, double lr, double beta1,

@@ -247,3 +247,58 @@ def test_sgd_rmsprop_clipping_known_answers(orc, golden):
     g = np.array([np.nan, 5.0], dtype=np.float32)
     orc.clip_grad_value([g], -1.0, 1.0)
     assert np.isnan(g[0]) and g[1] == 1.0
+
+
+def test_batch_norm_known_answers(orc, golden):
+    for case in golden["batch_norm"]:
+        if case.get("eval_only"):
+            rm = np.array(case["running_mean"], np.float32)
+            rv = np.array(case["running_var"], np.float32)
+        else:
+            x = np.array(case["train_x"], np.float32)
+            c = x.shape[1]
+            rm, rv = np.zeros(c, np.float32), np.ones(c, np.float32)
+            w = np.array(case["weight"], np.float32) if "weight" in case else None
+            b = np.array(case["bias"], np.float32) if "bias" in case else None
+            y, _, _ = orc.batch_norm(x, w, b, rm, rv, True, case["momentum"], case["eps"])
+            if "train_y" in case:
+                np.testing.assert_allclose(y, case["train_y"], rtol=0, atol=case["atol"])
+            if "running_mean_after" in case:
+                np.testing.assert_allclose(rm, case["running_mean_after"], rtol=0, atol=case["atol"])
+            if "running_var_after" in case:
+                np.testing.assert_allclose(rv, case["running_var_after"], rtol=0, atol=case["atol"])
+        if "eval_x" in case:
+            before = rm.copy()
+            y, _, _ = orc.batch_norm(np.array(case["eval_x"], np.float32), None, None, rm, rv, False, 0.1, case["eps"])
+            np.testing.assert_allclose(y, case["eval_y"], rtol=0, atol=case["atol"])
+            np.testing.assert_array_equal(rm, before)      # eval leaves the running estimates alone
+
+
+def test_batch_norm_backward_finite_difference_and_dropout_mask(orc, rng):
+    x = rng.standard_normal((5, 3, 4)).astype(np.float64)
+    w = rng.standard_normal(3)
+    b = rng.standard_normal(3)
+    go = rng.standard_normal(x.shape)
+    y, mean, invstd = orc.batch_norm(x, w, b, None, None, True, 0.1, 1e-5)
+    dx, dw, db = orc.batch_norm_backward(x, go, w, mean, invstd, True)
+    f = lambda xx, ww, bb: float((orc.batch_norm(xx, ww, bb, None, None, True, 0.1, 1e-5)[0] * go).sum())
+    h = 1e-6
+    for idx in [(0, 0, 0), (2, 1, 3), (4, 2, 1)]:
+        xp, xm = x.copy(), x.copy()
+        xp[idx] += h
+        xm[idx] -= h
+        assert abs((f(xp, w, b) - f(xm, w, b)) / (2 * h) - dx[idx]) < 1e-5
+    for c in range(3):
+        wp, wm = w.copy(), w.copy()
+        wp[c] += h
+        wm[c] -= h
+        assert abs((f(x, wp, b) - f(x, wm, b)) / (2 * h) - dw[c]) < 1e-5
+    np.testing.assert_allclose(db, go.sum(axis=(0, 2)), rtol=1e-12)
+    # dropout mask: extreme probabilities (tests/nn/test_functional.py:498-506), scale, keep rate, determinism
+    assert np.all(orc.dropout_mask(100, 0.0, 1) == 1.0) and not orc.dropout_mask(100, 1.0, 1).any()
+    m = orc.dropout_mask(200_000, 0.3, seed=42)
+    assert set(np.unique(m)) == {np.float32(0.0), np.float32(1.0) / np.float32(0.7)}
+    assert abs((m != 0).mean() - 0.7) < 0.005
+    np.testing.assert_array_equal(m, orc.dropout_mask(200_000, 0.3, seed=42))
+    np.testing.assert_array_equal(m[1000:], orc.dropout_mask(199_000, 0.3, seed=42, offset=1000))
+    assert (orc.dropout_mask(200_000, 0.3, seed=43) != m).mean() > 0.3

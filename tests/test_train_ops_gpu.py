@@ -192,3 +192,117 @@ def test_cross_entropy_general_known_answers_and_nn_mirror(be, golden):
         nn.cross_entropy(x, mt.Tensor(t_np), reduction="avg")
     with pytest.raises(IndexError):                                   # class index out of range
         nn.cross_entropy(mt.Tensor(np.zeros((2, 3), np.float32)), mt.Tensor(np.array([0, 3], np.int64)))
+
+
+# ------------------------------------------------------------------ batch norm
+@pytest.mark.parametrize("shape", [(64, 128), (37, 5), (8, 6, 50), (4, 3, 17, 19), (300, 4096)])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_batch_norm_forward_backward_against_oracle(be, orc, rng, shape, dtype):
+    x = (rng.standard_normal(shape) * 3 + 7).astype(dtype)      # a mean well away from zero
+    c = shape[1]
+    w, b = rng.standard_normal(c).astype(dtype), rng.standard_normal(c).astype(dtype)
+    rm, rv = rng.standard_normal(c).astype(dtype), (rng.random(c) + 0.5).astype(dtype)
+    go = rng.standard_normal(shape).astype(dtype)
+    tol = 2e-5 if dtype == np.float32 else 1e-11
+    for training in (True, False):
+        rm_o, rv_o = rm.copy(), rv.copy()
+        rm_d, rv_d = dev(be, rm), dev(be, rv)
+        y_ref, mean_ref, inv_ref = orc.batch_norm(x, w, b, rm_o, rv_o, training, 0.1, 1e-5)
+        y, mean, inv, batch_stats = be.batch_norm_fwd(dev(be, x), dev(be, w), dev(be, b), rm_d, rv_d, training=training,
+                                                      momentum=0.1, eps=1e-5)
+        assert batch_stats == training
+        be.sync()
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=tol, atol=tol * 10)
+        np.testing.assert_allclose(rm_d.cpu().numpy(), rm_o, rtol=tol, atol=tol)
+        np.testing.assert_allclose(rv_d.cpu().numpy(), rv_o, rtol=tol, atol=tol)
+        dx_ref, dw_ref, db_ref = orc.batch_norm_backward(x, go, w, mean_ref, inv_ref, batch_stats)
+        dx, dw, db = be.batch_norm_bwd(dev(be, x), dev(be, go), dev(be, w), mean, inv, batch_stats=batch_stats)
+        be.sync()
+        scale = max(1.0, float(np.abs(dw_ref).max()))
+        np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=tol * 5, atol=tol * 50)
+        np.testing.assert_allclose(dw.cpu().numpy(), dw_ref, rtol=tol * 5, atol=tol * 5 * scale)
+        np.testing.assert_allclose(db.cpu().numpy(), db_ref, rtol=tol * 5, atol=tol * 5 * scale)
+
+
+def test_batch_norm_known_answers_and_layers(be, golden):
+    import minitensor_b200.nn as nn
+    import minitensor_b200.tensor as mt
+    for case in golden["batch_norm"]:
+        if case.get("eval_only"):
+            rm = mt.Tensor(np.array(case["running_mean"], np.float32))
+            rv = mt.Tensor(np.array(case["running_var"], np.float32))
+        else:
+            x = mt.Tensor(np.array(case["train_x"], np.float32))
+            c = x.shape[1]
+            rm, rv = mt.Tensor(np.zeros(c, np.float32)), mt.Tensor(np.ones(c, np.float32))
+            w = mt.Tensor(np.array(case["weight"], np.float32)) if "weight" in case else None
+            b = mt.Tensor(np.array(case["bias"], np.float32)) if "bias" in case else None
+            y = nn.batch_norm(x, rm, rv, w, b, training=True, momentum=case["momentum"], eps=case["eps"])
+            if "train_y" in case:
+                np.testing.assert_allclose(y.numpy(), case["train_y"], rtol=0, atol=case["atol"])
+            if "running_mean_after" in case:
+                np.testing.assert_allclose(rm.numpy(), case["running_mean_after"], rtol=0, atol=case["atol"])
+            if "running_var_after" in case:
+                np.testing.assert_allclose(rv.numpy(), case["running_var_after"], rtol=0, atol=case["atol"])
+        if "eval_x" in case:
+            y = nn.batch_norm(mt.Tensor(np.array(case["eval_x"], np.float32)), rm, rv, training=False, eps=case["eps"])
+            np.testing.assert_allclose(y.numpy(), case["eval_y"], rtol=0, atol=case["atol"])
+    # layers: tests/nn/test_layers.py:48-70
+    layer = nn.BatchNorm1d(2)
+    out = layer(mt.Tensor(np.array([[1.0, 2.0], [3.0, 4.0]], np.float32))).numpy()
+    assert np.allclose(out.mean(axis=0), 0.0, atol=1e-5) and np.allclose(out.var(axis=0), 1.0, atol=1e-4)
+    assert layer.running_mean.numpy()[0] != 0.0
+    before = layer.running_mean.numpy().copy()
+    layer.eval()
+    layer(mt.Tensor(np.array([[5.0, 6.0], [7.0, 8.0]], np.float32)))
+    np.testing.assert_array_equal(layer.running_mean.numpy(), before)
+    l2 = nn.BatchNorm2d(3)
+    x = mt.Tensor(np.random.default_rng(0).standard_normal((2, 3, 4, 4)).astype(np.float32), requires_grad=True)
+    y = l2(x)
+    assert np.all(y.numpy().var(axis=(0, 2, 3)) > 0)
+    y.sum().backward()
+    assert np.abs(x.grad.numpy()).max() < 1e-4        # the sum of a normalised batch does not depend on x
+    np.testing.assert_allclose(l2.bias.grad.numpy(), [32.0, 32.0, 32.0])
+    with pytest.raises(ValueError):
+        layer(mt.Tensor(np.zeros((4, 3), np.float32)))
+    with pytest.raises(ValueError):
+        layer(mt.Tensor(np.zeros(2, np.float32)))
+
+
+# ------------------------------------------------------------------ dropout
+def test_dropout_mask_equals_oracle_and_layers(be, orc):
+    import minitensor_b200.nn as nn
+    import minitensor_b200.tensor as mt
+    for p, seed, off in [(0.3, 42, 0), (0.5, 7, 12345), (0.9, 1, 0), (0.0, 3, 0), (1.0, 3, 0)]:
+        m = be.dropout_mask(100_003, p, seed, off)
+        be.sync()
+        np.testing.assert_array_equal(m.cpu().numpy(), orc.dropout_mask(100_003, p, seed, off))
+    m64 = be.dropout_mask(1000, 0.25, 5, 0, torch.float64).cpu().numpy()
+    assert set(np.unique(m64)) <= {0.0, 1.0 / 0.75}
+    x_np = np.array([[1.0, 2.0], [3.0, 4.0]], np.float32)
+    x = mt.Tensor(x_np)
+    assert np.array_equal(nn.dropout(x, 0.0, True).numpy(), x_np)            # tests/nn/test_functional.py:498-506
+    assert not nn.dropout(x, 1.0, True).numpy().any()
+    assert np.array_equal(nn.dropout(x, 0.5, False).numpy(), x_np)
+    big = mt.Tensor(np.ones((512, 1024), np.float32), requires_grad=True)
+    y = nn.dropout(big, 0.3, True, seed=11)
+    kept = (y.numpy() != 0)
+    assert abs(kept.mean() - 0.7) < 0.01
+    np.testing.assert_allclose(y.numpy()[kept], 1.0 / 0.7, rtol=1e-6)
+    y.sum().backward()
+    np.testing.assert_array_equal(big.grad.numpy(), y.numpy())               # the same mask scales the gradient
+    np.testing.assert_array_equal(nn.dropout(big, 0.3, True, seed=11).numpy(), y.numpy())
+    nn.manual_seed(5)
+    a = nn.Dropout(0.5)(big).numpy()
+    b = nn.Dropout(0.5)(big).numpy()
+    nn.manual_seed(5)
+    assert np.array_equal(nn.Dropout(0.5)(big).numpy(), a) and not np.array_equal(a, b)
+    img = mt.Tensor(np.ones((8, 16, 5, 7), np.float32))
+    z = nn.Dropout2d(0.5)(img).numpy()
+    per_channel = z.reshape(8, 16, -1)
+    assert np.all((per_channel == per_channel[:, :, :1]).all(axis=2))        # whole channels kept or dropped
+    assert 0 < (per_channel[:, :, 0] == 0).mean() < 1
+    with pytest.raises(ValueError):
+        nn.Dropout2d(0.5)(big)
+    with pytest.raises(ValueError):
+        nn.Dropout(1.5)
