@@ -390,6 +390,28 @@ def run_case(args):
         p, gr = rnd(n), rnd(n)
         m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
         fn = lambda: be.adam_step(p, gr, m, v, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=1)
+    elif name == "optimizers":          # SGD (momentum), RMSprop (centered, momentum), norm clipping on 71.2 M parameters
+        n = 71_218_152
+        p, gr = rnd(n), rnd(n)
+        bufs = [torch.zeros(n, device=dev) for _ in range(4)]
+        fn = lambda: (be.sgd_step(p, gr, bufs[0], lr=1e-3, momentum=0.9, weight_decay=1e-4),
+                      be.rmsprop_step(p, gr, bufs[1], bufs[2], bufs[3], lr=1e-3, momentum=0.9),
+                      be.clip_grad_norm([gr], 1.0))
+    elif name == "batch_norm":          # [65536, 4096] f32 (1.07 GB): forward with batch statistics, then backward
+        x, dy = rnd(65536, 4096), rnd(65536, 4096)
+        w, b = rnd(4096), rnd(4096)
+        rm, rv = torch.zeros(4096, device=dev), torch.ones(4096, device=dev)
+
+        def fn():
+            y, mean, inv, bs = be.batch_norm_fwd(x, w, b, rm, rv, training=True)
+            be.batch_norm_bwd(x, dy, w, mean, inv, batch_stats=bs)
+    elif name == "dropout":             # x * mask on [65536, 4096] f32, mask generated on the fly
+        x = rnd(65536, 4096)
+        fn = lambda: be.dropout_apply(x, 0.3, 42)
+    elif name == "cross_entropy_soft":  # probability targets, per-sample losses: [65536, 1000]
+        x = rnd(65536, 1000)
+        t = torch.softmax(rnd(65536, 1000), dim=1)
+        fn = lambda: be.cross_entropy_ex(x, t, reduction="none")
     elif name == "dense_small":         # the small MLP's layers: launch / HBM-bound shapes
         x, w1, b1 = rnd(32, 784), rnd(128, 784), rnd(128)
         w2, b2 = rnd(10, 128), rnd(10)

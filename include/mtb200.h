@@ -292,11 +292,16 @@ int32_t mtb200_batch_norm_bwd(mtb200_handle h, int32_t dtype, int64_t N, int64_t
  * generate_dropout_mask + the element-wise product of Dropout / Dropout2d::forward
  * (engine/src/nn/dropout.rs:21-92,164-187,258-289).
  * mask[j] = 1/(1-p) with probability 1-p, else 0 (all ones for p = 0, zeros for p = 1).  The reference
- * draws from its thread-local StdRng, whose stream cannot be reproduced outside it; here entry j keeps
- * when the top 24 bits of mix64(seed + (offset + j + 1) * 0x9E3779B97F4A7C15) are below (1-p)*2^24
- * (mix64 = the splitmix64 finaliser), so a mask is a pure function of (seed, offset, j).
- * mask_mul: y[i] = x[i] * mask[i / inner] - inner = 1 for Dropout, H*W for Dropout2d (mask [N][C]);
- * the backward pass is the same call on the upstream gradient. */
+ * draws from its thread-local StdRng, whose stream cannot be reproduced outside it; here, with
+ * g = offset + j, entry j keeps when a 24-bit field of mix64(seed + (g/2 + 1) * 0x9E3779B97F4A7C15) -
+ * bits 63..40 for even g, bits 39..16 for odd g; mix64 = the splitmix64 finaliser - is below
+ * (1-p)*2^24, so a mask is a pure function of (seed, offset, j).
+ * dropout_apply: y[i] = x[i] * mask[i / inner] with the entries generated on the fly (one read, one
+ *   write, no mask tensor) - inner = 1 for Dropout, H*W for Dropout2d (mask [N][C]); the backward pass is
+ *   the same call on the upstream gradient with the same (seed, offset).
+ * dropout_mask / mask_mul: the same mask materialised, and the product with a stored mask. */
+int32_t mtb200_dropout_apply(mtb200_handle h, int32_t dtype, int64_t n, int64_t inner, const void* x,
+                             double p, uint64_t seed, uint64_t offset, void* y);
 int32_t mtb200_dropout_mask(mtb200_handle h, int32_t dtype, int64_t n, double p, uint64_t seed,
                             uint64_t offset, void* mask);
 int32_t mtb200_mask_mul(mtb200_handle h, int32_t dtype, int64_t n, int64_t inner, const void* x,

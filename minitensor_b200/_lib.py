@@ -52,6 +52,7 @@ SIGNATURES = {
     "mtb200_batch_norm_fwd": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _f64, _f64, _vp, _vp, _vp]),
     "mtb200_batch_norm_bwd": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp]),
     "mtb200_dropout_mask": (_i32, [_vp, _i32, _i64, _f64, C.c_uint64, C.c_uint64, _vp]),
+    "mtb200_dropout_apply": (_i32, [_vp, _i32, _i64, _i64, _vp, _f64, C.c_uint64, C.c_uint64, _vp]),
     "mtb200_mask_mul": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _vp]),
     "mtb200_sgd_step": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _i32]),
     "mtb200_rmsprop_step": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64]),

@@ -369,6 +369,15 @@ class Backend:
         self.launches += 1
         return mask
 
+    def dropout_apply(self, x: torch.Tensor, p: float, seed: int, offset: int = 0, inner: int = 1) -> torch.Tensor:
+        """``x * mask`` with the mask generated on the fly from ``(seed, offset)``; call it again on the upstream
+        gradient for the backward pass."""
+        y = torch.empty_like(x)
+        self._bind_stream()
+        check(self.lib.mtb200_dropout_apply(self._h, dtype_code(x), x.numel(), inner, _ptr(x), p, seed, offset, _ptr(y)))
+        self.launches += 1
+        return y
+
     def mask_mul(self, x: torch.Tensor, mask: torch.Tensor, inner: int = 1) -> torch.Tensor:
         y = torch.empty_like(x)
         self._bind_stream()

@@ -253,41 +253,72 @@ bn_reduce_general_kernel(const T* __restrict__ x, const T* __restrict__ dy, cons
   }
 }
 
-// [N][C] layout (S = 1): block = 32 channels x 8 row lanes over a band of rows; a warp reads 32 consecutive channels.
+// [N][C] layout (S = 1): a warp owns 128 consecutive channels (4 per lane, one 512-byte load per row), the 8 warps
+// of a block take rows r, r + 8, ... of the band and are folded through shared memory in a fixed order.
 template <typename T, int MODE>
 static __global__ void __launch_bounds__(256)
 bn_reduce_cols_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ a_c,
                       const T* __restrict__ b_c, long long N, int C, long long rows_per_band,
                       double* __restrict__ partial) {
-  __shared__ double r0[8][33], r1[8][33];
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + cx;
+  __shared__ double red[8][128][2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 128 + lane * 4;
   const int band = blockIdx.y;
   const long long lo = band * rows_per_band, hi = min(N, lo + rows_per_band);
-  double s0 = 0.0, s1 = 0.0;
-  if (c < C) {
-    const double a = MODE == 0 ? static_cast<double>(x[c]) : static_cast<double>(a_c[c]);
-    const double b = MODE == 0 ? 0.0 : static_cast<double>(b_c[c]);
-    for (long long n = lo + ry; n < hi; n += 8) {
-      const long long k = n * C + c;
+  constexpr int V = 16 / sizeof(T);  // elements per 16-byte vector: 4 (f32) or 2 (f64)
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((C % V) == 0) && (c0 + 3 < C) &&
+                   (MODE == 0 || (reinterpret_cast<uintptr_t>(dy) & 15) == 0);
+  double a[4], b[4], s0[4], s1[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = min(c0 + j, C - 1);
+    a[j] = MODE == 0 ? static_cast<double>(x[c]) : static_cast<double>(a_c[c]);
+    b[j] = MODE == 0 ? 0.0 : static_cast<double>(b_c[c]);
+    s0[j] = 0.0;
+    s1[j] = 0.0;
+  }
+  for (long long n = lo + warp; n < hi; n += 8) {
+    const long long k = n * C + c0;
+    T xv[4], dv[4];
+    if (vec) {
+#pragma unroll
+      for (int q = 0; q < 4 / V; ++q) {
+        *reinterpret_cast<uint4*>(xv + q * V) = *reinterpret_cast<const uint4*>(x + k + q * V);
+        if (MODE == 1) *reinterpret_cast<uint4*>(dv + q * V) = *reinterpret_cast<const uint4*>(dy + k + q * V);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        xv[j] = (c0 + j < C) ? x[k + j] : T(0);
+        dv[j] = (MODE == 1 && c0 + j < C) ? dy[k + j] : T(0);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
       double t0, t1;
-      bn_terms<T, MODE>(x[k], MODE == 1 ? dy[k] : T(0), a, b, t0, t1);
-      s0 += t0;
-      s1 += t1;
+      bn_terms<T, MODE>(xv[j], MODE == 1 ? dv[j] : T(0), a[j], b[j], t0, t1);
+      s0[j] += t0;
+      s1[j] += t1;
     }
   }
-  r0[ry][cx] = s0;
-  r1[ry][cx] = s1;
-  __syncthreads();
-  if (ry == 0 && c < C) {
-    double t0 = r0[0][cx], t1 = r1[0][cx];
 #pragma unroll
-    for (int k = 1; k < 8; ++k) {
-      t0 += r0[k][cx];
-      t1 += r1[k][cx];
+  for (int j = 0; j < 4; ++j) {
+    red[warp][lane * 4 + j][0] = s0[j];
+    red[warp][lane * 4 + j][1] = s1[j];
+  }
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c < C) {
+      double t0 = red[0][threadIdx.x][0], t1 = red[0][threadIdx.x][1];
+#pragma unroll
+      for (int k = 1; k < 8; ++k) {
+        t0 += red[k][threadIdx.x][0];
+        t1 += red[k][threadIdx.x][1];
+      }
+      partial[(static_cast<long long>(band) * C + c) * 2 + 0] = t0;
+      partial[(static_cast<long long>(band) * C + c) * 2 + 1] = t1;
     }
-    partial[(static_cast<long long>(band) * C + c) * 2 + 0] = t0;
-    partial[(static_cast<long long>(band) * C + c) * 2 + 1] = t1;
   }
 }
 
@@ -340,48 +371,99 @@ static __global__ void bn_finalize_bwd_kernel(const double* __restrict__ partial
   if (db) db[c] = static_cast<T>(s0);
   if (dw) dw[c] = static_cast<T>(s1);
 }
-// y = (x - mean) * invstd * w + b
-template <typename T>
-static __global__ void bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ mean, const T* __restrict__ invstd,
-                                       const T* __restrict__ w, const T* __restrict__ b, long long total, int C,
-                                       long long S, T* __restrict__ y) {
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>((i / S) % C);
-    T o = (x[i] - mean[c]) * invstd[c];
-    if (w) o = o * w[c];
-    if (b) o = o + b[c];
-    y[i] = o;
+// Element pass of both directions, indexed without a division per element: a block owns one channel run -
+// S > 1: the S contiguous elements of one (n, c) pair (blockIdx.y = n * C + c, blockIdx.x chunks the run);
+// S = 1: 256 consecutive channels of a band of rows (blockIdx.x = channel block, blockIdx.y = row band).
+//   MODE 0 (forward):  y  = (x - mean) * invstd * w + b
+//   MODE 1 (backward): dx = w*invstd * (dy - k1 - xhat*k2) with k1 = db/n, k2 = dw/n (batch statistics) or
+//                      dx = w*invstd * dy (fixed statistics)
+template <typename T, int MODE>
+static __global__ void __launch_bounds__(256)
+bn_element_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ mean,
+                  const T* __restrict__ invstd, const T* __restrict__ w, const T* __restrict__ b,
+                  const double* __restrict__ sums, double inv_count, int batch_stats, long long N, int C, long long S,
+                  long long rows_per_band, T* __restrict__ out) {
+  int c;
+  long long first, count, stride;
+  if (S == 1) {
+    c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= C) return;
+    const long long lo = blockIdx.y * rows_per_band, hi = min(N, lo + rows_per_band);
+    first = lo * C + c;
+    count = hi - lo;
+    stride = C;
+  } else {
+    c = static_cast<int>(blockIdx.y % C);
+    first = static_cast<long long>(blockIdx.y) * S + blockIdx.x * 1024LL + threadIdx.x;
+    const long long end = min(S, (blockIdx.x + 1) * 1024LL);
+    const long long begin = blockIdx.x * 1024LL + threadIdx.x;
+    count = begin < end ? (end - begin + 255) / 256 : 0;
+    stride = 256;
   }
-}
-// dx = w*invstd * (dy - db/n - xhat*dw/n)  (batch statistics)  |  w*invstd*dy  (fixed statistics)
-template <typename T>
-static __global__ void bn_dx_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ mean,
-                                    const T* __restrict__ invstd, const T* __restrict__ w,
-                                    const double* __restrict__ sums, double inv_count, int batch_stats,
-                                    long long total, int C, long long S, T* __restrict__ dx) {
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>((i / S) % C);
-    const double g = (w ? static_cast<double>(w[c]) : 1.0) * static_cast<double>(invstd[c]);
-    double v = static_cast<double>(dy[i]);
-    if (batch_stats) {
-      const double xh = (static_cast<double>(x[i]) - static_cast<double>(mean[c])) * static_cast<double>(invstd[c]);
-      v = v - sums[2 * c] * inv_count - xh * sums[2 * c + 1] * inv_count;
+  const T mu = mean[c], is = invstd[c];
+  const T wc = w ? w[c] : T(1);
+  if (MODE == 0) {
+    const T bc = b ? b[c] : T(0);
+    for (long long k = 0, i = first; k < count; ++k, i += stride) {
+      T o = (x[i] - mu) * is;
+      if (w) o = o * wc;
+      if (b) o = o + bc;
+      out[i] = o;
     }
-    dx[i] = static_cast<T>(g * v);
+  } else {
+    const T g = wc * is;
+    const T k1 = batch_stats ? static_cast<T>(sums[2 * c] * inv_count) : T(0);
+    const T k2 = batch_stats ? static_cast<T>(sums[2 * c + 1] * inv_count) : T(0);
+    for (long long k = 0, i = first; k < count; ++k, i += stride) {
+      T v = dy[i];
+      if (batch_stats) v = v - k1 - ((x[i] - mu) * is) * k2;
+      out[i] = g * v;
+    }
   }
 }
 
+template <typename T, int MODE>
+static int32_t bn_element_launch(mtb200_ctx* h, const T* x, const T* dy, const T* mean, const T* invstd, const T* w,
+                                 const T* b, const double* sums, double inv_count, int batch_stats, int64_t N, int64_t C,
+                                 int64_t S, T* out) {
+  if (S == 1) {
+    const int64_t cb = (C + 255) / 256;
+    int64_t bands = std::max<int64_t>(1, std::min<int64_t>((N + 15) / 16, (int64_t(h->sm_count) * 16) / cb));
+    bands = std::min<int64_t>(bands, 65535);
+    const int64_t rpb = (N + bands - 1) / bands;
+    bn_element_kernel<T, MODE><<<dim3(unsigned(cb), unsigned((N + rpb - 1) / rpb)), 256, 0, h->stream>>>(
+        x, dy, mean, invstd, w, b, sums, inv_count, batch_stats, N, int(C), S, rpb, out);
+  } else {
+    if (N * C > 65535) return fail(MTB200_ERR_INVALID, "batch_norm: N * C exceeds 65535 for inputs with spatial dimensions");
+    bn_element_kernel<T, MODE><<<dim3(unsigned((S + 1023) / 1024), unsigned(N * C)), 256, 0, h->stream>>>(
+        x, dy, mean, invstd, w, b, sums, inv_count, batch_stats, N, int(C), S, 0, out);
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
 // ------------------------------------------------------------------ dropout
-// Mask of generate_dropout_mask (engine/src/nn/dropout.rs:21-92): 1/(1-p) with probability 1-p, else 0.  Entry j
-// keeps when the top 24 bits of mix64(seed + (offset + j + 1) * 0x9E3779B97F4A7C15) are below keep * 2^24 (mix64 =
-// the splitmix64 finaliser): a counter-based stream, so any slice of a mask can be regenerated from (seed, offset).
+// Mask of generate_dropout_mask (engine/src/nn/dropout.rs:21-92): 1/(1-p) with probability 1-p, else 0.  With
+// g = offset + j, entry j keeps when a 24-bit field of mix64(seed + (g / 2 + 1) * 0x9E3779B97F4A7C15) - bits 63..40
+// for even g, 39..16 for odd g; mix64 = the splitmix64 finaliser - is below keep * 2^24: a counter-based stream, so
+// any entry can be regenerated from (seed, offset) and no mask tensor needs to exist.
 // y[i] = x[i] * mask[i / inner]; inner = 1 for Dropout, H*W for Dropout2d (one entry per (sample, channel)).
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
   z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
   return z ^ (z >> 31);
+}
+__device__ __forceinline__ unsigned long long dropout_hash(unsigned long long seed, unsigned long long pair) {
+  return mix64(seed + (pair + 1ULL) * 0x9E3779B97F4A7C15ULL);
+}
+template <typename T>
+__device__ __forceinline__ T dropout_entry(unsigned long long seed, unsigned long long g, double keep, unsigned int thresh,
+                                           T scale) {
+  if (keep >= 1.0) return T(1);
+  if (keep <= 0.0) return T(0);
+  const unsigned long long hsh = dropout_hash(seed, g >> 1);
+  const unsigned int u = static_cast<unsigned int>((g & 1ULL) ? (hsh >> 16) : (hsh >> 40)) & 0xFFFFFFu;
+  return u < thresh ? scale : T(0);
 }
 template <typename T>
 static __global__ void dropout_mask_kernel(long long n, double keep, unsigned long long seed, unsigned long long offset,
@@ -389,17 +471,8 @@ static __global__ void dropout_mask_kernel(long long n, double keep, unsigned lo
   const T scale = T(1) / static_cast<T>(keep);
   const unsigned int thresh = static_cast<unsigned int>(keep * 16777216.0);
   for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n;
-       j += static_cast<long long>(gridDim.x) * blockDim.x) {
-    T m;
-    if (keep >= 1.0) m = T(1);
-    else if (keep <= 0.0) m = T(0);
-    else {
-      const unsigned int u = static_cast<unsigned int>(
-          mix64(seed + (offset + static_cast<unsigned long long>(j) + 1ULL) * 0x9E3779B97F4A7C15ULL) >> 40);
-      m = u < thresh ? scale : T(0);
-    }
-    mask[j] = m;
-  }
+       j += static_cast<long long>(gridDim.x) * blockDim.x)
+    mask[j] = dropout_entry<T>(seed, offset + static_cast<unsigned long long>(j), keep, thresh, scale);
 }
 template <typename T>
 static __global__ void mask_mul_kernel(const T* __restrict__ x, const T* __restrict__ mask, long long n, long long inner,
@@ -407,6 +480,34 @@ static __global__ void mask_mul_kernel(const T* __restrict__ x, const T* __restr
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
     y[i] = r_mul(x[i], mask[inner == 1 ? i : i / inner]);
+}
+// y = x * mask with the mask entries generated on the fly (no mask tensor: one read, one write).  inner = 1: a
+// thread owns two neighbouring elements, which share one hash when offset is even.
+template <typename T>
+static __global__ void dropout_apply_kernel(const T* __restrict__ x, long long n, long long inner, double keep,
+                                            unsigned long long seed, unsigned long long offset, T* __restrict__ y) {
+  const T scale = T(1) / static_cast<T>(keep);
+  const unsigned int thresh = static_cast<unsigned int>(keep * 16777216.0);
+  if (inner == 1 && (offset & 1ULL) == 0 && keep > 0.0 && keep < 1.0) {
+    const long long pairs = (n + 1) >> 1;
+    for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < pairs;
+         q += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const unsigned long long hsh = dropout_hash(seed, (offset >> 1) + static_cast<unsigned long long>(q));
+      const long long i = q << 1;
+      const T m0 = (static_cast<unsigned int>(hsh >> 40) & 0xFFFFFFu) < thresh ? scale : T(0);
+      y[i] = r_mul(x[i], m0);
+      if (i + 1 < n) {
+        const T m1 = (static_cast<unsigned int>(hsh >> 16) & 0xFFFFFFu) < thresh ? scale : T(0);
+        y[i + 1] = r_mul(x[i + 1], m1);
+      }
+    }
+    return;
+  }
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const unsigned long long g = offset + static_cast<unsigned long long>(inner == 1 ? i : i / inner);
+    y[i] = r_mul(x[i], dropout_entry<T>(seed, g, keep, thresh, scale));
+  }
 }
 
 }  // namespace mtb
@@ -580,7 +681,7 @@ template <typename T, int MODE>
 static int32_t bn_reduce(mtb200_ctx* h, const T* x, const T* dy, const T* a_c, const T* b_c, int64_t N, int64_t C,
                          int64_t S, double* partial, int chunks, int64_t per_chunk) {
   if (S == 1)
-    bn_reduce_cols_kernel<T, MODE><<<dim3(unsigned((C + 31) / 32), unsigned(chunks)), 256, 0, h->stream>>>(
+    bn_reduce_cols_kernel<T, MODE><<<dim3(unsigned((C + 127) / 128), unsigned(chunks)), 256, 0, h->stream>>>(
         x, dy, a_c, b_c, N, int(C), per_chunk, partial);
   else
     bn_reduce_general_kernel<T, MODE><<<dim3(unsigned(C), unsigned(chunks)), 256, 0, h->stream>>>(
@@ -591,7 +692,7 @@ static int32_t bn_reduce(mtb200_ctx* h, const T* x, const T* dy, const T* a_c, c
 static void bn_chunking(const mtb200_ctx* h, int64_t N, int64_t C, int64_t S, int* chunks, int64_t* per_chunk) {
   // enough blocks to fill the machine about four times over, at least 2048 reduced elements per block
   const int64_t units = S == 1 ? N : N * S;                       // rows (cols kernel) or (n, s) pairs
-  const int64_t blocks_c = S == 1 ? (C + 31) / 32 : C;
+  const int64_t blocks_c = S == 1 ? (C + 127) / 128 : C;
   int64_t want = std::max<int64_t>(1, (int64_t(h->sm_count) * 4) / std::max<int64_t>(1, blocks_c));
   want = std::min<int64_t>(want, std::max<int64_t>(1, units / (S == 1 ? 64 : 2048)));
   want = std::min<int64_t>(want, 1024);
@@ -625,10 +726,8 @@ static int32_t batch_norm_fwd_t(mtb200_ctx* h, int64_t N, int64_t C, int64_t S, 
   } else {
     bn_from_running_kernel<T><<<unsigned((C + 255) / 256), 256, 0, h->stream>>>(rm, rv, int(C), eps, mean, invstd);
   }
-  const long long total = N * C * S;
-  bn_apply_kernel<T><<<ew_grid(total, h->sm_count), 256, 0, h->stream>>>(x, mean, invstd, w, b, total, int(C), S, y);
   MTB_CUDA(cudaGetLastError());
-  return MTB200_OK;
+  return bn_element_launch<T, 0>(h, x, nullptr, mean, invstd, w, b, nullptr, 0.0, 0, N, C, S, y);
 }
 
 template <typename T>
@@ -646,13 +745,10 @@ static int32_t batch_norm_bwd_t(mtb200_ctx* h, int64_t N, int64_t C, int64_t S, 
   rc = bn_reduce<T, 1>(h, x, dy, mean, invstd, N, C, S, partial, chunks, per_chunk);
   if (rc) return rc;
   bn_finalize_bwd_kernel<T><<<unsigned((C + 255) / 256), 256, 0, h->stream>>>(partial, chunks, int(C), sums, dw, db);
-  if (dx) {
-    const long long total = N * C * S;
-    bn_dx_kernel<T><<<ew_grid(total, h->sm_count), 256, 0, h->stream>>>(x, dy, mean, invstd, w, sums,
-                                                                        1.0 / (double(N) * double(S)), batch_stats, total,
-                                                                        int(C), S, dx);
-  }
   MTB_CUDA(cudaGetLastError());
+  if (dx)
+    return bn_element_launch<T, 1>(h, x, dy, mean, invstd, w, nullptr, sums, 1.0 / (double(N) * double(S)), batch_stats, N,
+                                   C, S, dx);
   return MTB200_OK;
 }
 
@@ -734,6 +830,25 @@ int32_t mtb200_mask_mul(mtb200_handle h, int32_t dtype, int64_t n, int64_t inner
   else
     mask_mul_kernel<double><<<grid, 256, 0, h->stream>>>(static_cast<const double*>(x), static_cast<const double*>(mask),
                                                          n, inner, static_cast<double*>(y));
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+int32_t mtb200_dropout_apply(mtb200_handle h, int32_t dtype, int64_t n, int64_t inner, const void* x, double p,
+                             uint64_t seed, uint64_t offset, void* y) {
+  MTB_CHECK_HANDLE(h);
+  if (int32_t rc = check_float_dtype(dtype, "dropout")) return rc;
+  if (!(p >= 0.0 && p <= 1.0)) return fail(MTB200_ERR_INVALID, "dropout probability must be in [0, 1], got %g", p);
+  if (n < 0 || inner < 1) return fail(MTB200_ERR_INVALID, "bad length");
+  if (n == 0) return MTB200_OK;
+  if (!x || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  const int grid = ew_grid((n + 1) / 2, h->sm_count);
+  if (dtype == MTB200_F32)
+    dropout_apply_kernel<float><<<grid, 256, 0, h->stream>>>(static_cast<const float*>(x), n, inner, 1.0 - p, seed, offset,
+                                                             static_cast<float*>(y));
+  else
+    dropout_apply_kernel<double><<<grid, 256, 0, h->stream>>>(static_cast<const double*>(x), n, inner, 1.0 - p, seed,
+                                                              offset, static_cast<double*>(y));
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
 }

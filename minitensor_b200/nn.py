@@ -264,9 +264,8 @@ def dropout(input: Tensor, p: float = 0.5, training: bool = True, seed: Optional
         seed = (_global_seed[0] * 0x9E3779B1 + _dropout_calls[0]) & 0xFFFFFFFFFFFFFFFF
     x = input._buf.contiguous()
     inner = x.shape[2] * x.shape[3] if _channels else 1
-    mask = be.dropout_mask(x.numel() // inner, p, seed, 0, x.dtype)
-    y = be.mask_mul(x, mask, inner)
-    return input._result(y, (input,), lambda g: (be.mask_mul(g.contiguous(), mask, inner),))
+    y = be.dropout_apply(x, p, seed, 0, inner)       # the mask is never stored: the backward pass regenerates it
+    return input._result(y, (input,), lambda g: (be.dropout_apply(g.contiguous(), p, seed, 0, inner),))
 
 
 _global_seed = [0]

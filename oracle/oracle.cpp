@@ -793,9 +793,9 @@ void orc_batch_norm_bwd_f64(int64_t N, int64_t C, int64_t S, const double* x, co
 
 // Dropout mask (engine/src/nn/dropout.rs:21-92): entries are 1/(1-p) with probability 1-p, else 0; p >= 1 gives
 // zeros, p <= 0 ones.  The reference draws from its thread-local StdRng, whose stream cannot be reproduced
-// outside it; this build's generator is counter-based: entry j of a mask with (seed, offset) keeps when the top
-// 24 bits of mix64(seed + (offset + j + 1) * 0x9E3779B97F4A7C15) are below keep * 2^24, mix64 being the
-// splitmix64 finaliser.
+// outside it; this build's generator is counter-based: with g = offset + j, entry j of a mask keeps when a 24-bit
+// field of mix64(seed + (g / 2 + 1) * 0x9E3779B97F4A7C15) is below keep * 2^24 - bits 63..40 for even g, bits
+// 39..16 for odd g - mix64 being the splitmix64 finaliser.
 static inline uint64_t mix64(uint64_t z) {
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
   z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
@@ -808,7 +808,9 @@ void orc_dropout_mask_f32(int64_t n, double p, uint64_t seed, uint64_t offset, f
   for (int64_t j = 0; j < n; ++j) {
     if (keep >= 1.0) { mask[j] = 1.0f; continue; }
     if (keep <= 0.0) { mask[j] = 0.0f; continue; }
-    const uint32_t u = static_cast<uint32_t>(mix64(seed + (offset + static_cast<uint64_t>(j) + 1) * 0x9E3779B97F4A7C15ULL) >> 40);
+    const uint64_t g = offset + static_cast<uint64_t>(j);
+    const uint64_t hsh = mix64(seed + ((g >> 1) + 1) * 0x9E3779B97F4A7C15ULL);
+    const uint32_t u = static_cast<uint32_t>((g & 1) ? (hsh >> 16) : (hsh >> 40)) & 0xFFFFFFu;
     mask[j] = u < thresh ? scale : 0.0f;
   }
 }

@@ -306,3 +306,21 @@ def test_dropout_mask_equals_oracle_and_layers(be, orc):
         nn.Dropout2d(0.5)(big)
     with pytest.raises(ValueError):
         nn.Dropout(1.5)
+
+
+def test_dropout_apply_equals_mask_product(be, orc, rng):
+    """The fused call (mask generated on the fly) equals x * oracle mask for both mask shapes and odd offsets."""
+    x = rng.standard_normal(100_001).astype(np.float32)
+    for p, seed, off in [(0.3, 42, 0), (0.5, 9, 7), (0.0, 1, 0), (1.0, 1, 0)]:
+        y = be.dropout_apply(dev(be, x), p, seed, off)
+        be.sync()
+        np.testing.assert_array_equal(y.cpu().numpy(), x * orc.dropout_mask(x.size, p, seed, off))
+    img = rng.standard_normal((4, 6, 5, 7)).astype(np.float32)
+    y = be.dropout_apply(dev(be, img), 0.4, 3, 0, inner=35)
+    be.sync()
+    mask = orc.dropout_mask(24, 0.4, 3, 0).reshape(4, 6, 1, 1)
+    np.testing.assert_array_equal(y.cpu().numpy(), img * mask)
+    x64 = rng.standard_normal(1001)
+    y64 = be.dropout_apply(dev(be, x64), 0.25, 5)
+    be.sync()
+    np.testing.assert_array_equal(y64.cpu().numpy() != 0, orc.dropout_mask(1001, 0.25, 5) != 0)
