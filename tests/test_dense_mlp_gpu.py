@@ -170,3 +170,22 @@ def test_mlp_trainer_graph_replay_equals_eager_steps(be, dims, batch):
     # eager steps still work after a capture
     la, lb = a.step(xs[0], ys[0]).item(), b.step(xs[0], ys[0]).item()
     assert la == lb and torch.equal(a.params, b.params)
+
+
+def test_mlp_trainer_checkpoint_resume(be, tmp_path):
+    """Save after two steps, restore into a fresh trainer, continue: same bits as the uninterrupted run."""
+    from minitensor_b200.mlp import MLPTrainer
+    from minitensor_b200.checkpoint import load_mlp_trainer, save_mlp_trainer
+    x, labels, *_ = _config2(5)
+    xd, yd = torch.from_numpy(x).to(be.device), torch.from_numpy(labels).to(be.device)
+    a = MLPTrainer([784, 128, 10], 32, seed=2)
+    for _ in range(2):
+        a.step(xd, yd)
+    path = str(tmp_path / "mlp.json")
+    save_mlp_trainer(a, path)
+    b = MLPTrainer([784, 128, 10], 32, seed=99)
+    load_mlp_trainer(b, path)
+    assert b.step_count == 2 and torch.equal(a.params, b.params) and torch.equal(a.m, b.m)
+    la, lb = a.step(xd, yd).item(), b.step(xd, yd).item()
+    be.sync()
+    assert la == lb and torch.equal(a.params, b.params) and torch.equal(a.v, b.v)
