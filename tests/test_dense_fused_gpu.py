@@ -214,3 +214,45 @@ def test_mlp_trainer_overlapped_schedule_gives_identical_parameters(be):
     assert la.item() == lb.item()
     assert torch.equal(a.grads, b.grads)
     assert torch.equal(a.params, b.params) and torch.equal(a.m, b.m) and torch.equal(a.v, b.v)
+
+
+def test_large_mlp_step_full_size_properties(be, orc):
+    """One training step of the large MLP at its full size (8192-4096-4096-4096-1000, batch 65536):
+    sampled rows of the first activation and sampled rows of the last weight gradient against f64 arithmetic,
+    the identity sum_j db_last[j] = 0 (every softmax row sums to one), the loss against the logits the step
+    produced, and bit-identical repeats."""
+    from minitensor_b200.mlp import MLPTrainer
+    dims, batch = [8192, 4096, 4096, 4096, 1000], 65536
+    g = torch.Generator(device="cpu").manual_seed(31)
+    x = torch.randn(batch, dims[0], generator=g).to(be.device)
+    y = torch.randint(0, dims[-1], (batch,), generator=g).to(be.device)
+    tr = MLPTrainer(dims, batch, seed=0)
+    w1 = tr.W[0].cpu().numpy().copy()
+    b1 = tr.b[0].cpu().numpy().copy()
+    loss = tr.step(x, y)
+    be.sync()
+    logits = tr.h[3].cpu().numpy().astype(np.float64)                  # the loss against the logits the step produced
+    lse = np.log(np.exp(logits - logits.max(axis=1, keepdims=True)).sum(axis=1)) + logits.max(axis=1)
+    ref_loss = float((lse - logits[np.arange(batch), y.cpu().numpy()]).mean())
+    assert abs(loss.item() - ref_loss) <= 2e-5 * ref_loss
+    assert np.log(1000.0) - 0.5 < ref_loss < np.log(1000.0) + 4.0      # random labels at initialisation
+    del logits, lse
+    rows = np.random.default_rng(2).choice(batch, 4, replace=False)
+    xr = x[rows].cpu().numpy()
+    ref_h1 = np.maximum(xr.astype(np.float64) @ w1.astype(np.float64).T + b1, 0.0)
+    assert nerr(tr.h[0][rows].cpu().numpy(), ref_h1, xr, w1.T) <= TIGHT
+    db_last = tr.db[3].cpu().numpy().astype(np.float64)
+    assert abs(db_last.sum()) <= 1e-5 * np.abs(db_last).sum() + 1e-7
+    # dW_last[o, :] = sum_b g[b, o] * h3[b, :] for three sampled outputs (g = dlogits is still in the trainer)
+    outs = [0, 499, 999]
+    gcols = tr.g[3][:, outs].cpu().numpy().astype(np.float64)          # [batch, 3]
+    h3 = tr.h[2].cpu().numpy()
+    ref_dw = gcols.T @ h3.astype(np.float64)
+    got = tr.dW[3][outs].cpu().numpy()
+    scale = np.linalg.norm(gcols, axis=0)[:, None] * np.linalg.norm(h3.astype(np.float64), axis=0)[None, :]
+    assert float((np.abs(got - ref_dw) / scale).max()) <= F32_TOL
+    grads_first = tr.grads.clone()
+    tr2 = MLPTrainer(dims, batch, seed=0)
+    tr2.step(x, y)
+    be.sync()
+    assert torch.equal(tr2.grads, grads_first) and torch.equal(tr2.params, tr.params)

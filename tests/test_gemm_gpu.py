@@ -409,3 +409,36 @@ def test_i32_limb_path_transposed_batched_and_mixed_range(be, orc, rng):
     np.testing.assert_array_equal(run_gemm(be, e1, e2, variant=0xFD), e1 @ e2)
     e1[0, 0] = 128
     np.testing.assert_array_equal(run_gemm(be, e1, e2, variant=0xFD), e1 @ e2)
+
+
+def test_largest_square_sizes_f32_f64_i32(be, orc):
+    """8192^3, the largest square of the sweep: f32 sampled rows against the f64-accumulated oracle; i32 with the
+    modular identity sum_j C[i,j] r[j] = sum_l A[i,l] (B r)[l]; f64 (at 4096^3) sampled rows against the oracle."""
+    g = torch.Generator(device="cpu").manual_seed(23)
+    n = 8192
+    a = torch.randn(n, n, generator=g)
+    b = torch.randn(n, n, generator=g)
+    c = be.gemm(a.to(be.device), b.to(be.device))
+    be.sync()
+    rows = np.random.default_rng(6).choice(n, 8, replace=False)
+    an, bn = a.numpy(), b.numpy()
+    wide = orc.matmul_acc_wide(np.ascontiguousarray(an[rows]), bn)
+    assert norm_scaled_error(c[rows].cpu().numpy(), wide, an[rows], bn) <= 4e-6
+    del c
+    ai = torch.randint(-8, 9, (n, n), generator=g, dtype=torch.int32).to(be.device)
+    bi = torch.randint(-8, 9, (n, n), generator=g, dtype=torch.int32).to(be.device)
+    r = torch.randint(-3, 4, (n, 1), generator=g, dtype=torch.int32).to(be.device)
+    ci = be.gemm(ai, bi)
+    assert torch.equal(be.gemm(ci, r), be.gemm(ai, be.gemm(bi, r)))
+    rows_i = rows[:4]
+    np.testing.assert_array_equal(ci[rows_i].cpu().numpy(),
+                                  orc.matmul(np.ascontiguousarray(ai[rows_i].cpu().numpy()), bi.cpu().numpy()))
+    del ai, bi, ci
+    m = 4096
+    a64 = torch.randn(m, m, generator=g, dtype=torch.float64)
+    b64 = torch.randn(m, m, generator=g, dtype=torch.float64)
+    c64 = be.gemm(a64.to(be.device), b64.to(be.device))
+    be.sync()
+    rows64 = rows[:6] % m
+    ref = orc.matmul(np.ascontiguousarray(a64.numpy()[rows64]), b64.numpy())
+    assert norm_scaled_error(c64[rows64].cpu().numpy(), ref, a64.numpy()[rows64], b64.numpy()) <= 1e-13
