@@ -52,7 +52,9 @@ enum {
  * multiplies on the tensor cores with f32 accumulation; they differ in how an
  * f32 operand is represented. */
 enum {
-  MTB200_F32_DEFAULT = 0, /* F16X3 when the output is larger than 128 x 128, else BF16X6     */
+  MTB200_F32_DEFAULT = 0, /* F16X3 when the output is larger than 128 x 128, else BF16X6;
+                           * products with K <= 64 and at most 4e6 multiply-adds run as one
+                           * launch of plain f32 multiply-add on the CUDA cores instead       */
   MTB200_F32_BF16X1 = 1,  /* single bf16 product: ~2^-8 relative, for experiments            */
   MTB200_F32_BF16X3 = 3,  /* two bf16 terms, three products: ~2^-16 relative                 */
   MTB200_F32_BF16X6 = 6,  /* three bf16 terms (24 bits), six products                        */
@@ -61,6 +63,11 @@ enum {
                            * scaling, three products: the accuracy class of 3xTF32 at half
                            * its tensor cost; needs M, N > 128                              */
 };
+
+/* Second byte of f32_mode (f32_mode = mode | variant << 8), for tests and experiments: 0 = choose;
+ * 1..6 = a fixed tile shape of the tensor kernels; 0xFE = the CUDA-core kernel (f32: IEEE multiply-add
+ * in one launch; int32: the IMAD kernel); 0xFD = the integer tensor path regardless of size;
+ * 0xFF (conv2d entries) = the gathered-patch lowering. */
 
 typedef struct mtb200_ctx* mtb200_handle;
 

@@ -26,6 +26,11 @@ struct SplitOperand {
 };
 
 inline int padded_k(int K) { return (K + 63) / 64 * 64; }
+// f32 products with a reduction of at most SMALL_GEMM_K and at most SMALL_GEMM_MACS multiply-adds take the
+// single-launch CUDA-core path: measured 11-15 us against 20-29 us for split + tensor kernel + gate on such shapes
+// (the small MLP's backward products); with longer reductions that kernel's serial K loop loses.
+constexpr double SMALL_GEMM_MACS = 4.0e6;
+constexpr int SMALL_GEMM_K = 64;
 inline size_t split_bytes(int rows, int Kp, int batch) {
   return align_up(size_t(3) * batch * rows * Kp * sizeof(__nv_bfloat16), 1024);
 }
@@ -278,6 +283,24 @@ inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int bat
   const int Kp = padded_k(K);
   const int batch_a = (stride_a == 0 || batch == 1) ? 1 : batch;
   const int batch_b = (stride_b == 0 || batch == 1) ? 1 : batch;
+  // Products too small to amortise operand preparation (two or three extra launches) run as ONE launch of the
+  // CUDA-core kernel in plain f32 multiply-add; variant 0xFE forces that path for any size.
+  const double macs = double(M) * double(N) * double(K) * double(batch);
+  if (variant == 0xFE || (variant == 0 && mode == 0 && K <= SMALL_GEMM_K && macs <= SMALL_GEMM_MACS)) {
+    StridedGemmArgs s;
+    s.M = M; s.N = N; s.K = K; s.batch = batch;
+    s.A = A; s.B = B; s.C = C;
+    s.a_si = trans_a ? 1 : K;  s.a_sk = trans_a ? M : 1;  s.a_sb = stride_a;
+    s.b_sk = trans_b ? 1 : N;  s.b_sj = trans_b ? K : 1;  s.b_sb = stride_b;
+    s.ldc = ldc; s.c_sb = stride_c;
+    s.bias = bias; s.aux = aux; s.epilogue = epilogue;
+    s.gate = nullptr; s.gate_value = 0;
+    ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * macs);
+    const long long tiles = static_cast<long long>((M + 63) / 64) * ((N + 63) / 64);
+    gemm_simt_kernel<float, 4, 4><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(s);
+    MTB_CUDA(cudaGetLastError());
+    return MTB200_OK;
+  }
   if (variant == 0 && M > 128 && N > 128) variant = 5;
   // default arithmetic: the fp16 two-plane mode wherever the pair-tile kernel runs, six bf16 products elsewhere
   const int eff_mode = mode == 0 ? (variant == 5 ? 23 : 6) : mode;
