@@ -167,17 +167,23 @@ def gemm4096(be, torch, peaks):
     for _ in range(3):
         be.gemm(a, b, out=out)
     torch.cuda.synchronize()
-    be.profile(True)
-    total = 0.0
     iters = 10
-    for _ in range(iters):
-        flush.fill_(1)
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        be.gemm(a, b, out=out)
-        e.record()
-        torch.cuda.synchronize()
-        total += s.elapsed_time(e)
+
+    def timed_calls():
+        total = 0.0
+        for _ in range(iters):
+            flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            be.gemm(a, b, out=out)
+            e.record()
+            torch.cuda.synchronize()
+            total += s.elapsed_time(e)
+        return total
+
+    total = timed_calls()                 # the call as a user makes it (launch profiler off)
+    be.profile(True)                      # a second pass with an event pair around the tensor kernel
+    timed_calls()
     launches, kms, kwork = be.profile_read(0)
     be.profile(False)
     ms = total / iters

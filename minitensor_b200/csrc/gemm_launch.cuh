@@ -201,25 +201,27 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
 // Scale + split one f32 operand into two fp16 planes and its exponent vector.
 //  k_major: source [mn][k] (scale per row); otherwise source [k][mn] (scale per column).
 inline int32_t launch_split16(mtb200_ctx* h, const float* src, bool k_major, int mn, int K, int batch,
-                              long long bstride, __half* planes, int* expo, uint32_t* nf_word, uint32_t epoch) {
+                              long long bstride, __half* planes, int* expo, uint32_t* nf_word, uint32_t epoch,
+                              cudaStream_t stream = nullptr) {
+  if (!stream) stream = h->stream;
   if (k_major) {
     const int Kp = padded_k(K);
     ProfScope prof(h, PROF_SPLIT, double(batch) * mn * (8.0 * K + 4.0 * Kp));
-    split16_rows_kernel<<<dim3(unsigned(std::min(mn, 65535)), 1, batch), 256, 0, h->stream>>>(
+    split16_rows_kernel<<<dim3(unsigned(std::min(mn, 65535)), 1, batch), 256, 0, stream>>>(
         src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
   } else {
     const int cp = padded_k(mn);
     ProfScope prof(h, PROF_SPLIT, double(batch) * K * (8.0 * mn + 4.0 * cp));
-    MTB_CUDA(cudaMemsetAsync(expo, 0, sizeof(int) * size_t(batch) * mn, h->stream));
+    MTB_CUDA(cudaMemsetAsync(expo, 0, sizeof(int) * size_t(batch) * mn, stream));
     const int bands = std::max(1, std::min((K + 63) / 64, (h->sm_count * 8) / std::max(1, (mn + 255) / 256)));
     const int rows_per_band = (K + bands - 1) / bands;
-    colabsmax_kernel<<<dim3((mn + 255) / 256, (K + rows_per_band - 1) / rows_per_band, batch), 256, 0, h->stream>>>(
+    colabsmax_kernel<<<dim3((mn + 255) / 256, (K + rows_per_band - 1) / rows_per_band, batch), 256, 0, stream>>>(
         src, mn, bstride, K, mn, rows_per_band, reinterpret_cast<uint32_t*>(expo), nf_word, epoch);
-    exponent_from_amax_kernel<<<(batch * mn + 255) / 256, 256, 0, h->stream>>>(reinterpret_cast<uint32_t*>(expo), expo,
+    exponent_from_amax_kernel<<<(batch * mn + 255) / 256, 256, 0, stream>>>(reinterpret_cast<uint32_t*>(expo), expo,
                                                                           batch * mn);
     const long long total = static_cast<long long>(K) * (cp / 8);
     const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
-    split16_cols_scaled_kernel<<<dim3(blocks, 1, batch), 256, 0, h->stream>>>(src, mn, bstride, planes, expo, K, mn, cp);
+    split16_cols_scaled_kernel<<<dim3(blocks, 1, batch), 256, 0, stream>>>(src, mn, bstride, planes, expo, K, mn, cp);
   }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
@@ -250,10 +252,23 @@ inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int
   int* eb = reinterpret_cast<int*>(base + bytes_a + bytes_b + bytes_ea);
   uint32_t* nf_word = h->status + 2;
   const uint32_t epoch = ++h->epoch;
+  // Operands of up to 32 M elements each do not fill the memory system alone (a 4096^2 split runs at a third to
+  // a half of the DRAM rate): B is then prepared on the side stream while A is prepared on the caller's.
+  const bool side_by_side = h->side_stream && !h->profiling &&
+                            double(batch_a) * M * K <= 33554432.0 && double(batch_b) * N * K <= 33554432.0;
+  if (side_by_side) {
+    MTB_CUDA(cudaEventRecord(h->ev_fork, h->stream));
+    MTB_CUDA(cudaStreamWaitEvent(h->side_stream, h->ev_fork, 0));
+  }
   rc = launch_split16(h, A, a_kmaj, M, K, batch_a, stride_a, pa, ea, nf_word, epoch);
   if (rc) return rc;
-  rc = launch_split16(h, B, b_kmaj, N, K, batch_b, stride_b, pb, eb, nf_word, epoch);
+  rc = launch_split16(h, B, b_kmaj, N, K, batch_b, stride_b, pb, eb, nf_word, epoch,
+                      side_by_side ? h->side_stream : nullptr);
   if (rc) return rc;
+  if (side_by_side) {
+    MTB_CUDA(cudaEventRecord(h->ev_join, h->side_stream));
+    MTB_CUDA(cudaStreamWaitEvent(h->stream, h->ev_join, 0));
+  }
   SplitOperand oa{reinterpret_cast<const __nv_bfloat16*>(pa), a_rows, batch_a > 1, batch_a, a_kmaj ? 0 : 1, a_cols_p, 2, ea};
   SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(pb), b_rows, batch_b > 1, batch_b, b_kmaj ? 0 : 1, b_cols_p, 2, eb};
   rc = run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, 23, 5, 0, 0, 0, K);

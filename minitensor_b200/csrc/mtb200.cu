@@ -194,12 +194,18 @@ int32_t mtb200_create(int32_t device_ordinal, mtb200_handle* out) {
   h->device = device_ordinal;
   h->sm_count = prop.multiProcessorCount;
   e = cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h->status), 4 * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(h->status, 0, 4 * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&h->status_host), 2 * sizeof(uint32_t));
   if (e != cudaSuccess) {
     if (h->status) cudaFree(h->status);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    if (h->side_stream) cudaStreamDestroy(h->side_stream);
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
     delete h;
     return fail(MTB200_ERR_CUDA, "handle set-up failed: %s", cudaGetErrorString(e));
   }
@@ -219,6 +225,12 @@ int32_t mtb200_destroy(mtb200_handle h) {
   if (h->workspace) cudaFree(h->workspace);
   if (h->status) cudaFree(h->status);
   if (h->status_host) cudaFreeHost(h->status_host);
+  if (h->side_stream) {
+    cudaStreamSynchronize(h->side_stream);
+    cudaStreamDestroy(h->side_stream);
+  }
+  if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+  if (h->ev_join) cudaEventDestroy(h->ev_join);
   if (h->own_stream) cudaStreamDestroy(h->own_stream);
   delete h;
   return MTB200_OK;

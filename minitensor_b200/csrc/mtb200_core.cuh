@@ -45,6 +45,9 @@ struct mtb200_ctx {
   int sm_count = 0;
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
+  // second stream + fork/join events: the two operands of a mid-size GEMM are prepared side by side
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
   uint32_t* status = nullptr;       // device, 4 words
