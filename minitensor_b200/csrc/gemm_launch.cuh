@@ -95,9 +95,11 @@ inline int32_t make_split_tmap_mn(CUtensorMap* out, const void* base, uint64_t k
   return MTB200_OK;
 }
 
+// allow_tail: the kernel walks K blocks of 64 and may split the tiles of a short last round (GemmArgs::tail_splits).
 template <typename Kern>
 inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int threads, long long tiles,
-                                  const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, double work) {
+                                  const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, double work,
+                                  bool allow_tail = false) {
   MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -116,10 +118,35 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
     cudaGetLastError();
     max_clusters = h->sm_count / 2;
   }
-  const int pairs = int(std::min<long long>(tiles, std::min(max_clusters, h->sm_count / 2)));
+  const int max_pairs = std::min(max_clusters, h->sm_count / 2);
+  int pairs = int(std::min<long long>(tiles, max_pairs));
+  // A last round that would keep at most half of the pairs busy: cut its tiles into K ranges so that the round
+  // takes 1 / splits of a tile time (4096^3: 256 tiles on 74 pairs, 34 tail tiles -> 68 half tiles).  An output
+  // of at most half as many tiles as there are pairs is all tail: every tile is cut.
+  g.tail_splits = 0;
+  if (allow_tail && tiles <= 0x3fffffff) {
+    const int rem = tiles > pairs ? int(tiles % pairs) : int(tiles);
+    int splits = rem ? std::min(4, max_pairs / rem) : 0;
+    while (splits >= 2 && g.num_kb < 4 * splits) --splits;
+    if (splits >= 2) {
+      if (!h->tail_partial) {
+        MTB_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->tail_partial), size_t(max_pairs) * 65536 * sizeof(float)));
+      }
+      g.tail_splits = splits;
+      g.tail_rounds = tiles > pairs ? int(tiles / pairs) : 0;
+      g.tail_tiles = rem;
+      g.partial = h->tail_partial;
+      if (tiles <= pairs) pairs = rem * splits;  // no whole-tile round: one pair per K range
+    }
+  }
   cfg.gridDim = dim3(2 * pairs);
   ProfScope prof(h, PROF_GEMM_UMMA, work);
   MTB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, g));
+  if (g.tail_splits > 1) {
+    const int tiles_m = (g.M + 255) / 256, tiles_n = (g.N + 255) / 256;
+    tail_fixup_kernel<<<dim3(unsigned(g.tail_tiles), 64), 256, 0, h->stream>>>(g, pairs, tiles_m, tiles_n);
+    MTB_CUDA(cudaGetLastError());
+  }
   return MTB200_OK;
 }
 
@@ -127,7 +154,7 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
 // K = logical reduction length; Kp = padded column count of K-major planes.
 template <int BK, int STAGES, int NP>
 inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp, GemmArgs g,
-                               int K = 0) {
+                               int K = 0, bool tail = true) {
   using Cfg = Gemm2Cfg<BK, STAGES, NP>;
   if (K <= 0) K = Kp;
   if (a.nplanes != NP || b.nplanes != NP) return fail(MTB200_ERR_INVALID, "operand planes do not match the GEMM mode");
@@ -148,18 +175,18 @@ inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const Split
   if constexpr (BK == 64) {
     if (a.mn_major && b.mn_major)
       return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, true, NP>, Cfg::SMEM_BYTES,
-                                Cfg::NUM_THREADS, tiles, ta, tb, g, work);
+                                Cfg::NUM_THREADS, tiles, ta, tb, g, work, tail);
     if (a.mn_major)
       return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, true, false, NP>, Cfg::SMEM_BYTES,
-                                Cfg::NUM_THREADS, tiles, ta, tb, g, work);
+                                Cfg::NUM_THREADS, tiles, ta, tb, g, work, tail);
     if (b.mn_major)
       return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, true, NP>, Cfg::SMEM_BYTES,
-                                Cfg::NUM_THREADS, tiles, ta, tb, g, work);
+                                Cfg::NUM_THREADS, tiles, ta, tb, g, work, tail);
   } else {
     if (a.mn_major || b.mn_major) return fail(MTB200_ERR_INVALID, "MN-major operands need the K-block-64 kernel");
   }
   return launch_pair_kernel(h, gemm_split_umma2_kernel<BK, STAGES, false, false, NP>, Cfg::SMEM_BYTES,
-                            Cfg::NUM_THREADS, tiles, ta, tb, g, work);
+                            Cfg::NUM_THREADS, tiles, ta, tb, g, work, tail && BK == 64);
 }
 
 // C[b] = epilogue(A_split[b] * B_split[b]^T + bias) on prepared operands.
@@ -185,7 +212,7 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
   g.num_kb = num_kb_override;  // 0: the whole padded K
   // two-CTA pair tiles whenever the output is at least one pair tile tall and wide
   if (variant == 0) variant = (M > 128 && N > 128) ? 5 : ((N > 128) ? 1 : (N > 64 ? 2 : 3));
-  if ((a.mn_major || b.mn_major || mode == 23) && variant != 5)
+  if ((a.mn_major || b.mn_major || mode == 23) && variant != 5 && variant != 7)
     return fail(MTB200_ERR_INVALID, "MN-major planes and the fp16 mode need the two-CTA kernel (variant 5)");
   switch (variant) {
     case 1: return launch_variant<256, 32, 3>(h, a, b, Kp, g);
@@ -193,6 +220,8 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
     case 3: return launch_variant<64, 64, 3>(h, a, b, Kp, g);
     case 4: return launch_variant<128, 32, 4>(h, a, b, Kp, g);
     case 5: return mode == 23 ? launch_variant2<64, 3, 2>(h, a, b, Kp, g, K) : launch_variant2<64, 2, 3>(h, a, b, Kp, g, K);
+    case 7: return mode == 23 ? launch_variant2<64, 3, 2>(h, a, b, Kp, g, K, false)   // 5 without tail splitting
+                              : launch_variant2<64, 2, 3>(h, a, b, Kp, g, K, false);
     case 6: return launch_variant2<32, 4, 3>(h, a, b, Kp, g);
     default: return fail(MTB200_ERR_INVALID, "unknown GEMM tile variant %d", variant);
   }
@@ -231,7 +260,7 @@ inline int32_t launch_split16(mtb200_ctx* h, const float* src, bool k_major, int
 inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int batch, int M, int N, int K,
                                   const float* A, long long stride_a, const float* B, long long stride_b, float* C,
                                   long long ldc, long long stride_c, const float* bias, int epilogue,
-                                  const float* aux) {
+                                  const float* aux, int variant = 5) {
   const int Kp = padded_k(K);
   const int batch_a = (stride_a == 0 || batch == 1) ? 1 : batch;
   const int batch_b = (stride_b == 0 || batch == 1) ? 1 : batch;
@@ -271,7 +300,7 @@ inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int
   }
   SplitOperand oa{reinterpret_cast<const __nv_bfloat16*>(pa), a_rows, batch_a > 1, batch_a, a_kmaj ? 0 : 1, a_cols_p, 2, ea};
   SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(pb), b_rows, batch_b > 1, batch_b, b_kmaj ? 0 : 1, b_cols_p, 2, eb};
-  rc = run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, 23, 5, 0, 0, 0, K);
+  rc = run_split_gemm(h, oa, ob, Kp, batch, M, N, C, ldc, stride_c, bias, epilogue, aux, 23, variant, 0, 0, 0, K);
   if (rc) return rc;
   StridedGemmArgs s;
   s.M = M; s.N = N; s.K = K; s.batch = batch;
@@ -318,14 +347,15 @@ inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int bat
   }
   if (variant == 0 && M > 128 && N > 128) variant = 5;
   // default arithmetic: the fp16 two-plane mode wherever the pair-tile kernel runs, six bf16 products elsewhere
-  const int eff_mode = mode == 0 ? (variant == 5 ? 23 : 6) : mode;
+  const bool pair_tile = (variant == 5 || variant == 7);
+  const int eff_mode = mode == 0 ? (pair_tile ? 23 : 6) : mode;
   const int nsplit = eff_mode == 1 ? 1 : (eff_mode == 3 ? 2 : 3);
   if (eff_mode == 23) {
-    if (variant != 5) return fail(MTB200_ERR_UNSUPPORTED, "the fp16 mode runs on the pair-tile kernel (M, N > 128)");
+    if (!pair_tile) return fail(MTB200_ERR_UNSUPPORTED, "the fp16 mode runs on the pair-tile kernel (M, N > 128)");
     return gemm_f32_split_f16(h, trans_a, trans_b, batch, M, N, K, A, stride_a, B, stride_b, C, ldc, stride_c, bias,
-                              epilogue, aux);
+                              epilogue, aux, variant);
   }
-  const bool straight = (variant == 5);
+  const bool straight = pair_tile;
   // plane geometry: rows x padded cols
   const int a_rows = (straight && trans_a) ? K : M, a_cols_p = (straight && trans_a) ? padded_k(M) : Kp;
   const int b_rows = (straight && !trans_b) ? K : N, b_cols_p = (straight && !trans_b) ? padded_k(N) : Kp;

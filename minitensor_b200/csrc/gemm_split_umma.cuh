@@ -54,6 +54,14 @@ struct GemmArgs {
   int bias_per_row;    // 0: bias[N] added along columns; 1: bias[M] added along rows
   int kb_batch_stride; // split-K: batch entry b reduces K blocks [b*stride, b*stride + num_kb)
   uint32_t* status;    // device word; a non-zero value reports a wait that ran out
+  // Tail splitting (pair-tile kernel): when the tile count leaves a last round that would occupy at most half of
+  // the SM pairs, each of those tail tiles is cut into tail_splits K ranges that run side by side on different
+  // pairs; the raw partial accumulators go to `partial` ([tail tile][split][256][256] f32) and a second kernel
+  // adds them in a fixed order and applies the epilogue.  tail_splits <= 1: off.
+  int tail_splits;
+  int tail_rounds;     // full rounds before the tail: tiles [0, tail_rounds * pairs) are whole
+  int tail_tiles;      // tiles in the tail round
+  float* partial;
   // Implicit-convolution mode (CONV kernels only): the B operand is read straight
   // from channels-last image planes {c, w, h, image*3+split}; a K block is one
   // (filter tap, channel block) and an N tile is cv_th full image rows.

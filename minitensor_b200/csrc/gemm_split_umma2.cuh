@@ -50,6 +50,101 @@ __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar_cluster
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
 
+// Work item `it` of SM pair `pair`: a whole tile, or one K range of a tail tile (see GemmArgs::tail_splits).
+// part = -1 for a whole tile, else the index of the K range.  Returns false when the pair has no such item.
+__device__ __forceinline__ bool pair_work_item(const GemmArgs& g, int it, int pair, int num_pairs, int num_tiles,
+                                               int& tile, int& kb0, int& kb1, int& part) {
+  part = -1;
+  kb0 = 0;
+  kb1 = g.num_kb;
+  if (g.tail_splits <= 1) {
+    tile = pair + it * num_pairs;
+    return tile < num_tiles;
+  }
+  if (it < g.tail_rounds) {
+    tile = it * num_pairs + pair;
+    return true;
+  }
+  if (it == g.tail_rounds && pair < g.tail_tiles * g.tail_splits) {
+    part = pair / g.tail_tiles;
+    tile = g.tail_rounds * num_pairs + (pair - part * g.tail_tiles);
+    kb0 = static_cast<int>(static_cast<long long>(g.num_kb) * part / g.tail_splits);
+    kb1 = static_cast<int>(static_cast<long long>(g.num_kb) * (part + 1) / g.tail_splits);
+    return true;
+  }
+  return false;
+}
+
+// One warp's 32 rows x 256 columns of a raw accumulator to dst[row][256] (row = lane's row inside the 256-row
+// pair tile), through the same shared-memory transposition as the final epilogue so that stores are row segments.
+template <int CW>
+__device__ __forceinline__ void epilogue_warp_raw(float* stage, uint32_t t_row, float* __restrict__ dst, int row0,
+                                                  int lane) {
+  constexpr int LPR = CW / 4, RPI = 32 / LPR, PITCH = CW + 1;
+  const int cq = (lane % LPR) * 4, rsub = lane / LPR;
+#pragma unroll 1
+  for (int c0 = 0; c0 < 256; c0 += CW) {
+    uint32_t v[CW];
+    if constexpr (CW == 32) tmem_ld_32x32(t_row + c0, v);
+    else tmem_ld_32x16(t_row + c0, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < CW; ++j) stage[lane * PITCH + j] = __uint_as_float(v[j]);
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < LPR; ++it) {
+      const int r = it * RPI + rsub;
+      *reinterpret_cast<float4*>(dst + static_cast<long long>(row0 + r) * 256 + c0 + cq) =
+          make_float4(stage[r * PITCH + cq], stage[r * PITCH + cq + 1], stage[r * PITCH + cq + 2],
+                      stage[r * PITCH + cq + 3]);
+    }
+    __syncwarp();
+  }
+}
+
+// Sum of the K-range partials of every tail tile (ascending range order), then scale / bias / activation / store:
+// what the in-kernel epilogue does for whole tiles.  blockIdx.x = tail tile, blockIdx.y = group of 4 rows; one
+// float4 per thread, so the kernel is a few thousand independent blocks (it is latency-bound otherwise).
+template <int EPI>
+__device__ __forceinline__ void tail_fixup_body(const GemmArgs& g, int num_pairs, int tiles_m, int tiles_n) {
+  const int j = blockIdx.x;
+  const int tile = g.tail_rounds * num_pairs + j;
+  int b, tm, tn;
+  tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+  const int r = blockIdx.y * 4 + (threadIdx.x >> 6), c = (threadIdx.x & 63) * 4;
+  const int grow = tm * 256 + r, gcol = tn * 256 + c;
+  if (grow >= g.M || gcol >= g.N) return;
+  const float* part = g.partial + static_cast<long long>(j) * g.tail_splits * 65536 + r * 256 + c;
+  float4 acc = *reinterpret_cast<const float4*>(part);
+  for (int p = 1; p < g.tail_splits; ++p) {
+    const float4 t = *reinterpret_cast<const float4*>(part + static_cast<long long>(p) * 65536);
+    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+  }
+  float x[4] = {acc.x, acc.y, acc.z, acc.w};
+  float* cptr = g.C + b * g.strideC + static_cast<long long>(grow) * g.ldc + gcol;
+  const float* aptr = (EPI == EPI_RELU_BWD) ? g.aux + b * g.strideC + static_cast<long long>(grow) * g.ldc + gcol : nullptr;
+  const int ea = g.exp_b ? g.exp_a[(g.a_batched ? static_cast<long long>(b) * g.M : 0) + grow] : 0;
+  const int* eb = g.exp_b ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) + gcol : nullptr;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    if (gcol + e >= g.N) break;
+    float v = x[e];
+    if (eb) v = scale_pow2(v, ea + eb[e]);
+    if (g.bias) v += g.bias_per_row ? g.bias[grow] : g.bias[gcol + e];
+    cptr[e] = apply_epilogue_t<EPI>(v, EPI == EPI_RELU_BWD ? aptr[e] : 0.0f);
+  }
+}
+static __global__ void __launch_bounds__(256)
+tail_fixup_kernel(const GemmArgs g, int num_pairs, int tiles_m, int tiles_n) {
+  switch (g.epilogue) {
+    case EPI_RELU: tail_fixup_body<EPI_RELU>(g, num_pairs, tiles_m, tiles_n); break;
+    case EPI_GELU_ERF: tail_fixup_body<EPI_GELU_ERF>(g, num_pairs, tiles_m, tiles_n); break;
+    case EPI_GELU_TANH: tail_fixup_body<EPI_GELU_TANH>(g, num_pairs, tiles_m, tiles_n); break;
+    case EPI_RELU_BWD: tail_fixup_body<EPI_RELU_BWD>(g, num_pairs, tiles_m, tiles_n); break;
+    default: tail_fixup_body<EPI_NONE>(g, num_pairs, tiles_m, tiles_n); break;
+  }
+}
+
 template <int BK, int STAGES, int NP = 3>
 struct Gemm2Cfg {
   static constexpr int BM = 128;        // rows per CTA
@@ -131,14 +226,15 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      int t, kbeg, kend, part;
+      for (int it = 0; ok && pair_work_item(g, it, pair, num_pairs, num_tiles, t, kbeg, kend, part); ++it) {
         int b, tm, tn;
         tile_coords(t, tiles_m, tiles_n, b, tm, tn);
         const int za = (g.a_batched ? b : 0) * g.planes_per_mat, zb = (g.b_batched ? b : 0) * g.planes_per_mat;
         const int kb0 = b * g.kb_batch_stride;
         const int row_a = tm * Cfg::TILE_M + int(rank) * Cfg::BM;
         const int row_b = tn * Cfg::TILE_N + int(rank) * Cfg::BNH;
-        for (int kb = 0; kb < g.num_kb; ++kb) {
+        for (int kb = kbeg; kb < kend; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word)) {
             *abort_word = 1;
             atomicMax(g.status, 0x100u | 2u);
@@ -178,7 +274,8 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
         constexpr uint32_t A_KSTEP = A_MN ? 2048u : 32u, B_KSTEP = B_MN ? 2048u : 32u;
         int stage = 0, acc = 0;
         uint32_t phase = 0, acc_phase = 0;
-        for (int t = pair; t < num_tiles; t += num_pairs) {
+        int t, kbeg, kend, part;
+        for (int it = 0; pair_work_item(g, it, pair, num_pairs, num_tiles, t, kbeg, kend, part); ++it) {
           if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_word)) {
             *abort_word = 1;
             atomicMax(g.status, 0x200u | 3u);
@@ -187,7 +284,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * Cfg::TILE_N;
           uint32_t accumulate = 0;
-          for (int kb = 0; kb < g.num_kb; ++kb) {
+          for (int kb = kbeg; kb < kend; ++kb) {
             if (!mbar_wait(full_bar(stage), phase, abort_word)) {
               *abort_word = 1;
               atomicMax(g.status, 0x200u | 4u);
@@ -235,7 +332,8 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) && ((g.ldc & 3) == 0) && ((g.strideC & 3) == 0);
-    for (int t = pair; t < num_tiles; t += num_pairs) {
+    int t, kbeg, kend, part;
+    for (int it = 0; pair_work_item(g, it, pair, num_pairs, num_tiles, t, kbeg, kend, part); ++it) {
       int b, tm, tn;
       tile_coords(t, tiles_m, tiles_n, b, tm, tn);
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_word)) {
@@ -246,8 +344,14 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::TILE_N;
       float* stage = reinterpret_cast<float*>(smem_raw + (bars + 256u - raw)) + (warp - 2) * 32 * (Cfg::EPI_CW + 1);
-      epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row, b, tm * Cfg::TILE_M + int(rank) * Cfg::BM + q * 32,
-                                      tn * Cfg::TILE_N, min(g.N, (tn + 1) * Cfg::TILE_N), lane, vec_ok);
+      if (part >= 0) {
+        // one K range of a tail tile: the raw accumulator goes to its slot, the fix-up kernel finishes the tile
+        float* slot = g.partial + (static_cast<long long>(t - g.tail_rounds * num_pairs) * g.tail_splits + part) * 65536;
+        epilogue_warp_raw<Cfg::EPI_CW>(stage, t_row, slot, int(rank) * Cfg::BM + q * 32, lane);
+      } else {
+        epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row, b, tm * Cfg::TILE_M + int(rank) * Cfg::BM + q * 32,
+                                        tn * Cfg::TILE_N, min(g.N, (tn + 1) * Cfg::TILE_N), lane, vec_ok);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(acc_empty_bar(acc), 0));

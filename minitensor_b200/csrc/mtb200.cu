@@ -225,6 +225,7 @@ int32_t mtb200_destroy(mtb200_handle h) {
   if (h->workspace) cudaFree(h->workspace);
   if (h->status) cudaFree(h->status);
   if (h->status_host) cudaFreeHost(h->status_host);
+  if (h->tail_partial) cudaFree(h->tail_partial);
   if (h->side_stream) {
     cudaStreamSynchronize(h->side_stream);
     cudaStreamDestroy(h->side_stream);

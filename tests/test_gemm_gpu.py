@@ -442,3 +442,46 @@ def test_largest_square_sizes_f32_f64_i32(be, orc):
     rows64 = rows[:6] % m
     ref = orc.matmul(np.ascontiguousarray(a64.numpy()[rows64]), b64.numpy())
     assert norm_scaled_error(c64[rows64].cpu().numpy(), ref, a64.numpy()[rows64], b64.numpy()) <= 1e-13
+
+
+# ------------------------------------------------------------------ tail splitting (a short last round cut into K ranges)
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_tail_split_tiles_match_oracle(be, orc, rng, ta, tb):
+    """77 pair tiles on 74 SM pairs: the last three tiles are computed as four K ranges each and finished by the
+    fix-up kernel (sum in range order, scaling, bias, activation).  Sampled rows - the tail tiles' among them -
+    against the f64-accumulated oracle, with every epilogue the fix-up implements."""
+    m, n, k = 2816 - 5, 1792 - 3, 2100
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    al = np.ascontiguousarray(a.T if ta else a)
+    bl = np.ascontiguousarray(b.T if tb else b)
+    rows = np.unique(np.concatenate([np.arange(0, m, 61), np.arange(2048, m, 23)]))
+    wide = orc.matmul_acc_wide(np.ascontiguousarray(al[rows]), bl)
+    ad, bd = dev(be, a), dev(be, b)
+    c = be.gemm(ad, bd, trans_a=ta, trans_b=tb)
+    be.sync()
+    assert norm_scaled_error(c[rows].cpu().numpy(), wide, al[rows], bl) <= 4e-6
+    if not (ta or tb):
+        bias = rng.standard_normal(n).astype(np.float32)
+        aux = rng.standard_normal((m, n)).astype(np.float32)
+        y = be.gemm(ad, bd, bias=dev(be, bias), epilogue=1)
+        z = be.gemm(ad, bd, epilogue=4, aux=dev(be, aux))
+        w6 = be.gemm(ad, bd, f32_mode=6)                      # the bf16 six-product mode splits its tail too
+        be.sync()
+        assert norm_scaled_error(y[rows].cpu().numpy(), np.maximum(wide + bias, 0.0), al[rows], bl) <= 4e-6
+        assert norm_scaled_error(z[rows].cpu().numpy(), wide * (aux[rows] > 0), al[rows], bl) <= 4e-6
+        assert norm_scaled_error(w6[rows].cpu().numpy(), wide, al[rows], bl) <= 4e-6
+        c2 = be.gemm(ad, bd)
+        be.sync()
+        assert torch.equal(c, c2)                             # fixed summation order: bit-identical repeats
+
+
+def test_tail_split_batched(be, orc, rng):
+    """5 x (1024 x 1024) = 80 pair tiles: six tail tiles, some of them in the last batch entry."""
+    a = rng.standard_normal((5, 1024, 2048)).astype(np.float32)
+    b = rng.standard_normal((5, 2048, 1024)).astype(np.float32)
+    c = run_gemm(be, a, b)
+    rows = np.arange(0, 1024, 37)
+    for i in (0, 3, 4):
+        wide = orc.matmul_acc_wide(np.ascontiguousarray(a[i][rows]), b[i])
+        assert norm_scaled_error(c[i][rows], wide, a[i][rows], b[i]) <= 4e-6
