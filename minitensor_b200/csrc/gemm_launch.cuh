@@ -235,9 +235,20 @@ inline int32_t launch_split16(mtb200_ctx* h, const float* src, bool k_major, int
   if (!stream) stream = h->stream;
   if (k_major) {
     const int Kp = padded_k(K);
-    ProfScope prof(h, PROF_SPLIT, double(batch) * mn * (8.0 * K + 4.0 * Kp));
-    split16_rows_kernel<<<dim3(unsigned(std::min(mn, 65535)), 1, batch), 256, 0, stream>>>(
-        src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
+    const dim3 grid(unsigned(std::min(mn, 65535)), 1, batch);
+    const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((bstride & 3) == 0);
+    // bytes: the row is read once when it is held in registers, twice (second time from L1/L2) otherwise
+    ProfScope prof(h, PROF_SPLIT, double(batch) * mn * ((vec && Kp <= 8192 ? 4.0 : 8.0) * K + 4.0 * Kp));
+    if (vec && Kp <= 1024)
+      split16_rows_reg_kernel<1><<<grid, 256, 0, stream>>>(src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
+    else if (vec && Kp <= 2048)
+      split16_rows_reg_kernel<2><<<grid, 256, 0, stream>>>(src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
+    else if (vec && Kp <= 4096)
+      split16_rows_reg_kernel<4><<<grid, 256, 0, stream>>>(src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
+    else if (vec && Kp <= 8192)
+      split16_rows_reg_kernel<8><<<grid, 256, 0, stream>>>(src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
+    else
+      split16_rows_kernel<<<grid, 256, 0, stream>>>(src, K, bstride, planes, expo, mn, K, Kp, nf_word, epoch);
   } else {
     const int cp = padded_k(mn);
     ProfScope prof(h, PROF_SPLIT, double(batch) * K * (8.0 * mn + 4.0 * cp));

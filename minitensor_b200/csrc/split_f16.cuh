@@ -129,6 +129,64 @@ split16_rows_kernel(const float* __restrict__ src, long long ld, long long bstri
   }
 }
 
+// The same for rows of at most J * 1024 elements that can be read as float4: the row stays in registers between
+// the maximum and the split, so it is read from memory once (the kernel above reads it twice, the second time
+// from L1/L2, and its scalar second pass is issue-bound).  K % 4 == 0, 16-byte aligned rows.
+template <int J>
+static __global__ void __launch_bounds__(256)
+split16_rows_reg_kernel(const float* __restrict__ src, long long ld, long long bstride, __half* __restrict__ dst,
+                        int* __restrict__ expo, int R, int K, int Kp, uint32_t* __restrict__ nf_word,
+                        uint32_t nf_epoch) {
+  __shared__ float red[8];
+  __shared__ int s_e;
+  const int b = blockIdx.z;
+  const long long plane = static_cast<long long>(R) * Kp;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const float* p = src + b * bstride + static_cast<long long>(r) * ld;
+    float4 v[J];
+    float amax = 0.0f;
+    bool nf = false;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int k = (j * 256 + threadIdx.x) * 4;
+      v[j] = (k < K) ? *reinterpret_cast<const float4*>(p + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+      nf |= is_nonfinite(v[j].x) | is_nonfinite(v[j].y) | is_nonfinite(v[j].z) | is_nonfinite(v[j].w);
+    }
+    if (nf && nf_word) atomicMax(nf_word, nf_epoch);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = red[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+      const int e = scale_exponent(m);
+      s_e = e;
+      expo[static_cast<long long>(b) * R + r] = e;
+    }
+    __syncthreads();
+    const int e = s_e;
+    __half* d0 = dst + (static_cast<long long>(b) * 2) * plane + static_cast<long long>(r) * Kp;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int k = (j * 256 + threadIdx.x) * 4;
+      if (k < Kp) {  // columns K..Kp-1 are written as zeros (v is zero there)
+        __align__(8) __half o0[4], o1[4];
+        split2_f16(v[j].x, e, o0[0], o1[0]);
+        split2_f16(v[j].y, e, o0[1], o1[1]);
+        split2_f16(v[j].z, e, o0[2], o1[2]);
+        split2_f16(v[j].w, e, o0[3], o1[3]);
+        *reinterpret_cast<uint2*>(d0 + k) = *reinterpret_cast<const uint2*>(o0);
+        *reinterpret_cast<uint2*>(d0 + plane + k) = *reinterpret_cast<const uint2*>(o1);
+      }
+    }
+    __syncthreads();  // red / s_e are rewritten by the next row
+  }
+}
+
 // amax_bits[b][c] = max over rows of |src[b][r][c]| as raw bits (non-negative floats order like unsigned ints).
 // The vector must be zeroed before the launch.
 static __global__ void __launch_bounds__(256)
