@@ -161,7 +161,15 @@ int32_t mtb200_dense_forward(mtb200_handle h, int32_t dtype, int64_t rows, int64
 int32_t mtb200_dense_backward(mtb200_handle h, int32_t dtype, int64_t rows, int64_t in_features,
                               int64_t out_features, const void* x, const void* W, const void* dY,
                               const void* saved, void* dX, int32_t dx_epilogue, const void* dx_aux,
-                              void* dW, void* db);
+                              void* dW, void* db, void* dy_block, int32_t dy_mode);
+/* dy_block / dy_mode (NULL / 0 for the plain use): data-parallel training wants the chain of input gradients
+ * first and the parameter gradients afterwards, largest layer first, so that their all-reduces overlap the
+ * remaining products.  A call with dy_mode 1 (dW NULL) computes dX and db and also leaves dY's prepared
+ * weight-gradient operand in dy_block (mtb200_dense_dy_bytes bytes, caller-owned); a later call with dy_mode 2
+ * (dX and db NULL) computes dW from that block without reading dY again.  dY, x and the block must be unchanged
+ * in between.  Ignored (plain products) where mtb200_dense_saved_bytes reports 0. */
+int32_t mtb200_dense_dy_bytes(int32_t dtype, int64_t rows, int64_t in_features, int64_t out_features,
+                              size_t* bytes);
 
 /* ---- bias gradient: out[n] = sum_m X[m][n]  (f32 / f64)
  * reduce_gradient_for_broadcasting -> sum over dim 0

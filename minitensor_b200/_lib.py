@@ -41,7 +41,8 @@ SIGNATURES = {
                            _vp, _i64, _vp, _i32, _vp, _i32]),
     "mtb200_dense_saved_bytes": (_i32, [_i32, _i64, _i64, _i64, C.POINTER(C.c_size_t)]),
     "mtb200_dense_forward": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _vp]),
-    "mtb200_dense_backward": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "mtb200_dense_backward": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32]),
+    "mtb200_dense_dy_bytes": (_i32, [_i32, _i64, _i64, _i64, C.POINTER(C.c_size_t)]),
     "mtb200_colsum": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
     "mtb200_colsum_noalloc": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
     "mtb200_act_fwd": (_i32, [_vp, _i32, _i32, _i64, _vp, _vp]),

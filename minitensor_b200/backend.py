@@ -134,6 +134,13 @@ class Backend:
         check(self.lib.mtb200_dense_saved_bytes(code, rows, in_features, out_features, C.byref(n)))
         return int(n.value)
 
+    def dense_dy_bytes(self, rows: int, in_features: int, out_features: int, dtype=torch.float32) -> int:
+        """Bytes of the block that carries dY's prepared operand between two ``dense_backward`` calls (0: unused)."""
+        n = C.c_size_t(0)
+        code = dtype_code(torch.empty(0, dtype=dtype))
+        check(self.lib.mtb200_dense_dy_bytes(code, rows, in_features, out_features, C.byref(n)))
+        return int(n.value)
+
     def dense_forward(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                       epilogue: int = EPI_NONE, out: Optional[torch.Tensor] = None,
                       saved: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -154,8 +161,13 @@ class Backend:
     def dense_backward(self, x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, saved: Optional[torch.Tensor], *,
                        dx: Optional[torch.Tensor] = None, need_dx: bool = True, dx_epilogue: int = EPI_NONE,
                        dx_aux: Optional[torch.Tensor] = None, dw: Optional[torch.Tensor] = None, need_dw: bool = True,
-                       db: Optional[torch.Tensor] = None, need_db: bool = True):
-        """Gradients of ``dense_forward``: returns ``(dx or None, dw, db or None)``."""
+                       db: Optional[torch.Tensor] = None, need_db: bool = True,
+                       dy_block: Optional[torch.Tensor] = None, dy_mode: int = 0):
+        """Gradients of ``dense_forward``: returns ``(dx or None, dw or None, db or None)``.
+
+        ``dy_block`` / ``dy_mode``: a call with ``dy_mode=1`` (no ``dw``) also leaves dY's prepared weight-gradient
+        operand in ``dy_block`` (``dense_dy_bytes`` bytes); a later call with ``dy_mode=2`` (no ``dx``, no ``db``)
+        computes ``dw`` from it without reading ``dy`` again."""
         rows, fin = x.shape
         fout = w.shape[0]
         if tuple(dy.shape) != (rows, fout):
@@ -169,9 +181,11 @@ class Backend:
         self._bind_stream()
         check(self.lib.mtb200_dense_backward(self._h, dtype_code(x), rows, fin, fout, _ptr(x), _ptr(w), _ptr(dy),
                                              _ptr(saved), _ptr(dx) if need_dx else None, dx_epilogue, _ptr(dx_aux),
-                                             _ptr(dw) if need_dw else None, _ptr(db) if need_db else None))
+                                             _ptr(dw) if need_dw else None, _ptr(db) if need_db else None,
+                                             _ptr(dy_block), dy_mode if dy_block is not None else 0))
         products = int(need_dx) + int(need_dw)
-        self.launches += (5 + 2 * products) if saved is not None else (4 * products + 2 * int(need_db))
+        prep = 1 if (dy_mode == 2 and dy_block is not None) else 5
+        self.launches += (prep + 2 * products) if saved is not None else (4 * products + 2 * int(need_db))
         return (dx if need_dx else None), (dw if need_dw else None), (db if need_db else None)
 
     # ------------------------------------------------------------------ reductions / elementwise

@@ -294,11 +294,34 @@ inline int32_t dense_forward_f32(mtb200_ctx* h, int M, int in, int out, const fl
   return launch_nonfinite_redo(h, false, true, M, out, in, x, W, y, bias, epilogue, aux, epoch);
 }
 
+// Layout of the optional block that carries dY's weight-gradient operand from one backward call to a later one
+// (dy_mode 1 writes it, dy_mode 2 consumes it): column-scaled planes [2][M][outp], their exponents, a non-finite flag.
+struct DenseDy {
+  size_t off_planes, off_ec, off_flag, total;
+};
+inline DenseDy dense_dy_layout(long long M, long long out) {
+  DenseDy d;
+  size_t o = 0;
+  d.off_planes = o; o += align_up(size_t(2) * M * padded_k(int(out)) * 2, 1024);
+  d.off_ec = o;     o += align_up(sizeof(int) * size_t(out), 1024);
+  d.off_flag = o;   o += 1024;
+  d.total = o;
+  return d;
+}
+
+// nf_word = epoch when either flag word is set (the operands of an earlier call held Inf / NaN)
+static __global__ void raise_nonfinite_kernel(const uint32_t* __restrict__ flag_a, const uint32_t* __restrict__ flag_b,
+                                              uint32_t* __restrict__ nf_word, uint32_t epoch) {
+  if ((flag_a && *flag_a) || (flag_b && *flag_b)) atomicMax(nf_word, epoch);
+}
+
 // dX = epilogue(dY W) (nullable), dW = dY^T x (nullable), db = column sums of dY (nullable), from the block a forward
 // call of the same shapes left in `saved`.  x and W themselves are read only by the Inf / NaN redo.
+// dy_mode 1 (dW null): the weight-gradient operand of dY is prepared all the same and left in dy_block;
+// dy_mode 2 (dX null): dy_block holds it and dY is not read at all (db must have been taken by the earlier call).
 inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const float* x, const float* W,
                                   const float* dY, const void* saved, float* dX, int epilogue, const float* aux,
-                                  float* dW, float* db) {
+                                  float* dW, float* db, void* dy_block = nullptr, int dy_mode = 0) {
   const DenseSaved L = dense_saved_layout(M, in, out);
   const char* sv = static_cast<const char*>(saved);
   const __half* xp = reinterpret_cast<const __half*>(sv + L.off_xp);
@@ -307,6 +330,11 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
   const int* we = reinterpret_cast<const int*>(sv + L.off_we);
   const uint32_t* flag = reinterpret_cast<const uint32_t*>(sv + L.off_flag);
   const int outp = padded_k(out);
+  const DenseDy D = dense_dy_layout(M, out);
+  char* dyb = static_cast<char*>(dy_block);
+  const bool keep_cols = dy_mode == 1 && dy_block;   // write the column planes into the block
+  const bool have_cols = dy_mode == 2 && dy_block;   // read them from the block
+  const bool want_cols = dW != nullptr || keep_cols; // this call prepares column planes
 
   const int col_blocks = (out + 2047) / 2048;
   int bands = std::max(1, std::min((M + 15) / 16, (h->sm_count * 4) / col_blocks));
@@ -318,26 +346,36 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
   const size_t bytes_ec = align_up(sizeof(int) * size_t(out), 1024);
   const size_t bytes_zero = align_up(sizeof(int) * size_t(in), 1024);
   const size_t bytes_part = db ? align_up(sizeof(float) * size_t(bands) * out, 1024) : 0;
+  const int ws_sets = (dX ? 1 : 0) + ((want_cols && !keep_cols && !have_cols) ? 1 : 0);
   void* ws = nullptr;
-  const int nsets = (dX ? 1 : 0) + (dW ? 1 : 0);
-  int32_t rc = workspace_reserve(h, nsets * bytes_planes + bytes_er + bytes_ec + bytes_zero + bytes_part, &ws);
+  int32_t rc = workspace_reserve(h, ws_sets * bytes_planes + bytes_er + bytes_ec + bytes_zero + bytes_part, &ws);
   if (rc) return rc;
   char* base = static_cast<char*>(ws);
-  __half* pc = dW ? reinterpret_cast<__half*>(base) : nullptr;                              // column-scaled planes (dW)
-  __half* pr = dX ? reinterpret_cast<__half*>(base + (dW ? bytes_planes : 0)) : nullptr;   // row-scaled planes (dX)
-  char* q = base + nsets * bytes_planes;
+  const bool cols_in_ws = want_cols && !keep_cols && !have_cols;
+  __half* pc = (keep_cols || have_cols) ? reinterpret_cast<__half*>(dyb + D.off_planes)
+                                        : (cols_in_ws ? reinterpret_cast<__half*>(base) : nullptr);   // column-scaled planes (dW)
+  __half* pr = dX ? reinterpret_cast<__half*>(base + (cols_in_ws ? bytes_planes : 0)) : nullptr;      // row-scaled planes (dX)
+  char* q = base + ws_sets * bytes_planes;
   int* er = reinterpret_cast<int*>(q);
-  int* ec = reinterpret_cast<int*>(q + bytes_er);
+  int* ec_ws = reinterpret_cast<int*>(q + bytes_er);
+  int* ec = (keep_cols || have_cols) ? reinterpret_cast<int*>(dyb + D.off_ec) : ec_ws;
   int* zero = reinterpret_cast<int*>(q + bytes_er + bytes_ec);
   float* part = db ? reinterpret_cast<float*>(q + bytes_er + bytes_ec + bytes_zero) : nullptr;
+  uint32_t* dy_flag = dy_block ? reinterpret_cast<uint32_t*>(dyb + D.off_flag) : nullptr;
 
   uint32_t* nf_word = h->status + 2;
   const uint32_t epoch = ++h->epoch;
-  {
-    // maxima + column sums: one read of dY; both plane sets: one more read and (one or) two plane writes
+  MTB_CUDA(cudaMemsetAsync(zero, 0, bytes_zero, h->stream));
+  if (have_cols) {
+    // nothing of dY is read: only the Inf / NaN state of the earlier calls is carried over
+    raise_nonfinite_kernel<<<1, 1, 0, h->stream>>>(flag, dy_flag, nf_word, epoch);
+    MTB_CUDA(cudaGetLastError());
+  } else {
+    // maxima + column sums: one read of dY; the plane sets: one more read and one write per set
+    const int nsets = (dX ? 1 : 0) + (want_cols ? 1 : 0);
     ProfScope prof(h, PROF_SPLIT, double(M) * (8.0 * out + 4.0 * nsets * outp));
-    MTB_CUDA(cudaMemsetAsync(er, 0x80, bytes_er + bytes_ec, h->stream));  // every key far below KEY_NONE / 2
-    MTB_CUDA(cudaMemsetAsync(zero, 0, bytes_zero, h->stream));
+    MTB_CUDA(cudaMemsetAsync(er, 0x80, bytes_er, h->stream));  // every key far below KEY_NONE / 2
+    MTB_CUDA(cudaMemsetAsync(ec, 0x80, sizeof(int) * size_t(out), h->stream));
     if (dX)
       dy_stats_kernel<true><<<dim3(col_blocks, bands), 256, 0, h->stream>>>(dY, out, M, out, rows_per_band, xe, we, er,
                                                                             ec, part, flag, nf_word, epoch);
@@ -345,18 +383,19 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
       dy_stats_kernel<false><<<dim3(col_blocks, bands), 256, 0, h->stream>>>(dY, out, M, out, rows_per_band, xe,
                                                                              nullptr, nullptr, ec, part, flag,
                                                                              nf_word, epoch);
-    keys_to_exponents_kernel<<<(M + 255) / 256, 256, 0, h->stream>>>(er, M);
+    if (dX) keys_to_exponents_kernel<<<(M + 255) / 256, 256, 0, h->stream>>>(er, M);
     keys_to_exponents_kernel<<<(out + 255) / 256, 256, 0, h->stream>>>(ec, out);
     if (db) colsum_bands_kernel<<<(out + 31) / 32, 256, 0, h->stream>>>(part, bands, out, db);
+    if (keep_cols) save_nonfinite_flag_kernel<<<1, 1, 0, h->stream>>>(nf_word, epoch, dy_flag);
     const int sp_cols = (outp / 8 + 255) / 256;
     const int sp_bands = std::max(1, std::min(M, (h->sm_count * 8 + sp_cols - 1) / sp_cols));
     const int sp_rows = (M + sp_bands - 1) / sp_bands;
     const dim3 sp_grid(sp_cols, (M + sp_rows - 1) / sp_rows);
-    if (dX && dW)
+    if (dX && want_cols)
       dy_split2_kernel<true, true><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, we, er, pr, pc);
     else if (dX)
       dy_split2_kernel<true, false><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, we, er, pr, nullptr);
-    else if (dW)
+    else if (want_cols)
       dy_split2_kernel<false, true><<<sp_grid, 256, 0, h->stream>>>(dY, out, M, out, outp, sp_rows, xe, ec, nullptr, nullptr, nullptr, pc);
     MTB_CUDA(cudaGetLastError());
   }

@@ -531,16 +531,29 @@ int32_t mtb200_dense_forward(mtb200_handle h, int32_t dtype, int64_t rows, int64
                            static_cast<float*>(y), saved);
 }
 
+int32_t mtb200_dense_dy_bytes(int32_t dtype, int64_t rows, int64_t in_features, int64_t out_features, size_t* bytes) {
+  if (!bytes) return fail(MTB200_ERR_INVALID, "null output pointer");
+  if (dtype != MTB200_F32 && dtype != MTB200_F64) return fail(MTB200_ERR_UNSUPPORTED, "dense layer: dtype must be f32 or f64");
+  if (rows < 0 || in_features < 0 || out_features < 0) return fail(MTB200_ERR_INVALID, "negative dimension");
+  *bytes = dense_uses_saved(dtype, rows, in_features, out_features) ? dense_dy_layout(rows, out_features).total : 0;
+  return MTB200_OK;
+}
+
 int32_t mtb200_dense_backward(mtb200_handle h, int32_t dtype, int64_t rows, int64_t in_features,
                               int64_t out_features, const void* x, const void* W, const void* dY,
                               const void* saved, void* dX, int32_t dx_epilogue, const void* dx_aux,
-                              void* dW, void* db) {
+                              void* dW, void* db, void* dy_block, int32_t dy_mode) {
   MTB_CHECK_HANDLE(h);
   if (dtype != MTB200_F32 && dtype != MTB200_F64) return fail(MTB200_ERR_UNSUPPORTED, "dense layer: dtype must be f32 or f64");
   if (dx_epilogue != MTB200_EPI_NONE && dx_epilogue != MTB200_EPI_RELU_BWD)
     return fail(MTB200_ERR_INVALID, "dense backward epilogue must be NONE or RELU_BWD");
   if (dX && dx_epilogue == MTB200_EPI_RELU_BWD && !dx_aux) return fail(MTB200_ERR_INVALID, "RELU_BWD epilogue needs aux");
-  if (!saved || !dense_uses_saved(dtype, rows, in_features, out_features)) {
+  if (dy_mode < 0 || dy_mode > 2) return fail(MTB200_ERR_INVALID, "dy_mode must be 0, 1 or 2");
+  if (dy_mode == 1 && dW) return fail(MTB200_ERR_INVALID, "dy_mode 1 prepares dY for a LATER weight-gradient call: dW must be NULL");
+  if (dy_mode == 2 && (dX || db)) return fail(MTB200_ERR_INVALID, "dy_mode 2 does not read dY: dX and db must be NULL");
+  const bool fused = saved && dense_uses_saved(dtype, rows, in_features, out_features);
+  if (!fused || !dy_block) dy_mode = 0;  // plain products keep nothing between calls
+  if (!fused) {
     int32_t rc = MTB200_OK;
     if (dW) {
       rc = mtb200_gemm(h, dtype, 1, 0, 1, out_features, in_features, rows, dY, 0, x, 0, dW, 0, nullptr,
@@ -559,7 +572,7 @@ int32_t mtb200_dense_backward(mtb200_handle h, int32_t dtype, int64_t rows, int6
   return dense_backward_f32(h, int(rows), int(in_features), int(out_features), static_cast<const float*>(x),
                             static_cast<const float*>(W), static_cast<const float*>(dY), saved,
                             static_cast<float*>(dX), dx_epilogue, static_cast<const float*>(dx_aux),
-                            static_cast<float*>(dW), static_cast<float*>(db));
+                            static_cast<float*>(dW), static_cast<float*>(db), dy_block, dy_mode);
 }
 
 // ------------------------------------------------------------------ activations

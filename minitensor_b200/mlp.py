@@ -122,6 +122,7 @@ class MLPTrainer:
         self._copy_done = [None, None]
         self._slot = 0
         self._side_stream = None
+        self._dy_blocks = None
         self._counted = False
         self._step_dev = None
         self._graph = None
@@ -243,16 +244,29 @@ class MLPTrainer:
         stream as soon as its all-reduce has landed (HBM-bound, so it overlaps the tensor-bound products)."""
         import torch.distributed as dist
         be = self.be
+        if self._dy_blocks is None:
+            self._dy_blocks = [None] * self.nl
+            for l in range(1, self.nl):
+                nbytes = be.dense_dy_bytes(self.batch, self.dims[l], self.dims[l + 1]) if self.saved[l] is not None else 0
+                if nbytes:
+                    self._dy_blocks[l] = torch.empty(nbytes, dtype=torch.uint8, device=be.device)
         for l in range(self.nl - 1, 0, -1):
+            # input gradient and bias gradient now; dY's operand for the weight gradient is kept for the second pass
             be.dense_backward(self.h[l - 1], self.W[l], self.g[l], self.saved[l], need_dx=True, dx=self.g[l - 1],
-                              dx_epilogue=EPI_RELU_BWD, dx_aux=self.h[l - 1], need_dw=False, need_db=False)
+                              dx_epilogue=EPI_RELU_BWD, dx_aux=self.h[l - 1], need_dw=False,
+                              need_db=self._dy_blocks[l] is not None, db=self.db[l],
+                              dy_block=self._dy_blocks[l], dy_mode=1)
         main = torch.cuda.current_stream(be.device)
         if self._side_stream is None:
             self._side_stream = torch.cuda.Stream(device=be.device)
         side = self._side_stream
         for l in range(self.nl):
             a_in = x if l == 0 else self.h[l - 1]
-            be.dense_backward(a_in, self.W[l], self.g[l], self.saved[l], need_dx=False, dw=self.dW[l], db=self.db[l])
+            if self._dy_blocks[l] is not None:
+                be.dense_backward(a_in, self.W[l], self.g[l], self.saved[l], need_dx=False, dw=self.dW[l], need_db=False,
+                                  dy_block=self._dy_blocks[l], dy_mode=2)
+            else:
+                be.dense_backward(a_in, self.W[l], self.g[l], self.saved[l], need_dx=False, dw=self.dW[l], db=self.db[l])
             lo, hi = self.w_off[l], self.b_off[l] + self.dims[l + 1]
             hnd = (dist.all_reduce(self.grads[lo:hi], op=dist.ReduceOp.SUM, async_op=True)
                    if self.world_size > 1 else None)

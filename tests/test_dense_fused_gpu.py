@@ -256,3 +256,30 @@ def test_large_mlp_step_full_size_properties(be, orc):
     tr2.step(x, y)
     be.sync()
     assert torch.equal(tr2.grads, grads_first) and torch.equal(tr2.params, tr.params)
+
+
+def test_dense_backward_in_two_calls_with_a_carried_dy_block(be, rng):
+    """dy_mode 1 (input and bias gradient now, dY's weight-gradient operand kept) followed by dy_mode 2 (weight
+    gradient from the kept block, dY not read) gives the bits of the single call; misuse is refused."""
+    rows, fin, fout = 384, 256, 300
+    x = dev(be, rng.standard_normal((rows, fin)).astype(np.float32))
+    w = dev(be, rng.standard_normal((fout, fin)).astype(np.float32))
+    dy = dev(be, rng.standard_normal((rows, fout)).astype(np.float32))
+    saved = torch.empty(be.dense_saved_bytes(rows, fin, fout), dtype=torch.uint8, device=be.device)
+    block = torch.empty(be.dense_dy_bytes(rows, fin, fout), dtype=torch.uint8, device=be.device)
+    assert block.numel() > 0 and be.dense_dy_bytes(100, fin, fout) == 0
+    be.dense_forward(x, w, None, 0, saved=saved)
+    dx0, dw0, db0 = be.dense_backward(x, w, dy, saved)
+    dx1, none_dw, db1 = be.dense_backward(x, w, dy, saved, need_dw=False, dy_block=block, dy_mode=1)
+    dy_scrambled = torch.full_like(dy, float("nan"))          # the second call must not look at dY
+    none_dx, dw1, none_db = be.dense_backward(x, w, dy_scrambled, saved, need_dx=False, need_db=False,
+                                              dy_block=block, dy_mode=2)
+    be.sync()
+    assert none_dw is None and none_dx is None and none_db is None
+    assert torch.equal(dx0, dx1) and torch.equal(db0, db1) and torch.equal(dw0, dw1)
+    with pytest.raises(ValueError):
+        be.dense_backward(x, w, dy, saved, dy_block=block, dy_mode=1)                       # dW asked for in mode 1
+    with pytest.raises(ValueError):
+        be.dense_backward(x, w, dy, saved, need_dx=False, dy_block=block, dy_mode=2)        # db asked for in mode 2
+    with pytest.raises(ValueError):
+        be.dense_backward(x, w, dy, saved, dy_block=block, dy_mode=3)
