@@ -83,6 +83,11 @@ int32_t mtb200_destroy(mtb200_handle h);
 /* Enqueue on an existing cudaStream_t / CUstream from now on (NULL = the CUDA
  * default stream).  A new handle uses a non-blocking stream of its own. */
 int32_t mtb200_set_stream(mtb200_handle h, void* cuda_stream);
+/* SMs the persistent tensor-core GEMM kernels may occupy from now on (0 = all).  (No counterpart in the
+ * reference.)  Those kernels launch one CTA per SM and deal tiles out statically, so a kernel that runs beside
+ * them and needs SMs of its own - a collective overlapping the backward pass - otherwise delays some CTAs and
+ * with them the whole GEMM; leaving it a few SMs costs less than that. */
+int32_t mtb200_set_gemm_sm_limit(mtb200_handle h, int32_t sms);
 /* CudaBackend::synchronize (engine/src/backends/cuda/mod.rs:153-161); also
  * reports MTB200_ERR_DEVICE_WAIT if a kernel recorded an expired wait. */
 int32_t mtb200_sync(mtb200_handle h);

@@ -28,6 +28,7 @@ SIGNATURES = {
     "mtb200_create": (_i32, [_i32, C.POINTER(_vp)]),
     "mtb200_destroy": (_i32, [_vp]),
     "mtb200_set_stream": (_i32, [_vp, _vp]),
+    "mtb200_set_gemm_sm_limit": (_i32, [_vp, _i32]),
     "mtb200_sync": (_i32, [_vp]),
     "mtb200_profile_enable": (_i32, [_vp, _i32]),
     "mtb200_profile_read": (_i32, [_vp, _i32, C.POINTER(_i64), C.POINTER(_f64), C.POINTER(_f64)]),

@@ -64,6 +64,10 @@ class Backend:
         except Exception:
             pass
 
+    def set_gemm_sm_limit(self, sms: int) -> None:
+        """SMs the persistent GEMM kernels may occupy (0 = all): leaves room for kernels that run beside them."""
+        check(self.lib.mtb200_set_gemm_sm_limit(self._h, int(sms)))
+
     def sync(self) -> None:
         """Wait for the stream and raise if a kernel reported an expired wait or a bad label."""
         check(self.lib.mtb200_sync(self._h))

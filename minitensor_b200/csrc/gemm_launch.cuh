@@ -112,13 +112,14 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
   cfg.stream = h->stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cfg.gridDim = dim3(2 * (h->sm_count / 2));
+  const int sms = (h->gemm_sm_limit > 0) ? std::min(h->gemm_sm_limit, h->sm_count) : h->sm_count;
+  cfg.gridDim = dim3(2 * (sms / 2));
   int max_clusters = 0;
   if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0) {
     cudaGetLastError();
-    max_clusters = h->sm_count / 2;
+    max_clusters = sms / 2;
   }
-  const int max_pairs = std::min(max_clusters, h->sm_count / 2);
+  const int max_pairs = std::min(max_clusters, sms / 2);
   int pairs = int(std::min<long long>(tiles, max_pairs));
   // A last round that would keep at most half of the pairs busy: cut its tiles into K ranges so that the round
   // takes 1 / splits of a tile time (4096^3: 256 tiles on 74 pairs, 34 tail tiles -> 68 half tiles).  An output
@@ -130,7 +131,7 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
     while (splits >= 2 && g.num_kb < 4 * splits) --splits;
     if (splits >= 2) {
       if (!h->tail_partial) {
-        MTB_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->tail_partial), size_t(max_pairs) * 65536 * sizeof(float)));
+        MTB_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->tail_partial), size_t(h->sm_count / 2) * 65536 * sizeof(float)));
       }
       g.tail_splits = splits;
       g.tail_rounds = tiles > pairs ? int(tiles / pairs) : 0;

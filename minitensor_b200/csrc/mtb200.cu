@@ -243,6 +243,13 @@ int32_t mtb200_set_stream(mtb200_handle h, void* cuda_stream) {
   return MTB200_OK;
 }
 
+int32_t mtb200_set_gemm_sm_limit(mtb200_handle h, int32_t sms) {
+  MTB_CHECK_HANDLE(h);
+  if (sms < 0) return fail(MTB200_ERR_INVALID, "negative SM count");
+  h->gemm_sm_limit = (sms == 0 || sms >= h->sm_count) ? 0 : std::max(2, sms);
+  return MTB200_OK;
+}
+
 int32_t mtb200_sync(mtb200_handle h) {
   MTB_CHECK_HANDLE(h);
   MTB_CUDA(cudaMemcpyAsync(h->status_host, h->status, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost,

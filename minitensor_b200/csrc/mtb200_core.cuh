@@ -48,6 +48,7 @@ struct mtb200_ctx {
   // second stream + fork/join events: the two operands of a mid-size GEMM are prepared side by side
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  int gemm_sm_limit = 0;            // SMs the persistent tensor kernels may occupy (0 = all), see mtb200_set_gemm_sm_limit
   float* tail_partial = nullptr;    // raw partial accumulators of split tail tiles (one 256 x 256 slot per SM pair)
   void* workspace = nullptr;
   size_t workspace_bytes = 0;

@@ -21,6 +21,7 @@ This is the reference's training loop of ``nn.Sequential`` + ``nn.CrossEntropyLo
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -79,6 +80,8 @@ class MLPTrainer:
         if self.fused_dense and f32_mode != 0:
             raise ValueError("fused_dense uses the default f32 mode")
         self.overlap_comm = (self.world_size > 1) if overlap_comm is None else bool(overlap_comm)
+        # SMs left to the collectives that overlap the backward products (MTB200_COMM_SMS, default 8 when world > 1)
+        self.comm_sms = int(os.environ.get("MTB200_COMM_SMS", "8")) if self.world_size > 1 else 0
         self.be: Backend = get_backend(device)
         dev = self.be.device
         self.w_off, self.b_off, total = mlp_layout(self.dims)
@@ -256,6 +259,9 @@ class MLPTrainer:
                               dx_epilogue=EPI_RELU_BWD, dx_aux=self.h[l - 1], need_dw=False,
                               need_db=self._dy_blocks[l] is not None, db=self.db[l],
                               dy_block=self._dy_blocks[l], dy_mode=1)
+        if self.comm_sms > 0:   # from here on all-reduces run beside the products: leave them SMs of their own
+            sm_total = torch.cuda.get_device_properties(be.device).multi_processor_count
+            be.set_gemm_sm_limit(sm_total - self.comm_sms)
         main = torch.cuda.current_stream(be.device)
         if self._side_stream is None:
             self._side_stream = torch.cuda.Stream(device=be.device)
@@ -279,6 +285,8 @@ class MLPTrainer:
                              beta1=self.beta1, beta2=self.beta2, eps=self.eps, step=self.step_count,
                              grad_scale=1.0 / self.world_size)
         main.wait_stream(side)
+        if self.comm_sms > 0:
+            be.set_gemm_sm_limit(0)   # the forward pass has nothing running beside it
 
     def flops_per_sample(self) -> int:
         return mlp_flops_per_sample(self.dims)

@@ -485,3 +485,20 @@ def test_tail_split_batched(be, orc, rng):
     for i in (0, 3, 4):
         wide = orc.matmul_acc_wide(np.ascontiguousarray(a[i][rows]), b[i])
         assert norm_scaled_error(c[i][rows], wide, a[i][rows], b[i]) <= 4e-6
+
+
+def test_gemm_sm_limit_changes_nothing_but_the_grid(be, rng):
+    """Fewer SMs for the persistent kernel (room for a collective beside it).  This shape has too few K blocks for
+    any tile to be cut into K ranges, so the result does not depend on the grid at all: same bits for every limit."""
+    a = dev(be, rng.standard_normal((1500, 700)).astype(np.float32))
+    b = dev(be, rng.standard_normal((700, 2100)).astype(np.float32))
+    ref = be.gemm(a, b)
+    try:
+        for sms in (140, 64, 3, 2):
+            be.set_gemm_sm_limit(sms)
+            assert torch.equal(be.gemm(a, b), ref)
+    finally:
+        be.set_gemm_sm_limit(0)
+    be.sync()
+    with pytest.raises(ValueError):
+        be.set_gemm_sm_limit(-1)
