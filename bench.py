@@ -138,6 +138,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # the launcher of multi-rank runs pins OMP_NUM_THREADS to 1; this arm is the CPU path on ALL host cores,
+    # and the OpenMP runtime reads the variable when the oracle library is first loaded
+    if "LOCAL_RANK" in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)) or 1)
     rows = 2048
     value, per_step, cores = cpu_mlp_samples_per_s(rows, max(1, args.steps), max(0, min(args.warmup, 1)))
     line = {
