@@ -34,6 +34,7 @@ struct I32LimbArgs {
   int a_batched, b_batched;
   const uint32_t* wide_word;  // device word: == wide_epoch when some element does not fit in int8
   uint32_t wide_epoch;
+  int skip_narrow;        // 1: return at once when the operands fit in int8 (another kernel takes that case)
   uint32_t* status;
 };
 
@@ -87,6 +88,44 @@ limb_split_kernel(const int32_t* __restrict__ src, long long ld, long long bstri
   }
 }
 
+// The untransposed case without shared memory: a thread takes 16 consecutive k of one row (four 16-byte loads)
+// and writes 16 bytes to each of the four limb planes, so a warp reads 2 KB and writes 4 x 512 B contiguously.
+// Needs K % 4 == 0 and 16-byte aligned rows (ld % 4 == 0).
+static __global__ void __launch_bounds__(256)
+limb_split_rows_kernel(const int32_t* __restrict__ src, long long ld, long long bstride, uint8_t* __restrict__ dst,
+                       int R, int K, int Kp, uint32_t* __restrict__ wide_word, uint32_t wide_epoch) {
+  const int b = blockIdx.z;
+  const int chunks = Kp >> 4;
+  const long long total = static_cast<long long>(R) * chunks;
+  const long long plane = static_cast<long long>(R) * Kp;
+  const int32_t* s = src + b * bstride;
+  bool wide = false;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / chunks);
+    const int k0 = static_cast<int>(i - static_cast<long long>(r) * chunks) << 4;
+    uint32_t v[16];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      int4 t = make_int4(0, 0, 0, 0);
+      if (k0 + q * 4 < K) t = *reinterpret_cast<const int4*>(s + static_cast<long long>(r) * ld + k0 + q * 4);
+      v[q * 4 + 0] = uint32_t(t.x); v[q * 4 + 1] = uint32_t(t.y); v[q * 4 + 2] = uint32_t(t.z); v[q * 4 + 3] = uint32_t(t.w);
+      wide |= (t.x < -128 || t.x > 127) | (t.y < -128 || t.y > 127) | (t.z < -128 || t.z > 127) | (t.w < -128 || t.w > 127);
+    }
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      uint32_t w[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        w[q] = ((v[q * 4 + 0] >> (8 * l)) & 0xffu) | (((v[q * 4 + 1] >> (8 * l)) & 0xffu) << 8) |
+               (((v[q * 4 + 2] >> (8 * l)) & 0xffu) << 16) | (((v[q * 4 + 3] >> (8 * l)) & 0xffu) << 24);
+      uint8_t* d = dst + (static_cast<long long>(b) * 4 + l) * plane + static_cast<long long>(r) * Kp + k0;
+      *reinterpret_cast<uint4*>(d) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (wide) atomicMax(wide_word, wide_epoch);
+}
+
 __global__ void __launch_bounds__(192, 1)
 gemm_i32_limb_umma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                           const I32LimbArgs g) {
@@ -108,6 +147,7 @@ gemm_i32_limb_umma_kernel(const __grid_constant__ CUtensorMap tmapA, const __gri
   const int tiles_m = (g.M + Cfg::BM - 1) / Cfg::BM, tiles_n = (g.N + Cfg::BN - 1) / Cfg::BN;
   const int num_tiles = tiles_m * tiles_n * g.batch;
   const bool narrow = (*g.wide_word != g.wide_epoch);  // every element of both operands fits in int8
+  if (narrow && g.skip_narrow) return;
   const int nlimb = narrow ? 1 : 4;
   const uint32_t stage_tx = 2u * nlimb * Cfg::TILE;
 

@@ -99,7 +99,7 @@ inline int32_t make_split_tmap_mn(CUtensorMap* out, const void* base, uint64_t k
 template <typename Kern>
 inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int threads, long long tiles,
                                   const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, double work,
-                                  bool allow_tail = false) {
+                                  bool allow_tail = false, int prof_class = PROF_GEMM_UMMA) {
   MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -141,7 +141,7 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
     }
   }
   cfg.gridDim = dim3(2 * pairs);
-  ProfScope prof(h, PROF_GEMM_UMMA, work);
+  ProfScope prof(h, prof_class, work);
   MTB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, g));
   if (g.tail_splits > 1) {
     const int tiles_m = (g.M + 255) / 256, tiles_n = (g.N + 255) / 256;

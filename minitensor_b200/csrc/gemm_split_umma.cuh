@@ -58,6 +58,11 @@ struct GemmArgs {
   // the SM pairs, each of those tail tiles is cut into tail_splits K ranges that run side by side on different
   // pairs; the raw partial accumulators go to `partial` ([tail tile][split][256][256] f32) and a second kernel
   // adds them in a fixed order and applies the epilogue.  tail_splits <= 1: off.
+  // Optional gate (the int8 use of the pair-tile kernel): the kernel returns at once unless
+  // (*gate == gate_value) == (gate_run_if_equal != 0).  gate == nullptr: always run.
+  const uint32_t* gate;
+  uint32_t gate_value;
+  int gate_run_if_equal;
   int tail_splits;
   int tail_rounds;     // full rounds before the tail: tiles [0, tail_rounds * pairs) are whole
   int tail_tiles;      // tiles in the tail round

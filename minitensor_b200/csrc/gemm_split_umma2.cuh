@@ -167,13 +167,18 @@ struct Gemm2Cfg {
 // memory, mn padded to a multiple of 64) and its tensor map is the 4-D view
 // {64, k, mn / 64, plane}; otherwise K-major planes [mn][k] with the 3-D map.
 // MN-major needs BK = 64 (128-byte swizzle rows of 64 elements).
-// NP = planes per operand held in a stage: 3 (bf16 modes) or 2 (fp16 mode).
-template <int BK, int STAGES, bool A_MN = false, bool B_MN = false, int NP = 3>
+// NP = planes per operand held in a stage: 3 (bf16 modes), 2 (fp16 mode) or 1.
+// I8: the planes hold signed bytes (a K block of 64 16-bit units is 128 bytes = 128 k), the product is one
+// tcgen05.mma.kind::i8 per 32 k with an s32 accumulator, and the epilogue moves the 32-bit results out unchanged
+// (no scaling, bias or activation: the float path of the epilogue only copies bits then).
+template <int BK, int STAGES, bool A_MN = false, bool B_MN = false, int NP = 3, bool I8 = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                         const GemmArgs g) {
   using Cfg = Gemm2Cfg<BK, STAGES, NP>;
   static_assert(!(A_MN || B_MN) || BK == 64, "MN-major operands need BK = 64");
+  static_assert(!I8 || (!A_MN && !B_MN && BK == 64), "the int8 product takes K-major byte planes");
+  if (g.gate && ((*g.gate == g.gate_value) != (g.gate_run_if_equal != 0))) return;  // every thread of both CTAs
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -264,8 +269,9 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = make_idesc(Cfg::TILE_M, Cfg::TILE_N, g.mode == 23 ? 0u /*f16*/ : 1u /*bf16*/, 1u,
-                                        A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      const uint32_t idesc = I8 ? make_idesc(Cfg::TILE_M, Cfg::TILE_N, 1u /*signed bytes*/, 2u /*s32*/)
+                                : make_idesc(Cfg::TILE_M, Cfg::TILE_N, g.mode == 23 ? 0u /*f16*/ : 1u /*bf16*/, 1u,
+                                             A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       // The whole issue loop, with the product schedule known at compile time: per product the
       // thread adds a constant to each operand's descriptor and issues the MMA.
       auto issue_all = [&](auto npairs_tag) {
@@ -304,7 +310,8 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
                 const int code = split_pair_at(NPAIRS, p);
                 const uint32_t offa = (code >> 2) * Cfg::A_TILE + kk * A_KSTEP;
                 const uint32_t offb = (code & 3) * Cfg::B_TILE + kk * B_KSTEP;
-                umma_f16<2>(d_tmem, da0 + (offa >> 4), db0 + (offb >> 4), idesc, accumulate);
+                if constexpr (I8) umma_i8<2>(d_tmem, da0 + (offa >> 4), db0 + (offb >> 4), idesc, accumulate);
+                else umma_f16<2>(d_tmem, da0 + (offa >> 4), db0 + (offb >> 4), idesc, accumulate);
                 accumulate = 1;
               }
             }

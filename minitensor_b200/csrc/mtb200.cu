@@ -115,10 +115,19 @@ static int32_t gemm_i32_limb(mtb200_ctx* h, bool trans_a, bool trans_b, int batc
   {
     ProfScope prof(h, PROF_SPLIT, 8.0 * (double(batch_a) * M + double(batch_b) * N) * K);
     // op(A) is [M][K]: source [M][K] or, transposed, [K][M];  op(B)^T is [N][K]: source [K][N] needs the turn
-    limb_split_kernel<<<dim3((M + 63) / 64, Kp / 64, batch_a), 256, 0, h->stream>>>(
-        A, trans_a ? M : K, stride_a, trans_a ? 1 : 0, pa, M, K, Kp, wide_word, epoch);
-    limb_split_kernel<<<dim3((N + 63) / 64, Kp / 64, batch_b), 256, 0, h->stream>>>(
-        B, trans_b ? K : N, stride_b, trans_b ? 0 : 1, pb, N, K, Kp, wide_word, epoch);
+    auto split = [&](const int32_t* src, bool turn, int rows, int nb, long long bstride, uint8_t* dst) {
+      const bool direct = !turn && (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((bstride & 3) == 0);
+      if (direct) {
+        const long long total = static_cast<long long>(rows) * (Kp / 16);
+        const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
+        limb_split_rows_kernel<<<dim3(blocks, 1, nb), 256, 0, h->stream>>>(src, K, bstride, dst, rows, K, Kp, wide_word, epoch);
+      } else {
+        limb_split_kernel<<<dim3((rows + 63) / 64, Kp / 64, nb), 256, 0, h->stream>>>(
+            src, turn ? rows : K, bstride, turn ? 1 : 0, dst, rows, K, Kp, wide_word, epoch);
+      }
+    };
+    split(A, trans_a, M, batch_a, stride_a, pa);
+    split(B, !trans_b, N, batch_b, stride_b, pb);
     MTB_CUDA(cudaGetLastError());
   }
   EncodeTiledFn enc = get_encode_tiled();
@@ -146,6 +155,30 @@ static int32_t gemm_i32_limb(mtb200_ctx* h, bool trans_a, bool trans_b, int batc
   const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128) * batch;
   const int grid = int(std::min<long long>(tiles, h->sm_count));
   const int total_kb = Kp / 64, chunk_kb = 8192 / 64;
+  // Operands that fit in int8 (known only on the device) and a reduction of one chunk: the pair-tile kernel with
+  // kind::i8 takes the product - 256 x 256 tiles, six stages, overlapped epilogue - and the limb kernel below
+  // returns at once; operands that need all four limbs make the pair-tile kernel return at once instead.
+  if (M > 128 && N > 128 && total_kb <= chunk_kb) {
+    using PC = Gemm2Cfg<64, 6, 1>;
+    CUtensorMap pa_map, pb_map;
+    rc = make_split_tmap(&pa_map, pa, uint64_t(Kp) / 2, uint64_t(M), uint64_t(4) * batch_a, 64, PC::BM);
+    if (rc) return rc;
+    rc = make_split_tmap(&pb_map, pb, uint64_t(Kp) / 2, uint64_t(N), uint64_t(4) * batch_b, 64, PC::BNH);
+    if (rc) return rc;
+    GemmArgs p = {};
+    p.M = M; p.N = N; p.batch = batch;
+    p.num_kb = (Kp + 127) / 128;
+    p.C = reinterpret_cast<float*>(C); p.ldc = N; p.strideC = stride_c;
+    p.epilogue = EPI_NONE; p.mode = 1; p.planes_per_mat = 4;
+    p.a_batched = batch_a > 1; p.b_batched = batch_b > 1;
+    p.status = h->status;
+    p.gate = wide_word; p.gate_value = epoch; p.gate_run_if_equal = 0;
+    const long long ptiles = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * batch;
+    rc = launch_pair_kernel(h, gemm_split_umma2_kernel<64, 6, false, false, 1, true>, PC::SMEM_BYTES, PC::NUM_THREADS,
+                            ptiles, pa_map, pb_map, p, 2.0 * M * N * double(Kp) * batch, false, PROF_GEMM_INT);
+    if (rc) return rc;
+    g.skip_narrow = 1;
+  }
   for (int kb0 = 0; kb0 < total_kb; kb0 += chunk_kb) {
     g.kb0 = kb0;
     g.num_kb = std::min(chunk_kb, total_kb - kb0);
