@@ -63,6 +63,7 @@ struct GemmArgs {
   const uint32_t* gate;
   uint32_t gate_value;
   int gate_run_if_equal;
+  int raw_int;         // 1: the accumulators are s32 (int8 product): partial tiles are added as integers
   int tail_splits;
   int tail_rounds;     // full rounds before the tail: tiles [0, tail_rounds * pairs) are whole
   int tail_tiles;      // tiles in the tail round

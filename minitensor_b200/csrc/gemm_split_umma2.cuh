@@ -120,8 +120,24 @@ __device__ __forceinline__ void tail_fixup_body(const GemmArgs& g, int num_pairs
     const float4 t = *reinterpret_cast<const float4*>(part + static_cast<long long>(p) * 65536);
     acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
   }
-  float x[4] = {acc.x, acc.y, acc.z, acc.w};
   float* cptr = g.C + b * g.strideC + static_cast<long long>(grow) * g.ldc + gcol;
+  if (g.raw_int) {
+    // s32 accumulators of an int8 product: the partials were added as floats above, redo the sum on the bit patterns
+    uint32_t sum[4];
+    const float4 first = *reinterpret_cast<const float4*>(part);
+    sum[0] = __float_as_uint(first.x); sum[1] = __float_as_uint(first.y);
+    sum[2] = __float_as_uint(first.z); sum[3] = __float_as_uint(first.w);
+    for (int p = 1; p < g.tail_splits; ++p) {
+      const float4 t = *reinterpret_cast<const float4*>(part + static_cast<long long>(p) * 65536);
+      sum[0] += __float_as_uint(t.x); sum[1] += __float_as_uint(t.y);
+      sum[2] += __float_as_uint(t.z); sum[3] += __float_as_uint(t.w);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (gcol + e < g.N) cptr[e] = __uint_as_float(sum[e]);
+    return;
+  }
+  float x[4] = {acc.x, acc.y, acc.z, acc.w};
   const float* aptr = (EPI == EPI_RELU_BWD) ? g.aux + b * g.strideC + static_cast<long long>(grow) * g.ldc + gcol : nullptr;
   const int ea = g.exp_b ? g.exp_a[(g.a_batched ? static_cast<long long>(b) * g.M : 0) + grow] : 0;
   const int* eb = g.exp_b ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) + gcol : nullptr;
@@ -136,6 +152,7 @@ __device__ __forceinline__ void tail_fixup_body(const GemmArgs& g, int num_pairs
 }
 static __global__ void __launch_bounds__(256)
 tail_fixup_kernel(const GemmArgs g, int num_pairs, int tiles_m, int tiles_n) {
+  if (g.gate && ((*g.gate == g.gate_value) != (g.gate_run_if_equal != 0))) return;  // the product itself did not run
   switch (g.epilogue) {
     case EPI_RELU: tail_fixup_body<EPI_RELU>(g, num_pairs, tiles_m, tiles_n); break;
     case EPI_GELU_ERF: tail_fixup_body<EPI_GELU_ERF>(g, num_pairs, tiles_m, tiles_n); break;

@@ -173,9 +173,10 @@ static int32_t gemm_i32_limb(mtb200_ctx* h, bool trans_a, bool trans_b, int batc
     p.a_batched = batch_a > 1; p.b_batched = batch_b > 1;
     p.status = h->status;
     p.gate = wide_word; p.gate_value = epoch; p.gate_run_if_equal = 0;
+    p.raw_int = 1;
     const long long ptiles = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * batch;
     rc = launch_pair_kernel(h, gemm_split_umma2_kernel<64, 6, false, false, 1, true>, PC::SMEM_BYTES, PC::NUM_THREADS,
-                            ptiles, pa_map, pb_map, p, 2.0 * M * N * double(Kp) * batch, false, PROF_GEMM_INT);
+                            ptiles, pa_map, pb_map, p, 2.0 * M * N * double(Kp) * batch, true, PROF_GEMM_INT);
     if (rc) return rc;
     g.skip_narrow = 1;
   }
