@@ -112,24 +112,10 @@ __device__ __forceinline__ float apply_epilogue(float x, int epi, float aux) {
   }
 }
 
-// Split-pair schedule: small-weight products first so they are accumulated
-// before the dominant a0*b0 term.  Encoded as (i << 2 | j), i = A split, j = B split.
-__device__ __forceinline__ int split_pairs(int mode, uint8_t (&pairs)[9]) {
-  if (mode == 1) { pairs[0] = 0; return 1; }
-  if (mode == 23) { pairs[0] = (0 << 2) | 1; pairs[1] = (1 << 2) | 0; pairs[2] = 0; return 3; }
-  if (mode == 3) { pairs[0] = (0 << 2) | 1; pairs[1] = (1 << 2) | 0; pairs[2] = 0; return 3; }
-  if (mode == 9) {
-    pairs[0] = (2 << 2) | 2; pairs[1] = (1 << 2) | 2; pairs[2] = (2 << 2) | 1;
-    pairs[3] = (0 << 2) | 2; pairs[4] = (2 << 2) | 0; pairs[5] = (1 << 2) | 1;
-    pairs[6] = (0 << 2) | 1; pairs[7] = (1 << 2) | 0; pairs[8] = 0; return 9;
-  }
-  pairs[0] = (0 << 2) | 2; pairs[1] = (2 << 2) | 0; pairs[2] = (1 << 2) | 1;
-  pairs[3] = (0 << 2) | 1; pairs[4] = (1 << 2) | 0; pairs[5] = 0; return 6;
-}
-
-// The same schedule as a compile-time function of (number of products, position), for issue loops
-// that are unrolled completely: the issuing thread then spends one add per descriptor instead of
-// a table lookup and a descriptor build per product.  3 products serve both two-plane modes.
+// Split-pair schedule: small-weight products first so they are accumulated before the dominant a0*b0 term.
+// Encoded as (i << 2 | j), i = A split, j = B split, as a compile-time function of (number of products,
+// position), for issue loops that are unrolled completely: the issuing thread then spends one add per
+// descriptor instead of a table lookup and a descriptor build per product.  3 products serve both two-plane modes.
 __host__ __device__ constexpr int split_pair_at(int npairs, int p) {
   if (npairs == 1) return 0;
   if (npairs == 3) return p == 0 ? ((0 << 2) | 1) : (p == 1 ? ((1 << 2) | 0) : 0);
