@@ -94,24 +94,6 @@ __device__ __forceinline__ float apply_epilogue_t(float x, float aux) {
   else return x;
 }
 
-__device__ __forceinline__ float apply_epilogue(float x, int epi, float aux) {
-  switch (epi) {
-    case EPI_RELU:
-      return (x != x) ? x : (x > 0.0f ? x : 0.0f);
-    case EPI_GELU_ERF:
-      return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
-    case EPI_GELU_TANH: {
-      const float c = 0.7978845608028654f;  // sqrt(2/pi)
-      float x3 = x * x * x;
-      return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x3)));
-    }
-    case EPI_RELU_BWD:
-      return x * (aux > 0.0f ? 1.0f : 0.0f);
-    default:
-      return x;
-  }
-}
-
 // Split-pair schedule: small-weight products first so they are accumulated before the dominant a0*b0 term.
 // Encoded as (i << 2 | j), i = A split, j = B split, as a compile-time function of (number of products,
 // position), for issue loops that are unrolled completely: the issuing thread then spends one add per
