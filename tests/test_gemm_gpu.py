@@ -502,3 +502,26 @@ def test_gemm_sm_limit_changes_nothing_but_the_grid(be, rng):
     be.sync()
     with pytest.raises(ValueError):
         be.set_gemm_sm_limit(-1)
+
+
+def test_plain_gemm_replays_from_a_cuda_graph(be, rng):
+    """A mid-size f32 product (operands prepared on two streams, tail tiles cut, fix-up kernel) recorded into a
+    CUDA graph after one eager call and replayed on new operand contents: same bits as the eager call."""
+    a = dev(be, rng.standard_normal((768, 1024)).astype(np.float32))
+    b = dev(be, rng.standard_normal((1024, 640)).astype(np.float32))
+    out = torch.empty(768, 640, device=be.device)
+    be.gemm(a, b, out=out)                       # sizes the scratch memory: nothing may allocate while capturing
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        be.gemm(a, b, out=out)
+    a2 = dev(be, rng.standard_normal((768, 1024)).astype(np.float32))
+    b2 = dev(be, rng.standard_normal((1024, 640)).astype(np.float32))
+    ref = be.gemm(a2, b2)
+    a.copy_(a2)
+    b.copy_(b2)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    be.sync()
+    assert torch.equal(out, ref)
