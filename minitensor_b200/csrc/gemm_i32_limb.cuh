@@ -88,6 +88,55 @@ limb_split_kernel(const int32_t* __restrict__ src, long long ld, long long bstri
   }
 }
 
+// The turned case (source [K][R], ld = R) with the bytes packed before they cross shared memory: a block takes
+// 128 k x 32 r; a thread loads 16 consecutive k of one r (every load of a warp is 128 contiguous bytes along r),
+// packs each group of four k into one word per limb and stores those words at tile[l][r][k / 4] (row pitch 33
+// words: lanes of one warp differ in r, so the stores hit 32 banks).  The second phase reads four consecutive
+// words (16 bytes of one limb plane row) per thread - lanes (r = lane / 8, chunk = lane % 8) again cover all
+// banks - and a warp's store is four rows of 128 contiguous bytes.
+static __global__ void __launch_bounds__(256)
+limb_split_turn_kernel(const int32_t* __restrict__ src, long long ld, long long bstride, uint8_t* __restrict__ dst,
+                       int R, int K, int Kp, uint32_t* __restrict__ wide_word, uint32_t wide_epoch) {
+  __shared__ uint32_t tile[4][32][33];
+  const int b = blockIdx.z;
+  const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 128;
+  const int32_t* s = src + b * bstride;
+  const int lane = threadIdx.x & 31, kg = threadIdx.x >> 5;     // kg: which 16 of the 128 k
+  const int r = r0 + lane;
+  int32_t v[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const int k = k0 + kg * 16 + e;
+    v[e] = (r < R && k < K) ? s[static_cast<long long>(k) * ld + r] : 0;
+  }
+  bool wide = false;
+#pragma unroll
+  for (int e = 0; e < 16; ++e) wide |= (v[e] < -128 || v[e] > 127);
+  if (wide) atomicMax(wide_word, wide_epoch);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t a0 = uint32_t(v[q * 4]), a1 = uint32_t(v[q * 4 + 1]), a2 = uint32_t(v[q * 4 + 2]), a3 = uint32_t(v[q * 4 + 3]);
+    // limb l of four elements in one word: byte permutes of the pairs (a0,a1) and (a2,a3), then of the halves
+    const uint32_t lo01 = __byte_perm(a0, a1, 0x5140), hi01 = __byte_perm(a0, a1, 0x7362);   // [a0.b0 a1.b0 a0.b1 a1.b1], [a0.b2 a1.b2 a0.b3 a1.b3]
+    const uint32_t lo23 = __byte_perm(a2, a3, 0x5140), hi23 = __byte_perm(a2, a3, 0x7362);
+    tile[0][lane][kg * 4 + q] = __byte_perm(lo01, lo23, 0x5410);
+    tile[1][lane][kg * 4 + q] = __byte_perm(lo01, lo23, 0x7632);
+    tile[2][lane][kg * 4 + q] = __byte_perm(hi01, hi23, 0x5410);
+    tile[3][lane][kg * 4 + q] = __byte_perm(hi01, hi23, 0x7632);
+  }
+  __syncthreads();
+  const long long plane = static_cast<long long>(R) * Kp;
+  const int rr = (threadIdx.x >> 3) & 31, c = threadIdx.x & 7;
+  if (r0 + rr < R && k0 + c * 16 < Kp) {
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t* t = &tile[l][rr][c * 4];
+      uint8_t* d = dst + (static_cast<long long>(b) * 4 + l) * plane + static_cast<long long>(r0 + rr) * Kp + k0 + c * 16;
+      *reinterpret_cast<uint4*>(d) = make_uint4(t[0], t[1], t[2], t[3]);
+    }
+  }
+}
+
 // The untransposed case without shared memory: a thread takes 16 consecutive k of one row (four 16-byte loads)
 // and writes 16 bytes to each of the four limb planes, so a warp reads 2 KB and writes 4 x 512 B contiguously.
 // Needs K % 4 == 0 and 16-byte aligned rows (ld % 4 == 0).

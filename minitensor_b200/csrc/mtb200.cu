@@ -121,9 +121,12 @@ static int32_t gemm_i32_limb(mtb200_ctx* h, bool trans_a, bool trans_b, int batc
         const long long total = static_cast<long long>(rows) * (Kp / 16);
         const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
         limb_split_rows_kernel<<<dim3(blocks, 1, nb), 256, 0, h->stream>>>(src, K, bstride, dst, rows, K, Kp, wide_word, epoch);
+      } else if (turn) {
+        limb_split_turn_kernel<<<dim3((rows + 31) / 32, (Kp + 127) / 128, nb), 256, 0, h->stream>>>(
+            src, rows, bstride, dst, rows, K, Kp, wide_word, epoch);
       } else {
         limb_split_kernel<<<dim3((rows + 63) / 64, Kp / 64, nb), 256, 0, h->stream>>>(
-            src, turn ? rows : K, bstride, turn ? 1 : 0, dst, rows, K, Kp, wide_word, epoch);
+            src, K, bstride, 0, dst, rows, K, Kp, wide_word, epoch);
       }
     };
     split(A, trans_a, M, batch_a, stride_a, pa);
