@@ -341,7 +341,11 @@ int32_t mtb200_adam_step_counted(mtb200_handle h, int64_t n, float* param, const
 /* ---- conv2d, NCHW input, OIHW weight, f32 (the reference supports nothing
  * else: engine/src/operations/conv.rs:85-93,202-204).
  * forward  = conv2d                     engine/src/operations/conv.rs:24-206
- * bwd_data / bwd_weight / bwd_bias = Conv2dBackward  engine/src/autograd/mod/shape.rs:57-197 */
+ * bwd_data / bwd_weight / bwd_bias = Conv2dBackward  engine/src/autograd/mod/shape.rs:57-197
+ * f32_mode: MTB200_F32_DEFAULT = F16X3 for the stride-1 forward and data gradient (one power-of-two
+ * scale per image and per weight row; Inf/NaN inputs give non-finite outputs in the windows they
+ * touch) and BF16X6 for the weight gradient and for strided convolutions; the BF16 modes may be
+ * asked for by value. */
 int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
                           int64_t c_out, int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w,
                           int64_t pad_h, int64_t pad_w, const float* x, const float* w,

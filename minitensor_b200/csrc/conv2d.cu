@@ -1,4 +1,5 @@
-// conv2d (NCHW / OIHW, f32) lowered to the split-bf16 tensor-core GEMM.
+// conv2d (NCHW / OIHW, f32) lowered to the split-plane tensor-core GEMM (fp16 two-plane mode for the implicit
+// forward and data gradient, bf16 planes elsewhere).
 //
 // The reference computes the convolution with direct loops
 // (engine/src/operations/conv.rs:111-157) and its backward with three more
@@ -28,6 +29,13 @@ namespace mtb {
 struct ConvGeom {
   int n, c_in, h, w, c_out, kh, kw, sh, sw, ph, pw, oh, ow;
 };
+
+// Mode byte for the gathered-patch lowerings, whose planes are bf16: the fp16 two-plane mode exists only for the
+// implicit (stride-1) kernels, so 23 asks for the default there.
+static int bf16_mode_of(int32_t f32_mode) {
+  const int m = f32_mode & 0xff;
+  return m == 23 ? 0 : m;
+}
 
 // Gather modes for the patch operand.
 //  PATCH_FWD : row = output pixel (oh,ow), k = (ic,kh,kw), value x[n][ic][oh*s+kh-p][ow*s+kw-p]
@@ -206,26 +214,50 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
   const int chan_p = padded_k(chan), taps = kh * kw;
   const int Kp = taps * chan_p;
   const int ipix = img_h * img_w, opix = out_h * out_w;
-  const size_t bytes_img = split_bytes(ipix, chan_p, n);
+  // Default: the fp16 two-plane mode (three products).  The reduction of one output runs over taps and channels
+  // of ONE image, so the image operand takes one power-of-two scale per image and the weights one per row; the
+  // bf16 modes (three planes, up to nine products, no scaling) stay selectable through the mode byte.
+  const int gemm_mode = (f32_mode & 0xff) ? (f32_mode & 0xff) : 23;
+  if (gemm_mode != 1 && gemm_mode != 3 && gemm_mode != 6 && gemm_mode != 9 && gemm_mode != 23)
+    return fail(MTB200_ERR_INVALID, "unknown f32 mode");
+  const bool f16 = gemm_mode == 23;
+  const int planes = f16 ? 2 : 3;
+  const size_t bytes_img = split_bytes(ipix, chan_p, n);      // sized for three planes; the fp16 mode uses two
   const size_t bytes_w = split_bytes(rows, Kp, 1);
   const size_t bytes_tmp = align_up(sizeof(float) * size_t(rows) * Kp, 1024);
+  const size_t bytes_ea = align_up(sizeof(int) * size_t(rows), 1024), bytes_eb = align_up(sizeof(int) * size_t(n), 1024);
   void* ws = nullptr;
-  int32_t rc = workspace_reserve(h, bytes_img + bytes_w + bytes_tmp, &ws);
+  int32_t rc = workspace_reserve(h, bytes_img + bytes_w + bytes_tmp + bytes_ea + 2 * bytes_eb, &ws);
   if (rc) return rc;
+  char* wbase = static_cast<char*>(ws);
   __nv_bfloat16* p_img = static_cast<__nv_bfloat16*>(ws);
-  __nv_bfloat16* p_w = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_img);
-  float* wtmp = reinterpret_cast<float*>(static_cast<char*>(ws) + bytes_img + bytes_w);
+  __nv_bfloat16* p_w = reinterpret_cast<__nv_bfloat16*>(wbase + bytes_img);
+  float* wtmp = reinterpret_cast<float*>(wbase + bytes_img + bytes_w);
+  int* ea = reinterpret_cast<int*>(wbase + bytes_img + bytes_w + bytes_tmp);
+  int* eb = reinterpret_cast<int*>(wbase + bytes_img + bytes_w + bytes_tmp + bytes_ea);
+  uint32_t* amax = reinterpret_cast<uint32_t*>(wbase + bytes_img + bytes_w + bytes_tmp + bytes_ea + bytes_eb);
+  const long long img_elems = static_cast<long long>(chan) * ipix;
   // channels-last planes: per image a [chan][pixels] -> [pixels][chan_p] turning split
-  {
+  if (f16) {
+    ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (8.0 * chan + 4.0 * chan_p));
+    MTB_CUDA(cudaMemsetAsync(amax, 0, sizeof(uint32_t) * size_t(n), h->stream));
+    const int chunks = int(std::max<long long>(1, std::min<long long>((img_elems + 4095) / 4096,
+                                                                      (4LL * h->sm_count + n - 1) / n)));
+    finite_absmax_kernel<<<dim3(chunks, n), 256, 0, h->stream>>>(img, img_elems, img_elems, amax);
+    split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, chan_p / 64, n), 256, 0, h->stream>>>(
+        img, ipix, img_elems, reinterpret_cast<__half*>(p_img), amax, 1, eb, ipix, chan, chan_p);
+    MTB_CUDA(cudaGetLastError());
+  } else {
     ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (4.0 * chan + 6.0 * chan_p));
-    rc = launch_split(h, img, true, ipix, chan, chan_p, n, static_cast<long long>(chan) * ipix, p_img, 3);
+    rc = launch_split(h, img, true, ipix, chan, chan_p, n, img_elems, p_img, 3);
     if (rc) return rc;
   }
   const long long wtotal = static_cast<long long>(rows) * Kp;
   weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
       wsrc, wtmp, rows, chan, chan_p, taps, mode);
   MTB_CUDA(cudaGetLastError());
-  rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3);
+  if (f16) rc = launch_split16(h, wtmp, true, rows, Kp, 1, 0, reinterpret_cast<__half*>(p_w), ea, nullptr, 0);
+  else rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3);
   if (rc) return rc;
 
   int th = std::max(1, 256 / out_w);
@@ -235,20 +267,20 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
   g.num_kb = Kp / BK;
   g.C = out; g.ldc = opix; g.strideC = static_cast<long long>(rows) * opix;
   g.bias = bias; g.aux = nullptr; g.epilogue = EPI_NONE;
-  g.mode = (f32_mode & 0xff) ? (f32_mode & 0xff) : 6;
-  if (g.mode != 1 && g.mode != 3 && g.mode != 6 && g.mode != 9) return fail(MTB200_ERR_INVALID, "unknown f32 mode");
+  g.mode = gemm_mode;
   g.a_batched = 0; g.b_batched = 1; g.bias_per_row = 1; g.kb_batch_stride = 0;
-  g.planes_per_mat = 3; g.exp_a = nullptr; g.exp_b = nullptr;
+  g.planes_per_mat = planes;
+  g.exp_a = f16 ? ea : nullptr; g.exp_b = f16 ? eb : nullptr; g.exp_b_per_batch = f16 ? 1 : 0;
   g.status = h->status;
   g.cv_th = th; g.cv_n_tile = th * out_w; g.cv_umma_n = (g.cv_n_tile + 15) / 16 * 16;
   g.cv_kb_per_tap = chan_p / BK; g.cv_kw = kw; g.cv_w0 = w0; g.cv_h0 = h0; g.cv_sgn = sgn;
 
   CUtensorMap ta, tb;
-  rc = make_split_tmap(&ta, p_w, Kp, rows, 3, BK, Cfg::BM);
+  rc = make_split_tmap(&ta, p_w, Kp, rows, planes, BK, Cfg::BM);
   if (rc) return rc;
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[4] = {cuuint64_t(chan_p), cuuint64_t(img_w), cuuint64_t(img_h), cuuint64_t(3) * n};
+  const cuuint64_t dims[4] = {cuuint64_t(chan_p), cuuint64_t(img_w), cuuint64_t(img_h), cuuint64_t(planes) * n};
   const cuuint64_t strides[3] = {cuuint64_t(chan_p) * 2, cuuint64_t(img_w) * chan_p * 2,
                                  cuuint64_t(ipix) * chan_p * 2};
   const cuuint32_t box[4] = {BK, cuuint32_t(out_w), cuuint32_t(th), 1};
@@ -268,10 +300,10 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
 }
 
 static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, int img_w, int img_h, int n,
-                                uint32_t box_c, uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle sw) {
+                                int planes, uint32_t box_c, uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle sw) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[4] = {cuuint64_t(chan_p), cuuint64_t(img_w), cuuint64_t(img_h), cuuint64_t(3) * n};
+  const cuuint64_t dims[4] = {cuuint64_t(chan_p), cuuint64_t(img_w), cuuint64_t(img_h), cuuint64_t(planes) * n};
   const cuuint64_t strides[3] = {cuuint64_t(chan_p) * 2, cuuint64_t(img_w) * chan_p * 2,
                                  cuuint64_t(img_h) * img_w * chan_p * 2};
   const cuuint32_t box[4] = {box_c, box_w, box_h, 1};
@@ -309,28 +341,52 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
   a.kb_per_split = int((total_kb + splits - 1) / splits);
   a.splits = int((total_kb + a.kb_per_split - 1) / a.kb_per_split);
   a.n_total = a.n_chunks * 64;
-  a.mode = (f32_mode & 0xff) ? (f32_mode & 0xff) : 6;
-  if (a.mode != 1 && a.mode != 3 && a.mode != 6 && a.mode != 9) return fail(MTB200_ERR_INVALID, "unknown f32 mode");
+  // Default: the fp16 two-plane mode with ONE power-of-two scale per tensor (the reduction runs over images and
+  // pixels, so only a scale that is constant over both factors out of the sum).
+  a.mode = (f32_mode & 0xff) ? (f32_mode & 0xff) : 23;
+  if (a.mode != 1 && a.mode != 3 && a.mode != 6 && a.mode != 9 && a.mode != 23)
+    return fail(MTB200_ERR_INVALID, "unknown f32 mode");
+  const bool f16 = a.mode == 23;
+  a.planes = f16 ? 2 : 3;
   a.status = h->status;
-  const size_t bytes_dy = split_bytes(opix, cop, g.n), bytes_x = split_bytes(ipix, cip, g.n);
+  const size_t bytes_dy = split_bytes(opix, cop, g.n), bytes_x = split_bytes(ipix, cip, g.n);   // room for three planes
   const size_t bytes_part = align_up(sizeof(float) * size_t(a.splits) * g.c_out * a.n_total, 1024);
+  const size_t bytes_e = align_up(sizeof(int) * size_t(g.n), 1024);
   void* ws = nullptr;
-  int32_t rc = workspace_reserve(h, bytes_dy + bytes_x + bytes_part, &ws);
+  int32_t rc = workspace_reserve(h, bytes_dy + bytes_x + bytes_part + 2 * bytes_e + 1024, &ws);
   if (rc) return rc;
+  char* wbase = static_cast<char*>(ws);
   __nv_bfloat16* p_dy = static_cast<__nv_bfloat16*>(ws);
-  __nv_bfloat16* p_x = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_dy);
-  a.part = reinterpret_cast<float*>(static_cast<char*>(ws) + bytes_dy + bytes_x);
-  {
+  __nv_bfloat16* p_x = reinterpret_cast<__nv_bfloat16*>(wbase + bytes_dy);
+  a.part = reinterpret_cast<float*>(wbase + bytes_dy + bytes_x);
+  int* e_dy = reinterpret_cast<int*>(wbase + bytes_dy + bytes_x + bytes_part);
+  int* e_x = reinterpret_cast<int*>(wbase + bytes_dy + bytes_x + bytes_part + bytes_e);
+  uint32_t* amax = reinterpret_cast<uint32_t*>(wbase + bytes_dy + bytes_x + bytes_part + 2 * bytes_e);   // [2]
+  const long long dy_img = static_cast<long long>(g.c_out) * opix, x_img = static_cast<long long>(g.c_in) * ipix;
+  if (f16) {
+    ProfScope prof(h, PROF_CONV_GATHER, double(g.n) * (opix * (8.0 * g.c_out + 4.0 * cop) + ipix * (8.0 * g.c_in + 4.0 * cip)));
+    MTB_CUDA(cudaMemsetAsync(amax, 0, 2 * sizeof(uint32_t), h->stream));
+    auto chunks_of = [&](long long total) {
+      return int(std::max<long long>(1, std::min<long long>((total + 4095) / 4096, 8LL * h->sm_count)));
+    };
+    finite_absmax_kernel<<<dim3(chunks_of(dy_img * g.n), 1), 256, 0, h->stream>>>(dy, 0, dy_img * g.n, amax);
+    finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, h->stream>>>(x, 0, x_img * g.n, amax + 1);
+    split16_turn_batch_kernel<<<dim3((opix + 63) / 64, cop / 64, g.n), 256, 0, h->stream>>>(
+        dy, opix, dy_img, reinterpret_cast<__half*>(p_dy), amax, 0, e_dy, opix, g.c_out, cop);
+    split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, cip / 64, g.n), 256, 0, h->stream>>>(
+        x, ipix, x_img, reinterpret_cast<__half*>(p_x), amax + 1, 0, e_x, ipix, g.c_in, cip);
+    MTB_CUDA(cudaGetLastError());
+  } else {
     ProfScope prof(h, PROF_CONV_GATHER, double(g.n) * (opix * (4.0 * g.c_out + 6.0 * cop) + ipix * (4.0 * g.c_in + 6.0 * cip)));
-    rc = launch_split(h, dy, true, opix, g.c_out, cop, g.n, static_cast<long long>(g.c_out) * opix, p_dy, 3);
+    rc = launch_split(h, dy, true, opix, g.c_out, cop, g.n, dy_img, p_dy, 3);
     if (rc) return rc;
-    rc = launch_split(h, x, true, ipix, g.c_in, cip, g.n, static_cast<long long>(g.c_in) * ipix, p_x, 3);
+    rc = launch_split(h, x, true, ipix, g.c_in, cip, g.n, x_img, p_x, 3);
     if (rc) return rc;
   }
   CUtensorMap tdy, tx;
-  rc = image_plane_tmap(&tdy, p_dy, cop, g.ow, g.oh, g.n, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = image_plane_tmap(&tdy, p_dy, cop, g.ow, g.oh, g.n, a.planes, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, a.planes, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   MTB_CUDA(cudaFuncSetAttribute(conv_wgrad_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
   {
@@ -340,7 +396,7 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
   }
   const long long total = static_cast<long long>(g.c_out) * g.c_in * taps;
   wgrad_reduce_kernel<<<int(std::min<long long>((total + 255) / 256, 4096)), 256, 0, h->stream>>>(
-      a.part, a.splits, g.c_out, g.c_in, cip, taps, dw);
+      a.part, a.splits, g.c_out, g.c_in, cip, taps, dw, f16 ? e_dy : nullptr, f16 ? e_x : nullptr);
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
 }
@@ -405,7 +461,7 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_out, 0, 1}, ob{sp, opix, g.n > 1, g.n};
   return run_split_gemm(h, oa, ob, Kp, g.n, g.c_out, opix, y, opix, static_cast<long long>(g.c_out) * opix,
-                        bias, EPI_NONE, nullptr, f32_mode & 0xff, force_explicit ? 0 : (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
+                        bias, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
 }
 
 int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
@@ -449,7 +505,7 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_in, 0, 1}, ob{sp, ipix, g.n > 1, g.n};
   return run_split_gemm(h, oa, ob, Kp, g.n, g.c_in, ipix, dx, ipix, static_cast<long long>(g.c_in) * ipix,
-                        nullptr, EPI_NONE, nullptr, f32_mode & 0xff, force_explicit ? 0 : (f32_mode >> 8) & 0xff);
+                        nullptr, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff);
 }
 
 int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
@@ -495,7 +551,7 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
   SplitOperand oa{sa, g.c_out, 0, 1}, ob{sb, rows_b, 0, 1};
   float* gemm_out = chunks == 1 ? dw : part;
   rc = run_split_gemm(h, oa, ob, int(Kp), chunks, g.c_out, rows_b, gemm_out, rows_b, (long long)out_elems,
-                      nullptr, EPI_NONE, nullptr, f32_mode & 0xff, 0, 0,
+                      nullptr, EPI_NONE, nullptr, bf16_mode_of(f32_mode), 0, 0,
                       /*kb_batch_stride=*/int(kb_per_chunk), /*num_kb (64-wide)=*/int(kb_per_chunk));
   if (rc) return rc;
   if (chunks > 1) {

@@ -1,10 +1,11 @@
 // Weight gradient of a stride-1 convolution as an implicit GEMM on the tcgen05
-// tensor cores (split-bf16 arithmetic, see gemm_split_umma.cuh).
+// tensor cores (split-plane arithmetic, see gemm_split_umma.cuh: three bf16 planes, or two fp16 planes of operands
+// scaled by one power of two per tensor - the reduction runs over images and pixels, so no finer scale factors out).
 //
 //   dW[oc][(tap, ic)] = sum over k = (image, oh, ow) of dy[k][oc] * x[k shifted by tap][ic]
 //
 // Both operands are read straight from channels-last bf16 planes
-// {c, w, h, image*3+split}: a K block is a window of 64 pixels (TH rows x TW
+// {c, w, h, image*planes+split}: a K block is a window of 64 pixels (TH rows x TW
 // columns, TW a power of two >= min(OW, 64)); the dy window and the x window
 // shifted by the tap's offset land in shared memory as [pixel][64 channels],
 // which is exactly an MN-major operand chunk (the reduction index walks down
@@ -33,7 +34,8 @@ struct WgradArgs {
   int tiles_m, tiles_n;      // ceil(c_out / 128), ceil(n_chunks / 2)
   int n_total;               // n_chunks * 64: row length of a partial
   float* part;               // [splits][c_out][n_total]
-  int mode;
+  int mode;                  // 1, 3, 6, 9: bf16 products; 23: fp16 two-plane mode
+  int planes;                // planes stored per image (3 bf16, 2 fp16)
   uint32_t* status;
 };
 
@@ -71,7 +73,7 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
   const int tm = (item % per_split) / g.tiles_n, tn = item % g.tiles_n;
   const int kb_begin = z * g.kb_per_split;
   const int kb_end = min(g.total_kb, kb_begin + g.kb_per_split);
-  const int nsplit = (g.mode == 1) ? 1 : (g.mode == 3 ? 2 : 3);
+  const int nsplit = (g.mode == 1) ? 1 : ((g.mode == 3 || g.mode == 23) ? 2 : 3);
   // chunks of this tile that exist (a tile past the end of M or N has fewer)
   const int a_chunks = min(2, (g.c_out + 63) / 64 - tm * 2);
   const int b_chunks = min(2, g.n_chunks - tn * 2);
@@ -118,21 +120,22 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
         for (int s = 0; s < nsplit; ++s)
           for (int c = 0; c < a_chunks; ++c)
             tma_load_4d(sa + s * Cfg::A_TILE + c * Cfg::CHUNK, &tmapDy, full_bar(stage), (tm * 2 + c) * 64, w0, h0,
-                        img * 3 + s);
+                        img * g.planes + s);
         for (int c = 0; c < b_chunks; ++c) {
           const int q = tn * 2 + c;
           const int tap = q / g.cb_per_tap, cb = q - tap * g.cb_per_tap;
           const int fh = tap / g.kw, fw = tap - fh * g.kw;
           for (int s = 0; s < nsplit; ++s)
             tma_load_4d(sb + s * Cfg::B_TILE + c * Cfg::CHUNK, &tmapX, full_bar(stage), cb * 64, w0 + fw - g.pad_w,
-                        h0 + fh - g.pad_h, img * 3 + s);
+                        h0 + fh - g.pad_h, img * g.planes + s);
         }
         if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && has_work) {
-      constexpr uint32_t idesc = make_idesc(Cfg::BM, Cfg::BN, 1u, 1u, 1u, 1u);  // both operands MN-major
+      // both operands MN-major; bf16 planes, or fp16 planes in mode 23
+      const uint32_t idesc = make_idesc(Cfg::BM, Cfg::BN, g.mode == 23 ? 0u : 1u, 1u, 1u, 1u);
       // issue loop with the product schedule known at compile time (one add per descriptor)
       auto issue_all = [&](auto npairs_tag) {
         constexpr int NPAIRS = decltype(npairs_tag)::value;
@@ -218,9 +221,12 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
   }
 }
 
-// dw[oc][ic][tap] = sum_z part[z][oc][tap*cin_p + ic]   (fixed order: deterministic)
+// dw[oc][ic][tap] = 2^(e1 + e2) * sum_z part[z][oc][tap*cin_p + ic]   (fixed order: deterministic); e1 / e2 = the
+// operands' scale exponents in the fp16 mode (first entry of each vector), nullptr otherwise.
 __global__ void wgrad_reduce_kernel(const float* __restrict__ part, int splits, int c_out, int c_in, int cin_p,
-                                    int taps, float* __restrict__ dw) {
+                                    int taps, float* __restrict__ dw, const int* __restrict__ e1,
+                                    const int* __restrict__ e2) {
+  const int e = e1 ? __ldg(e1) + __ldg(e2) : 0;
   const long long total = static_cast<long long>(c_out) * c_in * taps;
   const long long n_total = static_cast<long long>(taps) * cin_p;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -231,7 +237,7 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ part, int splits, 
     const float* p = part + static_cast<long long>(oc) * n_total + static_cast<long long>(t) * cin_p + ic;
     float s = 0.0f;
     for (int z = 0; z < splits; ++z) s += p[static_cast<long long>(z) * c_out * n_total];
-    dw[i] = s;
+    dw[i] = e1 ? scale_pow2(s, e) : s;
   }
 }
 

@@ -49,6 +49,7 @@ struct GemmArgs {
   int planes_per_mat;  // planes stored per matrix in the operand arrays (3 bf16, 2 fp16)
   const int* exp_a;    // fp16 mode: per-row scale exponents of A ([batch][M] if A is batched), else nullptr
   const int* exp_b;    // fp16 mode: per-column scale exponents of B ([batch][N] if B is batched)
+  int exp_b_per_batch; // 1: exp_b holds ONE exponent per batch entry ([batch]) that serves all its columns
   int a_batched;       // 0: one A shared by all batch entries
   int b_batched;
   int bias_per_row;    // 0: bias[N] added along columns; 1: bias[M] added along rows
@@ -69,7 +70,7 @@ struct GemmArgs {
   int tail_tiles;      // tiles in the tail round
   float* partial;
   // Implicit-convolution mode (CONV kernels only): the B operand is read straight
-  // from channels-last image planes {c, w, h, image*3+split}; a K block is one
+  // from channels-last image planes {c, w, h, image*planes+split}; a K block is one
   // (filter tap, channel block) and an N tile is cv_th full image rows.
   int cv_n_tile;       // columns per N tile = cv_th * tile width
   int cv_umma_n;       // MMA N: cv_n_tile rounded up to a multiple of 16
@@ -146,7 +147,10 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmArgs& g, float* s
   const int my_row = row0 + lane;
   const bool my_row_ok = my_row < g.M;
   const float row_bias_own = (g.bias && g.bias_per_row && my_row_ok) ? __ldg(g.bias + my_row) : 0.0f;
-  const int* eb = SCALED ? g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) : nullptr;
+  const int* eb = SCALED ? g.exp_b + (g.exp_b_per_batch ? static_cast<long long>(b)
+                                                           : (g.b_batched ? static_cast<long long>(b) * g.N : 0))
+                          : nullptr;
+  const int eb_all = (SCALED && g.exp_b_per_batch) ? __ldg(eb) : 0;
   const int ea_own =
       (SCALED && my_row_ok) ? __ldg(g.exp_a + (g.a_batched ? static_cast<long long>(b) * g.M : 0) + my_row) : 0;
   float* cbase = g.C + b * g.strideC;
@@ -168,7 +172,7 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmArgs& g, float* s
     for (int e = 0; e < 4; ++e) {
       const bool ok = col + e < col_end;
       cb[e] = (g.bias && !g.bias_per_row && ok) ? __ldg(g.bias + col + e) : 0.0f;
-      ce[e] = (SCALED && ok) ? __ldg(eb + col + e) : 0;
+      ce[e] = (SCALED && ok) ? (g.exp_b_per_batch ? eb_all : __ldg(eb + col + e)) : 0;
     }
 #pragma unroll
     for (int it = 0; it < LPR; ++it) {
@@ -296,7 +300,7 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
   const int tiles_m = (g.M + BM - 1) / BM;
   const int tiles_n = (g.N + n_tile - 1) / n_tile;
   const int num_tiles = tiles_m * tiles_n * g.batch;
-  const int nsplit = (g.mode == 1) ? 1 : (g.mode == 3 ? 2 : 3);
+  const int nsplit = (g.mode == 1) ? 1 : ((g.mode == 3 || g.mode == 23) ? 2 : 3);
   const uint32_t stage_tx = nsplit * (Cfg::A_TILE + (CONV ? n_tile * Cfg::ROW_BYTES : Cfg::B_TILE));
 
   if (threadIdx.x == 0) {
@@ -363,7 +367,8 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, CONV ? g.cv_umma_n : BN, /*bf16*/ 1u, /*f32*/ 1u);
+      // operand format: bf16 planes, or fp16 planes in the two-plane mode 23
+      const uint32_t idesc = make_idesc(BM, CONV ? g.cv_umma_n : BN, g.mode == 23 ? 0u : 1u, /*f32*/ 1u);
       // The whole issue loop with the product schedule known at compile time: per product the
       // thread adds a constant to each operand's descriptor and issues the MMA.
       auto issue_all = [&](auto npairs_tag) {

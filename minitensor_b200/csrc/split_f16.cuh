@@ -248,4 +248,73 @@ split16_cols_scaled_kernel(const float* __restrict__ src, long long ld, long lon
   }
 }
 
+// amax_bits[b] = largest FINITE magnitude of batch entry b's `count` contiguous values, as raw bits.  Inf and NaN
+// are left out so that one of them does not cost the finite values of the same entry their scaling.  The vector
+// must be zeroed before the launch.  Grid (chunks, batch).
+static __global__ void __launch_bounds__(256)
+finite_absmax_kernel(const float* __restrict__ src, long long bstride, long long count, uint32_t* __restrict__ amax_bits) {
+  __shared__ float red[8];
+  const float* p = src + blockIdx.y * bstride;
+  float amax = 0.0f;
+  const long long step = static_cast<long long>(gridDim.x) * 256;
+  const bool vec = ((reinterpret_cast<uintptr_t>(p) & 15) == 0);
+  const long long n4 = vec ? (count >> 2) : 0;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n4; i += step) {
+    const float4 u = reinterpret_cast<const float4*>(p)[i];
+    const float a = fabsf(u.x), b = fabsf(u.y), c = fabsf(u.z), d = fabsf(u.w);
+    amax = fmaxf(amax, fmaxf(fmaxf(is_nonfinite(a) ? 0.0f : a, is_nonfinite(b) ? 0.0f : b),
+                             fmaxf(is_nonfinite(c) ? 0.0f : c, is_nonfinite(d) ? 0.0f : d)));
+  }
+  for (long long i = n4 * 4 + blockIdx.x * 256LL + threadIdx.x; i < count; i += step) {
+    const float a = fabsf(p[i]);
+    amax = fmaxf(amax, is_nonfinite(a) ? 0.0f : a);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    atomicMax(amax_bits + blockIdx.y, __float_as_uint(m));
+  }
+}
+
+// Turning split with ONE scale per batch entry: src[b][k][r] (row stride ld) -> dst[(b*2 + s)][r][k] fp16, K padded
+// to Kp with zeros, every value of entry b scaled by 2^-e(b), e(b) = the scale exponent of the magnitude whose bits
+// are amax_bits[b * amax_stride] (amax_stride 0: one scale for all entries); the first block of each entry also
+// stores e(b) to expo[b] for the GEMM's epilogue.  64 (k) x 64 (r) tiles through shared memory: reads run along r,
+// writes along k.
+static __global__ void __launch_bounds__(256)
+split16_turn_batch_kernel(const float* __restrict__ src, long long ld, long long bstride, __half* __restrict__ dst,
+                          const uint32_t* __restrict__ amax_bits, int amax_stride, int* __restrict__ expo, int R, int K,
+                          int Kp) {
+  __shared__ float tile[64][65];
+  const int b = blockIdx.z;
+  const int r0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+  const float* s = src + b * bstride;
+  const int e = scale_exponent(__uint_as_float(__ldg(amax_bits + static_cast<long long>(b) * amax_stride)));
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) expo[b] = e;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+#pragma unroll 4
+  for (int kk = ty; kk < 64; kk += 4) {
+    const int k = k0 + kk, r = r0 + tx;
+    tile[kk][tx] = (k < K && r < R) ? s[static_cast<long long>(k) * ld + r] : 0.0f;
+  }
+  __syncthreads();
+  const long long plane = static_cast<long long>(R) * Kp;
+  for (int it = threadIdx.x; it < 512; it += 256) {
+    const int rr = it >> 3, kc = (it & 7) << 3;
+    const int r = r0 + rr;
+    if (r >= R || k0 + kc >= Kp) continue;
+    __align__(16) __half o0[8], o1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) split2_f16(tile[kc + i][rr], e, o0[i], o1[i]);
+    __half* d = dst + (static_cast<long long>(b) * 2) * plane + static_cast<long long>(r) * Kp + k0 + kc;
+    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(o0);
+    *reinterpret_cast<uint4*>(d + plane) = *reinterpret_cast<const uint4*>(o1);
+  }
+}
+
 }  // namespace mtb
