@@ -242,7 +242,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (8.0 * chan + 4.0 * chan_p));
     MTB_CUDA(cudaMemsetAsync(amax, 0, sizeof(uint32_t) * size_t(n), h->stream));
     const int chunks = int(std::max<long long>(1, std::min<long long>((img_elems + 4095) / 4096,
-                                                                      (4LL * h->sm_count + n - 1) / n)));
+                                                                      (16LL * h->sm_count + n - 1) / n)));
     finite_absmax_kernel<<<dim3(chunks, n), 256, 0, h->stream>>>(img, img_elems, img_elems, amax);
     split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, chan_p / 64, n), 256, 0, h->stream>>>(
         img, ipix, img_elems, reinterpret_cast<__half*>(p_img), amax, 1, eb, ipix, chan, chan_p);
@@ -289,12 +289,19 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (image planes) failed (%d)", int(r));
-  auto kern = gemm_split_umma_kernel<256, BK, 3, true>;
-  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
   const long long tiles = static_cast<long long>((rows + Cfg::BM - 1) / Cfg::BM) * ((out_h + th - 1) / th) * n;
   const int grid = int(std::min<long long>(tiles, h->sm_count));
   ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
-  kern<<<grid, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(ta, tb, g);
+  if (f16) {   // two planes per operand: four stages of 48 KB instead of three of 72 KB
+    using Cfg2 = GemmCfg<256, BK, 4, 2>;
+    auto kern = gemm_split_umma_kernel<256, BK, 4, true, 2>;
+    MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::SMEM_BYTES));
+    kern<<<grid, Cfg2::NUM_THREADS, Cfg2::SMEM_BYTES, h->stream>>>(ta, tb, g);
+  } else {
+    auto kern = gemm_split_umma_kernel<256, BK, 3, true>;
+    MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    kern<<<grid, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(ta, tb, g);
+  }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
 }
@@ -318,7 +325,6 @@ static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, 
 // Stride-1 weight gradient as implicit GEMM (conv_wgrad_umma.cuh).
 static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy, const float* x, float* dw,
                               int f32_mode) {
-  using Cfg = WgradCfg;
   const int cop = padded_k(g.c_out), cip = padded_k(g.c_in), taps = g.kh * g.kw;
   const int opix = g.oh * g.ow, ipix = g.h * g.w;
   WgradArgs a = {};
@@ -367,7 +373,7 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     ProfScope prof(h, PROF_CONV_GATHER, double(g.n) * (opix * (8.0 * g.c_out + 4.0 * cop) + ipix * (8.0 * g.c_in + 4.0 * cip)));
     MTB_CUDA(cudaMemsetAsync(amax, 0, 2 * sizeof(uint32_t), h->stream));
     auto chunks_of = [&](long long total) {
-      return int(std::max<long long>(1, std::min<long long>((total + 4095) / 4096, 8LL * h->sm_count)));
+      return int(std::max<long long>(1, std::min<long long>((total + 4095) / 4096, 16LL * h->sm_count)));
     };
     finite_absmax_kernel<<<dim3(chunks_of(dy_img * g.n), 1), 256, 0, h->stream>>>(dy, 0, dy_img * g.n, amax);
     finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, h->stream>>>(x, 0, x_img * g.n, amax + 1);
@@ -388,10 +394,17 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
   if (rc) return rc;
   rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, a.planes, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  MTB_CUDA(cudaFuncSetAttribute(conv_wgrad_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
   {
     ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.c_out * double(opix) * taps * g.c_in * g.n);
-    conv_wgrad_umma_kernel<<<a.splits * tiles, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(tdy, tx, a);
+    if (f16) {
+      using Cfg = WgradCfg<2>;
+      MTB_CUDA(cudaFuncSetAttribute(conv_wgrad_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+      conv_wgrad_umma_kernel<2><<<a.splits * tiles, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(tdy, tx, a);
+    } else {
+      using Cfg = WgradCfg<3>;
+      MTB_CUDA(cudaFuncSetAttribute(conv_wgrad_umma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+      conv_wgrad_umma_kernel<3><<<a.splits * tiles, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(tdy, tx, a);
+    }
     MTB_CUDA(cudaGetLastError());
   }
   const long long total = static_cast<long long>(g.c_out) * g.c_in * taps;

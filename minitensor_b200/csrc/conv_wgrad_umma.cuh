@@ -39,20 +39,24 @@ struct WgradArgs {
   uint32_t* status;
 };
 
+// PLANES = planes per operand held in a stage: 3 (bf16 modes, two stages of 96 KB) or 2 (fp16 mode, three stages
+// of 64 KB).
+template <int PLANES>
 struct WgradCfg {
-  static constexpr int BM = 128, BN = 128, BK = 64, STAGES = 2;
+  static constexpr int BM = 128, BN = 128, BK = 64, STAGES = PLANES == 2 ? 3 : 2;
   static constexpr int CHUNK = 64 * 128;                 // 64 pixels x 64 channels x 2 bytes
   static constexpr int A_TILE = 2 * CHUNK, B_TILE = 2 * CHUNK;
-  static constexpr int STAGE_BYTES = 3 * A_TILE + 3 * B_TILE;
+  static constexpr int STAGE_BYTES = PLANES * A_TILE + PLANES * B_TILE;
   static constexpr int TMEM_COLS = 128;
   static constexpr int NUM_THREADS = 192;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+template <int PLANES>
 __global__ void __launch_bounds__(192, 1)
 conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_constant__ CUtensorMap tmapX,
                        const WgradArgs g) {
-  using Cfg = WgradCfg;
+  using Cfg = WgradCfg<PLANES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -116,7 +120,7 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
         const int h0 = (r / g.wblocks) * g.th, w0 = (r % g.wblocks) * g.tw;
         mbar_expect_tx(full_bar(stage), stage_tx);
         const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-        const uint32_t sb = sa + 3 * Cfg::A_TILE;
+        const uint32_t sb = sa + PLANES * Cfg::A_TILE;
         for (int s = 0; s < nsplit; ++s)
           for (int c = 0; c < a_chunks; ++c)
             tma_load_4d(sa + s * Cfg::A_TILE + c * Cfg::CHUNK, &tmapDy, full_bar(stage), (tm * 2 + c) * 64, w0, h0,
@@ -149,7 +153,7 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
           }
           tc_fence_after();
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + 3 * Cfg::A_TILE;
+          const uint32_t sb = sa + PLANES * Cfg::A_TILE;
           const uint64_t da0 = make_mnmajor_desc(sa, Cfg::CHUNK);
           const uint64_t db0 = make_mnmajor_desc(sb, Cfg::CHUNK);
 #pragma unroll
@@ -168,11 +172,15 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
         }
         umma_commit<1>(acc_full);
       };
-      switch (split_pair_count(g.mode)) {
-        case 1: issue_all(std::integral_constant<int, 1>{}); break;
-        case 3: issue_all(std::integral_constant<int, 3>{}); break;
-        case 9: issue_all(std::integral_constant<int, 9>{}); break;
-        default: issue_all(std::integral_constant<int, 6>{}); break;
+      if constexpr (PLANES == 2) {
+        issue_all(std::integral_constant<int, 3>{});   // the fp16 mode's three products
+      } else {
+        switch (split_pair_count(g.mode)) {
+          case 1: issue_all(std::integral_constant<int, 1>{}); break;
+          case 3: issue_all(std::integral_constant<int, 3>{}); break;
+          case 9: issue_all(std::integral_constant<int, 9>{}); break;
+          default: issue_all(std::integral_constant<int, 6>{}); break;
+        }
       }
     }
   } else {

@@ -236,13 +236,14 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmArgs& g, float* sta
 #undef MTB_EPI_CASE
 }
 
-template <int BN, int BK, int STAGES>
+// PLANES = planes per operand a stage has room for: 3 (bf16 modes) or 2 (the fp16 two-plane mode only).
+template <int BN, int BK, int STAGES, int PLANES = 3>
 struct GemmCfg {
   static constexpr int BM = 128;
   static constexpr int ROW_BYTES = BK * 2;                 // bf16
   static constexpr int A_TILE = BM * ROW_BYTES;            // one split of A
   static constexpr int B_TILE = BN * ROW_BYTES;
-  static constexpr int STAGE_BYTES = 3 * A_TILE + 3 * B_TILE;
+  static constexpr int STAGE_BYTES = PLANES * A_TILE + PLANES * B_TILE;
   static constexpr int ACC_COLS = BN;                      // f32 columns per accumulator
   static constexpr int TMEM_COLS = 2 * BN;                 // two accumulators (power of two)
   static constexpr int NUM_THREADS = 192;
@@ -271,11 +272,11 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = in_band / rows_in_band;
 }
 
-template <int BN, int BK, int STAGES, bool CONV = false>
+template <int BN, int BK, int STAGES, bool CONV = false, int PLANES = 3>
 __global__ void __launch_bounds__(192, 1)
 gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
                        const __grid_constant__ CUtensorMap tmapB, const GemmArgs g) {
-  using Cfg = GemmCfg<BN, BK, STAGES>;
+  using Cfg = GemmCfg<BN, BK, STAGES, PLANES>;
   constexpr int BM = Cfg::BM;
   extern __shared__ uint8_t smem_raw[];
 
@@ -347,7 +348,7 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
           }
           mbar_expect_tx(full_bar(stage), stage_tx);
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + 3 * Cfg::A_TILE;
+          const uint32_t sb = sa + PLANES * Cfg::A_TILE;
           for (int s = 0; s < nsplit; ++s)
             tma_load_3d(sa + s * Cfg::A_TILE, &tmapA, full_bar(stage), (kb0 + kb) * BK, tm * BM, za + s);
           if constexpr (CONV) {
@@ -392,7 +393,7 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
             }
             tc_fence_after();
             const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
-            const uint32_t sb = sa + 3 * Cfg::A_TILE;
+            const uint32_t sb = sa + PLANES * Cfg::A_TILE;
             // descriptors of plane 0, k = 0; the start address sits in the low 14 bits in units of
             // 16 bytes and shared memory ends below 2^18, so adding an offset never carries out
             const uint64_t da0 = make_kmajor_desc<Cfg::ROW_BYTES>(sa);
@@ -415,11 +416,15 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
           if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
       };
-      switch (split_pair_count(g.mode)) {
-        case 1: issue_all(std::integral_constant<int, 1>{}); break;
-        case 3: issue_all(std::integral_constant<int, 3>{}); break;
-        case 9: issue_all(std::integral_constant<int, 9>{}); break;
-        default: issue_all(std::integral_constant<int, 6>{}); break;
+      if constexpr (PLANES == 2) {
+        issue_all(std::integral_constant<int, 3>{});   // only the two-plane modes fit this layout
+      } else {
+        switch (split_pair_count(g.mode)) {
+          case 1: issue_all(std::integral_constant<int, 1>{}); break;
+          case 3: issue_all(std::integral_constant<int, 3>{}); break;
+          case 9: issue_all(std::integral_constant<int, 9>{}); break;
+          default: issue_all(std::integral_constant<int, 6>{}); break;
+        }
       }
     }
   } else {

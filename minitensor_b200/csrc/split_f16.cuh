@@ -259,8 +259,9 @@ finite_absmax_kernel(const float* __restrict__ src, long long bstride, long long
   const long long step = static_cast<long long>(gridDim.x) * 256;
   const bool vec = ((reinterpret_cast<uintptr_t>(p) & 15) == 0);
   const long long n4 = vec ? (count >> 2) : 0;
+#pragma unroll 4
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n4; i += step) {
-    const float4 u = reinterpret_cast<const float4*>(p)[i];
+    const float4 u = __ldg(reinterpret_cast<const float4*>(p) + i);
     const float a = fabsf(u.x), b = fabsf(u.y), c = fabsf(u.z), d = fabsf(u.w);
     amax = fmaxf(amax, fmaxf(fmaxf(is_nonfinite(a) ? 0.0f : a, is_nonfinite(b) ? 0.0f : b),
                              fmaxf(is_nonfinite(c) ? 0.0f : c, is_nonfinite(d) ? 0.0f : d)));
@@ -290,30 +291,42 @@ static __global__ void __launch_bounds__(256)
 split16_turn_batch_kernel(const float* __restrict__ src, long long ld, long long bstride, __half* __restrict__ dst,
                           const uint32_t* __restrict__ amax_bits, int amax_stride, int* __restrict__ expo, int R, int K,
                           int Kp) {
-  __shared__ float tile[64][65];
+  // [plane][r][9 x 16 bytes]: a row holds 64 k as fp16 (128 bytes) plus 16 bytes of padding, so that the 16-byte
+  // stores of lanes with consecutive r and the 16-byte loads of lanes with consecutive k chunks both spread
+  // over all banks.  The values are scaled, split and packed BEFORE they cross shared memory.
+  __shared__ __align__(16) uint4 tile[2][64][9];
   const int b = blockIdx.z;
   const int r0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
   const float* s = src + b * bstride;
   const int e = scale_exponent(__uint_as_float(__ldg(amax_bits + static_cast<long long>(b) * amax_stride)));
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) expo[b] = e;
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-#pragma unroll 4
-  for (int kk = ty; kk < 64; kk += 4) {
-    const int k = k0 + kk, r = r0 + tx;
-    tile[kk][tx] = (k < K && r < R) ? s[static_cast<long long>(k) * ld + r] : 0.0f;
+  const int tx = threadIdx.x & 63, kg = threadIdx.x >> 6;
+  const int r = r0 + tx;
+  float v[2][8];
+#pragma unroll
+  for (int g = 0; g < 2; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = k0 + (kg + 4 * g) * 8 + i;
+      v[g][i] = (k < K && r < R) ? s[static_cast<long long>(k) * ld + r] : 0.0f;
+    }
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    __align__(16) __half o0[8], o1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) split2_f16(v[g][i], e, o0[i], o1[i]);
+    tile[0][tx][kg + 4 * g] = *reinterpret_cast<const uint4*>(o0);
+    tile[1][tx][kg + 4 * g] = *reinterpret_cast<const uint4*>(o1);
   }
   __syncthreads();
   const long long plane = static_cast<long long>(R) * Kp;
-  for (int it = threadIdx.x; it < 512; it += 256) {
-    const int rr = it >> 3, kc = (it & 7) << 3;
-    const int r = r0 + rr;
-    if (r >= R || k0 + kc >= Kp) continue;
-    __align__(16) __half o0[8], o1[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) split2_f16(tile[kc + i][rr], e, o0[i], o1[i]);
-    __half* d = dst + (static_cast<long long>(b) * 2) * plane + static_cast<long long>(r) * Kp + k0 + kc;
-    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(o0);
-    *reinterpret_cast<uint4*>(d + plane) = *reinterpret_cast<const uint4*>(o1);
+  for (int j = 0; j < 4; ++j) {
+    const int idx = threadIdx.x + 256 * j;
+    const int pl = idx >> 9, rr = (idx >> 3) & 63, c = idx & 7;
+    if (r0 + rr >= R || k0 + c * 8 >= Kp) continue;
+    __half* d = dst + (static_cast<long long>(b) * 2 + pl) * plane + static_cast<long long>(r0 + rr) * Kp + k0 + c * 8;
+    *reinterpret_cast<uint4*>(d) = tile[pl][rr][c];
   }
 }
 
