@@ -132,3 +132,38 @@ def test_both_lowerings_match_oracle(be, orc, rng, geom, lowering):
     wnorm = np.linalg.norm(wn.reshape(co, -1), axis=1).max()
     assert np.abs(y.cpu().numpy() - ref).max() <= F32_TOL * xnorm * wnorm
     assert np.abs(dx.cpu().numpy() - gx).max() <= F32_TOL * (co * kh * kw) * np.abs(go).max() * np.abs(wn).max()
+
+
+def test_implicit_conv_scales_every_image_on_its_own(be, orc, rng):
+    """The default mode of the stride-1 kernels (two fp16 planes) scales each image by its own power of two:
+    images 40 orders of magnitude apart, an all-zero image and an image holding an Inf keep, per image, the
+    accuracy of the plain case, and the Inf stays inside the windows that touch it."""
+    n, c, h, w, co = 5, 6, 9, 11, 7
+    xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    xn[0] *= 1e-20
+    xn[2] *= 1e20
+    xn[3] = 0.0
+    xn[4, 2, 4, 5] = np.inf
+    wn = (rng.standard_normal((co, c, 3, 3)) * np.sqrt(2.0 / (c * 9))).astype(np.float32)
+    dev = lambda a: torch.from_numpy(a).to(be.device)
+    y = be.conv2d_fwd(dev(xn), dev(wn), None, (1, 1), (1, 1)).cpu().numpy()
+    wnorm = np.linalg.norm(wn.reshape(co, -1), axis=1).max()
+    for i in range(4):
+        ref = orc.conv2d(xn[i:i + 1], wn, None, (1, 1), (1, 1))[0]
+        assert np.abs(y[i] - ref).max() <= F32_TOL * np.sqrt(c * 9) * np.abs(xn[i]).max() * wnorm, i
+    assert not y[3].any()
+    finite_part = xn[4:5].copy()
+    finite_part[0, 2, 4, 5] = 0.0
+    ref = orc.conv2d(finite_part, wn, None, (1, 1), (1, 1))[0]
+    touched = np.zeros((h, w), bool)
+    touched[3:6, 4:7] = True                       # outputs whose 3x3 window covers (4, 5)
+    assert not np.isfinite(y[4][:, touched]).any()
+    assert np.abs(y[4][:, ~touched] - ref[:, ~touched]).max() <= F32_TOL * np.sqrt(c * 9) * np.abs(finite_part).max() * wnorm
+    # the data gradient runs on the same kernel with dy as the image operand
+    go = rng.standard_normal((n, co, h, w)).astype(np.float32)
+    go[1] *= 1e-25
+    go[2] *= 1e15
+    dx = be.conv2d_bwd_data(dev(go), dev(wn), xn.shape, (1, 1), (1, 1)).cpu().numpy()
+    for i in range(n):
+        gx, _, _ = orc.conv2d_backward(np.zeros_like(xn[i:i + 1]), wn, go[i:i + 1], (1, 1), (1, 1), need_b=False)
+        assert np.abs(dx[i] - gx[0]).max() <= F32_TOL * (co * 9) * np.abs(go[i]).max() * np.abs(wn).max(), i
