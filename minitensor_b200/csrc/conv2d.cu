@@ -239,6 +239,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
   const long long img_elems = static_cast<long long>(chan) * ipix;
   // channels-last planes: per image a [chan][pixels] -> [pixels][chan_p] turning split
   if (f16) {
+    if (h->side_stream && !h->profiling) MTB_CUDA(cudaEventRecord(h->ev_fork, h->stream));   // the weights fork here
     ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (8.0 * chan + 4.0 * chan_p));
     MTB_CUDA(cudaMemsetAsync(amax, 0, sizeof(uint32_t) * size_t(n), h->stream));
     const int chunks = int(std::max<long long>(1, std::min<long long>((img_elems + 4095) / 4096,
@@ -253,12 +254,27 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     if (rc) return rc;
   }
   const long long wtotal = static_cast<long long>(rows) * Kp;
-  weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
-      wsrc, wtmp, rows, chan, chan_p, taps, mode);
-  MTB_CUDA(cudaGetLastError());
-  if (f16) rc = launch_split16(h, wtmp, true, rows, Kp, 1, 0, reinterpret_cast<__half*>(p_w), ea, nullptr, 0);
-  else rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3);
-  if (rc) return rc;
+  if (f16) {
+    // the weights (a few hundred KB, two launches) are prepared beside the image
+    const bool side = h->side_stream && !h->profiling;
+    cudaStream_t sw = side ? h->side_stream : h->stream;
+    if (side) MTB_CUDA(cudaStreamWaitEvent(sw, h->ev_fork, 0));
+    weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, sw>>>(
+        wsrc, wtmp, rows, chan, chan_p, taps, mode);
+    MTB_CUDA(cudaGetLastError());
+    rc = launch_split16(h, wtmp, true, rows, Kp, 1, 0, reinterpret_cast<__half*>(p_w), ea, nullptr, 0, sw);
+    if (rc) return rc;
+    if (side) {
+      MTB_CUDA(cudaEventRecord(h->ev_join, sw));
+      MTB_CUDA(cudaStreamWaitEvent(h->stream, h->ev_join, 0));
+    }
+  } else {
+    weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
+        wsrc, wtmp, rows, chan, chan_p, taps, mode);
+    MTB_CUDA(cudaGetLastError());
+    rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3);
+    if (rc) return rc;
+  }
 
   int th = std::max(1, 256 / out_w);
   th = std::min(th, out_h);
@@ -375,13 +391,24 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     auto chunks_of = [&](long long total) {
       return int(std::max<long long>(1, std::min<long long>((total + 4095) / 4096, 16LL * h->sm_count)));
     };
+    // the two tensors are prepared side by side: neither pass fills the memory system alone
+    const bool side = h->side_stream && !h->profiling;
+    cudaStream_t sx = side ? h->side_stream : h->stream;
+    if (side) {
+      MTB_CUDA(cudaEventRecord(h->ev_fork, h->stream));
+      MTB_CUDA(cudaStreamWaitEvent(sx, h->ev_fork, 0));
+    }
     finite_absmax_kernel<<<dim3(chunks_of(dy_img * g.n), 1), 256, 0, h->stream>>>(dy, 0, dy_img * g.n, amax);
-    finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, h->stream>>>(x, 0, x_img * g.n, amax + 1);
     split16_turn_batch_kernel<<<dim3((opix + 63) / 64, cop / 64, g.n), 256, 0, h->stream>>>(
         dy, opix, dy_img, reinterpret_cast<__half*>(p_dy), amax, 0, e_dy, opix, g.c_out, cop);
-    split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, cip / 64, g.n), 256, 0, h->stream>>>(
+    finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, sx>>>(x, 0, x_img * g.n, amax + 1);
+    split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, cip / 64, g.n), 256, 0, sx>>>(
         x, ipix, x_img, reinterpret_cast<__half*>(p_x), amax + 1, 0, e_x, ipix, g.c_in, cip);
     MTB_CUDA(cudaGetLastError());
+    if (side) {
+      MTB_CUDA(cudaEventRecord(h->ev_join, sx));
+      MTB_CUDA(cudaStreamWaitEvent(h->stream, h->ev_join, 0));
+    }
   } else {
     ProfScope prof(h, PROF_CONV_GATHER, double(g.n) * (opix * (4.0 * g.c_out + 6.0 * cop) + ipix * (4.0 * g.c_in + 6.0 * cip)));
     rc = launch_split(h, dy, true, opix, g.c_out, cop, g.n, dy_img, p_dy, 3);
