@@ -4,7 +4,7 @@
 // The reference computes the convolution with direct loops
 // (engine/src/operations/conv.rs:111-157) and its backward with three more
 // (engine/src/autograd/mod/shape.rs:57-197).  Here each of the four results is
-// a GEMM whose operands are gathered straight into the bf16 split planes the
+// a GEMM whose operands are gathered straight into the split planes the
 // GEMM kernel consumes, with the image as the batch entry so the output lands
 // in NCHW without a transpose:
 //   forward   y[n]  [C_out][OH*OW] = W [C_out][C_in*kH*kW]   * patches(x[n])^T  (+ bias per row)
@@ -13,7 +13,8 @@
 //   bwd bias  db[oc] = sum_{n,oh,ow} dy
 //
 // Stride-1 forward and data gradient run as an IMPLICIT GEMM: the image is
-// split once into channels-last bf16 planes [image*3+split][h][w][c] and the
+// split once into channels-last planes [image*planes+split][h][w][c] (two fp16
+// planes scaled per image by default, three bf16 planes otherwise) and the
 // GEMM kernel's TMA producer reads, for every (filter tap, channel block), the
 // shifted window {c block, full rows} of those planes with out-of-range
 // coordinates zero-filled by the hardware: the padding and the im2col matrix
