@@ -70,7 +70,8 @@ __device__ __forceinline__ float patch_value(const float* __restrict__ img, cons
 template <int MODE>
 __global__ void __launch_bounds__(256) patch_split_kernel(const float* __restrict__ src, ConvGeom g,
                                                           int rows, int K, int Kp, long long img_stride,
-                                                          __nv_bfloat16* __restrict__ dst) {
+                                                          __nv_bfloat16* __restrict__ dst,
+                                                          uint32_t* __restrict__ nf_word) {
   __shared__ float tile[64][65];
   const int n = blockIdx.z;
   const int r0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
@@ -78,7 +79,9 @@ __global__ void __launch_bounds__(256) patch_split_kernel(const float* __restric
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
   for (int kk = ty; kk < 64; kk += 4) {
     const int k = k0 + kk, r = r0 + tx;
-    tile[kk][tx] = (k < K && r < rows) ? patch_value<MODE>(img, g, r, k) : 0.0f;
+    const float v = (k < K && r < rows) ? patch_value<MODE>(img, g, r, k) : 0.0f;
+    if (is_nonfinite(v)) atomicMax(nf_word, MTB_FLAG_SET);
+    tile[kk][tx] = v;
   }
   __syncthreads();
   const long long plane = static_cast<long long>(rows) * Kp;
@@ -107,7 +110,8 @@ enum { WG_DY = 0, WG_PATCH = 1 };
 template <int MODE>
 __global__ void __launch_bounds__(256) wgrad_split_kernel(const float* __restrict__ src, ConvGeom g,
                                                           int rows, long long Ktot, long long Kp,
-                                                          __nv_bfloat16* __restrict__ dst) {
+                                                          __nv_bfloat16* __restrict__ dst,
+                                                          uint32_t* __restrict__ nf_word) {
   const long long chunks = Kp >> 3;
   const long long total = rows * chunks;
   const int opix = g.oh * g.ow;
@@ -141,6 +145,7 @@ __global__ void __launch_bounds__(256) wgrad_split_kernel(const float* __restric
             v = src[((static_cast<long long>(n) * g.c_in + ch) * g.h + iy) * g.w + ix];
         }
       }
+      if (is_nonfinite(v)) atomicMax(nf_word, MTB_FLAG_SET);
       const Split3 t = split3(v);
       o0[e] = t.s0; o1[e] = t.s1; o2[e] = t.s2;
     }
@@ -185,6 +190,114 @@ __global__ void __launch_bounds__(256) conv_bias_partial_kernel(const float* __r
   if (threadIdx.x == 0) partial[static_cast<long long>(chunk) * c_out + oc] = red[0];
 }
 
+// ---- Inf / NaN operands: the same results as the reference's direct loops.
+// Any split scheme turns Inf times a finite value into NaN (Inf times the zero low-order plane), where the
+// reference's `sum += x * w` (engine/src/operations/conv.rs:121-147, engine/src/autograd/mod/shape.rs:86-169)
+// gives +-Inf.  The preparation kernels of a call raise its flag word when they meet a non-finite value and the
+// kernels below then recompute the whole result on the CUDA cores with separately rounded multiply and add in the
+// reference's summation order; for finite operands they return at once.
+__global__ void __launch_bounds__(256) conv_direct_fwd_kernel(ConvGeom g, const float* __restrict__ x,
+                                                              const float* __restrict__ w,
+                                                              const float* __restrict__ bias, float* __restrict__ y,
+                                                              const uint32_t* __restrict__ gate) {
+  if (*gate != MTB_FLAG_SET) return;
+  const long long total = static_cast<long long>(g.n) * g.c_out * g.oh * g.ow;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
+    const int ox = static_cast<int>(i % g.ow);
+    long long q = i / g.ow;
+    const int oy = static_cast<int>(q % g.oh);
+    q /= g.oh;
+    const int oc = static_cast<int>(q % g.c_out), n = static_cast<int>(q / g.c_out);
+    float sum = 0.0f;
+    for (int ic = 0; ic < g.c_in; ++ic)
+      for (int fh = 0; fh < g.kh; ++fh) {
+        const int iy = oy * g.sh + fh - g.ph;
+        if (iy < 0 || iy >= g.h) continue;
+        for (int fw = 0; fw < g.kw; ++fw) {
+          const int ix = ox * g.sw + fw - g.pw;
+          if (ix < 0 || ix >= g.w) continue;
+          const float a = x[((static_cast<long long>(n) * g.c_in + ic) * g.h + iy) * g.w + ix];
+          const float b = w[((static_cast<long long>(oc) * g.c_in + ic) * g.kh + fh) * g.kw + fw];
+          sum = __fadd_rn(sum, __fmul_rn(a, b));
+        }
+      }
+    if (bias) sum = __fadd_rn(sum, bias[oc]);
+    y[i] = sum;
+  }
+}
+
+// dx[n][ic][iy][ix]: the reference scatters over (oc, oh, ow, kh, kw); gathered per input pixel the same terms arrive
+// in ascending (oc, oh, ow).
+__global__ void __launch_bounds__(256) conv_direct_dgrad_kernel(ConvGeom g, const float* __restrict__ dy,
+                                                                const float* __restrict__ w, float* __restrict__ dx,
+                                                                const uint32_t* __restrict__ gate) {
+  if (*gate != MTB_FLAG_SET) return;
+  const long long total = static_cast<long long>(g.n) * g.c_in * g.h * g.w;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
+    const int ix = static_cast<int>(i % g.w);
+    long long q = i / g.w;
+    const int iy = static_cast<int>(q % g.h);
+    q /= g.h;
+    const int ic = static_cast<int>(q % g.c_in), n = static_cast<int>(q / g.c_in);
+    float sum = 0.0f;
+    for (int oc = 0; oc < g.c_out; ++oc)
+      for (int oy = 0; oy < g.oh; ++oy) {
+        const int fh = iy + g.ph - oy * g.sh;
+        if (fh < 0 || fh >= g.kh) continue;
+        for (int ox = 0; ox < g.ow; ++ox) {
+          const int fw = ix + g.pw - ox * g.sw;
+          if (fw < 0 || fw >= g.kw) continue;
+          const float a = dy[((static_cast<long long>(n) * g.c_out + oc) * g.oh + oy) * g.ow + ox];
+          const float b = w[((static_cast<long long>(oc) * g.c_in + ic) * g.kh + fh) * g.kw + fw];
+          sum = __fadd_rn(sum, __fmul_rn(a, b));
+        }
+      }
+    dx[i] = sum;
+  }
+}
+
+// dw[oc][ic][fh][fw]: one block per output, the (n, oh, ow) terms dealt round-robin to its threads and the 256
+// partial sums folded in a fixed order.
+__global__ void __launch_bounds__(256) conv_direct_wgrad_kernel(ConvGeom g, const float* __restrict__ dy,
+                                                                const float* __restrict__ x, float* __restrict__ dw,
+                                                                const uint32_t* __restrict__ gate) {
+  if (*gate != MTB_FLAG_SET) return;
+  __shared__ float red[256];
+  const long long outputs = static_cast<long long>(g.c_out) * g.c_in * g.kh * g.kw;
+  const int opix = g.oh * g.ow;
+  for (long long o = blockIdx.x; o < outputs; o += gridDim.x) {
+    const int fw = static_cast<int>(o % g.kw);
+    long long q = o / g.kw;
+    const int fh = static_cast<int>(q % g.kh);
+    q /= g.kh;
+    const int ic = static_cast<int>(q % g.c_in), oc = static_cast<int>(q / g.c_in);
+    float sum = 0.0f;
+    const long long terms = static_cast<long long>(g.n) * opix;
+    for (long long k = threadIdx.x; k < terms; k += 256) {
+      const int n = static_cast<int>(k / opix);
+      const int pix = static_cast<int>(k - static_cast<long long>(n) * opix);
+      const int oy = pix / g.ow, ox = pix - oy * g.ow;
+      const int iy = oy * g.sh + fh - g.ph, ix = ox * g.sw + fw - g.pw;
+      if (iy < 0 || iy >= g.h || ix < 0 || ix >= g.w) continue;
+      const float a = dy[(static_cast<long long>(n) * g.c_out + oc) * opix + pix];
+      const float b = x[((static_cast<long long>(n) * g.c_in + ic) * g.h + iy) * g.w + ix];
+      sum = __fadd_rn(sum, __fmul_rn(a, b));
+    }
+    red[threadIdx.x] = sum;
+    __syncthreads();
+    for (int s = 128; s; s >>= 1) {
+      if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) dw[o] = red[0];
+    __syncthreads();
+  }
+}
+
+static inline int direct_grid(const mtb200_ctx* h, long long items) {
+  return int(std::max<long long>(1, std::min<long long>((items + 255) / 256, 8LL * h->sm_count)));
+}
+
 // dst[r][t][cp] (f32, zero for cp >= channels): the A operand of the implicit GEMM.
 //  mode 0 (forward):       r = oc, channel = ic : w[(r*chan + c)*taps + t]
 //  mode 1 (data gradient): r = ic, channel = oc : w[(c*rows + r)*taps + t]
@@ -209,7 +322,8 @@ __global__ void weight_taps_kernel(const float* __restrict__ w, float* __restric
 //  the window of tap (fh,fw) for output pixel (y,x) starts at (y + h0 + sgn*fh, x + w0 + sgn*fw).
 static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, int img_h, int img_w,
                              const float* wsrc, int rows, int kh, int kw, int mode, int out_h, int out_w,
-                             int w0, int h0, int sgn, const float* bias, float* out, int f32_mode) {
+                             int w0, int h0, int sgn, const float* bias, float* out, int f32_mode,
+                             uint32_t* nf_word) {
   constexpr int BK = 32;
   using Cfg = GemmCfg<256, BK, 3>;
   const int chan_p = padded_k(chan), taps = kh * kw;
@@ -245,13 +359,13 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     MTB_CUDA(cudaMemsetAsync(amax, 0, sizeof(uint32_t) * size_t(n), h->stream));
     const int chunks = int(std::max<long long>(1, std::min<long long>((img_elems + 4095) / 4096,
                                                                       (16LL * h->sm_count + n - 1) / n)));
-    finite_absmax_kernel<<<dim3(chunks, n), 256, 0, h->stream>>>(img, img_elems, img_elems, amax);
+    finite_absmax_kernel<<<dim3(chunks, n), 256, 0, h->stream>>>(img, img_elems, img_elems, amax, nf_word, MTB_FLAG_SET);
     split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, chan_p / 64, n), 256, 0, h->stream>>>(
         img, ipix, img_elems, reinterpret_cast<__half*>(p_img), amax, 1, eb, ipix, chan, chan_p);
     MTB_CUDA(cudaGetLastError());
   } else {
     ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (4.0 * chan + 6.0 * chan_p));
-    rc = launch_split(h, img, true, ipix, chan, chan_p, n, img_elems, p_img, 3);
+    rc = launch_split(h, img, true, ipix, chan, chan_p, n, img_elems, p_img, 3, nf_word, MTB_FLAG_SET);
     if (rc) return rc;
   }
   const long long wtotal = static_cast<long long>(rows) * Kp;
@@ -263,7 +377,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, sw>>>(
         wsrc, wtmp, rows, chan, chan_p, taps, mode);
     MTB_CUDA(cudaGetLastError());
-    rc = launch_split16(h, wtmp, true, rows, Kp, 1, 0, reinterpret_cast<__half*>(p_w), ea, nullptr, 0, sw);
+    rc = launch_split16(h, wtmp, true, rows, Kp, 1, 0, reinterpret_cast<__half*>(p_w), ea, nf_word, MTB_FLAG_SET, sw);
     if (rc) return rc;
     if (side) {
       MTB_CUDA(cudaEventRecord(h->ev_join, sw));
@@ -273,7 +387,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
         wsrc, wtmp, rows, chan, chan_p, taps, mode);
     MTB_CUDA(cudaGetLastError());
-    rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3);
+    rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3, nf_word, MTB_FLAG_SET);
     if (rc) return rc;
   }
 
@@ -341,7 +455,7 @@ static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, 
 
 // Stride-1 weight gradient as implicit GEMM (conv_wgrad_umma.cuh).
 static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy, const float* x, float* dw,
-                              int f32_mode) {
+                              int f32_mode, uint32_t* nf_word) {
   const int cop = padded_k(g.c_out), cip = padded_k(g.c_in), taps = g.kh * g.kw;
   const int opix = g.oh * g.ow, ipix = g.h * g.w;
   WgradArgs a = {};
@@ -399,10 +513,10 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
       MTB_CUDA(cudaEventRecord(h->ev_fork, h->stream));
       MTB_CUDA(cudaStreamWaitEvent(sx, h->ev_fork, 0));
     }
-    finite_absmax_kernel<<<dim3(chunks_of(dy_img * g.n), 1), 256, 0, h->stream>>>(dy, 0, dy_img * g.n, amax);
+    finite_absmax_kernel<<<dim3(chunks_of(dy_img * g.n), 1), 256, 0, h->stream>>>(dy, 0, dy_img * g.n, amax, nf_word, MTB_FLAG_SET);
     split16_turn_batch_kernel<<<dim3((opix + 63) / 64, cop / 64, g.n), 256, 0, h->stream>>>(
         dy, opix, dy_img, reinterpret_cast<__half*>(p_dy), amax, 0, e_dy, opix, g.c_out, cop);
-    finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, sx>>>(x, 0, x_img * g.n, amax + 1);
+    finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, sx>>>(x, 0, x_img * g.n, amax + 1, nf_word, MTB_FLAG_SET);
     split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, cip / 64, g.n), 256, 0, sx>>>(
         x, ipix, x_img, reinterpret_cast<__half*>(p_x), amax + 1, 0, e_x, ipix, g.c_in, cip);
     MTB_CUDA(cudaGetLastError());
@@ -412,9 +526,9 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     }
   } else {
     ProfScope prof(h, PROF_CONV_GATHER, double(g.n) * (opix * (4.0 * g.c_out + 6.0 * cop) + ipix * (4.0 * g.c_in + 6.0 * cip)));
-    rc = launch_split(h, dy, true, opix, g.c_out, cop, g.n, dy_img, p_dy, 3);
+    rc = launch_split(h, dy, true, opix, g.c_out, cop, g.n, dy_img, p_dy, 3, nf_word, MTB_FLAG_SET);
     if (rc) return rc;
-    rc = launch_split(h, x, true, ipix, g.c_in, cip, g.n, x_img, p_x, 3);
+    rc = launch_split(h, x, true, ipix, g.c_in, cip, g.n, x_img, p_x, 3, nf_word, MTB_FLAG_SET);
     if (rc) return rc;
   }
   CUtensorMap tdy, tx;
@@ -485,9 +599,20 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
   if (K == 0) return fail(MTB200_ERR_UNSUPPORTED, "conv2d with zero input channels is not supported");
   if (!x || !w) return fail(MTB200_ERR_INVALID, "null input pointer");
   const bool force_explicit = ((f32_mode >> 8) & 0xff) == 0xff;  // test hook: gathered-patch lowering
-  if (g.sh == 1 && g.sw == 1 && g.ow <= 256 && !force_explicit)
-    return implicit_conv(h, x, g.n, g.c_in, g.h, g.w, w, g.c_out, g.kh, g.kw, 0, g.oh, g.ow, -g.pw, -g.ph, +1,
-                         bias, y, f32_mode);
+  uint32_t* nf_word = nullptr;
+  rc = call_flag_begin(h, &nf_word);
+  if (rc) return rc;
+  auto redo = [&]() -> int32_t {   // returns at once unless the operands held Inf / NaN
+    conv_direct_fwd_kernel<<<direct_grid(h, static_cast<long long>(g.n) * g.c_out * opix), 256, 0, h->stream>>>(
+        g, x, w, bias, y, nf_word);
+    MTB_CUDA(cudaGetLastError());
+    return MTB200_OK;
+  };
+  if (g.sh == 1 && g.sw == 1 && g.ow <= 256 && !force_explicit) {
+    rc = implicit_conv(h, x, g.n, g.c_in, g.h, g.w, w, g.c_out, g.kh, g.kw, 0, g.oh, g.ow, -g.pw, -g.ph, +1,
+                       bias, y, f32_mode, nf_word);
+    return rc ? rc : redo();
+  }
   const int Kp = padded_k(K);
   const size_t bytes_w = split_bytes(g.c_out, Kp, 1), bytes_p = split_bytes(opix, Kp, g.n);
   void* ws = nullptr;
@@ -495,14 +620,15 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
   if (rc) return rc;
   __nv_bfloat16* sw_ = static_cast<__nv_bfloat16*>(ws);
   __nv_bfloat16* sp = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_w);
-  rc = launch_split(h, w, false, g.c_out, K, Kp, 1, 0, sw_, 3);
+  rc = launch_split(h, w, false, g.c_out, K, Kp, 1, 0, sw_, 3, nf_word, MTB_FLAG_SET);
   if (rc) return rc;
   patch_split_kernel<PATCH_FWD><<<dim3((opix + 63) / 64, Kp / 64, g.n), 256, 0, h->stream>>>(
-      x, g, opix, K, Kp, static_cast<long long>(g.c_in) * g.h * g.w, sp);
+      x, g, opix, K, Kp, static_cast<long long>(g.c_in) * g.h * g.w, sp, nf_word);
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_out, 0, 1}, ob{sp, opix, g.n > 1, g.n};
-  return run_split_gemm(h, oa, ob, Kp, g.n, g.c_out, opix, y, opix, static_cast<long long>(g.c_out) * opix,
-                        bias, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
+  rc = run_split_gemm(h, oa, ob, Kp, g.n, g.c_out, opix, y, opix, static_cast<long long>(g.c_out) * opix,
+                      bias, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
+  return rc ? rc : redo();
 }
 
 int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
@@ -523,9 +649,20 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
   }
   if (!dy || !w) return fail(MTB200_ERR_INVALID, "null input pointer");
   const bool force_explicit = ((f32_mode >> 8) & 0xff) == 0xff;
-  if (g.sh == 1 && g.sw == 1 && g.w <= 256 && !force_explicit)
-    return implicit_conv(h, dy, g.n, g.c_out, g.oh, g.ow, w, g.c_in, g.kh, g.kw, 1, g.h, g.w, g.pw, g.ph, -1,
-                         nullptr, dx, f32_mode);
+  uint32_t* nf_word = nullptr;
+  rc = call_flag_begin(h, &nf_word);
+  if (rc) return rc;
+  auto redo = [&]() -> int32_t {
+    conv_direct_dgrad_kernel<<<direct_grid(h, static_cast<long long>(g.n) * g.c_in * ipix), 256, 0, h->stream>>>(
+        g, dy, w, dx, nf_word);
+    MTB_CUDA(cudaGetLastError());
+    return MTB200_OK;
+  };
+  if (g.sh == 1 && g.sw == 1 && g.w <= 256 && !force_explicit) {
+    rc = implicit_conv(h, dy, g.n, g.c_out, g.oh, g.ow, w, g.c_in, g.kh, g.kw, 1, g.h, g.w, g.pw, g.ph, -1,
+                       nullptr, dx, f32_mode, nf_word);
+    return rc ? rc : redo();
+  }
   const int Kp = padded_k(K);
   const size_t bytes_w = split_bytes(g.c_in, Kp, 1), bytes_p = split_bytes(ipix, Kp, g.n);
   const size_t bytes_perm = align_up(sizeof(float) * size_t(g.c_in) * K, 1024);
@@ -539,14 +676,15 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
   permute_weight_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
       w, wperm, g.c_out, g.c_in, g.kh * g.kw);
   MTB_CUDA(cudaGetLastError());
-  rc = launch_split(h, wperm, false, g.c_in, K, Kp, 1, 0, sw_, 3);
+  rc = launch_split(h, wperm, false, g.c_in, K, Kp, 1, 0, sw_, 3, nf_word, MTB_FLAG_SET);
   if (rc) return rc;
   patch_split_kernel<PATCH_BWD><<<dim3((ipix + 63) / 64, Kp / 64, g.n), 256, 0, h->stream>>>(
-      dy, g, ipix, K, Kp, static_cast<long long>(g.c_out) * g.oh * g.ow, sp);
+      dy, g, ipix, K, Kp, static_cast<long long>(g.c_out) * g.oh * g.ow, sp, nf_word);
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_in, 0, 1}, ob{sp, ipix, g.n > 1, g.n};
-  return run_split_gemm(h, oa, ob, Kp, g.n, g.c_in, ipix, dx, ipix, static_cast<long long>(g.c_in) * ipix,
-                        nullptr, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff);
+  rc = run_split_gemm(h, oa, ob, Kp, g.n, g.c_in, ipix, dx, ipix, static_cast<long long>(g.c_in) * ipix,
+                      nullptr, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff);
+  return rc ? rc : redo();
 }
 
 int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
@@ -567,7 +705,19 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
     return MTB200_OK;
   }
   if (!dy || !x) return fail(MTB200_ERR_INVALID, "null input pointer");
-  if (g.sh == 1 && g.sw == 1 && ((f32_mode >> 8) & 0xff) != 0xff) return implicit_wgrad(h, g, dy, x, dw, f32_mode);
+  uint32_t* nf_word = nullptr;
+  rc = call_flag_begin(h, &nf_word);
+  if (rc) return rc;
+  auto redo = [&]() -> int32_t {
+    conv_direct_wgrad_kernel<<<int(std::min<size_t>(out_elems, size_t(16) * h->sm_count)), 256, 0, h->stream>>>(
+        g, dy, x, dw, nf_word);
+    MTB_CUDA(cudaGetLastError());
+    return MTB200_OK;
+  };
+  if (g.sh == 1 && g.sw == 1 && ((f32_mode >> 8) & 0xff) != 0xff) {
+    rc = implicit_wgrad(h, g, dy, x, dw, f32_mode, nf_word);
+    return rc ? rc : redo();
+  }
   // split K: enough chunks to occupy the machine, each a whole number of 64-wide K blocks
   const long long kblocks = (Ktot + 63) / 64;
   const int tiles = ((g.c_out + 127) / 128) * ((rows_b + 255) / 256);
@@ -586,8 +736,8 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
   __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_a);
   float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + bytes_a + bytes_b);
   const int gsz = h->sm_count * 16;
-  wgrad_split_kernel<WG_DY><<<gsz, 256, 0, h->stream>>>(dy, g, g.c_out, Ktot, Kp, sa);
-  wgrad_split_kernel<WG_PATCH><<<gsz, 256, 0, h->stream>>>(x, g, rows_b, Ktot, Kp, sb);
+  wgrad_split_kernel<WG_DY><<<gsz, 256, 0, h->stream>>>(dy, g, g.c_out, Ktot, Kp, sa, nf_word);
+  wgrad_split_kernel<WG_PATCH><<<gsz, 256, 0, h->stream>>>(x, g, rows_b, Ktot, Kp, sb, nf_word);
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sa, g.c_out, 0, 1}, ob{sb, rows_b, 0, 1};
   float* gemm_out = chunks == 1 ? dw : part;
@@ -599,7 +749,7 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
     colsum_stage2_kernel<float><<<int((out_elems + 255) / 256), 256, 0, h->stream>>>(part, chunks, int(out_elems), dw);
     MTB_CUDA(cudaGetLastError());
   }
-  return MTB200_OK;
+  return redo();
 }
 
 int32_t mtb200_conv2d_bwd_bias(mtb200_handle h, int64_t n, int64_t c_out, int64_t out_h, int64_t out_w,

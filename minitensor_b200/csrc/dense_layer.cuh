@@ -47,7 +47,7 @@ inline DenseSaved dense_saved_layout(long long M, long long in, long long out) {
   return s;
 }
 
-// flag[0] = 1 when a split kernel of the call with this epoch met an Inf or NaN operand.
+// flag[0] = 1 when a split kernel of this call met an Inf or NaN operand (the call's flag word holds `epoch`).
 static __global__ void save_nonfinite_flag_kernel(const uint32_t* __restrict__ nf_word, uint32_t epoch,
                                                   uint32_t* __restrict__ flag) {
   flag[0] = (*nf_word == epoch) ? 1u : 0u;
@@ -255,7 +255,7 @@ inline bool dense_fused_shapes(long long M, long long in, long long out) {
 // Gated IEEE redo of C = op(A) op(B) for operands that held Inf / NaN (returns at once otherwise).
 inline int32_t launch_nonfinite_redo(mtb200_ctx* h, bool trans_a, bool trans_b, int M, int N, int K, const float* A,
                                      const float* B, float* C, const float* bias, int epilogue, const float* aux,
-                                     uint32_t epoch) {
+                                     const uint32_t* nf_word) {
   StridedGemmArgs s;
   s.M = M; s.N = N; s.K = K; s.batch = 1;
   s.A = A; s.B = B; s.C = C;
@@ -263,7 +263,7 @@ inline int32_t launch_nonfinite_redo(mtb200_ctx* h, bool trans_a, bool trans_b, 
   s.b_sk = trans_b ? 1 : N;  s.b_sj = trans_b ? K : 1;  s.b_sb = 0;
   s.ldc = N; s.c_sb = 0;
   s.bias = bias; s.aux = aux; s.epilogue = epilogue;
-  s.gate = h->status + 2; s.gate_value = epoch;
+  s.gate = nf_word; s.gate_value = MTB_FLAG_SET;
   const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
   gemm_simt_kernel<float, 8, 8><<<dim3(unsigned(tiles), 1), 256, 0, h->stream>>>(s);
   MTB_CUDA(cudaGetLastError());
@@ -280,9 +280,11 @@ inline int32_t dense_forward_f32(mtb200_ctx* h, int M, int in, int out, const fl
   __half* wp = reinterpret_cast<__half*>(sv + L.off_wp);
   int* we = reinterpret_cast<int*>(sv + L.off_we);
   uint32_t* flag = reinterpret_cast<uint32_t*>(sv + L.off_flag);
-  uint32_t* nf_word = h->status + 2;
-  const uint32_t epoch = ++h->epoch;
-  int32_t rc = launch_split16(h, x, true, M, in, 1, 0, xp, xe, nf_word, epoch);
+  uint32_t* nf_word = nullptr;
+  int32_t rc = call_flag_begin(h, &nf_word);
+  if (rc) return rc;
+  const uint32_t epoch = MTB_FLAG_SET;
+  rc = launch_split16(h, x, true, M, in, 1, 0, xp, xe, nf_word, epoch);
   if (rc) return rc;
   rc = launch_split16(h, W, true, out, in, 1, 0, wp, we, nf_word, epoch);
   if (rc) return rc;
@@ -291,7 +293,7 @@ inline int32_t dense_forward_f32(mtb200_ctx* h, int M, int in, int out, const fl
   SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(wp), out, 0, 1, 0, L.inp, 2, we};
   rc = run_split_gemm(h, oa, ob, L.inp, 1, M, out, y, out, 0, bias, epilogue, aux, 23, 5, 0, 0, 0, in);
   if (rc) return rc;
-  return launch_nonfinite_redo(h, false, true, M, out, in, x, W, y, bias, epilogue, aux, epoch);
+  return launch_nonfinite_redo(h, false, true, M, out, in, x, W, y, bias, epilogue, aux, nf_word);
 }
 
 // Layout of the optional block that carries dY's weight-gradient operand from one backward call to a later one
@@ -363,8 +365,10 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
   float* part = db ? reinterpret_cast<float*>(q + bytes_er + bytes_ec + bytes_zero) : nullptr;
   uint32_t* dy_flag = dy_block ? reinterpret_cast<uint32_t*>(dyb + D.off_flag) : nullptr;
 
-  uint32_t* nf_word = h->status + 2;
-  const uint32_t epoch = ++h->epoch;
+  uint32_t* nf_word = nullptr;
+  rc = call_flag_begin(h, &nf_word);
+  if (rc) return rc;
+  const uint32_t epoch = MTB_FLAG_SET;
   MTB_CUDA(cudaMemsetAsync(zero, 0, bytes_zero, h->stream));
   if (have_cols) {
     // nothing of dY is read: only the Inf / NaN state of the earlier calls is carried over
@@ -406,7 +410,7 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
     SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(xp), M, 0, 1, 1, L.inp, 2, zero};
     rc = run_split_gemm(h, oa, ob, padded_k(M), 1, out, in, dW, in, 0, nullptr, EPI_NONE, nullptr, 23, 5, 0, 0, 0, M);
     if (rc) return rc;
-    rc = launch_nonfinite_redo(h, true, false, out, in, M, dY, x, dW, nullptr, EPI_NONE, nullptr, epoch);
+    rc = launch_nonfinite_redo(h, true, false, out, in, M, dY, x, dW, nullptr, EPI_NONE, nullptr, nf_word);
     if (rc) return rc;
   }
   // dX [M][in] = dY W: A = row-scaled dY planes (K-major), B = the forward pass's W planes (MN-major here).
@@ -415,7 +419,7 @@ inline int32_t dense_backward_f32(mtb200_ctx* h, int M, int in, int out, const f
     SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(wp), out, 0, 1, 1, L.inp, 2, zero};
     rc = run_split_gemm(h, oa, ob, outp, 1, M, in, dX, in, 0, nullptr, epilogue, aux, 23, 5, 0, 0, 0, out);
     if (rc) return rc;
-    rc = launch_nonfinite_redo(h, false, false, M, in, out, dY, W, dX, nullptr, epilogue, aux, epoch);
+    rc = launch_nonfinite_redo(h, false, false, M, in, out, dY, W, dX, nullptr, epilogue, aux, nf_word);
     if (rc) return rc;
   }
   return MTB200_OK;

@@ -291,8 +291,10 @@ inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int
   __half* pb = reinterpret_cast<__half*>(base + bytes_a);
   int* ea = reinterpret_cast<int*>(base + bytes_a + bytes_b);
   int* eb = reinterpret_cast<int*>(base + bytes_a + bytes_b + bytes_ea);
-  uint32_t* nf_word = h->status + 2;
-  const uint32_t epoch = ++h->epoch;
+  uint32_t* nf_word = nullptr;
+  rc = call_flag_begin(h, &nf_word);
+  if (rc) return rc;
+  const uint32_t epoch = MTB_FLAG_SET;
   // Operands of up to 32 M elements each do not fill the memory system alone (a 4096^2 split runs at a third to
   // a half of the DRAM rate): B is then prepared on the side stream while A is prepared on the caller's.
   const bool side_by_side = h->side_stream && !h->profiling &&
@@ -378,8 +380,10 @@ inline int32_t gemm_f32_split(mtb200_ctx* h, bool trans_a, bool trans_b, int bat
   if (rc) return rc;
   __nv_bfloat16* sa = static_cast<__nv_bfloat16*>(ws);
   __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + bytes_a);
-  uint32_t* nf_word = h->status + 2;
-  const uint32_t epoch = ++h->epoch;
+  uint32_t* nf_word = nullptr;
+  rc = call_flag_begin(h, &nf_word);
+  if (rc) return rc;
+  const uint32_t epoch = MTB_FLAG_SET;
   SplitOperand oa{sa, a_rows, batch_a > 1, batch_a, 0, a_cols_p}, ob{sb, b_rows, batch_b > 1, batch_b, 0, b_cols_p};
   if (straight) {
     oa.mn_major = trans_a ? 1 : 0;

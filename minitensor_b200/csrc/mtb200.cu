@@ -110,8 +110,10 @@ static int32_t gemm_i32_limb(mtb200_ctx* h, bool trans_a, bool trans_b, int batc
   if (rc) return rc;
   uint8_t* pa = static_cast<uint8_t*>(ws);
   uint8_t* pb = pa + bytes_a;
-  uint32_t* wide_word = h->status + 3;
-  const uint32_t epoch = ++h->epoch;
+  uint32_t* wide_word = nullptr;
+  rc = call_flag_begin(h, &wide_word);
+  if (rc) return rc;
+  const uint32_t epoch = MTB_FLAG_SET;
   {
     ProfScope prof(h, PROF_SPLIT, 8.0 * (double(batch_a) * M + double(batch_b) * N) * K);
     // op(A) is [M][K]: source [M][K] or, transposed, [K][M];  op(B)^T is [N][K]: source [K][N] needs the turn
@@ -234,8 +236,8 @@ int32_t mtb200_create(int32_t device_ordinal, mtb200_handle* out) {
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
-  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h->status), 4 * sizeof(uint32_t));
-  if (e == cudaSuccess) e = cudaMemset(h->status, 0, 4 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h->status), (4 + MTB_FLAG_SLOTS) * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(h->status, 0, (4 + MTB_FLAG_SLOTS) * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&h->status_host), 2 * sizeof(uint32_t));
   if (e != cudaSuccess) {
     if (h->status) cudaFree(h->status);

@@ -37,9 +37,12 @@ inline int32_t fail(int32_t code, const char* fmt, ...) {
 }  // namespace mtb
 
 // Device status word layout: [0] expired-wait code of the GEMM kernels,
-// [1] bad-label flag of cross entropy, [2] epoch of the last f32 GEMM whose
-// operands held an Inf or NaN, [3] epoch of the last int32 GEMM with an operand
-// element outside the int8 range.
+// [1] bad-label flag of cross entropy, [2..3] unused, [4 .. 4 + MTB_FLAG_SLOTS) a ring of per-call
+// flag words.  A call that needs a data-dependent decision on the device (an f32 product whose
+// operands hold Inf / NaN, an int32 product with an operand element outside the int8 range) takes
+// the next slot, clears it on its stream, lets its preparation kernels set it to 1 and gates the
+// kernels that depend on it by (word != 0).  Clear, set and test are all stream-ordered work of the
+// one call, so a call captured into a CUDA graph decides afresh on every replay.
 struct mtb200_ctx {
   int device = 0;
   int sm_count = 0;
@@ -52,9 +55,9 @@ struct mtb200_ctx {
   float* tail_partial = nullptr;    // raw partial accumulators of split tail tiles (one 256 x 256 slot per SM pair)
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
-  uint32_t* status = nullptr;       // device, 4 words
+  uint32_t* status = nullptr;       // device, 4 + MTB_FLAG_SLOTS words
   uint32_t* status_host = nullptr;  // pinned, 2 words
-  uint32_t epoch = 0;               // f32 GEMM call counter (see status[2])
+  uint32_t epoch = 0;               // call counter: picks the flag slot of a call
   // optional per-launch timing (mtb200_profile_*): event pairs around kernels
   struct ProfRec { cudaEvent_t start, stop; double work; int cls; };
   bool profiling = false;
@@ -96,6 +99,18 @@ int32_t make_split_tmap(CUtensorMap* out, const void* base, uint64_t Kp, uint64_
                         uint64_t planes, uint32_t bk, uint32_t box_rows);
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Per-call flag word (see the status layout above): takes the next slot of the ring and clears it on
+// the handle's stream.  Kernels raise it with atomicMax(word, MTB_FLAG_SET); gated kernels run when
+// *word == MTB_FLAG_SET.
+constexpr int MTB_FLAG_SLOTS = 64;
+constexpr uint32_t MTB_FLAG_SET = 1u;
+inline int32_t call_flag_begin(mtb200_ctx* h, uint32_t** word) {
+  uint32_t* w = h->status + 4 + (h->epoch++ % MTB_FLAG_SLOTS);
+  MTB_CUDA(cudaMemsetAsync(w, 0, sizeof(uint32_t), h->stream));
+  *word = w;
+  return MTB200_OK;
+}
 
 // Kernel classes of the launch profiler.
 enum ProfClass { PROF_GEMM_UMMA = 0, PROF_SPLIT = 1, PROF_GEMM_F64 = 2, PROF_GEMM_INT = 3, PROF_CONV_GATHER = 4,

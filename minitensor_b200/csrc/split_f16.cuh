@@ -249,13 +249,15 @@ split16_cols_scaled_kernel(const float* __restrict__ src, long long ld, long lon
 }
 
 // amax_bits[b] = largest FINITE magnitude of batch entry b's `count` contiguous values, as raw bits.  Inf and NaN
-// are left out so that one of them does not cost the finite values of the same entry their scaling.  The vector
-// must be zeroed before the launch.  Grid (chunks, batch).
+// are left out so that one of them does not cost the finite values of the same entry their scaling; a block that
+// meets one raises *nf_word to nf_value (nullable).  The vector must be zeroed before the launch.  Grid (chunks, batch).
 static __global__ void __launch_bounds__(256)
-finite_absmax_kernel(const float* __restrict__ src, long long bstride, long long count, uint32_t* __restrict__ amax_bits) {
+finite_absmax_kernel(const float* __restrict__ src, long long bstride, long long count, uint32_t* __restrict__ amax_bits,
+                     uint32_t* __restrict__ nf_word = nullptr, uint32_t nf_value = 0) {
   __shared__ float red[8];
   const float* p = src + blockIdx.y * bstride;
   float amax = 0.0f;
+  bool nf = false;
   const long long step = static_cast<long long>(gridDim.x) * 256;
   const bool vec = ((reinterpret_cast<uintptr_t>(p) & 15) == 0);
   const long long n4 = vec ? (count >> 2) : 0;
@@ -263,13 +265,17 @@ finite_absmax_kernel(const float* __restrict__ src, long long bstride, long long
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n4; i += step) {
     const float4 u = __ldg(reinterpret_cast<const float4*>(p) + i);
     const float a = fabsf(u.x), b = fabsf(u.y), c = fabsf(u.z), d = fabsf(u.w);
-    amax = fmaxf(amax, fmaxf(fmaxf(is_nonfinite(a) ? 0.0f : a, is_nonfinite(b) ? 0.0f : b),
-                             fmaxf(is_nonfinite(c) ? 0.0f : c, is_nonfinite(d) ? 0.0f : d)));
+    const bool na = is_nonfinite(a), nb = is_nonfinite(b), nc = is_nonfinite(c), nd = is_nonfinite(d);
+    nf |= na | nb | nc | nd;
+    amax = fmaxf(amax, fmaxf(fmaxf(na ? 0.0f : a, nb ? 0.0f : b), fmaxf(nc ? 0.0f : c, nd ? 0.0f : d)));
   }
   for (long long i = n4 * 4 + blockIdx.x * 256LL + threadIdx.x; i < count; i += step) {
     const float a = fabsf(p[i]);
-    amax = fmaxf(amax, is_nonfinite(a) ? 0.0f : a);
+    const bool na = is_nonfinite(a);
+    nf |= na;
+    amax = fmaxf(amax, na ? 0.0f : a);
   }
+  if (nf && nf_word) atomicMax(nf_word, nf_value);
 #pragma unroll
   for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;

@@ -49,13 +49,68 @@ def xavier_uniform(shape, dtype="float32", rng=None) -> np.ndarray:
 
 
 def he_uniform(shape, dtype="float32", rng=None) -> np.ndarray:
-    """bound = sqrt(6 / fan_in) (``engine/src/nn/init.rs:471-491``)."""
+    """bound = sqrt(6 / fan_in) (``engine/src/nn/init.rs:419-430``)."""
     fan_in, _ = _fans(shape)
     return _uniform(shape, math.sqrt(6.0 / fan_in), dtype, rng)
 
 
+def _normal(shape, std: float, dtype: str, rng: Optional[np.random.Generator]) -> np.ndarray:
+    rng = rng or np.random.default_rng()
+    return (rng.standard_normal(size=shape) * std).astype(dtype)
+
+
+def he_normal(shape, dtype="float32", rng=None) -> np.ndarray:
+    """Kaiming-normal: mean 0, std = sqrt(2 / fan_in) (``engine/src/nn/init.rs:432-443``,
+    ``InitMethod::HeNormal`` at ``:37,68``) - the distribution of the large conv config's weights."""
+    fan_in, _ = _fans(shape)
+    return _normal(shape, math.sqrt(2.0 / fan_in), dtype, rng)
+
+
+def xavier_normal(shape, dtype="float32", rng=None) -> np.ndarray:
+    """std = sqrt(2 / (fan_in + fan_out)) (``engine/src/nn/init.rs:406-417``)."""
+    fan_in, fan_out = _fans(shape)
+    return _normal(shape, math.sqrt(2.0 / (fan_in + fan_out)), dtype, rng)
+
+
+def init_tensor(method, shape, dtype="float32", rng=None) -> np.ndarray:
+    """``InitMethod::init_tensor`` (``engine/src/nn/init.rs:14-74``).  ``method`` is a name - "zeros", "ones",
+    "xavier_uniform", "xavier_normal", "he_uniform", "he_normal", "lecun_uniform", "lecun_normal" - or a tuple
+    ("constant", v), ("uniform", a, b), ("normal", mean, std)."""
+    name, args = (method, ()) if isinstance(method, str) else (method[0], tuple(method[1:]))
+    fan_in, _ = _fans(shape)
+    if name == "zeros":
+        return np.zeros(shape, dtype=dtype)
+    if name == "ones":
+        return np.ones(shape, dtype=dtype)
+    if name == "constant":
+        return np.full(shape, args[0], dtype=dtype)
+    if name == "uniform":
+        return (rng or np.random.default_rng()).uniform(args[0], args[1], size=shape).astype(dtype)
+    if name == "normal":
+        return (args[0] + _normal(shape, args[1], "float64", rng)).astype(dtype)
+    if name == "xavier_uniform":
+        return xavier_uniform(shape, dtype, rng)
+    if name == "xavier_normal":
+        return xavier_normal(shape, dtype, rng)
+    if name == "he_uniform":
+        return he_uniform(shape, dtype, rng)
+    if name == "he_normal":
+        return he_normal(shape, dtype, rng)
+    if name == "lecun_uniform":
+        return _uniform(shape, math.sqrt(3.0 / fan_in), dtype, rng)
+    if name == "lecun_normal":
+        return _normal(shape, math.sqrt(1.0 / fan_in), dtype, rng)
+    raise ValueError(f"unknown initialisation method {method!r}")
+
+
 def _fans(shape) -> Tuple[int, int]:
-    # calculate_fan_in_fan_out: dims[1] (x receptive field) in, dims[0] (x receptive field) out
+    """calculate_fan_in_fan_out (``engine/src/nn/init.rs:471-491``): scalar (1, 1); vector (d0, d0); matrix
+    (d1, d0); beyond that dims[1] and dims[0] times the receptive field."""
+    shape = tuple(int(d) for d in shape)
+    if len(shape) == 0:
+        return 1, 1
+    if len(shape) == 1:
+        return shape[0], shape[0]
     recept = int(np.prod(shape[2:])) if len(shape) > 2 else 1
     return shape[1] * recept, shape[0] * recept
 
@@ -114,15 +169,17 @@ class Module:
 
 
 class DenseLayer(Module):
-    """Weight ``[out, in]`` Xavier-uniform, bias zeros (``dense_layer.rs:47-49``, ``init.rs:503-506``)."""
+    """Weight ``[out, in]`` Xavier-uniform, bias zeros (``dense_layer.rs:47-49``, ``init.rs:503-506``);
+    ``weight_init`` / ``bias_init`` choose other methods as ``DenseLayer::new_with_init`` does
+    (``dense_layer.rs:68-100``; see :func:`init_tensor` for the names)."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, dtype: str = "float32",
-                 rng: Optional[np.random.Generator] = None):
+                 rng: Optional[np.random.Generator] = None, weight_init="xavier_uniform", bias_init="zeros"):
         if in_features <= 0 or out_features <= 0:
             raise ValueError("in_features and out_features must be positive")
         self.in_features, self.out_features = in_features, out_features
-        self.weight = Tensor(xavier_uniform((out_features, in_features), dtype, rng), requires_grad=True)
-        self.bias = Tensor(np.zeros(out_features, dtype=dtype), requires_grad=True) if bias else None
+        self.weight = Tensor(init_tensor(weight_init, (out_features, in_features), dtype, rng), requires_grad=True)
+        self.bias = Tensor(init_tensor(bias_init, (out_features,), dtype, rng), requires_grad=True) if bias else None
 
     def forward(self, x: Tensor, _epilogue: int = EPI_NONE) -> Tensor:
         return dense_layer(x, self.weight, self.bias, _epilogue=_epilogue)
@@ -338,15 +395,18 @@ def conv2d(input: Tensor, weight: Tensor, bias: Optional[Tensor] = None, stride:
 
 
 class Conv2d(Module):
-    """He-uniform weight, zero bias (``engine/src/nn/conv.rs:60-74``)."""
+    """He-uniform weight, zero bias (``engine/src/nn/conv.rs:60-74``); ``weight_init`` picks another method of
+    :func:`init_tensor`, e.g. "he_normal" for the Kaiming-normal weights of the large conv config."""
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size: _Pair, stride: _Pair = 1,
-                 padding: _Pair = 0, bias: bool = True, rng: Optional[np.random.Generator] = None):
+                 padding: _Pair = 0, bias: bool = True, rng: Optional[np.random.Generator] = None,
+                 weight_init="he_uniform"):
         kh, kw = _pair(kernel_size, "kernel_size")
         if in_channels <= 0 or out_channels <= 0 or kh <= 0 or kw <= 0:
             raise ValueError("channels and kernel size must be positive")
         self.stride, self.padding = _pair(stride, "stride"), _pair(padding, "padding")
-        self.weight = Tensor(he_uniform((out_channels, in_channels, kh, kw), "float32", rng), requires_grad=True)
+        self.weight = Tensor(init_tensor(weight_init, (out_channels, in_channels, kh, kw), "float32", rng),
+                             requires_grad=True)
         self.bias = Tensor(np.zeros(out_channels, dtype=np.float32), requires_grad=True) if bias else None
 
     def forward(self, x: Tensor) -> Tensor:

@@ -3,9 +3,25 @@ import numpy as np
 import pytest
 import torch
 
+import conv_f64
+
 pytestmark = pytest.mark.gpu
 
+# The path's tolerance: |device - reference loops (oracle)| <= F32_TOL * (norm product of the output's two operand
+# vectors), per output.  TIGHT is what the default arithmetic (22 bits kept per operand, f32 accumulation) has to
+# meet against float64 dot products: an order of magnitude below what a single 16-bit product would give.
 F32_TOL = 1e-4
+TIGHT = 8e-6
+
+
+def check_outputs(name, got, ref32, ref64, norms, extra=0.0):
+    """got vs the oracle at F32_TOL and vs float64 at TIGHT, both relative to each output's own norm product."""
+    floor = np.finfo(np.float32).tiny
+    e32 = np.abs(got.astype(np.float64) - ref32.astype(np.float64)) / (norms + extra + floor)
+    e64 = np.abs(got.astype(np.float64) - ref64) / (norms + extra + floor)
+    assert e32.max() <= F32_TOL, (name, "vs oracle", float(e32.max()))
+    assert e64.max() <= TIGHT, (name, "vs float64", float(e64.max()))
+    return float(e64.max())
 
 
 def test_known_answers_and_errors(be, golden):
@@ -55,18 +71,46 @@ def test_forward_backward_match_oracle(be, orc, rng, geom):
     y = nn.conv2d(x, wt, b, stride=stride, padding=padding)
     ref = orc.conv2d(xn, wn, bn, stride, padding)
     assert y.shape == ref.shape
-    # every output is a dot product of <= c*kh*kw terms: scale the tolerance by the operand norms
-    xnorm = np.sqrt(c * kh * kw) * np.abs(xn).max()
-    wnorm = np.linalg.norm(wn.reshape(co, -1), axis=1).max()
-    assert np.abs(y.numpy() - ref).max() <= F32_TOL * xnorm * wnorm
+    # the bias is one more term of every output's sum
+    check_outputs("y", y.numpy(), ref, conv_f64.forward(xn, wn, bn, stride, padding),
+                  conv_f64.forward_norms(xn, wn, stride, padding), extra=np.abs(bn)[None, :, None, None])
     go = rng.standard_normal(ref.shape).astype(np.float32)
     y.backward(mt.Tensor(go))
     gx, gw, gb = orc.conv2d_backward(xn, wn, go, stride, padding)
-    gnorm = np.abs(go).max()
-    assert np.abs(x.grad.numpy() - gx).max() <= F32_TOL * np.sqrt(co * kh * kw) * gnorm * np.abs(wn).max() * np.sqrt(co * kh * kw)
+    check_outputs("dx", x.grad.numpy(), gx, conv_f64.grad_input(go, wn, xn.shape, stride, padding),
+                  conv_f64.grad_input_norms(go, wn, xn.shape, stride, padding))
+    check_outputs("dw", wt.grad.numpy(), gw, conv_f64.grad_weight(go, xn, wn.shape, stride, padding),
+                  conv_f64.grad_weight_norms(go, xn, wn.shape, stride, padding))
+    # db[o] = <dy[:,o], ones>
     k_w = n * ref.shape[2] * ref.shape[3]
-    assert np.abs(wt.grad.numpy() - gw).max() <= F32_TOL * k_w * gnorm * np.abs(xn).max()
-    assert np.abs(b.grad.numpy() - gb).max() <= 1e-5 * k_w * gnorm
+    gbn = np.sqrt((go.astype(np.float64) ** 2).sum(axis=(0, 2, 3)) * k_w)
+    assert (np.abs(b.grad.numpy() - gb) <= F32_TOL * gbn).all()
+    assert (np.abs(b.grad.numpy() - go.astype(np.float64).sum(axis=(0, 2, 3))) <= TIGHT * gbn).all()
+
+
+def test_tolerance_tells_a_single_product_from_the_default(be, orc, rng):
+    """The bounds above are not vacuous: the same layer computed with ONE bf16 product per f32 product
+    (mode BF16X1, 8 bits kept) fails the float64 bound for y, dx and dw, and by a wide margin."""
+    n, c, h, w, co, k = 8, 64, 28, 28, 64, 3
+    xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wn = (rng.standard_normal((co, c, k, k)) * np.sqrt(2.0 / (c * k * k))).astype(np.float32)
+    go = rng.standard_normal((n, co, h, w)).astype(np.float32)
+    dev = lambda a: torch.from_numpy(a).to(be.device)
+    s1, p1 = (1, 1), (1, 1)
+    refs = (conv_f64.forward(xn, wn, None, s1, p1), conv_f64.grad_input(go, wn, xn.shape, s1, p1),
+            conv_f64.grad_weight(go, xn, wn.shape, s1, p1))
+    norms = (conv_f64.forward_norms(xn, wn, s1, p1), conv_f64.grad_input_norms(go, wn, xn.shape, s1, p1),
+             conv_f64.grad_weight_norms(go, xn, wn.shape, s1, p1))
+    for mode, passes in ((0, True), (1, False)):
+        outs = (be.conv2d_fwd(dev(xn), dev(wn), None, s1, p1, f32_mode=mode),
+                be.conv2d_bwd_data(dev(go), dev(wn), xn.shape, s1, p1, f32_mode=mode),
+                be.conv2d_bwd_weight(dev(go), dev(xn), wn.shape, s1, p1, f32_mode=mode))
+        be.sync()
+        for name, out, ref, nrm in zip(("y", "dx", "dw"), outs, refs, norms):
+            err = float((np.abs(out.cpu().numpy() - ref) / nrm).max())
+            assert (err <= TIGHT) == passes, (name, mode, err)
+            if not passes:
+                assert err >= 3 * TIGHT, (name, mode, err)
 
 
 def test_conv2d_layer_defaults(be):
@@ -103,6 +147,26 @@ def test_full_size_layer_properties(be):
     assert abs(lhs - float(w.double().mul(dw.double()).sum())) <= 1e-5 * abs(lhs) + 1.0
     ref_db = dy.double().sum(dim=(0, 2, 3))
     assert float((db.double() - ref_db).abs().max()) <= 1e-5 * float(dy.abs().double().sum(dim=(0, 2, 3)).max())
+    # element-wise at full size: 256 outputs each of y, dx and dw as float64 dot products on the host
+    # (576 terms for y and dx, 128*56*56 = 401,408 terms for dw), each within TIGHT of its own norm product
+    xh, wh, bh, dyh = x.cpu().numpy(), w.cpu().numpy(), b.cpu().numpy(), dy.cpu().numpy()
+    yh, dxh, dwh = y1.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy()
+    pick = np.random.default_rng(11)
+    worst = {"y": 0.0, "dx": 0.0, "dw": 0.0}
+    for _ in range(256):
+        n_, o_, c_ = pick.integers(128), pick.integers(64), pick.integers(64)
+        # image borders are where the zero fill matters: half of the samples sit on one
+        edge = pick.integers(2)
+        h_ = int(pick.choice([0, 55])) if edge else int(pick.integers(56))
+        w_ = int(pick.choice([0, 55])) if pick.integers(2) else int(pick.integers(56))
+        v, s = conv_f64.sample_forward(xh, wh, bh, (1, 1), n_, o_, h_, w_)
+        worst["y"] = max(worst["y"], abs(float(yh[n_, o_, h_, w_]) - v) / (s + abs(float(bh[o_]))))
+        v, s = conv_f64.sample_grad_input(dyh, wh, (1, 1), n_, c_, h_, w_)
+        worst["dx"] = max(worst["dx"], abs(float(dxh[n_, c_, h_, w_]) - v) / s)
+        i_, j_ = pick.integers(3), pick.integers(3)
+        v, s = conv_f64.sample_grad_weight(dyh, xh, (1, 1), o_, c_, i_, j_)
+        worst["dw"] = max(worst["dw"], abs(float(dwh[o_, c_, i_, j_]) - v) / s)
+    assert max(worst.values()) <= TIGHT, worst
 
 
 @pytest.mark.parametrize("geom", [g for g in GEOMS if g[7] == (1, 1)] + [(2, 5, 9, 300, 3, 3, 3, (1, 1), (1, 1)),
@@ -126,44 +190,80 @@ def test_both_lowerings_match_oracle(be, orc, rng, geom, lowering):
     dw = be.conv2d_bwd_weight(dev(go), dev(xn), wn.shape, stride, padding, f32_mode=mode)
     be.sync()
     gx, gw, _ = orc.conv2d_backward(xn, wn, go, stride, padding, need_b=False)
-    k_w = n * ref.shape[2] * ref.shape[3]
-    assert np.abs(dw.cpu().numpy() - gw).max() <= F32_TOL * k_w * np.abs(go).max() * np.abs(xn).max()
-    xnorm = np.sqrt(c * kh * kw) * np.abs(xn).max()
-    wnorm = np.linalg.norm(wn.reshape(co, -1), axis=1).max()
-    assert np.abs(y.cpu().numpy() - ref).max() <= F32_TOL * xnorm * wnorm
-    assert np.abs(dx.cpu().numpy() - gx).max() <= F32_TOL * (co * kh * kw) * np.abs(go).max() * np.abs(wn).max()
+    check_outputs("y", y.cpu().numpy(), ref, conv_f64.forward(xn, wn, bn, stride, padding),
+                  conv_f64.forward_norms(xn, wn, stride, padding), extra=np.abs(bn)[None, :, None, None])
+    check_outputs("dx", dx.cpu().numpy(), gx, conv_f64.grad_input(go, wn, xn.shape, stride, padding),
+                  conv_f64.grad_input_norms(go, wn, xn.shape, stride, padding))
+    check_outputs("dw", dw.cpu().numpy(), gw, conv_f64.grad_weight(go, xn, wn.shape, stride, padding),
+                  conv_f64.grad_weight_norms(go, xn, wn.shape, stride, padding))
 
 
 def test_implicit_conv_scales_every_image_on_its_own(be, orc, rng):
     """The default mode of the stride-1 kernels (two fp16 planes) scales each image by its own power of two:
-    images 40 orders of magnitude apart, an all-zero image and an image holding an Inf keep, per image, the
-    accuracy of the plain case, and the Inf stays inside the windows that touch it."""
-    n, c, h, w, co = 5, 6, 9, 11, 7
+    images 40 orders of magnitude apart and an all-zero image keep, per output, the accuracy of the plain case."""
+    n, c, h, w, co = 4, 6, 9, 11, 7
     xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
     xn[0] *= 1e-20
     xn[2] *= 1e20
     xn[3] = 0.0
-    xn[4, 2, 4, 5] = np.inf
     wn = (rng.standard_normal((co, c, 3, 3)) * np.sqrt(2.0 / (c * 9))).astype(np.float32)
     dev = lambda a: torch.from_numpy(a).to(be.device)
-    y = be.conv2d_fwd(dev(xn), dev(wn), None, (1, 1), (1, 1)).cpu().numpy()
-    wnorm = np.linalg.norm(wn.reshape(co, -1), axis=1).max()
-    for i in range(4):
-        ref = orc.conv2d(xn[i:i + 1], wn, None, (1, 1), (1, 1))[0]
-        assert np.abs(y[i] - ref).max() <= F32_TOL * np.sqrt(c * 9) * np.abs(xn[i]).max() * wnorm, i
+    s1, p1 = (1, 1), (1, 1)
+    y = be.conv2d_fwd(dev(xn), dev(wn), None, s1, p1).cpu().numpy()
+    check_outputs("y", y, orc.conv2d(xn, wn, None, s1, p1), conv_f64.forward(xn, wn, None, s1, p1),
+                  conv_f64.forward_norms(xn, wn, s1, p1))
     assert not y[3].any()
-    finite_part = xn[4:5].copy()
-    finite_part[0, 2, 4, 5] = 0.0
-    ref = orc.conv2d(finite_part, wn, None, (1, 1), (1, 1))[0]
-    touched = np.zeros((h, w), bool)
-    touched[3:6, 4:7] = True                       # outputs whose 3x3 window covers (4, 5)
-    assert not np.isfinite(y[4][:, touched]).any()
-    assert np.abs(y[4][:, ~touched] - ref[:, ~touched]).max() <= F32_TOL * np.sqrt(c * 9) * np.abs(finite_part).max() * wnorm
     # the data gradient runs on the same kernel with dy as the image operand
     go = rng.standard_normal((n, co, h, w)).astype(np.float32)
     go[1] *= 1e-25
     go[2] *= 1e15
-    dx = be.conv2d_bwd_data(dev(go), dev(wn), xn.shape, (1, 1), (1, 1)).cpu().numpy()
-    for i in range(n):
-        gx, _, _ = orc.conv2d_backward(np.zeros_like(xn[i:i + 1]), wn, go[i:i + 1], (1, 1), (1, 1), need_b=False)
-        assert np.abs(dx[i] - gx[0]).max() <= F32_TOL * (co * 9) * np.abs(go[i]).max() * np.abs(wn).max(), i
+    dx = be.conv2d_bwd_data(dev(go), dev(wn), xn.shape, s1, p1).cpu().numpy()
+    gx, _, _ = orc.conv2d_backward(np.zeros_like(xn), wn, go, s1, p1, need_b=False)
+    check_outputs("dx", dx, gx, conv_f64.grad_input(go, wn, xn.shape, s1, p1),
+                  conv_f64.grad_input_norms(go, wn, xn.shape, s1, p1))
+
+
+@pytest.mark.parametrize("stride", [(1, 1), (2, 2)])
+def test_nonfinite_operands_give_the_reference_results(be, orc, rng, stride):
+    """Inf and NaN in x, w or dy: the reference's direct loops give +-Inf where an Inf meets finite values and NaN
+    where it meets a zero, an Inf of the other sign or a NaN.  The split-plane kernels cannot (Inf times a zero
+    low-order plane is NaN), so a call whose operands held a non-finite value is recomputed on the CUDA cores in
+    the reference's own summation order: every output then equals the oracle's, non-finite ones included, and a
+    later call on finite data is the tensor-core result again."""
+    n, c, h, w, co = 3, 6, 10, 12, 7
+    p1 = (1, 1)
+    xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wn = (rng.standard_normal((co, c, 3, 3)) * np.sqrt(2.0 / (c * 9))).astype(np.float32)
+    xn[0, 2, 4, 5] = np.inf
+    xn[1, 0, 0, 0] = -np.inf
+    xn[1, 3, 7, 7] = np.nan
+    wn[2, 1, 1, 1] = 0.0            # Inf * 0 = NaN in the outputs of channel 2 whose centre tap sees an Inf
+    dev = lambda a: torch.from_numpy(a).to(be.device)
+    y = be.conv2d_fwd(dev(xn), dev(wn), None, stride, p1).cpu().numpy()
+    ref = orc.conv2d(xn, wn, None, stride, p1)
+    assert np.isinf(ref).any() and np.isnan(ref).any() and np.isfinite(ref).any()
+    np.testing.assert_array_equal(y, ref)          # NaN == NaN here; signs of the infinities included
+    go = rng.standard_normal(ref.shape).astype(np.float32)
+    go[2, 1, 1, 2] = np.inf
+    go[0, 0, 0, 0] = np.nan
+    xf = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wf = np.abs(wn) + 0.01
+    wf[3, 2, 0, 0] = -np.inf
+    gx, _, _ = orc.conv2d_backward(xf, wf, go, stride, p1, need_w=False, need_b=False)
+    dx = be.conv2d_bwd_data(dev(go), dev(wf), xn.shape, stride, p1).cpu().numpy()
+    assert np.isinf(gx).any() and np.isnan(gx).any()
+    np.testing.assert_array_equal(dx, gx)
+    _, gw, _ = orc.conv2d_backward(xn, wn, go, stride, p1, need_x=False, need_b=False)
+    dw = be.conv2d_bwd_weight(dev(go), dev(xn), wn.shape, stride, p1).cpu().numpy()
+    assert (~np.isfinite(gw)).any()
+    assert np.array_equal(np.isnan(dw), np.isnan(gw)) and np.array_equal(np.isposinf(dw), np.isposinf(gw))
+    assert np.array_equal(np.isneginf(dw), np.isneginf(gw))
+    fin = np.isfinite(gw)
+    nrm = conv_f64.grad_weight_norms(np.where(np.isfinite(go), go, 0), np.where(np.isfinite(xn), xn, 0), wn.shape, stride, p1)
+    assert (np.abs(dw[fin] - gw[fin]) <= F32_TOL * nrm[fin]).all()
+    # the flag is per call: finite operands afterwards take the tensor-core path and meet its bounds
+    xc = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wc = (rng.standard_normal((co, c, 3, 3)) * np.sqrt(2.0 / (c * 9))).astype(np.float32)
+    y2 = be.conv2d_fwd(dev(xc), dev(wc), None, stride, p1).cpu().numpy()
+    check_outputs("y after a non-finite call", y2, orc.conv2d(xc, wc, None, stride, p1),
+                  conv_f64.forward(xc, wc, None, stride, p1), conv_f64.forward_norms(xc, wc, stride, p1))

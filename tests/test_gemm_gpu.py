@@ -193,9 +193,26 @@ def test_bmm_f32(be, orc, rng):
     b = rng.standard_normal((5, 96, 80)).astype(np.float32)
     c = run_gemm(be, a, b)
     assert norm_scaled_error(c, orc.matmul(a, b), a, b) <= F32_TOL
-    a = rng.standard_normal((64, 128, 128)).astype(np.float32)   # reduced-size stand-in of bmm [64,512,512]
+    a = rng.standard_normal((64, 128, 128)).astype(np.float32)
     b = rng.standard_normal((64, 128, 128)).astype(np.float32)
     assert norm_scaled_error(run_gemm(be, a, b), orc.matmul(a, b), a, b) <= F32_TOL
+
+
+def test_bmm_f32_config_size(be, orc):
+    """bmm [64,512,512] x [64,512,512] at size: in EVERY batch entry, sampled rows against the oracle in the
+    reference's order (1e-4) and against the f64-accumulated oracle (4e-6), through the Tensor mirror's bmm."""
+    import minitensor_b200.tensor as mt
+    g = np.random.default_rng(7)
+    a = g.standard_normal((64, 512, 512)).astype(np.float32)
+    b = g.standard_normal((64, 512, 512)).astype(np.float32)
+    c = mt.Tensor(a).bmm(mt.Tensor(b)).numpy()
+    assert c.shape == (64, 512, 512)
+    pick = np.random.default_rng(8)
+    for i in range(64):
+        rows = np.sort(pick.choice(512, 6, replace=False))
+        ar = np.ascontiguousarray(a[i][rows])
+        assert norm_scaled_error(c[i][rows], orc.matmul(ar, b[i]), ar, b[i]) <= F32_TOL, i
+        assert norm_scaled_error(c[i][rows], orc.matmul_acc_wide(ar, b[i]), ar, b[i]) <= 4e-6, i
 
 
 def test_fused_epilogues_match_unfused_oracle(be, orc, rng):
@@ -304,7 +321,7 @@ def test_large_f32_sampled_rows_and_linearity(be, orc):
     assert float(((lhs - rhs).double().abs() / scale).max()) <= F32_TOL
 
 
-def test_large_int_modular_identity(be):
+def test_large_int_modular_identity(be, orc):
     """i32 4096^3, entries in [-8,8]: sum_j C[i,j] r[j] == sum_l A[i,l] (B r)[l], exact in wrapping arithmetic."""
     n = 4096
     g = torch.Generator(device="cpu").manual_seed(3)
@@ -317,6 +334,10 @@ def test_large_int_modular_identity(be):
     be.sync()
     assert torch.equal(lhs, rhs)
     assert int(c.abs().max()) <= 64 * n  # |sum| <= 8*8*K: no overflow at these magnitudes
+    # sampled rows, every column, against the reference's triple loop
+    rows = np.random.default_rng(4).choice(n, 12, replace=False)
+    np.testing.assert_array_equal(c[rows].cpu().numpy(),
+                                  orc.matmul(np.ascontiguousarray(a[rows].cpu().numpy()), b.cpu().numpy()))
 
 
 # ------------------------------------------------------------------ fp16 two-plane mode (the default for large outputs)
@@ -442,6 +463,23 @@ def test_largest_square_sizes_f32_f64_i32(be, orc):
     rows64 = rows[:6] % m
     ref = orc.matmul(np.ascontiguousarray(a64.numpy()[rows64]), b64.numpy())
     assert norm_scaled_error(c64[rows64].cpu().numpy(), ref, a64.numpy()[rows64], b64.numpy()) <= 1e-13
+
+
+def test_f64_8192_sampled_rows(be, orc):
+    """f64 8192^3, the largest f64 square of the sweep: sampled rows against the oracle in the reference's order
+    and against the extended-precision (long double) accumulation, both at the f64 tolerance."""
+    g = torch.Generator(device="cpu").manual_seed(29)
+    n = 8192
+    a = torch.randn(n, n, generator=g, dtype=torch.float64)
+    b = torch.randn(n, n, generator=g, dtype=torch.float64)
+    c = be.gemm(a.to(be.device), b.to(be.device))
+    be.sync()
+    rows = np.random.default_rng(9).choice(n, 6, replace=False)
+    an, bn = a.numpy(), b.numpy()
+    ar = np.ascontiguousarray(an[rows])
+    got = c[rows].cpu().numpy()
+    assert norm_scaled_error(got, orc.matmul(ar, bn), ar, bn) <= F64_TOL
+    assert norm_scaled_error(got, orc.matmul_acc_wide(ar, bn), ar, bn) <= 1e-13
 
 
 # ------------------------------------------------------------------ tail splitting (a short last round cut into K ranges)

@@ -31,6 +31,30 @@ def test_init_bounds_follow_reference():
     assert np.abs(w).max() <= math.sqrt(6.0 / 576)
 
 
+def test_normal_initialisers_follow_reference():
+    """he_normal: std sqrt(2 / fan_in) (engine/src/nn/init.rs:432-443), the large conv config's weights;
+    xavier_normal: std sqrt(2 / (fan_in + fan_out)); fans of vectors and scalars as calculate_fan_in_fan_out."""
+    rng = np.random.default_rng(1)
+    w = nn.he_normal((64, 64, 3, 3), rng=rng)
+    assert w.dtype == np.float32 and w.shape == (64, 64, 3, 3)
+    assert abs(float(w.std()) / math.sqrt(2.0 / 576) - 1.0) < 0.02 and abs(float(w.mean())) < 3e-3
+    w = nn.he_normal((512, 2048), rng=rng)
+    assert abs(float(w.std()) / math.sqrt(2.0 / 2048) - 1.0) < 0.01
+    w = nn.xavier_normal((300, 500), rng=rng)
+    assert abs(float(w.std()) / math.sqrt(2.0 / 800) - 1.0) < 0.02
+    assert nn._fans(()) == (1, 1) and nn._fans((7,)) == (7, 7) and nn._fans((3, 5)) == (5, 3)
+    assert nn._fans((8, 4, 3, 3)) == (36, 72)
+    w = nn.init_tensor("lecun_uniform", (10, 48), rng=rng)
+    assert np.abs(w).max() <= math.sqrt(3.0 / 48)
+    assert (nn.init_tensor(("constant", 0.1), (4,)) == np.float32(0.1)).all()
+    u = nn.init_tensor(("uniform", -2.0, 3.0), (1000,), rng=rng)
+    assert u.min() >= -2.0 and u.max() <= 3.0 and u.max() > 2.5
+    g = nn.init_tensor(("normal", 5.0, 0.5), (20000,), rng=rng)
+    assert abs(float(g.mean()) - 5.0) < 0.02 and abs(float(g.std()) - 0.5) < 0.02
+    with pytest.raises(ValueError):
+        nn.init_tensor("orthogonal", (3, 3))
+
+
 def test_flat_layout_and_flops():
     dims = [8192, 4096, 4096, 4096, 1000]
     w_off, b_off, total = mlp.mlp_layout(dims)
