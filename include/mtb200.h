@@ -188,9 +188,10 @@ int32_t mtb200_colsum(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, cons
  * inside the library instead of the handle's growable workspace, so the call
  * never reaches cudaMalloc / cudaFree (nor their device-wide synchronisation)
  * and needs no handle: work is enqueued on `cuda_stream` of the CURRENT device.
- * Meant for callers that run where allocation is off limits: between the
- * begin and end of a stream capture, inside an application whose own pool
- * owns all device memory, or in a loop that cannot afford an allocator stall.
+ * Meant for callers that run where allocation is off limits: inside an
+ * application whose own pool owns all device memory (minitensor's memory
+ * manager is one), or in a loop that cannot afford the device-wide stall of
+ * cudaMalloc / cudaFree.
  * Limits and rules:
  *  - N * sizeof(element) must not exceed MTB200_COLSUM_NOALLOC_SCRATCH_BYTES
  *    (1,048,576 f32 or 524,288 f64 columns); wider inputs are rejected with
@@ -360,6 +361,48 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
                                  const float* dy, const float* x, float* dw, int32_t f32_mode);
 int32_t mtb200_conv2d_bwd_bias(mtb200_handle h, int64_t n, int64_t c_out, int64_t out_h,
                                int64_t out_w, const float* dy, float* db);
+
+/* ---- gradient exchange of data-parallel training: all-reduce (sum) of f32 buffers over NCCL.
+ * The reference has no distributed code.  The step this exchange is inserted into is its
+ * single-process training loop (backward engine/src/autograd/graph.rs:222-282, then
+ * Adam::step engine/src/optim/adam.rs:483-514): every rank runs that step on its own rows of the
+ * batch, the parameter gradients are summed over the ranks between backward and the optimizer, and
+ * the optimizer applies 1 / world_size (grad_scale of mtb200_adam_step), so all replicas stay equal.
+ * NCCL is looked up at run time (the copy already loaded into the process, else libnccl.so.2 on the
+ * loader path, else the file named by the environment variable MTB200_NCCL_LIB); without it these
+ * calls return MTB200_ERR_UNSUPPORTED and everything else still works.
+ *
+ * Two ways to form the communicator:
+ *  - one process per GPU: rank 0 calls mtb200_comm_unique_id and hands the MTB200_COMM_ID_BYTES bytes to
+ *    every rank (any channel: a file, a socket, MPI); each rank then calls mtb200_comm_init_rank, which
+ *    blocks until all world_size ranks have called it;
+ *  - one process driving ndev GPUs: mtb200_comm_init(ndev, devs); rank i is devs[i], and the
+ *    per-rank calls of one exchange are bracketed by mtb200_comm_group_begin / _end.
+ * mtb200_allreduce_sum_f32 enqueues, on the stream set for `rank` (mtb200_comm_set_stream; default: the
+ * CUDA default stream), buf[i] = scale * sum over ranks of buf[i] for i < n, in place.  Every rank must
+ * issue the same sequence of exchanges with the same n.  scale == 1 skips the multiply.  Asynchronous:
+ * ordered after earlier work on that stream; synchronise the stream (or order another stream after it)
+ * before reading buf. */
+typedef struct mtb200_comm_s* mtb200_comm;
+#define MTB200_COMM_ID_BYTES 128
+int32_t mtb200_comm_unique_id(void* id_out);
+int32_t mtb200_comm_init_rank(int32_t world_size, int32_t rank, const void* id, int32_t device_ordinal,
+                              mtb200_comm* out);
+int32_t mtb200_comm_init(int32_t ndev, const int32_t* devs, mtb200_comm* out);
+int32_t mtb200_comm_set_stream(mtb200_comm c, int32_t rank, void* cuda_stream);
+int32_t mtb200_comm_group_begin(mtb200_comm c);
+int32_t mtb200_comm_group_end(mtb200_comm c);
+int32_t mtb200_allreduce_sum_f32(mtb200_comm c, int32_t rank, float* buf, size_t n, float scale);
+int32_t mtb200_comm_destroy(mtb200_comm c);
+
+/* ---- self-test of the bounded waits.  (No counterpart in the reference.)
+ * Every wait inside the tensor-core kernels (on a shared-memory barrier that a TMA load or an MMA
+ * completion signals) gives up after a time limit, records a code in the handle's status word and lets
+ * the kernel wind down; mtb200_sync then returns MTB200_ERR_DEVICE_WAIT once and clears the word.  This
+ * call exercises exactly that path without any fault: it launches one small block that waits, with a
+ * limit of `limit_us` microseconds (1 .. 100000), on a barrier nothing ever signals, and records the
+ * expiry the way the GEMM kernels do.  The context stays usable. */
+int32_t mtb200_selftest_wait_expiry(mtb200_handle h, int32_t limit_us);
 
 #ifdef __cplusplus
 }

@@ -68,6 +68,15 @@ SIGNATURES = {
     "mtb200_conv2d_bwd_data": (_i32, [_vp] + [_i64] * 11 + [_vp, _vp, _vp, _i32]),
     "mtb200_conv2d_bwd_weight": (_i32, [_vp] + [_i64] * 11 + [_vp, _vp, _vp, _i32]),
     "mtb200_conv2d_bwd_bias": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "mtb200_comm_unique_id": (_i32, [_vp]),
+    "mtb200_comm_init_rank": (_i32, [_i32, _i32, _vp, _i32, C.POINTER(_vp)]),
+    "mtb200_comm_init": (_i32, [_i32, C.POINTER(_i32), C.POINTER(_vp)]),
+    "mtb200_comm_set_stream": (_i32, [_vp, _i32, _vp]),
+    "mtb200_comm_group_begin": (_i32, [_vp]),
+    "mtb200_comm_group_end": (_i32, [_vp]),
+    "mtb200_allreduce_sum_f32": (_i32, [_vp, _i32, _vp, C.c_size_t, _f32]),
+    "mtb200_comm_destroy": (_i32, [_vp]),
+    "mtb200_selftest_wait_expiry": (_i32, [_vp, _i32]),
 }
 
 _lib = None

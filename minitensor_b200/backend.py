@@ -30,9 +30,25 @@ def dtype_code(t: torch.Tensor) -> int:
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    """Device address of a buffer handed to the C ABI.  The library reads raw dense row-major memory, so a strided
+    view (a transpose, a channels_last tensor) or a host tensor would be read as something else: refuse it here
+    rather than copy, so that training buffers keep their aliasing."""
     if t is None or t.numel() == 0:
         return None
+    if not t.is_cuda:
+        raise ValueError("mtb200 operators take CUDA tensors")
+    if not t.is_contiguous():
+        raise ValueError("mtb200 operators take contiguous (dense row-major) tensors")
     return t.data_ptr()
+
+
+def _same_dtype(what: str, first: torch.Tensor, *rest: Optional[torch.Tensor], want=None) -> None:
+    """Every buffer of one call must have the element type the kernel is about to read it as."""
+    if want is not None and first.dtype != want:
+        raise TypeError(f"{what}: expected dtype {want}, got {first.dtype}")
+    for t in rest:
+        if t is not None and t.dtype != first.dtype:
+            raise TypeError(f"{what}: dtype mismatch ({first.dtype} vs {t.dtype})")
 
 
 class Backend:
@@ -154,6 +170,7 @@ class Backend:
         fout = w.shape[0]
         if w.shape[1] != fin or x.dtype != w.dtype:
             raise ValueError(f"shape/dtype mismatch: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}")
+        _same_dtype("dense_forward", x, w, bias, out)
         if out is None:
             out = torch.empty(rows, fout, dtype=x.dtype, device=x.device)
         self._bind_stream()
@@ -174,6 +191,7 @@ class Backend:
         computes ``dw`` from it without reading ``dy`` again."""
         rows, fin = x.shape
         fout = w.shape[0]
+        _same_dtype("dense_backward", x, w, dy, dx, dx_aux, dw, db)
         if tuple(dy.shape) != (rows, fout):
             raise ValueError(f"dy must be [{rows}, {fout}], got {tuple(dy.shape)}")
         if need_dx and dx is None:
@@ -195,6 +213,7 @@ class Backend:
     # ------------------------------------------------------------------ reductions / elementwise
     def colsum(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         m, n = x.shape
+        _same_dtype("colsum", x, out)
         if out is None:
             out = torch.empty(n, dtype=x.dtype, device=x.device)
         self._bind_stream()
@@ -205,6 +224,7 @@ class Backend:
     def bias_act(self, x: torch.Tensor, bias: Optional[torch.Tensor], act: int = 0) -> torch.Tensor:
         """``act(x + bias)`` with ``bias`` broadcast over the rows of the 2-D view of ``x``."""
         n = x.shape[-1]
+        _same_dtype("bias_act", x, bias)
         y = torch.empty_like(x)
         self._bind_stream()
         check(self.lib.mtb200_bias_act(self._h, dtype_code(x), x.numel() // max(n, 1), n, _ptr(x), _ptr(bias),
@@ -220,6 +240,7 @@ class Backend:
         return y
 
     def act_bwd(self, ref: torch.Tensor, dy: torch.Tensor, act: int) -> torch.Tensor:
+        _same_dtype("act_bwd", dy, ref)
         dx = torch.empty_like(dy)
         self._bind_stream()
         check(self.lib.mtb200_act_bwd(self._h, dtype_code(dy), act, dy.numel(), _ptr(ref), _ptr(dy), _ptr(dx)))
@@ -230,8 +251,11 @@ class Backend:
                       upstream: float = 1.0, want_grad: bool = True):
         """Returns ``(loss[1], dlogits or None)``; labels int32/int64 class indices."""
         bsz, ncls = logits.shape
+        _same_dtype("cross_entropy", logits, want=torch.float32)
         if labels.dtype not in (torch.int32, torch.int64):
             raise TypeError("Unsupported target dtype for classification loss")
+        if tuple(labels.shape) != (bsz,):
+            raise ValueError(f"shape mismatch: labels {tuple(labels.shape)} for logits {tuple(logits.shape)}")
         loss = torch.empty(1, dtype=torch.float32, device=logits.device)
         dl = torch.empty_like(logits) if want_grad else None
         self._bind_stream()
@@ -245,8 +269,11 @@ class Backend:
                            mean: bool = True, upstream: float = 1.0):
         """Same as :meth:`cross_entropy` with the gradient written into ``dlogits``."""
         bsz, ncls = logits.shape
-        if tuple(dlogits.shape) != (bsz, ncls) or dlogits.dtype != torch.float32:
-            raise ValueError("bad gradient buffer")
+        _same_dtype("cross_entropy", logits, want=torch.float32)
+        if labels.dtype not in (torch.int32, torch.int64):
+            raise TypeError("Unsupported target dtype for classification loss")
+        if tuple(dlogits.shape) != (bsz, ncls) or dlogits.dtype != torch.float32 or tuple(labels.shape) != (bsz,):
+            raise ValueError("bad gradient buffer or label shape")
         loss = torch.empty(1, dtype=torch.float32, device=logits.device)
         self._bind_stream()
         check(self.lib.mtb200_cross_entropy(self._h, bsz, ncls, _ptr(logits), _ptr(labels),
@@ -258,6 +285,9 @@ class Backend:
     def adam_step(self, p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *,
                   lr: float, beta1: float, beta2: float, eps: float, weight_decay: float = 0.0,
                   decoupled: bool = False, step: int = 1, grad_scale: float = 1.0) -> None:
+        _same_dtype("adam_step", p, g, m, v, want=torch.float32)
+        if not (p.numel() == g.numel() == m.numel() == v.numel()):
+            raise ValueError("adam_step: parameter, gradient and moment buffers differ in length")
         self._bind_stream()
         check(self.lib.mtb200_adam_step(self._h, p.numel(), _ptr(p), _ptr(g), _ptr(m), _ptr(v), lr, beta1,
                                         beta2, eps, weight_decay, int(decoupled), step, grad_scale))
@@ -270,6 +300,7 @@ class Backend:
         ``[B, C]`` (float32); ``reduction`` is "sum", "mean" or "none".  Returns ``(loss, dlogits or None)``,
         the loss a 1-element tensor or ``[B]`` for "none"."""
         bsz, ncls = logits.shape
+        _same_dtype("cross_entropy", logits, upstream_rows, want=torch.float32)
         red = {"sum": 0, "mean": 1, "none": 2}.get(reduction)
         if red is None:
             raise ValueError(f"Invalid reduction mode: {reduction}. Must be 'mean', 'sum', or 'none'")
@@ -292,6 +323,9 @@ class Backend:
     def sgd_step(self, p: torch.Tensor, g: torch.Tensor, v: Optional[torch.Tensor] = None, *, lr: float,
                  momentum: float = 0.0, dampening: float = 0.0, weight_decay: float = 0.0,
                  nesterov: bool = False) -> None:
+        _same_dtype("sgd_step", p, g, v)
+        if p.numel() != g.numel() or (v is not None and v.numel() != p.numel()):
+            raise ValueError("sgd_step: buffers differ in length")
         self._bind_stream()
         check(self.lib.mtb200_sgd_step(self._h, dtype_code(p), p.numel(), _ptr(p), _ptr(g), _ptr(v), lr, momentum,
                                        dampening, weight_decay, int(nesterov)))
@@ -300,6 +334,9 @@ class Backend:
     def rmsprop_step(self, p: torch.Tensor, g: torch.Tensor, sq: torch.Tensor, mb: Optional[torch.Tensor] = None,
                      ga: Optional[torch.Tensor] = None, *, lr: float, alpha: float = 0.99, eps: float = 1e-8,
                      weight_decay: float = 0.0, momentum: float = 0.0) -> None:
+        _same_dtype("rmsprop_step", p, g, sq, mb, ga)
+        if any(t is not None and t.numel() != p.numel() for t in (g, sq, mb, ga)):
+            raise ValueError("rmsprop_step: buffers differ in length")
         self._bind_stream()
         check(self.lib.mtb200_rmsprop_step(self._h, dtype_code(p), p.numel(), _ptr(p), _ptr(g), _ptr(sq), _ptr(mb),
                                            _ptr(ga), lr, alpha, eps, weight_decay, momentum))
@@ -337,6 +374,7 @@ class Backend:
         """Adam with the step count in the one-element int64 device tensor ``counter`` (graph-replayable)."""
         if counter.dtype != torch.int64 or counter.numel() != 1:
             raise ValueError("counter must be a one-element int64 device tensor")
+        _same_dtype("adam_step_counted", p, g, m, v, want=torch.float32)
         self._bind_stream()
         check(self.lib.mtb200_adam_step_counted(self._h, p.numel(), _ptr(p), _ptr(g), _ptr(m), _ptr(v), lr, beta1,
                                                 beta2, eps, weight_decay, int(decoupled), _ptr(counter), int(advance),
@@ -357,6 +395,7 @@ class Backend:
                        training: bool = True, momentum: float = 0.1, eps: float = 1e-5):
         """Returns ``(y, save_mean, save_invstd, used_batch_stats)``; running estimates are updated in place."""
         n, c, sp = self._ncs(x)
+        _same_dtype("batch_norm", x, weight, bias, running_mean, running_var)
         y = torch.empty_like(x)
         mean = torch.empty(c, dtype=x.dtype, device=x.device)
         invstd = torch.empty(c, dtype=x.dtype, device=x.device)
@@ -371,6 +410,9 @@ class Backend:
     def batch_norm_bwd(self, x, dy, weight, mean, invstd, *, batch_stats: bool = True, need_dx: bool = True,
                        need_dw: bool = True, need_db: bool = True):
         n, c, sp = self._ncs(x)
+        _same_dtype("batch_norm_backward", x, dy, weight, mean, invstd)
+        if dy.shape != x.shape:
+            raise ValueError("batch_norm_backward: dy and x differ in shape")
         dx = torch.empty_like(x) if need_dx else None
         dw = torch.empty(c, dtype=x.dtype, device=x.device) if need_dw else None
         db = torch.empty(c, dtype=x.dtype, device=x.device) if need_db else None
@@ -397,6 +439,7 @@ class Backend:
         return y
 
     def mask_mul(self, x: torch.Tensor, mask: torch.Tensor, inner: int = 1) -> torch.Tensor:
+        _same_dtype("mask_mul", x, mask)
         y = torch.empty_like(x)
         self._bind_stream()
         check(self.lib.mtb200_mask_mul(self._h, dtype_code(x), x.numel(), inner, _ptr(x), _ptr(mask), _ptr(y)))
@@ -413,6 +456,7 @@ class Backend:
     def conv2d_fwd(self, x, w, bias, stride, padding, f32_mode: int = 0):
         n, c, h, wd = x.shape
         co, ci, kh, kw = w.shape
+        _same_dtype("conv2d", x, w, bias, want=torch.float32)
         oh = (h + 2 * padding[0] - kh) // stride[0] + 1 if stride[0] > 0 else 0
         ow = (wd + 2 * padding[1] - kw) // stride[1] + 1 if stride[1] > 0 else 0
         y = torch.empty((n, co, max(oh, 0), max(ow, 0)), dtype=torch.float32, device=x.device)
@@ -423,6 +467,7 @@ class Backend:
         return y
 
     def conv2d_bwd_data(self, dy, w, xshape, stride, padding, f32_mode: int = 0):
+        _same_dtype("conv2d_bwd_data", dy, w, want=torch.float32)
         dx = torch.empty(tuple(xshape), dtype=torch.float32, device=dy.device)
         self._bind_stream()
         check(self.lib.mtb200_conv2d_bwd_data(self._h, *self._geom(xshape, w.shape, stride, padding),
@@ -431,6 +476,7 @@ class Backend:
         return dx
 
     def conv2d_bwd_weight(self, dy, x, wshape, stride, padding, f32_mode: int = 0):
+        _same_dtype("conv2d_bwd_weight", dy, x, want=torch.float32)
         dw = torch.empty(tuple(wshape), dtype=torch.float32, device=dy.device)
         self._bind_stream()
         check(self.lib.mtb200_conv2d_bwd_weight(self._h, *self._geom(x.shape, wshape, stride, padding),
@@ -440,6 +486,7 @@ class Backend:
 
     def conv2d_bwd_bias(self, dy):
         n, co, oh, ow = dy.shape
+        _same_dtype("conv2d_bwd_bias", dy, want=torch.float32)
         db = torch.empty(co, dtype=torch.float32, device=dy.device)
         self._bind_stream()
         check(self.lib.mtb200_conv2d_bwd_bias(self._h, n, co, oh, ow, _ptr(dy), _ptr(db)))

@@ -3,7 +3,7 @@
 // mtb200_colsum needs scratch memory for its per-band partial sums and takes it
 // from the handle's growable workspace, which may call cudaMalloc (and
 // synchronise the device) when a larger input arrives.  Some callers cannot
-// tolerate that: code running between the begin and end of a stream capture,
+// tolerate that:
 // a host application whose own pool owns every byte of device memory and
 // forbids foreign allocations (minitensor's memory manager is such a pool),
 // or a latency-critical loop that must never hit the implicit device-wide

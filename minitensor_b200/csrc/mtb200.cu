@@ -744,4 +744,37 @@ int32_t mtb200_adam_step_counted(mtb200_handle h, int64_t n, float* param, const
   return MTB200_OK;
 }
 
+// ------------------------------------------------------------------ bounded-wait self-test
+namespace mtb {
+// One thread waits on a barrier that nothing signals, with the same loop shape as mbar_wait but a caller-chosen
+// limit, and reports the expiry through the status word exactly as the GEMM kernels' roles do (role 15, site 1).
+__global__ void wait_expiry_selftest_kernel(uint32_t* __restrict__ status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = globaltimer_ns();
+    bool done = mbar_try_wait(b, 0);
+    uint32_t spins = 0;
+    while (!done) {
+      done = mbar_try_wait(b, 0);
+      if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > limit_ns) break;
+    }
+    if (!done) atomicMax(status, 0xF00u | 1u);
+  }
+}
+}  // namespace mtb
+
+int32_t mtb200_selftest_wait_expiry(mtb200_handle h, int32_t limit_us) {
+  MTB_CHECK_HANDLE(h);
+  if (limit_us < 1 || limit_us > 100000) return fail(MTB200_ERR_INVALID, "limit must be 1 .. 100000 microseconds");
+  mtb::wait_expiry_selftest_kernel<<<1, 32, 0, h->stream>>>(h->status, 1000ull * static_cast<unsigned long long>(limit_us));
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
 }  // extern "C"

@@ -372,7 +372,8 @@ static __global__ void bn_finalize_bwd_kernel(const double* __restrict__ partial
   if (dw) dw[c] = static_cast<T>(s1);
 }
 // Element pass of both directions, indexed without a division per element: a block owns one channel run -
-// S > 1: the S contiguous elements of one (n, c) pair (blockIdx.y = n * C + c, blockIdx.x chunks the run);
+// S > 1: the S contiguous elements of one (n, c) pair (blockIdx.x = n * C + c; blockIdx.y takes a span of
+//        rows_per_band elements of the run, a multiple of 256);
 // S = 1: 256 consecutive channels of a band of rows (blockIdx.x = channel block, blockIdx.y = row band).
 //   MODE 0 (forward):  y  = (x - mean) * invstd * w + b
 //   MODE 1 (backward): dx = w*invstd * (dy - k1 - xhat*k2) with k1 = db/n, k2 = dw/n (batch statistics) or
@@ -393,10 +394,10 @@ bn_element_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __
     count = hi - lo;
     stride = C;
   } else {
-    c = static_cast<int>(blockIdx.y % C);
-    first = static_cast<long long>(blockIdx.y) * S + blockIdx.x * 1024LL + threadIdx.x;
-    const long long end = min(S, (blockIdx.x + 1) * 1024LL);
-    const long long begin = blockIdx.x * 1024LL + threadIdx.x;
+    c = static_cast<int>(blockIdx.x % C);
+    const long long begin = blockIdx.y * rows_per_band + threadIdx.x;
+    const long long end = min(S, (blockIdx.y + 1LL) * rows_per_band);
+    first = static_cast<long long>(blockIdx.x) * S + begin;
     count = begin < end ? (end - begin + 255) / 256 : 0;
     stride = 256;
   }
@@ -434,9 +435,12 @@ static int32_t bn_element_launch(mtb200_ctx* h, const T* x, const T* dy, const T
     bn_element_kernel<T, MODE><<<dim3(unsigned(cb), unsigned((N + rpb - 1) / rpb)), 256, 0, h->stream>>>(
         x, dy, mean, invstd, w, b, sums, inv_count, batch_stats, N, int(C), S, rpb, out);
   } else {
-    if (N * C > 65535) return fail(MTB200_ERR_INVALID, "batch_norm: N * C exceeds 65535 for inputs with spatial dimensions");
-    bn_element_kernel<T, MODE><<<dim3(unsigned((S + 1023) / 1024), unsigned(N * C)), 256, 0, h->stream>>>(
-        x, dy, mean, invstd, w, b, sums, inv_count, batch_stats, N, int(C), S, 0, out);
+    // (n, c) pairs on grid.x (limit 2^31 - 1, checked by bn_check_dims before anything was launched); the run of S
+    // elements is cut into at most 65535 spans of a multiple of 256 elements, about 1024 each when S allows
+    const int64_t spans = std::min<int64_t>((S + 1023) / 1024, 65535);
+    const int64_t span = ((S + spans - 1) / spans + 255) / 256 * 256;
+    bn_element_kernel<T, MODE><<<dim3(unsigned(N * C), unsigned((S + span - 1) / span)), 256, 0, h->stream>>>(
+        x, dy, mean, invstd, w, b, sums, inv_count, batch_stats, N, int(C), S, span, out);
   }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
@@ -755,6 +759,9 @@ static int32_t batch_norm_bwd_t(mtb200_ctx* h, int64_t N, int64_t C, int64_t S, 
 static int32_t bn_check_dims(int64_t N, int64_t C, int64_t S) {
   if (N < 0 || C < 0 || S < 0) return fail(MTB200_ERR_INVALID, "negative dimension");
   if (C > INT32_MAX) return fail(MTB200_ERR_INVALID, "channel count exceeds the 32-bit limit of the device kernels");
+  // every geometry the kernels refuse is refused here, before a launch could have touched the running estimates
+  if (S > 1 && N > 0 && C > 0 && N > INT32_MAX / C)
+    return fail(MTB200_ERR_INVALID, "batch_norm: N * C exceeds 2^31 - 1 for inputs with spatial dimensions");
   return MTB200_OK;
 }
 

@@ -14,9 +14,10 @@ This is the reference's training loop of ``nn.Sequential`` + ``nn.CrossEntropyLo
             g   <- (g W_l) * (h_l > 0)           one GEMM, ReLU mask in the epilogue
   (no dX for the first layer: the input does not require grad, ``autograd/mod/core.rs:763``);
 * with ``world_size`` > 1 the batch is sharded by rows, each layer's slice of the
-  flat gradient is all-reduced (sum, NCCL) as soon as it is written, while the
-  remaining backward GEMMs run, and Adam applies ``1/world_size`` so every rank
-  takes the same step on the mean of the per-rank gradients.
+  flat gradient is all-reduced (sum; NCCL through the library's ``mtb200_allreduce_sum_f32``)
+  as soon as it is written, while the remaining backward GEMMs run, and Adam applies
+  ``1/world_size`` so every rank takes the same step on the mean of the per-rank gradients.
+  ``torch.distributed`` is used only to hand the NCCL id from rank 0 to the other ranks.
 """
 from __future__ import annotations
 
@@ -60,14 +61,16 @@ class MLPTrainer:
     def __init__(self, dims: Sequence[int], batch: int, *, lr: float = 1e-3, beta1: float = 0.9,
                  beta2: float = 0.999, eps: float = 1e-8, device: int = 0, world_size: int = 1,
                  seed: int = 0, f32_mode: int = 0, init_params: Optional[np.ndarray] = None,
-                 fused_dense: Optional[bool] = None, overlap_comm: Optional[bool] = None):
+                 fused_dense: Optional[bool] = None, overlap_comm: Optional[bool] = None, comm=None):
         """``batch`` is the number of rows THIS process handles per step.
 
         ``fused_dense`` (default: on for the default f32 mode) runs every layer through the dense-layer
         entry points, whose backward re-uses the operands the forward prepared; off, each product is a
         separate GEMM call as the reference's autograd issues them.  ``overlap_comm`` (default: on when
         ``world_size > 1``) selects the backward order that hides the gradient all-reduces and the Adam
-        update behind the products (see ``_backward_overlapped``); the results do not depend on it."""
+        update behind the products (see ``_backward_overlapped``); the results do not depend on it.
+        ``comm``: the :class:`minitensor_b200.comm.Communicator` of this rank; by default one is formed over
+        the initialised ``torch.distributed`` group when ``world_size > 1``."""
         if len(dims) < 2 or any(d <= 0 for d in dims) or batch <= 0:
             raise ValueError("dims needs at least two positive entries and batch must be positive")
         self.dims = [int(d) for d in dims]
@@ -125,6 +128,15 @@ class MLPTrainer:
         self._copy_done = [None, None]
         self._slot = 0
         self._side_stream = None
+        self._comm_stream = None
+        self.comm = comm
+        if self.world_size > 1:
+            if self.comm is None:
+                from .comm import Communicator
+                self.comm = Communicator.from_process_group(device)
+            if self.comm.world_size != self.world_size:
+                raise ValueError("communicator and trainer disagree on the world size")
+            self._comm_stream = torch.cuda.Stream(device=dev)
         self._dy_blocks = None
         self._counted = False
         self._step_dev = None
@@ -209,7 +221,6 @@ class MLPTrainer:
         if self.overlap_comm and self.fused_dense:
             self._backward_overlapped(x)
             return loss
-        handles = []
         for l in range(self.nl - 1, -1, -1):
             g = self.g[l]
             a_in = x if l == 0 else self.h[l - 1]
@@ -222,15 +233,14 @@ class MLPTrainer:
                 be.colsum(g, out=self.db[l])
                 be.gemm(g, a_in, trans_a=True, out=self.dW[l], f32_mode=self.f32_mode)      # dW = g^T a
             if self.world_size > 1:
-                import torch.distributed as dist
                 lo = self.w_off[l]
                 hi = self.b_off[l] + self.dims[l + 1]
-                handles.append(dist.all_reduce(self.grads[lo:hi], op=dist.ReduceOp.SUM, async_op=True))
+                self._all_reduce(lo, hi)
             if l > 0 and not self.fused_dense:
                 be.gemm(g, self.W[l], epilogue=EPI_RELU_BWD, aux=self.h[l - 1], out=self.g[l - 1],
                         f32_mode=self.f32_mode)                                            # (g W) * relu'
-        for hnd in handles:
-            hnd.wait()
+        if self.world_size > 1:
+            torch.cuda.current_stream(be.device).wait_stream(self._comm_stream)
         if self._counted:
             be.adam_step_counted(self.params, self.grads, self.m, self.v, lr=self.lr, beta1=self.beta1,
                                  beta2=self.beta2, eps=self.eps, counter=self._step_dev, advance=True)
@@ -245,7 +255,6 @@ class MLPTrainer:
         FIRST layer on - the first layer's is the largest, so its all-reduce starts earliest and the one
         left exposed at the end is the last layer's small one - and each layer's Adam update on a side
         stream as soon as its all-reduce has landed (HBM-bound, so it overlaps the tensor-bound products)."""
-        import torch.distributed as dist
         be = self.be
         if self._dy_blocks is None:
             self._dy_blocks = [None] * self.nl
@@ -274,19 +283,29 @@ class MLPTrainer:
             else:
                 be.dense_backward(a_in, self.W[l], self.g[l], self.saved[l], need_dx=False, dw=self.dW[l], db=self.db[l])
             lo, hi = self.w_off[l], self.b_off[l] + self.dims[l + 1]
-            hnd = (dist.all_reduce(self.grads[lo:hi], op=dist.ReduceOp.SUM, async_op=True)
-                   if self.world_size > 1 else None)
-            if hnd is None:
+            if self.world_size > 1:
+                self._all_reduce(lo, hi)
+                side.wait_stream(self._comm_stream)   # the side stream waits for the collective, the main stream keeps issuing products
+            else:
                 side.wait_stream(main)
             with torch.cuda.stream(side):
-                if hnd is not None:
-                    hnd.wait()   # the side stream waits for the collective, the main stream keeps issuing products
                 be.adam_step(self.params[lo:hi], self.grads[lo:hi], self.m[lo:hi], self.v[lo:hi], lr=self.lr,
                              beta1=self.beta1, beta2=self.beta2, eps=self.eps, step=self.step_count,
                              grad_scale=1.0 / self.world_size)
         main.wait_stream(side)
         if self.comm_sms > 0:
             be.set_gemm_sm_limit(0)   # the forward pass has nothing running beside it
+
+    def _all_reduce(self, lo: int, hi: int) -> None:
+        """Sum ``grads[lo:hi]`` over the ranks on the communication stream, ordered after the work enqueued so far
+        on the current stream (the product that wrote the slice)."""
+        self._comm_stream.wait_stream(torch.cuda.current_stream(self.be.device))
+        self.comm.all_reduce_sum(self.grads[lo:hi], self._comm_stream)
+
+    def params_checksum(self) -> torch.Tensor:
+        """[sum, sum of squares] of the parameters in f64 on the device: equal on every rank while the replicas agree."""
+        p = self.params.double()
+        return torch.stack([p.sum(), (p * p).sum()])
 
     def flops_per_sample(self) -> int:
         return mlp_flops_per_sample(self.dims)

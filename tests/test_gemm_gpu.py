@@ -563,3 +563,36 @@ def test_plain_gemm_replays_from_a_cuda_graph(be, rng):
     torch.cuda.synchronize()
     be.sync()
     assert torch.equal(out, ref)
+
+
+def test_nonfinite_redo_decides_afresh_on_every_graph_replay(be, rng):
+    """The Inf / NaN redo is gated by a per-call flag that the call itself clears, sets and tests on the stream, so
+    a captured product takes the decision on every replay: finite -> Inf in an operand -> finite again gives,
+    each time, the bits of the eager call on the same contents (the reference's Inf where Inf meets finite values)."""
+    m, n, k = 384, 512, 256
+    a = dev(be, rng.standard_normal((m, k)).astype(np.float32))
+    b = dev(be, rng.standard_normal((k, n)).astype(np.float32))
+    out = torch.empty(m, n, device=be.device)
+    be.gemm(a, b, out=out)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        be.gemm(a, b, out=out)
+    for _ in range(70):                                    # more eager calls than there are flag slots
+        be.gemm(a[:130], b)
+    finite_a = a.clone()
+    inf_a = a.clone()
+    inf_a[5, 7] = float("inf")
+    inf_a[9, 1] = float("-inf")
+    for contents in (finite_a, inf_a, finite_a, inf_a):
+        a.copy_(contents)
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = be.gemm(contents.clone(), b)
+        be.sync()
+        assert torch.equal(torch.isnan(out), torch.isnan(ref))
+        assert torch.equal(out[~torch.isnan(ref)], ref[~torch.isnan(ref)])
+        if contents is inf_a:
+            assert torch.isinf(out[5]).all() and torch.isinf(out[9]).all() and not torch.isnan(out).any()
+            assert torch.isfinite(out[6]).all()

@@ -133,3 +133,48 @@ def test_adam_bit_exact_with_oracle(be, orc, rng, golden):
         np.testing.assert_array_equal(pd.cpu().numpy(), pn)
         np.testing.assert_array_equal(md.cpu().numpy(), mn)
         np.testing.assert_array_equal(vd.cpu().numpy(), vn)
+
+
+def test_wrappers_refuse_buffers_the_library_would_misread(be, rng):
+    """The C ABI reads raw dense memory: a strided view, a host tensor or a buffer of another element type is
+    refused by the Python layer instead of being read as something else."""
+    x = torch.from_numpy(rng.standard_normal((64, 48)).astype(np.float32)).to(be.device)
+    with pytest.raises(ValueError):
+        be.colsum(x.t())                                   # transposed view
+    with pytest.raises(ValueError):
+        be.colsum(x.cpu())                                 # host memory
+    with pytest.raises(ValueError):
+        be.conv2d_fwd(torch.zeros(2, 4, 6, 6, device=be.device).to(memory_format=torch.channels_last),
+                      torch.zeros(3, 4, 3, 3, device=be.device), None, (1, 1), (1, 1))
+    p = torch.zeros(100, dtype=torch.float64, device=be.device)
+    with pytest.raises(TypeError):
+        be.adam_step(p, p, p, p, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)          # Adam is f32 only
+    with pytest.raises(TypeError):
+        be.sgd_step(p, torch.zeros(100, device=be.device), lr=0.1)                   # f64 parameters, f32 gradient
+    with pytest.raises(TypeError):
+        be.cross_entropy(torch.zeros(4, 3, dtype=torch.float64, device=be.device),
+                         torch.zeros(4, dtype=torch.int64, device=be.device))
+    with pytest.raises(ValueError):
+        be.sgd_step(torch.zeros(10, device=be.device), torch.zeros(9, device=be.device), lr=0.1)
+
+
+def test_expired_wait_is_reported_and_the_context_survives(be, rng):
+    """Every wait inside the tensor-core kernels is bounded.  The self-test launches a block that waits 2 ms on a
+    barrier nothing signals: the next sync reports MTB200_ERR_DEVICE_WAIT exactly once, and the handle keeps
+    working (a GEMM right after gives the usual result)."""
+    from minitensor_b200._lib import ERR_DEVICE_WAIT, Mtb200Error, check
+    be.sync()
+    check(be.lib.mtb200_selftest_wait_expiry(be._h, 2000))
+    with pytest.raises(Mtb200Error) as err:
+        be.sync()
+    assert err.value.status == ERR_DEVICE_WAIT and "bounded wait" in str(err.value)
+    be.sync()                                              # reported once, then cleared
+    a = rng.standard_normal((300, 200)).astype(np.float32)
+    b = rng.standard_normal((200, 260)).astype(np.float32)
+    c = be.gemm(torch.from_numpy(a).to(be.device), torch.from_numpy(b).to(be.device))
+    be.sync()
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    scale = np.linalg.norm(a, axis=1)[:, None] * np.linalg.norm(b, axis=0)[None, :]
+    assert (np.abs(c.cpu().numpy() - ref) / scale).max() <= 4e-6
+    with pytest.raises(ValueError):
+        check(be.lib.mtb200_selftest_wait_expiry(be._h, 0))

@@ -195,7 +195,9 @@ def test_cross_entropy_general_known_answers_and_nn_mirror(be, golden):
 
 
 # ------------------------------------------------------------------ batch norm
-@pytest.mark.parametrize("shape", [(64, 128), (37, 5), (8, 6, 50), (4, 3, 17, 19), (300, 4096)])
+@pytest.mark.parametrize("shape", [(64, 128), (37, 5), (8, 6, 50), (4, 3, 17, 19), (300, 4096),
+                                   (256, 300, 3, 2),      # N * C = 76,800 (n, c) planes: beyond a 16-bit grid dimension
+                                   (2, 3, 1500, 3)])      # planes of 4500 elements: several spans, the last one ragged
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_batch_norm_forward_backward_against_oracle(be, orc, rng, shape, dtype):
     x = (rng.standard_normal(shape) * 3 + 7).astype(dtype)      # a mean well away from zero
@@ -222,6 +224,21 @@ def test_batch_norm_forward_backward_against_oracle(be, orc, rng, shape, dtype):
         np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=tol * 5, atol=tol * 50)
         np.testing.assert_allclose(dw.cpu().numpy(), dw_ref, rtol=tol * 5, atol=tol * 5 * scale)
         np.testing.assert_allclose(db.cpu().numpy(), db_ref, rtol=tol * 5, atol=tol * 5 * scale)
+
+
+def test_batch_norm_refused_geometry_leaves_running_estimates_alone(be):
+    """A geometry the kernels cannot take is refused before anything is launched: the running estimates keep
+    their values (the call's only side effect besides its outputs)."""
+    import ctypes as C
+    rm = torch.full((4,), 3.0, device=be.device)
+    rv = torch.full((4,), 5.0, device=be.device)
+    x = torch.zeros(16, device=be.device)
+    rc = be.lib.mtb200_batch_norm_fwd(be._h, 0, 2 ** 31, 4, 2, C.c_void_p(x.data_ptr()), None, None,
+                                      C.c_void_p(rm.data_ptr()), C.c_void_p(rv.data_ptr()), 1, 0.1, 1e-5,
+                                      C.c_void_p(x.data_ptr()), None, None)
+    assert rc == 1
+    be.sync()
+    assert float(rm.min()) == 3.0 == float(rm.max()) and float(rv.min()) == 5.0 == float(rv.max())
 
 
 def test_batch_norm_known_answers_and_layers(be, golden):

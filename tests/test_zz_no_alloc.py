@@ -1,9 +1,8 @@
 """The allocation-free column sum (mtb200_colsum_noalloc) against the regular one.
 
-Some users of the library cannot let a call allocate device memory: they are inside a stream
-capture, or their application's pool owns the whole GPU, or they cannot afford the device-wide
-stall of cudaMalloc.  For them the library offers a column sum whose scratch is a fixed array
-inside the library.  This file checks, through the C ABI, that it returns what mtb200_colsum
+Some users of the library cannot let a call allocate device memory: their application's own pool
+owns the whole GPU, or they cannot afford the device-wide stall of cudaMalloc.  For them the
+library offers a column sum whose scratch is a fixed array inside the library.  This file checks, through the C ABI, that it returns what mtb200_colsum
 returns, on two calls in a row that share that array, and that inputs wider than the fixed
 scratch are refused.  It is named so that pytest collects it last.
 """
@@ -15,7 +14,19 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-SCRATCH_BYTES = 4 << 20
+
+def _scratch_bytes() -> int:
+    """The limit as the header states it (MTB200_COLSUM_NOALLOC_SCRATCH_BYTES), so a changed macro is noticed."""
+    import os
+    import re
+    from conftest import ROOT
+    text = open(os.path.join(ROOT, "include", "mtb200.h")).read()
+    m = re.search(r"#define\s+MTB200_COLSUM_NOALLOC_SCRATCH_BYTES\s+\((\d+)u?\s*<<\s*(\d+)\)", text)
+    assert m, "the header no longer defines the scratch size in the expected form"
+    return int(m.group(1)) << int(m.group(2))
+
+
+SCRATCH_BYTES = _scratch_bytes()
 
 
 def _call_noalloc(lib, x: torch.Tensor) -> torch.Tensor:
