@@ -36,6 +36,56 @@ UNIT = "samples/s"
 WORKLOAD = "MLP 8192-4096-4096-4096-1000 ReLU + CrossEntropy + Adam, f32, global batch 65536"
 
 
+def _traffic(key: str):
+    """A record of profiles/dram_traffic.json (DRAM bytes per launch from an ncu capture), or None."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        return json.load(open(p)).get(key)
+    except (OSError, ValueError):
+        return None
+
+
+def record_traffic(csv_path: str, key: str, kernel_regex: str, command: str):
+    """Fold an ncu raw CSV (--page raw --csv, or --csv --log-file) into profiles/dram_traffic.json: mean of
+    dram__bytes_read.sum + dram__bytes_write.sum over the captured launches whose kernel name matches."""
+    import csv
+    import re
+    rows = list(csv.reader(open(csv_path, errors="replace")))
+    hdr_i = next(i for i, r in enumerate(rows) if "Kernel Name" in r)
+    hdr = rows[hdr_i]
+    per_launch = {}
+    if "Metric Name" in hdr:        # long form: one row per (launch, metric)
+        ki, mi, vi, ui, idi = (hdr.index(c) for c in ("Kernel Name", "Metric Name", "Metric Value", "Metric Unit", "ID"))
+        for r in rows[hdr_i + 1:]:
+            if len(r) <= vi or not re.search(kernel_regex, r[ki]) or not r[mi].startswith("dram__bytes_"):
+                continue
+            mult = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}.get(r[ui], 1.0)
+            per_launch[r[idi]] = per_launch.get(r[idi], 0.0) + float(r[vi].replace(",", "")) * mult
+    else:                           # wide form: one row per launch, a units row after the header
+        units = rows[hdr_i + 1]
+        ki = hdr.index("Kernel Name")
+        cols = [i for i, c in enumerate(hdr) if c in ("dram__bytes_read.sum", "dram__bytes_write.sum")]
+        for n, r in enumerate(rows[hdr_i + 2:]):
+            if len(r) <= max(cols) or not re.search(kernel_regex, r[ki]):
+                continue
+            tot = 0.0
+            for i in cols:
+                mult = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}.get(units[i], 1.0)
+                tot += float(r[i].replace(",", "")) * mult
+            per_launch[n] = tot
+    if not per_launch:
+        raise SystemExit(f"no launch of /{kernel_regex}/ with DRAM byte counters in {csv_path}")
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    data = json.load(open(p)) if os.path.exists(p) else {}
+    commit = subprocess.run(["git", "-C", ROOT, "rev-parse", "--short", "HEAD"], stdout=subprocess.PIPE, text=True).stdout.strip()
+    rec = data.get(key, {})
+    rec.update(command=command, commit=commit, launches_captured=len(per_launch),
+               dram_bytes_per_launch=sum(per_launch.values()) / len(per_launch))
+    data[key] = rec
+    json.dump(data, open(p, "w"), indent=2)
+    print(json.dumps({key: rec}))
+
+
 def _peaks():
     """Measured peaks of this pool (driver-written file), else the stated fallback."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -67,7 +117,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20", "-i",
                  str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -202,7 +252,248 @@ def gemm4096(be, torch, peaks):
             "peak_tflops": peak, "peak_3xtf32_emulated_tflops": peak_3xtf32, "f32_mode": "f16x3",
             "peak_def": "measured 16-bit dense tensor burst (cuBLAS bf16) / 3 products per f32 product; the "
                         "3xTF32-emulated peak is the same burst / 6",
-            "dram_traffic_mb_per_launch": 361.9, "algorithmic_mb_per_launch": 201.3}
+            "dram_traffic": _traffic("gemm_f32_4096.whole_call_tensor_kernel_plus_fixup")}
+
+
+
+def _time_gpu(torch, fn, flush, iters=5, warm=2):
+    """Median device time (ms) of fn() over `iters` calls, event-timed on the current stream, L2 flushed (a buffer
+    larger than L2 is rewritten) before every timed call."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    return statistics.median(times)
+
+
+def _norm_err(c, ref, a, b):
+    """max |c - ref| / (||a_row|| ||b_col||) over the given rows (a [r,K], b [K,N], float64 arithmetic)."""
+    na = np.linalg.norm(a.astype(np.float64), axis=-1)[..., :, None]
+    nb = np.linalg.norm(b.astype(np.float64), axis=-2)[..., None, :]
+    return float((np.abs(c.astype(np.float64) - ref.astype(np.float64)) / np.maximum(na * nb, 1e-300)).max())
+
+
+def config_table(be, torch, peaks, with_cpu: bool):
+    """Every configuration of the benchmark list beside the headline one, each as one record: whole-call device
+    time (operand preparation included, L2 flushed between calls), rate, fraction of the roofline that bounds it,
+    and - in the CPU leg - the oracle's time on the host cores with its thread count and the largest
+    norm-scaled error of the device result.  Sizes whose CPU time is impractical are timed on the CPU at a
+    smaller, stated size and never extrapolated."""
+    dev = be.device
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    orc = None
+    if with_cpu:
+        import oracle as orc
+        orc.build()
+    threads = orc.num_threads() if orc else None
+    f32_peak = peaks["bf16_burst"] / 3.0          # fp16 two-plane mode: three 16-bit products per f32 product
+    i8_peak = peaks["bf16_burst"] * 2.0           # kind::i8 runs at twice the 16-bit rate; entries in [-8,8] need one product
+    out = []
+
+    def cpu_time(fn, reps=1):
+        best = None
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            r = fn()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        return best * 1e3, r
+
+    # ---- C1: 1024^3 f32 forward + backward (upstream gradient of ones)
+    n = 1024
+    a, b = torch.randn(n, n, generator=g), torch.randn(n, n, generator=g)
+    ad, bd, dy = a.to(dev), b.to(dev), torch.ones(n, n, device=dev)
+    c, da, db_ = (torch.empty(n, n, device=dev) for _ in range(3))
+    fwd = lambda: be.gemm(ad, bd, out=c)
+    bwd = lambda: (be.gemm(dy, bd, trans_b=True, out=da), be.gemm(ad, dy, trans_a=True, out=db_))
+    ms_f, ms_b = _time_gpu(torch, fwd, flush), _time_gpu(torch, bwd, flush)
+    rec = {"config": "C1 matmul f32 1024^3 forward + backward (dY = ones)", "dtype": "f32", "gpu_ms": ms_f + ms_b,
+           "gpu_ms_forward": ms_f, "gpu_ms_backward": ms_b, "tflops": 3 * 2.0 * n ** 3 / (ms_f + ms_b) / 1e9,
+           "tflops_forward": 2.0 * n ** 3 / ms_f / 1e9, "bound": "tensor", "peak_tflops": f32_peak}
+    rec["roofline_frac"] = rec["tflops"] / f32_peak
+    if orc:
+        an, bn = a.numpy(), b.numpy()
+        ones = np.ones((n, n), np.float32)
+        t1, ref = cpu_time(lambda: orc.matmul(an, bn), 2)
+        t2, (rda, rdb) = cpu_time(lambda: orc.matmul_backward(an, bn, ones), 2)
+        rec.update(cpu_ms=t1 + t2, cpu_threads=threads, cpu_size="same",
+                   max_err=max(_norm_err(c.cpu().numpy(), ref, an, bn), _norm_err(da.cpu().numpy(), rda, ones, bn.T),
+                               _norm_err(db_.cpu().numpy(), rdb, an.T, ones)))
+    out.append(rec)
+
+    # ---- bmm f32 [64,512,512] x [64,512,512]
+    a, b = torch.randn(64, 512, 512, generator=g), torch.randn(64, 512, 512, generator=g)
+    ad, bd = a.to(dev), b.to(dev)
+    c = torch.empty(64, 512, 512, device=dev)
+    ms = _time_gpu(torch, lambda: be.gemm(ad, bd, out=c), flush)
+    rec = {"config": "bmm f32 [64,512,512] x [64,512,512]", "dtype": "f32", "gpu_ms": ms,
+           "tflops": 64 * 2.0 * 512 ** 3 / ms / 1e9, "bound": "tensor", "peak_tflops": f32_peak}
+    rec["roofline_frac"] = rec["tflops"] / f32_peak
+    if orc:
+        an, bn = a.numpy(), b.numpy()
+        t1, ref = cpu_time(lambda: orc.matmul(an, bn))
+        rec.update(cpu_ms=t1, cpu_threads=threads, cpu_size="same", max_err=_norm_err(c.cpu().numpy(), ref, an, bn))
+    out.append(rec)
+    del a, b, ad, bd, c
+
+    # ---- square sweep, M = N = K in {256, 1024, 4096, 8192} x {f32, f64, i32}
+    cpu_budget_s = 16.0     # a single CPU timing predicted (from the previous size, x8) to exceed this is not run
+    for dt_name, tdt in (("f32", torch.float32), ("f64", torch.float64), ("i32", torch.int32)):
+        last_cpu = None     # (size, ms) of the largest CPU run of this dtype
+        for n in (256, 1024, 4096, 8192):
+            if dt_name == "i32":
+                a = torch.randint(-8, 9, (n, n), generator=g, dtype=torch.int32)
+                b = torch.randint(-8, 9, (n, n), generator=g, dtype=torch.int32)
+            else:
+                a, b = torch.randn(n, n, generator=g, dtype=tdt), torch.randn(n, n, generator=g, dtype=tdt)
+            ad, bd = a.to(dev), b.to(dev)
+            c = torch.empty(n, n, dtype=tdt, device=dev)
+            ms = _time_gpu(torch, lambda: be.gemm(ad, bd, out=c), flush, iters=5 if n < 8192 else 3)
+            ops = 2.0 * n ** 3
+            rec = {"config": f"square {dt_name} {n}^3", "dtype": dt_name, "gpu_ms": ms, "tflops": ops / ms / 1e9}
+            algo_bytes = 3.0 * n * n * a.element_size()
+            if n == 256:      # launch / HBM-bound: microseconds and bytes are the meaningful figures
+                rec.update(bound="hbm", gpu_us=ms * 1e3, gbs=algo_bytes / ms / 1e6, peak_gbs=peaks["hbm_gbs"],
+                           roofline_frac=algo_bytes / ms / 1e6 / peaks["hbm_gbs"])
+            elif dt_name == "f32":
+                rec.update(bound="tensor", peak_tflops=f32_peak, roofline_frac=rec["tflops"] / f32_peak,
+                           frac_of_3xtf32_emulated_peak=rec["tflops"] / (peaks["bf16_burst"] / 6.0))
+            elif dt_name == "i32":
+                rec.update(bound="tensor", pipe="int8 tensor cores (tcgen05 kind::i8), one s8 product per int32 product "
+                           "for entries that fit in int8", peak_tflops=i8_peak, roofline_frac=rec["tflops"] / i8_peak,
+                           peak_def="2 x measured 16-bit dense tensor burst")
+            else:
+                # no measured FP64 tensor peak exists for this pool: the anchor is the vendor library's dgemm on
+                # the same operands in the same run (measurement only; it is not on the product path)
+                cref = torch.empty(n, n, dtype=tdt, device=dev)
+                ms_lib = _time_gpu(torch, lambda: torch.matmul(ad, bd, out=cref), flush, iters=5 if n < 8192 else 3)
+                rec.update(bound="fp64 tensor (mma.sync)", cublas_dgemm_ms=ms_lib, cublas_dgemm_tflops=ops / ms_lib / 1e9,
+                           roofline_frac=ms_lib / ms, peak_def="vendor dgemm measured in the same run")
+                del cref
+            if orc:
+                an, bn = a.numpy(), b.numpy()
+                predicted = last_cpu[1] * (n / last_cpu[0]) ** 3 / 1e3 if last_cpu else 0.0
+                if predicted <= cpu_budget_s:
+                    t1, ref = cpu_time(lambda: orc.matmul(an, bn), 2 if n <= 1024 else 1)
+                    last_cpu = (n, t1)
+                    rec.update(cpu_ms=t1, cpu_threads=threads, cpu_size="same")
+                    got = c.cpu().numpy()
+                    rec["max_err"] = 0.0 if dt_name == "i32" and np.array_equal(got, ref) else (
+                        _norm_err(got, ref, an, bn) if dt_name != "i32" else float("inf"))
+                    if dt_name == "i32":
+                        rec["bit_exact"] = bool(np.array_equal(got, ref))
+                else:
+                    rec.update(cpu_ms=last_cpu[1], cpu_threads=threads,
+                               cpu_size=f"{last_cpu[0]}^3 (this size is impractical for the CPU loop; not extrapolated)")
+                    rows = np.random.default_rng(n).choice(n, 8, replace=False)
+                    ar = np.ascontiguousarray(an[rows])
+                    got = c[torch.from_numpy(rows).to(dev)].cpu().numpy()
+                    if dt_name == "i32":
+                        rec["bit_exact"] = bool(np.array_equal(got, orc.matmul(ar, bn)))
+                        rec["max_err"] = 0.0 if rec["bit_exact"] else float("inf")
+                    else:
+                        rec["max_err"] = _norm_err(got, orc.matmul_acc_wide(ar, bn), ar, bn)
+                    rec["err_sample"] = "8 rows, all columns"
+            out.append(rec)
+            del a, b, ad, bd, c
+
+    # ---- C4: conv2d f32 [128,64,56,56] * [64,64,3,3], stride 1, pad 1, bias: forward, dX, dW, db
+    N, C_, H, W_, O = 128, 64, 56, 56, 64
+    x = torch.randn(N, C_, H, W_, generator=g)
+    w = torch.randn(O, C_, 3, 3, generator=g) * (2.0 / (C_ * 9)) ** 0.5      # Kaiming-normal
+    bias = torch.randn(O, generator=g)
+    dy = torch.randn(N, O, H, W_, generator=g)
+    xd, wd, bd, dyd = x.to(dev), w.to(dev), bias.to(dev), dy.to(dev)
+    s1, p1 = (1, 1), (1, 1)
+    res = {}
+    calls = {"forward": lambda: res.__setitem__("y", be.conv2d_fwd(xd, wd, bd, s1, p1)),
+             "dX": lambda: res.__setitem__("dx", be.conv2d_bwd_data(dyd, wd, xd.shape, s1, p1)),
+             "dW": lambda: res.__setitem__("dw", be.conv2d_bwd_weight(dyd, xd, wd.shape, s1, p1)),
+             "db": lambda: res.__setitem__("db", be.conv2d_bwd_bias(dyd))}
+    flops = 2.0 * N * O * H * W_ * C_ * 9
+    rec = {"config": "C4 conv2d f32 [128,64,56,56] * [64,64,3,3] s1 p1 + bias: forward, dX, dW, db", "dtype": "f32",
+           "bound": "tensor", "peak_tflops": f32_peak, "parts": {}}
+    total_ms = 0.0
+    for name, fn in calls.items():
+        ms = _time_gpu(torch, fn, flush)
+        total_ms += ms
+        part = {"gpu_ms": ms}
+        if name == "db":
+            part.update(gbs=4.0 * dy.numel() / ms / 1e6, roofline_frac=4.0 * dy.numel() / ms / 1e6 / peaks["hbm_gbs"], bound="hbm")
+        else:
+            part.update(tflops=flops / ms / 1e9, roofline_frac=flops / ms / 1e9 / f32_peak)
+        rec["parts"][name] = part
+    rec["gpu_ms"] = total_ms
+    rec["tflops"] = 3 * flops / total_ms / 1e9
+    rec["roofline_frac"] = rec["tflops"] / f32_peak
+    if orc:
+        from oracle import conv_f64
+        xn, wn, bn_, dyn = x.numpy(), w.numpy(), bias.numpy(), dy.numpy()
+        t1, _ = cpu_time(lambda: orc.conv2d(xn, wn, bn_, s1, p1))
+        t2, _ = cpu_time(lambda: orc.conv2d_backward(xn, wn, dyn, s1, p1))
+        rec.update(cpu_ms=t1 + t2, cpu_ms_forward=t1, cpu_ms_backward=t2, cpu_threads=threads, cpu_size="same")
+        yh, dxh, dwh = res["y"].cpu().numpy(), res["dx"].cpu().numpy(), res["dw"].cpu().numpy()
+        pick = np.random.default_rng(11)
+        worst = 0.0
+        for _ in range(96):
+            n_, o_, c_, h_, w_ = (int(pick.integers(k)) for k in (N, O, C_, H, W_))
+            v, sc = conv_f64.sample_forward(xn, wn, bn_, p1, n_, o_, h_, w_)
+            worst = max(worst, abs(float(yh[n_, o_, h_, w_]) - v) / (sc + abs(float(bn_[o_]))))
+            v, sc = conv_f64.sample_grad_input(dyn, wn, p1, n_, c_, h_, w_)
+            worst = max(worst, abs(float(dxh[n_, c_, h_, w_]) - v) / sc)
+            i_, j_ = int(pick.integers(3)), int(pick.integers(3))
+            v, sc = conv_f64.sample_grad_weight(dyn, xn, p1, o_, c_, i_, j_)
+            worst = max(worst, abs(float(dwh[o_, c_, i_, j_]) - v) / sc)
+        rec.update(max_err=worst, err_sample="96 outputs each of y, dX, dW as float64 dot products")
+    out.append(rec)
+    return out
+
+
+def dp_check(torch, dist, world, rank, local, comm):
+    """Data-parallel parity on the real collective path, before anything is timed: one training step of a small
+    fixed model (512-384-256-100, global batch 2048, the same seeds on every rank) through MLPTrainer(world_size =
+    N) with its overlapped schedule and the library's NCCL all-reduce, against a world_size = 1 trainer of the same
+    process fed the whole batch.  Reports the largest relative Frobenius distance between a layer's averaged
+    gradient and the full-batch gradient, the largest parameter difference after the Adam step, and whether the
+    parameter checksums of all ranks agree."""
+    from minitensor_b200.mlp import MLPTrainer, mlp_layout, shard_rows
+    dims, gbatch = [512, 384, 256, 100], 2048
+    g = torch.Generator(device="cpu").manual_seed(4242)
+    x = torch.randn(gbatch, dims[0], generator=g)
+    y = torch.randint(0, dims[-1], (gbatch,), generator=g, dtype=torch.int64)
+    lo, hi = shard_rows(gbatch, world, rank)
+    dev = torch.device("cuda", local)
+    shard = MLPTrainer(dims, hi - lo, device=local, world_size=world, seed=5, comm=comm)
+    full = MLPTrainer(dims, gbatch, device=local, world_size=1, seed=5)
+    shard.step(x[lo:hi].to(dev), y[lo:hi].to(dev))
+    full.step(x.to(dev), y.to(dev))
+    torch.cuda.synchronize()
+    w_off, b_off, total = mlp_layout(dims)
+    err = 0.0
+    for l in range(len(dims) - 1):
+        a, b = w_off[l], b_off[l] + dims[l + 1]
+        gs, gf = shard.grads[a:b].double() / world, full.grads[a:b].double()
+        err = max(err, float((gs - gf).norm() / gf.norm()))
+    pdiff = float((shard.params - full.params).abs().max())
+    chk = shard.params_checksum()
+    lo_t, hi_t = chk.clone(), chk.clone()
+    dist.all_reduce(lo_t, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi_t, op=dist.ReduceOp.MAX)
+    e = torch.tensor([err, pdiff], dtype=torch.float64, device=dev)
+    dist.all_reduce(e, op=dist.ReduceOp.MAX)
+    return {"model": "512-384-256-100, global batch 2048, one step", "grad_err_norm_scaled": float(e[0]),
+            "grad_err_def": "max over layers and ranks of ||g_allreduced / N - g_full_batch||_F / ||g_full_batch||_F",
+            "param_max_abs_diff_after_adam": float(e[1]),
+            "params_equal_across_ranks": bool(torch.equal(lo_t, hi_t))}
 
 
 def run_ours(args):
@@ -224,10 +515,15 @@ def run_ours(args):
             os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = _peaks()
+    comm = None
+    if world > 1:   # one NCCL communicator of the library for every trainer of this process
+        from minitensor_b200.comm import Communicator
+        comm = Communicator.from_process_group(local)
+    dp = dp_check(torch, dist, world, rank, local, comm) if world > 1 else None
     lo, hi = shard_rows(GLOBAL_BATCH, world, rank)
     rows = hi - lo
     trainer = MLPTrainer(DIMS, rows, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, device=local, world_size=world, seed=0,
-                         fused_dense=not args.per_product)
+                         fused_dense=not args.per_product, comm=comm)
     be = trainer.be
     dev = be.device
 
@@ -258,26 +554,53 @@ def run_ours(args):
         trainer.step(x, y)
     barrier()
     sampler.mark_begin()
-    be.profile(True)
-    launches0 = be.launches
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    loss = None
-    for _ in range(args.steps):
-        loss = trainer.step(x, y)
-    e.record()
-    barrier()
+    # Blocks of exactly `steps` steps, each bracketed by barrier + synchronize and timed with events (max over
+    # ranks), repeated until the region has run for MIN_REGION_S so that clocks and power have settled; the
+    # reported figure is the median block.  The launch profiler brackets the last block only.
+    blocks_ms, loss = [], None
+    region_t0 = time.time()
+    while True:
+        last = (time.time() - region_t0) >= args.min_region_s or len(blocks_ms) + 1 >= args.max_blocks
+        if world > 1:   # every rank must take the same decision
+            flag = torch.tensor([1 if last else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            last = bool(flag.item())
+        if last:
+            be.profile(True)
+            launches0 = be.launches
+        barrier()
+        s.record()
+        for _ in range(args.steps):
+            loss = trainer.step(x, y)
+        e.record()
+        barrier()
+        blocks_ms.append(max_over_ranks(s.elapsed_time(e)))
+        if last:
+            break
     sampler.mark_end()
-    ms_total = max_over_ranks(s.elapsed_time(e))
+    ms_last = blocks_ms[-1]
+    ms_total = statistics.median(blocks_ms)
     clocks = sampler.stop() if rank == 0 else None
     gpu_launches = be.launches - launches0
     k_launches, k_ms, k_flops = be.profile_read(0)
     s_launches, s_ms, s_bytes = be.profile_read(1)
     be.profile(False)
     be.sync()
-    final_loss = float(loss.item())
+    mean_loss = loss.clone()
+    if world > 1:
+        dist.all_reduce(mean_loss, op=dist.ReduceOp.SUM)
+        mean_loss /= world
+    final_loss = float(mean_loss.item())
     ms_per_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_per_step * 1e-3)
+    chk = trainer.params_checksum()
+    replicas_equal = True
+    if world > 1:
+        lo_t, hi_t = chk.clone(), chk.clone()
+        dist.all_reduce(lo_t, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi_t, op=dist.ReduceOp.MAX)
+        replicas_equal = bool(torch.equal(lo_t, hi_t))
 
     # ---- end to end: every step copies its batch from pinned host memory and reads the loss back
     slot = trainer.prefetch(host_x[0], host_y[0])
@@ -296,6 +619,18 @@ def run_ours(args):
     e2e_ms = max_over_ranks(s.elapsed_time(e)) / args.steps
     e2e_value = GLOBAL_BATCH / (e2e_ms * 1e-3)
     h2d = rows * DIMS[0] * 4 + rows * 8
+    # what the host link gives this rank while every rank copies at once and nothing else runs: the ceiling of
+    # the end-to-end figure when the copy cannot hide behind the step any more
+    stage = torch.empty(rows, DIMS[0], dtype=torch.float32, device=dev)
+    barrier()
+    s.record()
+    for i in range(4):
+        stage.copy_(host_x[i % 2], non_blocking=True)
+    e.record()
+    barrier()
+    copy_ms = max_over_ranks(s.elapsed_time(e)) / 4
+    h2d_ceiling_gbs = rows * DIMS[0] * 4 / copy_ms / 1e6
+    del stage
 
     if rank != 0:
         if world > 1:
@@ -304,6 +639,7 @@ def run_ours(args):
         return 0
 
     peak_f32 = peaks["bf16_sustained"] / 3.0
+    tall = _traffic("gemm_split_umma2_kernel.tall_16384x4096x4096")
     achieved = k_flops / k_ms / 1e9 if k_ms else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -313,10 +649,18 @@ def run_ours(args):
                    "parallelism": f"dp{world}", "f32_mode": "f16x3: two fp16 planes per operand after exact power-of-two row/column "
                                "scaling, three tensor products per f32 product (3xTF32-class accuracy)",
                    "l2": "inputs larger than L2 (2.1 GB batch, 1 GB activations per layer)",
-                   "flops_per_sample": mlp_flops_per_sample(DIMS), "final_loss": final_loss},
+                   "flops_per_sample": mlp_flops_per_sample(DIMS),
+                   "mean_loss_over_ranks_after_timed_steps": final_loss,
+                   "timed_region": f"{len(blocks_ms)} blocks of {args.steps} steps, median block reported"},
+        "blocks_ms": blocks_ms,
         "clocks": clocks,
+        "ms_per_step_x_sm_mhz": (ms_per_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,
+        "params_equal_across_ranks_after_timed_steps": replicas_equal,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4, "note": "next batch's host->device copy overlaps the current step"},
+                "d2h_bytes_per_step": 4, "note": "next batch's host->device copy overlaps the current step",
+                "h2d_gbs_per_rank_needed": h2d / (ms_per_step * 1e6),
+                "h2d_gbs_per_rank_bare_copy_all_ranks_at_once": h2d_ceiling_gbs,
+                "floor_ms_per_step_from_host_link": copy_ms},
         "gpu_launches": gpu_launches,
         "roofline": {
             "kernel": "gemm_split_umma2_kernel", "bound": "tensor", "achieved": achieved, "peak": peak_f32,
@@ -324,21 +668,25 @@ def run_ours(args):
             "peak_def": f"{peaks['source']} 16-bit dense tensor sustained {peaks['bf16_sustained']} TFLOP/s / 3 "
                         "(three fp16 tensor products per f32 product); a 3xTF32 emulation's roofline is half of this",
             "launches": k_launches, "avg_launch_ms": k_ms / k_launches if k_launches else None,
-            "share_of_step": k_ms / ms_total if ms_total else None,
+            "share_of_step": k_ms / ms_last if ms_last else None,
             # DRAM bytes per launch: the step's GEMMs hold 3-6 GB each, above the ncu capture size rule, so the
-            # figure is the ncu capture of the same kernel on 16384x4096x4096 (1.511 GB read + written for
-            # 549.8 GFLOP) scaled by the flops of an average launch of this step (traffic per flop is set by the
-            # tile shape and the walk order, which are the same)
-            "traffic": (1.511e9 * (mlp_flops_per_sample(DIMS) * rows / 11) / 549.8e9),
-            "traffic_note": "bytes per average launch, scaled by flops from the ncu capture of the same kernel on "
-                            "16384x4096x4096 (profiles/gemm_split_umma2_f32_4096.md)",
+            # figure is the ncu capture of the same kernel on 16384x4096x4096 scaled by the flops of an average
+            # launch of this step (traffic per flop is set by the tile shape and the walk order, which are the same)
+            "traffic": (tall["dram_bytes_per_launch"] * (k_flops / max(k_launches, 1)) / tall["flops_per_launch"]) if tall else None,
+            "traffic_note": "bytes per average launch of this step, scaled by flops from the recorded ncu capture of the "
+                            "same kernel on 16384x4096x4096",
+            "traffic_capture": tall,
             "split_kernels": {"launches": s_launches, "ms": s_ms, "gbs": s_bytes / s_ms / 1e6 if s_ms else None,
-                              "share_of_step": s_ms / ms_total if ms_total else None},
+                              "share_of_step": s_ms / ms_last if ms_last else None},
         },
         "step_tflops": mlp_flops_per_sample(DIMS) * value / 1e12,
     }
+    if dp is not None:
+        line["dp_check"] = dp
     if world == 1:
         line["gemm_f32_4096"] = gemm4096(be, torch, peaks)
+        if not args.no_configs:
+            line["configs"] = config_table(be, torch, peaks, with_cpu=not args.no_cpu)
         if not args.no_cpu:
             rows_cpu = 2048
             v, per_step, cores = cpu_mlp_samples_per_s(rows_cpu, 1, 1)
@@ -454,11 +802,25 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table of the N = 1 line")
     ap.add_argument("--per-product", action="store_true",
                     help="one GEMM call per product (as the reference's autograd issues them) instead of the dense-layer pair")
+    ap.add_argument("--min-region-s", type=float, default=2.0,
+                    help="repeat the block of --steps timed steps until the timed region has run this long")
+    ap.add_argument("--max-blocks", type=int, default=40)
     ap.add_argument("--case", default=None, help="run one small fixed workload (profiling target) and exit")
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--record-traffic", default=None, metavar="NCU_CSV",
+                    help="fold an ncu CSV's DRAM byte counters into profiles/dram_traffic.json and exit")
+    ap.add_argument("--traffic-key", default=None)
+    ap.add_argument("--traffic-kernel", default=".", help="regular expression the kernel name must match")
+    ap.add_argument("--traffic-command", default="", help="the ncu command line that made the CSV")
     args = ap.parse_args()
+    if args.record_traffic:
+        if not args.traffic_key:
+            ap.error("--record-traffic needs --traffic-key")
+        record_traffic(args.record_traffic, args.traffic_key, args.traffic_kernel, args.traffic_command)
+        return 0
     if args.case:
         return run_case(args)
     if args.impl == "reference":

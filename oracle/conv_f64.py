@@ -1,5 +1,5 @@
 """float64 NumPy statement of conv2d and its gradients, plus the per-output operand norms the parity
-tolerances are scaled by.  Test infrastructure only.
+tolerances are scaled by.  Test infrastructure only (like the rest of this package): it is never on the product path.
 
 Every output of the three products is a dot product; the path's tolerance is stated per output as a fraction
 of (norm of the one operand's terms) x (norm of the other's), exactly as for a GEMM's ||a_row|| ||b_col||:

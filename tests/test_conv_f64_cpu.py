@@ -3,7 +3,7 @@ reference's loops) and with itself: full tensors, per-output norms and the singl
 import numpy as np
 import pytest
 
-import conv_f64
+from oracle import conv_f64
 
 GEOMS = [  # n, c, h, w, co, kh, kw, stride, padding
     (2, 3, 8, 9, 5, 3, 3, (1, 1), (1, 1)),

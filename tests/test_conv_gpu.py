@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-import conv_f64
+from oracle import conv_f64
 
 pytestmark = pytest.mark.gpu
 
