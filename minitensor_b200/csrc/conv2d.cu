@@ -23,6 +23,8 @@
 #include "mtb200_core.cuh"
 #include "gemm_launch.cuh"
 #include "conv_wgrad_umma.cuh"
+#include "conv_halo_umma.cuh"
+#include "conv_pix_umma.cuh"
 #include "rowcol_kernels.cuh"
 
 namespace mtb {
@@ -36,6 +38,13 @@ struct ConvGeom {
 static int bf16_mode_of(int32_t f32_mode) {
   const int m = f32_mode & 0xff;
   return m == 23 ? 0 : m;
+}
+
+// Tile-variant byte handed on to the plain GEMM by the gathered-patch lowerings: the conv-only values (0xff = this
+// lowering, 0xfc / 0xfb = particular implicit kernels) mean "choose" there.
+static int gemm_variant_of(int32_t f32_mode) {
+  const int v = (f32_mode >> 8) & 0xff;
+  return (v == 0xff || v == 0xfc || v == 0xfb) ? 0 : v;
 }
 
 // Gather modes for the patch operand.
@@ -169,25 +178,40 @@ __global__ void permute_weight_kernel(const float* __restrict__ w, float* __rest
   }
 }
 
-// partial[chunk][oc] = sum over the images of the chunk and all pixels of dy[n][oc][.]
+// partial[chunk][oc] = sum over the images of the chunk and all pixels of dy[n][oc][.]; 16-byte loads when the
+// pixel planes allow it, four independent accumulators per thread.
 __global__ void __launch_bounds__(256) conv_bias_partial_kernel(const float* __restrict__ dy, int n, int c_out,
                                                                 int opix, int imgs_per_chunk,
                                                                 float* __restrict__ partial) {
-  __shared__ float red[256];
+  __shared__ float red[8];
   const int oc = blockIdx.x, chunk = blockIdx.y;
   const int n0 = chunk * imgs_per_chunk, n1 = min(n, n0 + imgs_per_chunk);
-  float s = 0.0f;
+  const bool vec = ((opix & 3) == 0) && ((reinterpret_cast<uintptr_t>(dy) & 15) == 0);
+  float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
   for (int i = n0; i < n1; ++i) {
     const float* p = dy + (static_cast<long long>(i) * c_out + oc) * opix;
-    for (int k = threadIdx.x; k < opix; k += 256) s += p[k];
+    if (vec) {
+      const float4* p4 = reinterpret_cast<const float4*>(p);
+      const int q = opix >> 2;
+      for (int k = threadIdx.x; k < q; k += 256) {
+        const float4 v = __ldg(p4 + k);
+        s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
+      }
+    } else {
+      for (int k = threadIdx.x; k < opix; k += 256) s0 += p[k];
+    }
   }
-  red[threadIdx.x] = s;
+  float s = (s0 + s1) + (s2 + s3);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
   __syncthreads();
-  for (int o = 128; o; o >>= 1) {
-    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
-    __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += red[w];
+    partial[static_cast<long long>(chunk) * c_out + oc] = t;
   }
-  if (threadIdx.x == 0) partial[static_cast<long long>(chunk) * c_out + oc] = red[0];
 }
 
 // ---- Inf / NaN operands: the same results as the reference's direct loops.
@@ -317,6 +341,9 @@ __global__ void weight_taps_kernel(const float* __restrict__ w, float* __restric
   }
 }
 
+static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, int img_w, int img_h, int n,
+                                int planes, uint32_t box_c, uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle sw);
+
 // out[n][rows][out_h*out_w] = A[rows][taps*chan_p] * windows(img planes) (+ bias per row), stride 1.
 //  img: f32 NCHW [n][chan][img_h][img_w]; wsrc: OIHW weights; mode as in weight_taps_kernel;
 //  the window of tap (fh,fw) for output pixel (y,x) starts at (y + h0 + sgn*fh, x + w0 + sgn*fw).
@@ -389,6 +416,158 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     MTB_CUDA(cudaGetLastError());
     rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3, nf_word, MTB_FLAG_SET);
     if (rc) return rc;
+  }
+
+  // Pixels-on-M kernel (conv_pix_umma.cuh): the default.  Pick the output tile (tr x tc), the number of 128-position
+  // M blocks and whether the weights stay resident by a small cost model: per tile the tensor core needs
+  // mb * taps * cbs * 2 * products MMAs of width n_tile and the TMA engine one request per 64-byte halo-pixel piece
+  // (measured: about 4 ns each), whichever is longer bounds the tile.
+  {
+    const size_t smem_limit = 232448;
+    const bool three = planes == 3;
+    const int nsplit = gemm_mode == 1 ? 1 : ((gemm_mode == 3 || gemm_mode == 23) ? 2 : 3);
+    const int products = split_pair_count(gemm_mode);
+    const int cbs = chan_p / 32;
+    const int tiles_n = (rows + 255) / 256;
+    const int n_tile = (((rows + tiles_n - 1) / tiles_n) + 15) / 16 * 16;
+    const size_t w_tile = size_t(n_tile) * 64;
+    struct Plan { double cost; int tr, tc, wp, mb, w_stages; bool resident; size_t img_plane; } best = {1e300, 0, 0, 0, 0, 0, false, 0};
+    const double t_mma = std::max(26.7, 0.273 * n_tile) * 1.35;   // ns per MMA under load
+    for (int mb = 1; mb <= 4 && 2 * mb * n_tile <= 512; mb *= 2)
+      for (int sx = 1; sx <= 16; ++sx) {
+        const int tc = (out_w + sx - 1) / sx;
+        const int wp = tc + kw - 1;
+        if (wp > 256 || wp > 128 * mb) continue;
+        const int tr = std::min(out_h, (128 * mb) / wp);
+        if (tr < 1 || tr + kh - 1 > 256) continue;
+        const size_t img_plane = align_up(size_t(mb * 128 + (kh - 1) * wp + (kw - 1)) * 64, 512);
+        const size_t fixed = three ? ConvPixCfg<3>::fixed_bytes(img_plane) : ConvPixCfg<2>::fixed_bytes(img_plane);
+        if (fixed >= smem_limit) continue;
+        const bool resident = tiles_n == 1 && fixed + size_t(taps) * cbs * planes * w_tile <= smem_limit;
+        int w_stages = taps * cbs;
+        if (!resident) {
+          w_stages = int(std::min<size_t>(ConvPixCfg<2>::MAX_W_STAGES, (smem_limit - fixed) / (planes * w_tile)));
+          if (w_stages < 3) continue;
+        }
+        const double tiles = double(tiles_n) * ((out_w + tc - 1) / tc) * ((out_h + tr - 1) / tr) * n;
+        const double mma_ns = double(mb) * taps * cbs * 2 * products * t_mma;
+        const double tma_ns = (double(tr + kh - 1) * wp * cbs * nsplit + (resident ? 0.0 : double(taps) * cbs * nsplit * n_tile)) * 4.1;
+        const double cost = std::ceil(tiles / h->sm_count) * (std::max(mma_ns, tma_ns) + 500.0);
+        if (cost < best.cost) best = {cost, tr, tc, wp, mb, w_stages, resident, img_plane};
+      }
+    const int vbyte = (f32_mode >> 8) & 0xff;    // test hooks: 0xFB = the channels-on-M halo kernel, 0xFC = the per-tap kernel
+    if (best.tr >= 1 && taps <= ConvPixCfg<2>::MAX_TAPS && vbyte != 0xFB && vbyte != 0xFC) {
+      ConvPixArgs a = {};
+      a.n_out = rows; a.out_h = out_h; a.out_w = out_w; a.batch = n;
+      a.C = out; a.bias = bias; a.mode = gemm_mode; a.planes_per_mat = planes;
+      a.exp_w = f16 ? ea : nullptr; a.exp_img = f16 ? eb : nullptr;
+      a.tr = best.tr; a.tc = best.tc; a.wp = best.wp; a.hh = best.tr + kh - 1; a.mb = best.mb; a.n_tile = n_tile;
+      a.kh = kh; a.kw = kw; a.cbs = cbs; a.chan_p = chan_p;
+      a.flip = sgn < 0 ? 1 : 0;
+      a.w_org = w0 - (a.flip ? kw - 1 : 0);
+      a.h_org = h0 - (a.flip ? kh - 1 : 0);
+      a.img_plane_bytes = uint32_t(best.img_plane);
+      a.w_tile_bytes = uint32_t(w_tile);
+      a.w_stages = best.w_stages; a.w_resident = best.resident ? 1 : 0;
+      a.status = h->status;
+      CUtensorMap tw, ti;
+      rc = make_split_tmap(&tw, p_w, Kp, rows, planes, 32, uint32_t(n_tile));
+      if (rc) return rc;
+      rc = image_plane_tmap(&ti, p_img, chan_p, img_w, img_h, n, planes, 32, uint32_t(a.wp), uint32_t(a.hh),
+                            CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc) return rc;
+      const long long tiles = static_cast<long long>(tiles_n) * ((out_w + a.tc - 1) / a.tc) * ((out_h + a.tr - 1) / a.tr) * n;
+      const int grid = int(std::min<long long>(tiles, h->sm_count));
+      const size_t smem = three ? ConvPixCfg<3>::smem_bytes(a.img_plane_bytes, w_tile, a.w_stages)
+                                : ConvPixCfg<2>::smem_bytes(a.img_plane_bytes, w_tile, a.w_stages);
+      ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
+      if (three) {
+        MTB_CUDA(cudaFuncSetAttribute(conv_pix_umma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        conv_pix_umma_kernel<3><<<grid, ConvPixCfg<3>::NUM_THREADS, smem, h->stream>>>(tw, ti, a);
+      } else {
+        MTB_CUDA(cudaFuncSetAttribute(conv_pix_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        conv_pix_umma_kernel<2><<<grid, ConvPixCfg<2>::NUM_THREADS, smem, h->stream>>>(tw, ti, a);
+      }
+      MTB_CUDA(cudaGetLastError());
+      return MTB200_OK;
+    }
+  }
+
+  // Halo kernel (conv_halo_umma.cuh): the image block is staged once per (row block, channel block) and every tap
+  // multiplies against it.  Geometry: halo row pitch wh (a multiple of 4), th output rows per tile with th * wh <= 256
+  // MMA columns, and image stages that fit beside the weights - all of them resident when they fit, a ring otherwise.
+  // Very wide rows or very tall filters take the per-tap kernel below.
+  {
+    const int wh = (out_w + kw - 1 + 3) / 4 * 4;
+    const bool three = planes == 3;
+    const size_t smem_limit = 232448;
+    const int cbs = chan_p / 32;
+    auto plane_bytes_for = [&](int th_) {
+      const int un = (th_ * wh + 15) / 16 * 16;
+      return align_up(size_t((kh - 1) * wh + (kw - 1) + un) * 64, 1024);
+    };
+    auto fixed_for = [&](int th_) {
+      return three ? ConvHaloCfg<3>::fixed_bytes(plane_bytes_for(th_)) : ConvHaloCfg<2>::fixed_bytes(plane_bytes_for(th_));
+    };
+    const int a_rows = rows <= 64 ? 64 : 128;
+    const size_t a_stage = three ? ConvHaloCfg<3>::a_stage_bytes(a_rows) : ConvHaloCfg<2>::a_stage_bytes(a_rows);
+    const int th_max = wh <= 256 ? std::min(out_h, 256 / wh) : 0;
+    // resident weights: the tallest tile that leaves room for every (tap, channel block) tile; worth it while the
+    // MMA keeps a useful width
+    int th_res = 0;
+    if (rows <= 128 && size_t(taps) * cbs * a_stage < smem_limit) {
+      th_res = th_max;
+      while (th_res >= 1 && fixed_for(th_res) + size_t(taps) * cbs * a_stage > smem_limit) --th_res;
+      if (th_res >= 1 && th_res * wh < 96 && th_res < th_max) th_res = 0;
+    }
+    // streamed weights: the tallest tile that leaves a ring of at least four tiles
+    auto ring_for = [&](int th_) {
+      const size_t fixed = fixed_for(th_);
+      if (fixed + 2 * a_stage > smem_limit) return 0;
+      return int(std::min<size_t>(ConvHaloCfg<2>::MAX_A_STAGES, (smem_limit - fixed) / a_stage));
+    };
+    int th_ring = th_max;
+    while (th_ring > 1 && ring_for(th_ring) < 4) --th_ring;
+    const bool resident = th_res >= 1;
+    const int th_h = resident ? th_res : th_ring;
+    const bool per_tap_forced = ((f32_mode >> 8) & 0xff) == 0xFC;   // test hook: the per-tap kernel
+    if (th_h >= 1 && th_h + kh - 1 <= 256 && taps <= ConvHaloCfg<2>::MAX_TAPS && (resident || ring_for(th_h) >= 3) &&
+        !per_tap_forced) {
+      ConvHaloArgs a = {};
+      a.M = rows; a.out_h = out_h; a.out_w = out_w; a.batch = n;
+      a.C = out; a.bias = bias; a.mode = gemm_mode; a.planes_per_mat = planes;
+      a.exp_a = f16 ? ea : nullptr; a.exp_b = f16 ? eb : nullptr;
+      a.th = th_h; a.wh = wh; a.hh = th_h + kh - 1; a.umma_n = (th_h * wh + 15) / 16 * 16;
+      a.kh = kh; a.kw = kw; a.cbs = cbs; a.chan_p = chan_p;
+      a.flip = sgn < 0 ? 1 : 0;
+      a.w_org = w0 - (a.flip ? kw - 1 : 0);
+      a.h_org = h0 - (a.flip ? kh - 1 : 0);
+      a.b_plane_bytes = uint32_t(plane_bytes_for(th_h));
+      a.a_rows = a_rows;
+      a.a_resident = resident ? 1 : 0;
+      a.a_stages = resident ? taps * cbs : ring_for(th_h);
+      a.status = h->status;
+      CUtensorMap ta, tb;
+      rc = make_split_tmap(&ta, p_w, Kp, rows, planes, 32, uint32_t(a_rows));
+      if (rc) return rc;
+      rc = image_plane_tmap(&tb, p_img, chan_p, img_w, img_h, n, planes, 32, uint32_t(wh), uint32_t(a.hh),
+                            CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc) return rc;
+      const long long tiles = static_cast<long long>((rows + 127) / 128) * ((out_h + th_h - 1) / th_h) * n;
+      const int grid = int(std::min<long long>(tiles, h->sm_count));
+      const size_t smem = three ? ConvHaloCfg<3>::smem_bytes(a.b_plane_bytes, a_rows, a.a_stages)
+                                : ConvHaloCfg<2>::smem_bytes(a.b_plane_bytes, a_rows, a.a_stages);
+      ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
+      if (three) {
+        MTB_CUDA(cudaFuncSetAttribute(conv_halo_umma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        conv_halo_umma_kernel<3><<<grid, ConvHaloCfg<3>::NUM_THREADS, smem, h->stream>>>(ta, tb, a);
+      } else {
+        MTB_CUDA(cudaFuncSetAttribute(conv_halo_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        conv_halo_umma_kernel<2><<<grid, ConvHaloCfg<2>::NUM_THREADS, smem, h->stream>>>(ta, tb, a);
+      }
+      MTB_CUDA(cudaGetLastError());
+      return MTB200_OK;
+    }
   }
 
   int th = std::max(1, 256 / out_w);
@@ -627,7 +806,7 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_out, 0, 1}, ob{sp, opix, g.n > 1, g.n};
   rc = run_split_gemm(h, oa, ob, Kp, g.n, g.c_out, opix, y, opix, static_cast<long long>(g.c_out) * opix,
-                      bias, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff, /*bias_per_row=*/1);
+                      bias, EPI_NONE, nullptr, bf16_mode_of(f32_mode), gemm_variant_of(f32_mode), /*bias_per_row=*/1);
   return rc ? rc : redo();
 }
 
@@ -683,7 +862,7 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
   MTB_CUDA(cudaGetLastError());
   SplitOperand oa{sw_, g.c_in, 0, 1}, ob{sp, ipix, g.n > 1, g.n};
   rc = run_split_gemm(h, oa, ob, Kp, g.n, g.c_in, ipix, dx, ipix, static_cast<long long>(g.c_in) * ipix,
-                      nullptr, EPI_NONE, nullptr, bf16_mode_of(f32_mode), force_explicit ? 0 : (f32_mode >> 8) & 0xff);
+                      nullptr, EPI_NONE, nullptr, bf16_mode_of(f32_mode), gemm_variant_of(f32_mode));
   return rc ? rc : redo();
 }
 
@@ -766,7 +945,7 @@ int32_t mtb200_conv2d_bwd_bias(mtb200_handle h, int64_t n, int64_t c_out, int64_
     return MTB200_OK;
   }
   if (!dy) return fail(MTB200_ERR_INVALID, "null input pointer");
-  int chunks = int(std::min<int64_t>(n, std::max<int64_t>(1, (4 * h->sm_count) / c_out)));
+  int chunks = int(std::min<int64_t>(n, std::max<int64_t>(1, (16 * h->sm_count) / c_out)));
   chunks = std::min(chunks, 65535);
   const int per = int((n + chunks - 1) / chunks);
   chunks = int((n + per - 1) / per);

@@ -171,14 +171,22 @@ def test_full_size_layer_properties(be):
 
 @pytest.mark.parametrize("geom", [g for g in GEOMS if g[7] == (1, 1)] + [(2, 5, 9, 300, 3, 3, 3, (1, 1), (1, 1)),
                                                                          (1, 70, 6, 13, 9, 3, 3, (1, 1), (2, 2)),
-                                                                         (3, 2, 20, 5, 4, 2, 4, (1, 1), (0, 3))])
-@pytest.mark.parametrize("lowering", ["implicit", "explicit"])
+                                                                         (3, 2, 20, 5, 4, 2, 4, (1, 1), (0, 3)),
+                                                                         (2, 40, 23, 61, 140, 5, 5, (1, 1), (2, 2)),
+                                                                         (2, 33, 9, 250, 20, 3, 3, (1, 1), (1, 1)),
+                                                                         (1, 8, 40, 12, 8, 7, 7, (1, 1), (3, 3)),
+                                                                         (2, 6, 5, 254, 4, 1, 3, (1, 1), (0, 2))])
+@pytest.mark.parametrize("lowering", ["implicit", "implicit_bf16x6", "channels_on_m", "channels_on_m_bf16x6", "per_tap",
+                                      "explicit"])
 def test_both_lowerings_match_oracle(be, orc, rng, geom, lowering):
-    """Stride-1 forward and data gradient exist twice: as implicit GEMM over channels-last planes
-    (default; falls back by itself when a row is wider than 256) and as the gathered-patch lowering
-    (forced here with the variant byte 0xff)."""
+    """Stride-1 forward and data gradient exist four times.  Implicit GEMM over channels-last planes with the image
+    block staged once per channel block as a halo tile: output pixels on the MMA's M side (default; two fp16 planes,
+    or three bf16 planes when a bf16 mode is asked for) or output channels on the M side (variant byte 0xfb).
+    Implicit GEMM that fetches the window of every tap (variant byte 0xfc; the last resort of the implicit path).
+    And the gathered-patch lowering (variant byte 0xff; taken by itself when a row is wider than 256)."""
     n, c, h, w, co, kh, kw, stride, padding = geom
-    mode = 0 if lowering == "implicit" else 0xFF00
+    mode = {"implicit": 0, "implicit_bf16x6": 6, "channels_on_m": 0xFB00, "channels_on_m_bf16x6": 0xFB06,
+            "per_tap": 0xFC00, "explicit": 0xFF00}[lowering]
     xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
     wn = (rng.standard_normal((co, c, kh, kw)) * np.sqrt(2.0 / (c * kh * kw))).astype(np.float32)
     bn = rng.standard_normal(co).astype(np.float32)
