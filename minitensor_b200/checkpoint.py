@@ -1,5 +1,7 @@
-"""Checkpoints in the reference's JSON model format, read and written from device buffers, with the optimizer
-state the reference leaves out.
+"""Checkpoints in the reference's model formats - JSON, bincode (``.bin``) and MessagePack (``.msgpack``) - read and
+written from device buffers, with the optimizer state the reference leaves out.  The format follows the file
+extension as ``ModelSerializer::save_auto`` / ``load_auto`` do (``engine/src/serialization.rs:490-520``: ``.json``,
+``.msgpack``, anything else binary); the two binary encodings are in :mod:`minitensor_b200.serial_formats`.
 
 The layout is what ``serde_json`` produces for ``SerializedModel`` (``engine/src/serialization.rs:345-357``):
 ``metadata`` (``ModelMetadata``, ``:64-105``, with ``version`` = ``ModelVersion`` ``:20-47``), ``state_dict`` with
@@ -25,6 +27,8 @@ from typing import Dict, Mapping, Optional, Tuple
 
 import numpy as np
 import torch
+
+from . import serial_formats
 
 FORMAT_VERSION = (1, 0, 0)          # ModelVersion::current()
 ENGINE_VERSION = "minitensor_b200"
@@ -57,7 +61,7 @@ def serialize_tensor(t) -> dict:
         "shape": {"dims": [int(d) for d in arr.shape]},
         "dtype": _DTYPE_NAMES[arr.dtype],
         "device": {"device_type": "Cpu" if ordinal is None else "Cuda", "device_id": ordinal},
-        "data": np.frombuffer(raw, dtype=np.uint8).tolist(),
+        "data": np.frombuffer(raw, dtype=np.uint8),      # a list of integers once it is written as JSON
         "requires_grad": requires_grad,
     }
 
@@ -107,17 +111,50 @@ def save_checkpoint(path: str, parameters: Mapping[str, object], buffers: Option
         "state_dict": {"parameters": {k: serialize_tensor(v) for k, v in parameters.items()}, "buffers": all_buffers},
         "architecture_config": architecture_config,
     }
-    with open(path, "w") as f:
-        json.dump(model, f)
+    write_model(path, model)
+
+
+def format_of(path: str) -> str:
+    """"json", "msgpack" or "binary" by file extension (``save_auto`` / ``load_auto``)."""
+    ext = path.rsplit(".", 1)[-1].lower() if "." in path.rsplit("/", 1)[-1] else ""
+    return {"json": "json", "msgpack": "msgpack"}.get(ext, "binary")
+
+
+def write_model(path: str, model: dict) -> None:
+    fmt = format_of(path)
+    if fmt == "json":
+        class _Enc(json.JSONEncoder):
+            def default(self, o):
+                if isinstance(o, np.ndarray):
+                    return o.tolist()
+                return super().default(o)
+        with open(path, "w") as f:
+            json.dump(model, f, cls=_Enc)
+        return
+    blob = serial_formats.encode_msgpack(model) if fmt == "msgpack" else serial_formats.encode_bincode(model)
+    with open(path, "wb") as f:
+        f.write(blob)
+
+
+def read_model(path: str) -> dict:
+    fmt = format_of(path)
+    try:
+        if fmt == "json":
+            with open(path) as f:
+                return json.load(f)
+        with open(path, "rb") as f:
+            blob = f.read()
+        return serial_formats.decode_msgpack(blob) if fmt == "msgpack" else serial_formats.decode_bincode(blob)
+    except json.JSONDecodeError as exc:
+        raise SerializationError(f"JSON deserialization failed: {exc}") from None
+    except serial_formats.FormatError as exc:
+        kind = "MessagePack" if fmt == "msgpack" else "Binary"
+        raise SerializationError(f"{kind} deserialization failed: {exc}") from None
 
 
 def load_checkpoint(path: str, device: Optional[torch.device] = None):
     """Returns ``(parameters, buffers, optimizer_buffers, optimizer_scalars, metadata)``; tensors go to ``device``."""
-    with open(path) as f:
-        try:
-            model = json.load(f)
-        except json.JSONDecodeError as exc:
-            raise SerializationError(f"JSON deserialization failed: {exc}") from None
+    model = read_model(path)
     try:
         meta = model["metadata"]
         version = meta["version"]

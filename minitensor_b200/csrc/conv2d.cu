@@ -482,10 +482,10 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
                                 : ConvPixCfg<2>::smem_bytes(a.img_plane_bytes, w_tile, a.w_stages);
       ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
       if (three) {
-        MTB_CUDA(cudaFuncSetAttribute(conv_pix_umma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        if (int32_t rc_attr = grant_dynamic_smem(h, conv_pix_umma_kernel<3>, int(int(smem)))) return rc_attr;
         conv_pix_umma_kernel<3><<<grid, ConvPixCfg<3>::NUM_THREADS, smem, h->stream>>>(tw, ti, a);
       } else {
-        MTB_CUDA(cudaFuncSetAttribute(conv_pix_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        if (int32_t rc_attr = grant_dynamic_smem(h, conv_pix_umma_kernel<2>, int(int(smem)))) return rc_attr;
         conv_pix_umma_kernel<2><<<grid, ConvPixCfg<2>::NUM_THREADS, smem, h->stream>>>(tw, ti, a);
       }
       MTB_CUDA(cudaGetLastError());
@@ -559,10 +559,10 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
                                 : ConvHaloCfg<2>::smem_bytes(a.b_plane_bytes, a_rows, a.a_stages);
       ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
       if (three) {
-        MTB_CUDA(cudaFuncSetAttribute(conv_halo_umma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        if (int32_t rc_attr = grant_dynamic_smem(h, conv_halo_umma_kernel<3>, int(int(smem)))) return rc_attr;
         conv_halo_umma_kernel<3><<<grid, ConvHaloCfg<3>::NUM_THREADS, smem, h->stream>>>(ta, tb, a);
       } else {
-        MTB_CUDA(cudaFuncSetAttribute(conv_halo_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        if (int32_t rc_attr = grant_dynamic_smem(h, conv_halo_umma_kernel<2>, int(int(smem)))) return rc_attr;
         conv_halo_umma_kernel<2><<<grid, ConvHaloCfg<2>::NUM_THREADS, smem, h->stream>>>(ta, tb, a);
       }
       MTB_CUDA(cudaGetLastError());
@@ -605,11 +605,11 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
   if (f16) {   // two planes per operand: four stages of 48 KB instead of three of 72 KB
     using Cfg2 = GemmCfg<256, BK, 4, 2>;
     auto kern = gemm_split_umma_kernel<256, BK, 4, true, 2>;
-    MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::SMEM_BYTES));
+    if (int32_t rc_attr = grant_dynamic_smem(h, kern, int(Cfg2::SMEM_BYTES))) return rc_attr;
     kern<<<grid, Cfg2::NUM_THREADS, Cfg2::SMEM_BYTES, h->stream>>>(ta, tb, g);
   } else {
     auto kern = gemm_split_umma_kernel<256, BK, 3, true>;
-    MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    if (int32_t rc_attr = grant_dynamic_smem(h, kern, int(Cfg::SMEM_BYTES))) return rc_attr;
     kern<<<grid, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(ta, tb, g);
   }
   MTB_CUDA(cudaGetLastError());
@@ -719,11 +719,11 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.c_out * double(opix) * taps * g.c_in * g.n);
     if (f16) {
       using Cfg = WgradCfg<2>;
-      MTB_CUDA(cudaFuncSetAttribute(conv_wgrad_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+      if (int32_t rc_attr = grant_dynamic_smem(h, conv_wgrad_umma_kernel<2>, int(Cfg::SMEM_BYTES))) return rc_attr;
       conv_wgrad_umma_kernel<2><<<a.splits * tiles, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(tdy, tx, a);
     } else {
       using Cfg = WgradCfg<3>;
-      MTB_CUDA(cudaFuncSetAttribute(conv_wgrad_umma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+      if (int32_t rc_attr = grant_dynamic_smem(h, conv_wgrad_umma_kernel<3>, int(Cfg::SMEM_BYTES))) return rc_attr;
       conv_wgrad_umma_kernel<3><<<a.splits * tiles, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(tdy, tx, a);
     }
     MTB_CUDA(cudaGetLastError());

@@ -284,10 +284,16 @@ inline int32_t dense_forward_f32(mtb200_ctx* h, int M, int in, int out, const fl
   int32_t rc = call_flag_begin(h, &nf_word);
   if (rc) return rc;
   const uint32_t epoch = MTB_FLAG_SET;
-  rc = launch_split16(h, x, true, M, in, 1, 0, xp, xe, nf_word, epoch);
-  if (rc) return rc;
-  rc = launch_split16(h, W, true, out, in, 1, 0, wp, we, nf_word, epoch);
-  if (rc) return rc;
+  if (prep16_pair_eligible(x, true, in, 1, 0) && prep16_pair_eligible(W, true, in, 1, 0)) {
+    rc = launch_prep16_pair(h, prep16_operand(h, x, true, M, in, 1, 0, xp, xe),
+                            prep16_operand(h, W, true, out, in, 1, 0, wp, we), nf_word, epoch);
+    if (rc) return rc;
+  } else {
+    rc = launch_split16(h, x, true, M, in, 1, 0, xp, xe, nf_word, epoch);
+    if (rc) return rc;
+    rc = launch_split16(h, W, true, out, in, 1, 0, wp, we, nf_word, epoch);
+    if (rc) return rc;
+  }
   save_nonfinite_flag_kernel<<<1, 1, 0, h->stream>>>(nf_word, epoch, flag);
   SplitOperand oa{reinterpret_cast<const __nv_bfloat16*>(xp), M, 0, 1, 0, L.inp, 2, xe};
   SplitOperand ob{reinterpret_cast<const __nv_bfloat16*>(wp), out, 0, 1, 0, L.inp, 2, we};

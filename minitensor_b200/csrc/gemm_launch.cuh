@@ -6,8 +6,10 @@
 #include "gemm_split_umma2.cuh"
 #include "split_bf16.cuh"
 #include "split_f16.cuh"
+#include "prep_f16.cuh"
 #include "gemm_f64_int.cuh"
 #include <algorithm>
+#include <cstdlib>
 
 namespace mtb {
 
@@ -60,7 +62,7 @@ inline int32_t launch_variant(mtb200_ctx* h, const SplitOperand& a, const SplitO
   using Cfg = GemmCfg<BN, BK, STAGES>;
   auto kern = gemm_split_umma_kernel<BN, BK, STAGES>;
   // per-device attribute; setting it on every launch keeps multi-device processes correct
-  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  if (int32_t rc_attr = grant_dynamic_smem(h, kern, int(Cfg::SMEM_BYTES))) return rc_attr;
   CUtensorMap ta, tb;
   int32_t rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(a.nplanes) * a.batch, BK, Cfg::BM);
   if (rc) return rc;
@@ -100,7 +102,7 @@ template <typename Kern>
 inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int threads, long long tiles,
                                   const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, double work,
                                   bool allow_tail = false, int prof_class = PROF_GEMM_UMMA) {
-  MTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  if (int32_t rc_attr = grant_dynamic_smem(h, kern, int(smem_bytes))) return rc_attr;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -114,10 +116,18 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
   cfg.numAttrs = 1;
   const int sms = (h->gemm_sm_limit > 0) ? std::min(h->gemm_sm_limit, h->sm_count) : h->sm_count;
   cfg.gridDim = dim3(2 * (sms / 2));
+  // clusters of this kernel the device can hold at once: asked once per kernel and SM limit
+  const void* occ_key = reinterpret_cast<const char*>(reinterpret_cast<const void*>(kern)) + sms;
   int max_clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0) {
-    cudaGetLastError();
-    max_clusters = sms / 2;
+  auto occ = h->cluster_occupancy.find(occ_key);
+  if (occ != h->cluster_occupancy.end()) {
+    max_clusters = occ->second;
+  } else {
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0) {
+      cudaGetLastError();
+      max_clusters = sms / 2;
+    }
+    h->cluster_occupancy[occ_key] = max_clusters;
   }
   const int max_pairs = std::min(max_clusters, sms / 2);
   int pairs = int(std::min<long long>(tiles, max_pairs));
@@ -268,6 +278,47 @@ inline int32_t launch_split16(mtb200_ctx* h, const float* src, bool k_major, int
   return MTB200_OK;
 }
 
+// Both operands of an fp16-mode product in ONE launch (prep_f16.cuh).  Returns false when an operand does not meet
+// the kernel's conditions (a rows-mode operand must be readable as float4 and at most 8192 long); the caller then
+// prepares the operands one by one.
+inline bool prep16_pair_eligible(const float* src, bool k_major, int K, int batch, long long bstride) {
+  if (!k_major) return true;
+  return (K % 4 == 0) && padded_k(K) <= 8192 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
+         (batch == 1 || (bstride & 3) == 0);
+}
+inline PrepOperand prep16_operand(const mtb200_ctx* h, const float* src, bool k_major, int mn, int K, int batch,
+                                  long long bstride, __half* planes, int* expo) {
+  PrepOperand o;
+  o.src = src; o.bstride = bstride; o.planes = planes; o.expo = expo;
+  o.kmajor = k_major ? 1 : 0; o.mn = mn; o.K = K; o.batch = batch;
+  if (k_major) {
+    o.ld = K; o.pitch = padded_k(K);
+    o.blocks = std::min((mn + 7) / 8 * 8, 8 * 1024);
+  } else {
+    o.ld = mn; o.pitch = padded_k(mn);
+    const int strips = (mn + 63) / 64;
+    o.blocks = 8 * std::min(strips, std::max(1, 2 * h->sm_count));
+  }
+  return o;
+}
+inline int32_t launch_prep16_pair(mtb200_ctx* h, const PrepOperand& a, const PrepOperand& b, uint32_t* nf_word,
+                                  uint32_t nf_value) {
+  int kp_rows = 0;
+  if (a.kmajor) kp_rows = std::max(kp_rows, a.pitch);
+  if (b.kmajor) kp_rows = std::max(kp_rows, b.pitch);
+  auto bytes_of = [](const PrepOperand& o) {
+    return double(o.batch) * o.mn * (4.0 * o.K * (o.kmajor ? 1.0 : 2.0)) + double(o.batch) * 4.0 * (o.kmajor ? double(o.mn) * o.pitch : double(o.K) * o.pitch);
+  };
+  ProfScope prof(h, PROF_SPLIT, bytes_of(a) + bytes_of(b));
+  const dim3 grid(unsigned(a.blocks + b.blocks), unsigned(std::max(a.batch, b.batch)));
+  if (kp_rows <= 1024) prep16_pair_kernel<1><<<grid, 256, 0, h->stream>>>(a, b, nf_word, nf_value);
+  else if (kp_rows <= 2048) prep16_pair_kernel<2><<<grid, 256, 0, h->stream>>>(a, b, nf_word, nf_value);
+  else if (kp_rows <= 4096) prep16_pair_kernel<4><<<grid, 256, 0, h->stream>>>(a, b, nf_word, nf_value);
+  else prep16_pair_kernel<8><<<grid, 256, 0, h->stream>>>(a, b, nf_word, nf_value);
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
 // f32 GEMM in the fp16 two-plane mode (pair-tile kernel only).
 inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int batch, int M, int N, int K,
                                   const float* A, long long stride_a, const float* B, long long stride_b, float* C,
@@ -295,19 +346,30 @@ inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int
   rc = call_flag_begin(h, &nf_word);
   if (rc) return rc;
   const uint32_t epoch = MTB_FLAG_SET;
-  // Operands of up to 32 M elements each do not fill the memory system alone (a 4096^2 split runs at a third to
-  // a half of the DRAM rate): B is then prepared on the side stream while A is prepared on the caller's.
-  const bool side_by_side = h->side_stream && !h->profiling &&
+  // Both operands in one launch when they qualify (the usual case); otherwise one by one, side by side on two
+  // streams when they are small enough not to fill the memory system alone.
+  static const double pair_max = getenv("MTB200_PREP_PAIR_MAX") ? atof(getenv("MTB200_PREP_PAIR_MAX")) : 1e18;
+  const bool pair = batch <= 65535 && prep16_pair_eligible(A, a_kmaj, K, batch_a, stride_a) &&
+                    prep16_pair_eligible(B, b_kmaj, K, batch_b, stride_b) &&
+                    (double(batch_a) * M + double(batch_b) * N) * K <= pair_max;
+  if (pair) {
+    rc = launch_prep16_pair(h, prep16_operand(h, A, a_kmaj, M, K, batch_a, stride_a, pa, ea),
+                            prep16_operand(h, B, b_kmaj, N, K, batch_b, stride_b, pb, eb), nf_word, epoch);
+    if (rc) return rc;
+  }
+  const bool side_by_side = !pair && h->side_stream && !h->profiling &&
                             double(batch_a) * M * K <= 33554432.0 && double(batch_b) * N * K <= 33554432.0;
   if (side_by_side) {
     MTB_CUDA(cudaEventRecord(h->ev_fork, h->stream));
     MTB_CUDA(cudaStreamWaitEvent(h->side_stream, h->ev_fork, 0));
   }
-  rc = launch_split16(h, A, a_kmaj, M, K, batch_a, stride_a, pa, ea, nf_word, epoch);
-  if (rc) return rc;
-  rc = launch_split16(h, B, b_kmaj, N, K, batch_b, stride_b, pb, eb, nf_word, epoch,
-                      side_by_side ? h->side_stream : nullptr);
-  if (rc) return rc;
+  if (!pair) {
+    rc = launch_split16(h, A, a_kmaj, M, K, batch_a, stride_a, pa, ea, nf_word, epoch);
+    if (rc) return rc;
+    rc = launch_split16(h, B, b_kmaj, N, K, batch_b, stride_b, pb, eb, nf_word, epoch,
+                        side_by_side ? h->side_stream : nullptr);
+    if (rc) return rc;
+  }
   if (side_by_side) {
     MTB_CUDA(cudaEventRecord(h->ev_join, h->side_stream));
     MTB_CUDA(cudaStreamWaitEvent(h->stream, h->ev_join, 0));

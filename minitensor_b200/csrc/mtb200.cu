@@ -151,7 +151,7 @@ static int32_t gemm_i32_limb(mtb200_ctx* h, bool trans_a, bool trans_b, int batc
   if (rc) return rc;
   rc = make(&tb, pb, N, 4 * batch_b);
   if (rc) return rc;
-  MTB_CUDA(cudaFuncSetAttribute(gemm_i32_limb_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  if (int32_t rc_attr = grant_dynamic_smem(h, gemm_i32_limb_umma_kernel, int(Cfg::SMEM_BYTES))) return rc_attr;
   I32LimbArgs g = {};
   g.M = M; g.N = N; g.batch = batch;
   g.C = reinterpret_cast<uint32_t*>(C); g.strideC = stride_c;
@@ -492,7 +492,7 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
   ProfScope prof(h, dtype == MTB200_F64 ? PROF_GEMM_F64 : PROF_GEMM_INT, 2.0 * M * N * K * batch);
   if (dtype == MTB200_F64) {
     const int smem = 4 * D_BK * D_PITCH * int(sizeof(double));
-    MTB_CUDA(cudaFuncSetAttribute(gemm_f64_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (int32_t rc_attr = grant_dynamic_smem(h, gemm_f64_dmma_kernel, int(smem))) return rc_attr;
     const long long tiles = ((M + D_BM - 1) / D_BM) * ((N + D_BN - 1) / D_BN);
     gemm_f64_dmma_kernel<<<dim3(unsigned(tiles), unsigned(batch)), 256, smem, h->stream>>>(g);
   } else if (dtype == MTB200_I32) {

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/mtb200.h"
@@ -62,6 +63,10 @@ struct mtb200_ctx {
   struct ProfRec { cudaEvent_t start, stop; double work; int cls; };
   bool profiling = false;
   std::vector<ProfRec> prof;
+  // per-kernel set-up that costs microseconds of host time and does not change: the largest dynamic shared-memory
+  // size already granted to a kernel on this device, and the cluster occupancy of the pair-tile kernels
+  std::unordered_map<const void*, int> smem_granted;
+  std::unordered_map<const void*, int> cluster_occupancy;
 };
 
 namespace mtb {
@@ -99,6 +104,18 @@ int32_t make_split_tmap(CUtensorMap* out, const void* base, uint64_t Kp, uint64_
                         uint64_t planes, uint32_t bk, uint32_t box_rows);
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize for `fn` on the handle's device, raised only when a launch needs more
+// than an earlier one asked for (the attribute is per device and per function; the handle is per device).
+template <typename Fn>
+inline int32_t grant_dynamic_smem(mtb200_ctx* h, Fn fn, int bytes) {
+  const void* key = reinterpret_cast<const void*>(fn);
+  auto it = h->smem_granted.find(key);
+  if (it != h->smem_granted.end() && it->second >= bytes) return MTB200_OK;
+  MTB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  h->smem_granted[key] = bytes;
+  return MTB200_OK;
+}
 
 // Per-call flag word (see the status layout above): takes the next slot of the ring and clears it on
 // the handle's stream.  Kernels raise it with atomicMax(word, MTB_FLAG_SET); gated kernels run when
