@@ -284,7 +284,8 @@ inline int32_t dense_forward_f32(mtb200_ctx* h, int M, int in, int out, const fl
   int32_t rc = call_flag_begin(h, &nf_word);
   if (rc) return rc;
   const uint32_t epoch = MTB_FLAG_SET;
-  if (prep16_pair_eligible(x, true, in, 1, 0) && prep16_pair_eligible(W, true, in, 1, 0)) {
+  if ((double(M) + double(out)) * in <= 2.2e6 && prep16_pair_eligible(x, true, in, 1, 0) &&
+      prep16_pair_eligible(W, true, in, 1, 0)) {
     rc = launch_prep16_pair(h, prep16_operand(h, x, true, M, in, 1, 0, xp, xe),
                             prep16_operand(h, W, true, out, in, 1, 0, wp, we), nf_word, epoch);
     if (rc) return rc;

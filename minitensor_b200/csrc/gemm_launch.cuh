@@ -346,12 +346,13 @@ inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int
   rc = call_flag_begin(h, &nf_word);
   if (rc) return rc;
   const uint32_t epoch = MTB_FLAG_SET;
-  // Both operands in one launch when they qualify (the usual case); otherwise one by one, side by side on two
-  // streams when they are small enough not to fill the memory system alone.
-  static const double pair_max = getenv("MTB200_PREP_PAIR_MAX") ? atof(getenv("MTB200_PREP_PAIR_MAX")) : 1e18;
-  const bool pair = batch <= 65535 && prep16_pair_eligible(A, a_kmaj, K, batch_a, stride_a) &&
-                    prep16_pair_eligible(B, b_kmaj, K, batch_b, stride_b) &&
-                    (double(batch_a) * M + double(batch_b) * N) * K <= pair_max;
+  // Small products: both operands in one launch.  Otherwise one by one, side by side on two streams when they are
+  // small enough not to fill the memory system alone.
+  // (measured: for products up to about 1024^3 the single launch wins - 512^3 53 -> 39 us, 1024^3 57 -> 49 us whole
+  // call - beyond that the two tuned kernels running side by side do)
+  const bool pair = batch == 1 && (double(M) + double(N)) * K <= 2.2e6 &&
+                    prep16_pair_eligible(A, a_kmaj, K, batch_a, stride_a) &&
+                    prep16_pair_eligible(B, b_kmaj, K, batch_b, stride_b);
   if (pair) {
     rc = launch_prep16_pair(h, prep16_operand(h, A, a_kmaj, M, K, batch_a, stride_a, pa, ea),
                             prep16_operand(h, B, b_kmaj, N, K, batch_b, stride_b, pb, eb), nf_word, epoch);
