@@ -497,6 +497,20 @@ def dp_check(torch, dist, world, rank, local, comm):
 
 
 def run_ours(args):
+    # stdout carries exactly one JSON line: whatever libraries print on the way (NCCL's version banner, warnings)
+    # goes to stderr; the descriptor is put back just before the line is printed
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        return _run_ours(args, saved_stdout)
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
+
+
+def _run_ours(args, saved_stdout):
     import torch
     import torch.distributed as dist
     from minitensor_b200.mlp import MLPTrainer, mlp_flops_per_sample, shard_rows
@@ -506,7 +520,8 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
-            print(json.dumps({"error": f"--gpus {args.gpus} needs torchrun with {args.gpus} processes"}))
+            os.dup2(saved_stdout, 1)
+            print(json.dumps({"error": f"--gpus {args.gpus} needs torchrun with {args.gpus} processes"}), flush=True)
             return 2
     torch.cuda.set_device(local)
     if world > 1:
@@ -693,7 +708,10 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": f"one reference-ordered training step on {rows_cpu} rows (of "
                                               f"{GLOBAL_BATCH}), {per_step:.2f} s"}
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
     print(json.dumps(line), flush=True)
+    os.dup2(2, 1)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

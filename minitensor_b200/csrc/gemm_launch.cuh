@@ -131,23 +131,36 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
   }
   const int max_pairs = std::min(max_clusters, sms / 2);
   int pairs = int(std::min<long long>(tiles, max_pairs));
-  // A last round that would keep at most half of the pairs busy: cut its tiles into K ranges so that the round
-  // takes 1 / splits of a tile time (4096^3: 256 tiles on 74 pairs, 34 tail tiles -> 68 half tiles).  An output
-  // of at most half as many tiles as there are pairs is all tail: every tile is cut.
+  // A partial last round costs a whole tile time whatever its size.  Cutting each of its `rem` tiles into s K ranges
+  // and dealing the rem * s shorter items out over the pairs costs ceil(rem * s / pairs) / s of a tile time plus the
+  // partial-sum traffic and the fix-up kernel (4096^3: 256 tiles on 74 pairs, 34 tail tiles -> 68 half tiles, half a
+  // tile time; 8192 x 4096 per rank on 70 pairs: 46 tail tiles -> 138 thirds in two short rounds, two thirds).  An
+  // output of fewer tiles than pairs is all tail.
   g.tail_splits = 0;
   if (allow_tail && tiles <= 0x3fffffff) {
     const int rem = tiles > pairs ? int(tiles % pairs) : int(tiles);
-    int splits = rem ? std::min(4, max_pairs / rem) : 0;
-    while (splits >= 2 && g.num_kb < 4 * splits) --splits;
+    int splits = 0;
+    double best = 0.88;     // take a split only when it saves at least an eighth of a tile time
+    for (int s2 = 2; rem && s2 <= 6 && g.num_kb >= 4 * s2; ++s2) {
+      const double t = double((static_cast<long long>(rem) * s2 + max_pairs - 1) / max_pairs) / s2 + 0.03 * s2;
+      if (t < best - 1e-9) { best = t; splits = s2; }
+    }
     if (splits >= 2) {
-      if (!h->tail_partial) {
-        MTB_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->tail_partial), size_t(h->sm_count / 2) * 65536 * sizeof(float)));
+      const size_t slots = size_t(rem) * splits;
+      if (slots > h->tail_partial_slots) {
+        MTB_CUDA(cudaStreamSynchronize(h->stream));
+        if (h->tail_partial) MTB_CUDA(cudaFree(h->tail_partial));
+        h->tail_partial = nullptr;
+        h->tail_partial_slots = 0;
+        const size_t want = std::max(slots, size_t(h->sm_count));
+        MTB_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->tail_partial), want * 65536 * sizeof(float)));
+        h->tail_partial_slots = want;
       }
       g.tail_splits = splits;
       g.tail_rounds = tiles > pairs ? int(tiles / pairs) : 0;
       g.tail_tiles = rem;
       g.partial = h->tail_partial;
-      if (tiles <= pairs) pairs = rem * splits;  // no whole-tile round: one pair per K range
+      if (tiles <= pairs) pairs = int(std::min<long long>(static_cast<long long>(rem) * splits, max_pairs));
     }
   }
   cfg.gridDim = dim3(2 * pairs);

@@ -55,10 +55,10 @@ struct GemmArgs {
   int bias_per_row;    // 0: bias[N] added along columns; 1: bias[M] added along rows
   int kb_batch_stride; // split-K: batch entry b reduces K blocks [b*stride, b*stride + num_kb)
   uint32_t* status;    // device word; a non-zero value reports a wait that ran out
-  // Tail splitting (pair-tile kernel): when the tile count leaves a last round that would occupy at most half of
-  // the SM pairs, each of those tail tiles is cut into tail_splits K ranges that run side by side on different
-  // pairs; the raw partial accumulators go to `partial` ([tail tile][split][256][256] f32) and a second kernel
-  // adds them in a fixed order and applies the epilogue.  tail_splits <= 1: off.
+  // Tail splitting (pair-tile kernel): when the tile count leaves a partial last round, each of its tiles may be
+  // cut into tail_splits K ranges that are dealt out over the SM pairs like (shorter) tiles; the raw partial
+  // accumulators go to `partial` ([tail tile][split][256][256] f32) and a second kernel adds them in a fixed order
+  // and applies the epilogue.  tail_splits <= 1: off.
   // Optional gate (the int8 use of the pair-tile kernel): the kernel returns at once unless
   // (*gate == gate_value) == (gate_run_if_equal != 0).  gate == nullptr: always run.
   const uint32_t* gate;

@@ -65,9 +65,12 @@ __device__ __forceinline__ bool pair_work_item(const GemmArgs& g, int it, int pa
     tile = it * num_pairs + pair;
     return true;
   }
-  if (it == g.tail_rounds && pair < g.tail_tiles * g.tail_splits) {
-    part = pair / g.tail_tiles;
-    tile = g.tail_rounds * num_pairs + (pair - part * g.tail_tiles);
+  // the K ranges of the tail tiles are dealt out like tiles, range-major: item j = range j / tail_tiles of tail
+  // tile j % tail_tiles; there may be more items than pairs (several short rounds)
+  const int j = (it - g.tail_rounds) * num_pairs + pair;
+  if (j < g.tail_tiles * g.tail_splits) {
+    part = j / g.tail_tiles;
+    tile = g.tail_rounds * num_pairs + (j - part * g.tail_tiles);
     kb0 = static_cast<int>(static_cast<long long>(g.num_kb) * part / g.tail_splits);
     kb1 = static_cast<int>(static_cast<long long>(g.num_kb) * (part + 1) / g.tail_splits);
     return true;

@@ -53,7 +53,8 @@ struct mtb200_ctx {
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   int gemm_sm_limit = 0;            // SMs the persistent tensor kernels may occupy (0 = all), see mtb200_set_gemm_sm_limit
-  float* tail_partial = nullptr;    // raw partial accumulators of split tail tiles (one 256 x 256 slot per SM pair)
+  float* tail_partial = nullptr;    // raw partial accumulators of split tail tiles (256 x 256 slots)
+  size_t tail_partial_slots = 0;
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
   uint32_t* status = nullptr;       // device, 4 + MTB_FLAG_SLOTS words
