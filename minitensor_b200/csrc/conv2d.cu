@@ -350,12 +350,17 @@ static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, 
 static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, int img_h, int img_w,
                              const float* wsrc, int rows, int kh, int kw, int mode, int out_h, int out_w,
                              int w0, int h0, int sgn, const float* bias, float* out, int f32_mode,
-                             uint32_t* nf_word) {
+                             uint32_t* nf_word, int sh = 1, int sw = 1, int pad_h = 0, int pad_w = 0) {
+  // sh, sw > 1 (forward only, fp16 mode only - the caller checks): the image planes are written as sh * sw phase
+  // images so that every tap reads a stride-1 window of one of them (conv_pix_umma.cuh).
   constexpr int BK = 32;
   using Cfg = GemmCfg<256, BK, 3>;
   const int chan_p = padded_k(chan), taps = kh * kw;
   const int Kp = taps * chan_p;
+  const int phases = sh * sw;
+  const int hq = (img_h + sh - 1) / sh, wq = (img_w + sw - 1) / sw;          // phase-image extent
   const int ipix = img_h * img_w, opix = out_h * out_w;
+  const int ppix = phases > 1 ? phases * hq * wq : ipix;                      // plane rows per image
   // Default: the fp16 two-plane mode (three products).  The reduction of one output runs over taps and channels
   // of ONE image, so the image operand takes one power-of-two scale per image and the weights one per row; the
   // bf16 modes (three planes, up to nine products, no scaling) stay selectable through the mode byte.
@@ -364,7 +369,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     return fail(MTB200_ERR_INVALID, "unknown f32 mode");
   const bool f16 = gemm_mode == 23;
   const int planes = f16 ? 2 : 3;
-  const size_t bytes_img = split_bytes(ipix, chan_p, n);      // sized for three planes; the fp16 mode uses two
+  const size_t bytes_img = split_bytes(ppix, chan_p, n);      // sized for three planes; the fp16 mode uses two
   const size_t bytes_w = split_bytes(rows, Kp, 1);
   const size_t bytes_tmp = align_up(sizeof(float) * size_t(rows) * Kp, 1024);
   const size_t bytes_ea = align_up(sizeof(int) * size_t(rows), 1024), bytes_eb = align_up(sizeof(int) * size_t(n), 1024);
@@ -387,8 +392,11 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     const int chunks = int(std::max<long long>(1, std::min<long long>((img_elems + 4095) / 4096,
                                                                       (16LL * h->sm_count + n - 1) / n)));
     finite_absmax_kernel<<<dim3(chunks, n), 256, 0, h->stream>>>(img, img_elems, img_elems, amax, nf_word, MTB_FLAG_SET);
+    if (phases > 1 && ppix != ipix)   // phase images have rows / columns no pixel maps to: they must read as zero
+      MTB_CUDA(cudaMemsetAsync(p_img, 0, size_t(2) * n * ppix * chan_p * sizeof(__half), h->stream));
     split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, chan_p / 64, n), 256, 0, h->stream>>>(
-        img, ipix, img_elems, reinterpret_cast<__half*>(p_img), amax, 1, eb, ipix, chan, chan_p);
+        img, ipix, img_elems, reinterpret_cast<__half*>(p_img), amax, 1, eb, ipix, chan, chan_p,
+        RowPhases{img_w, sh, sw, hq, wq});
     MTB_CUDA(cudaGetLastError());
   } else {
     ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (4.0 * chan + 6.0 * chan_p));
@@ -433,14 +441,20 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     const size_t w_tile = size_t(n_tile) * 64;
     struct Plan { double cost; int tr, tc, wp, mb, w_stages; bool resident; size_t img_plane; } best = {1e300, 0, 0, 0, 0, 0, false, 0};
     const double t_mma = std::max(26.7, 0.273 * n_tile) * 1.35;   // ns per MMA under load
+    // halo origin and reach of the taps, in (phase-)image coordinates relative to the output pixel
+    auto fdiv = [](int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); };
+    const int org_x = phases > 1 ? fdiv(-pad_w, sw) : w0 - (sgn < 0 ? kw - 1 : 0);
+    const int org_y = phases > 1 ? fdiv(-pad_h, sh) : h0 - (sgn < 0 ? kh - 1 : 0);
+    const int dxr = phases > 1 ? fdiv(kw - 1 - pad_w, sw) - org_x : kw - 1;    // halo columns beyond the tile's own
+    const int dyr = phases > 1 ? fdiv(kh - 1 - pad_h, sh) - org_y : kh - 1;
     for (int mb = 1; mb <= 4 && 2 * mb * n_tile <= 512; mb *= 2)
       for (int sx = 1; sx <= 16; ++sx) {
         const int tc = (out_w + sx - 1) / sx;
-        const int wp = tc + kw - 1;
+        const int wp = tc + dxr;
         if (wp > 256 || wp > 128 * mb) continue;
         const int tr = std::min(out_h, (128 * mb) / wp);
-        if (tr < 1 || tr + kh - 1 > 256) continue;
-        const size_t img_plane = align_up(size_t(mb * 128 + (kh - 1) * wp + (kw - 1)) * 64, 512);
+        if (tr < 1 || tr + dyr > 256 || phases * (tr + dyr) * wp * 64 > (1 << 20) - 1) continue;
+        const size_t img_plane = align_up(size_t((phases - 1) * (tr + dyr) * wp + mb * 128 + dyr * wp + dxr) * 64, 512);
         const size_t fixed = three ? ConvPixCfg<3>::fixed_bytes(img_plane) : ConvPixCfg<2>::fixed_bytes(img_plane);
         if (fixed >= smem_limit) continue;
         const bool resident = tiles_n == 1 && fixed + size_t(taps) * cbs * planes * w_tile <= smem_limit;
@@ -451,7 +465,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
         }
         const double tiles = double(tiles_n) * ((out_w + tc - 1) / tc) * ((out_h + tr - 1) / tr) * n;
         const double mma_ns = double(mb) * taps * cbs * 2 * products * t_mma;
-        const double tma_ns = (double(tr + kh - 1) * wp * cbs * nsplit + (resident ? 0.0 : double(taps) * cbs * nsplit * n_tile)) * 4.1;
+        const double tma_ns = (double(phases) * (tr + dyr) * wp * cbs * nsplit + (resident ? 0.0 : double(taps) * cbs * nsplit * n_tile)) * 4.1;
         const double cost = std::ceil(tiles / h->sm_count) * (std::max(mma_ns, tma_ns) + 500.0);
         if (cost < best.cost) best = {cost, tr, tc, wp, mb, w_stages, resident, img_plane};
       }
@@ -461,11 +475,12 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
       a.n_out = rows; a.out_h = out_h; a.out_w = out_w; a.batch = n;
       a.C = out; a.bias = bias; a.mode = gemm_mode; a.planes_per_mat = planes;
       a.exp_w = f16 ? ea : nullptr; a.exp_img = f16 ? eb : nullptr;
-      a.tr = best.tr; a.tc = best.tc; a.wp = best.wp; a.hh = best.tr + kh - 1; a.mb = best.mb; a.n_tile = n_tile;
+      a.tr = best.tr; a.tc = best.tc; a.wp = best.wp; a.hh = best.tr + dyr; a.mb = best.mb; a.n_tile = n_tile;
       a.kh = kh; a.kw = kw; a.cbs = cbs; a.chan_p = chan_p;
       a.flip = sgn < 0 ? 1 : 0;
-      a.w_org = w0 - (a.flip ? kw - 1 : 0);
-      a.h_org = h0 - (a.flip ? kh - 1 : 0);
+      a.w_org = org_x;
+      a.h_org = org_y;
+      a.sh = sh; a.sw = sw; a.pad_h = pad_h; a.pad_w = pad_w;
       a.img_plane_bytes = uint32_t(best.img_plane);
       a.w_tile_bytes = uint32_t(w_tile);
       a.w_stages = best.w_stages; a.w_resident = best.resident ? 1 : 0;
@@ -473,8 +488,21 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
       CUtensorMap tw, ti;
       rc = make_split_tmap(&tw, p_w, Kp, rows, planes, 32, uint32_t(n_tile));
       if (rc) return rc;
-      rc = image_plane_tmap(&ti, p_img, chan_p, img_w, img_h, n, planes, 32, uint32_t(a.wp), uint32_t(a.hh),
-                            CU_TENSOR_MAP_SWIZZLE_64B);
+      if (phases == 1) {
+        rc = image_plane_tmap(&ti, p_img, chan_p, img_w, img_h, n, planes, 32, uint32_t(a.wp), uint32_t(a.hh),
+                              CU_TENSOR_MAP_SWIZZLE_64B);
+      } else {   // {c, x, y, phase, image*planes + split} over the phase images
+        EncodeTiledFn enc = get_encode_tiled();
+        if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        const cuuint64_t dims[5] = {cuuint64_t(chan_p), cuuint64_t(wq), cuuint64_t(hq), cuuint64_t(phases), cuuint64_t(planes) * n};
+        const cuuint64_t strides[4] = {cuuint64_t(chan_p) * 2, cuuint64_t(wq) * chan_p * 2, cuuint64_t(hq) * wq * chan_p * 2,
+                                       cuuint64_t(phases) * hq * wq * chan_p * 2};
+        const cuuint32_t box[5] = {32, cuuint32_t(a.wp), cuuint32_t(a.hh), cuuint32_t(phases), 1};
+        const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUresult r5 = enc(&ti, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, p_img, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        rc = r5 == CUDA_SUCCESS ? MTB200_OK : fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (phase images) failed (%d)", int(r5));
+      }
       if (rc) return rc;
       const long long tiles = static_cast<long long>(tiles_n) * ((out_w + a.tc - 1) / a.tc) * ((out_h + a.tr - 1) / a.tr) * n;
       const int grid = int(std::min<long long>(tiles, h->sm_count));
@@ -493,6 +521,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     }
   }
 
+  if (phases > 1) return fail(MTB200_ERR_UNSUPPORTED, "strided implicit convolution: no tile plan fits");
   // Halo kernel (conv_halo_umma.cuh): the image block is staged once per (row block, channel block) and every tap
   // multiplies against it.  Geometry: halo row pitch wh (a multiple of 4), th output rows per tile with th * wh <= 256
   // MMA columns, and image stages that fit beside the weights - all of them resident when they fit, a ring otherwise.
@@ -791,6 +820,16 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
     rc = implicit_conv(h, x, g.n, g.c_in, g.h, g.w, w, g.c_out, g.kh, g.kw, 0, g.oh, g.ow, -g.pw, -g.ph, +1,
                        bias, y, f32_mode, nf_word);
     return rc ? rc : redo();
+  }
+  // Strided forward: the same implicit kernel over phase images (default arithmetic only; strides up to 8 and
+  // filters of at most 128 taps; anything else takes the gathered-patch lowering below).
+  const int vb = (f32_mode >> 8) & 0xff;
+  if ((g.sh > 1 || g.sw > 1) && g.sh <= 8 && g.sw <= 8 && g.kh * g.kw <= 128 && !force_explicit && vb != 0xFB && vb != 0xFC &&
+      ((f32_mode & 0xff) == 0 || (f32_mode & 0xff) == 23)) {
+    rc = implicit_conv(h, x, g.n, g.c_in, g.h, g.w, w, g.c_out, g.kh, g.kw, 0, g.oh, g.ow, 0, 0, +1, bias, y, f32_mode,
+                       nf_word, g.sh, g.sw, g.ph, g.pw);
+    if (rc == MTB200_OK) return redo();
+    if (rc != MTB200_ERR_UNSUPPORTED) return rc;
   }
   const int Kp = padded_k(K);
   const size_t bytes_w = split_bytes(g.c_out, Kp, 1), bytes_p = split_bytes(opix, Kp, g.n);

@@ -61,6 +61,11 @@ struct ConvPixArgs {
   int chan_p;              // padded channel count: the weights' K index is tap * chan_p + c
   int w_org, h_org;        // halo origin relative to the tile's first output pixel
   int flip;                // 0: tap (fh, fw) reads halo offset (fh, fw); 1: (kh-1-fh, kw-1-fw)  (data gradient)
+  // Strided forward convolution: the image planes are stored as sh * sw phase images (split_f16.cuh, RowPhases),
+  // output pixel (y, x) under tap (fh, fw) reads phase ((fh - pad_h) mod sh, (fw - pad_w) mod sw) at
+  // (y + floor((fh - pad_h) / sh), x + floor((fw - pad_w) / sw)): a stride-1 window again.  The halo box then has
+  // a phase dimension and w_org / h_org are in phase-image coordinates.  sh = sw = 1: one phase, as above.
+  int sh, sw, pad_h, pad_w;
   uint32_t img_plane_bytes;  // shared-memory bytes per image plane of a stage (multiple of 512)
   uint32_t w_tile_bytes;     // shared-memory bytes per weight plane of one (channel block, tap): n_tile * 64
   int w_stages;            // weight tiles shared memory holds: the ring depth, or taps * cbs when resident
@@ -127,9 +132,18 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
     b = q / tiles_y;
   };
 
+  const int phases = g.sh * g.sw;
   for (int tap = threadIdx.x; tap < taps; tap += blockDim.x) {
     const int fh = tap / g.kw, fw = tap - fh * g.kw;
-    const int off = g.flip ? ((g.kh - 1 - fh) * g.wp + (g.kw - 1 - fw)) : (fh * g.wp + fw);
+    int off;
+    if (phases == 1) {
+      off = g.flip ? ((g.kh - 1 - fh) * g.wp + (g.kw - 1 - fw)) : (fh * g.wp + fw);
+    } else {
+      const int ay = fh - g.pad_h, ax = fw - g.pad_w;
+      const int py = ((ay % g.sh) + g.sh) % g.sh, px = ((ax % g.sw) + g.sw) % g.sw;
+      const int dy = (ay - py) / g.sh - g.h_org, dx = (ax - px) / g.sw - g.w_org;   // exact divisions
+      off = (py * g.sw + px) * (g.hh * g.wp) + dy * g.wp + dx;
+    }
     tap_off16[tap] = static_cast<uint32_t>(off) * (Cfg::ROW_BYTES >> 4);
   }
   if (threadIdx.x == 0) {
@@ -194,7 +208,7 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      const uint32_t box_bytes = static_cast<uint32_t>(g.wp) * g.hh * Cfg::ROW_BYTES;
+      const uint32_t box_bytes = static_cast<uint32_t>(g.wp) * g.hh * phases * Cfg::ROW_BYTES;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int b, ty, tx, tn;
         decode(t, b, ty, tx, tn);
@@ -207,9 +221,14 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
           }
           mbar_expect_tx(i_full(stage), nsplit * box_bytes);
           const uint32_t si = img_ring + stage * img_stage;
-          for (int s = 0; s < nsplit; ++s)
-            tma_load_4d(si + s * g.img_plane_bytes, &tmapImg, i_full(stage), cb * Cfg::BK, tx * g.tc + g.w_org,
-                        ty * g.tr + g.h_org, b * g.planes_per_mat + s);
+          for (int s = 0; s < nsplit; ++s) {
+            if (phases == 1)
+              tma_load_4d(si + s * g.img_plane_bytes, &tmapImg, i_full(stage), cb * Cfg::BK, tx * g.tc + g.w_org,
+                          ty * g.tr + g.h_org, b * g.planes_per_mat + s);
+            else   // {c, x, y, phase, plane}: every phase image's halo in one request
+              tma_load_5d(si + s * g.img_plane_bytes, &tmapImg, i_full(stage), cb * Cfg::BK, tx * g.tc + g.w_org,
+                          ty * g.tr + g.h_org, 0, b * g.planes_per_mat + s);
+          }
           if (++stage == IST) { stage = 0; phase ^= 1u; }
         }
       }

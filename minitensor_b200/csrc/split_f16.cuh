@@ -293,10 +293,16 @@ finite_absmax_kernel(const float* __restrict__ src, long long bstride, long long
 // are amax_bits[b * amax_stride] (amax_stride 0: one scale for all entries); the first block of each entry also
 // stores e(b) to expo[b] for the GEMM's epilogue.  64 (k) x 64 (r) tiles through shared memory: reads run along r,
 // writes along k.
+// Optional phase separation of the rows (strided convolutions): with r = y * ph.w + x an image pixel, the row goes
+// to ((y % sh) * sw + x % sw) * hq * wq + (y / sh) * wq + x / sw, i.e. the image is stored as sh * sw sub-images of
+// hq x wq pixels, one per residue of the coordinates; destination rows no pixel maps to must be zero beforehand.
+struct RowPhases {
+  int w, sh, sw, hq, wq;   // sh == 1 && sw == 1: rows stay where they are
+};
 static __global__ void __launch_bounds__(256)
 split16_turn_batch_kernel(const float* __restrict__ src, long long ld, long long bstride, __half* __restrict__ dst,
                           const uint32_t* __restrict__ amax_bits, int amax_stride, int* __restrict__ expo, int R, int K,
-                          int Kp) {
+                          int Kp, RowPhases ph = RowPhases{0, 1, 1, 0, 0}) {
   // [plane][r][9 x 16 bytes]: a row holds 64 k as fp16 (128 bytes) plus 16 bytes of padding, so that the 16-byte
   // stores of lanes with consecutive r and the 16-byte loads of lanes with consecutive k chunks both spread
   // over all banks.  The values are scaled, split and packed BEFORE they cross shared memory.
@@ -325,13 +331,20 @@ split16_turn_batch_kernel(const float* __restrict__ src, long long ld, long long
     tile[1][tx][kg + 4 * g] = *reinterpret_cast<const uint4*>(o1);
   }
   __syncthreads();
-  const long long plane = static_cast<long long>(R) * Kp;
+  const bool phased = ph.sh * ph.sw > 1;
+  const long long rows_out = phased ? static_cast<long long>(ph.sh) * ph.sw * ph.hq * ph.wq : R;
+  const long long plane = rows_out * Kp;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int idx = threadIdx.x + 256 * j;
     const int pl = idx >> 9, rr = (idx >> 3) & 63, c = idx & 7;
     if (r0 + rr >= R || k0 + c * 8 >= Kp) continue;
-    __half* d = dst + (static_cast<long long>(b) * 2 + pl) * plane + static_cast<long long>(r0 + rr) * Kp + k0 + c * 8;
+    long long row = r0 + rr;
+    if (phased) {
+      const int y = (r0 + rr) / ph.w, x = (r0 + rr) - y * ph.w;
+      row = (static_cast<long long>((y % ph.sh) * ph.sw + x % ph.sw) * ph.hq + y / ph.sh) * ph.wq + x / ph.sw;
+    }
+    __half* d = dst + (static_cast<long long>(b) * 2 + pl) * plane + row * Kp + k0 + c * 8;
     *reinterpret_cast<uint4*>(d) = tile[pl][rr][c];
   }
 }

@@ -206,6 +206,39 @@ def test_both_lowerings_match_oracle(be, orc, rng, geom, lowering):
                   conv_f64.grad_weight_norms(go, xn, wn.shape, stride, padding))
 
 
+STRIDED = [  # n, c, h, w, co, kh, kw, stride, padding
+    (2, 3, 8, 9, 5, 3, 2, (2, 1), (1, 2)),
+    (4, 16, 14, 14, 32, 3, 3, (2, 2), (1, 1)),
+    (2, 4, 9, 9, 6, 5, 5, (3, 3), (2, 2)),
+    (3, 64, 56, 56, 64, 3, 3, (2, 2), (1, 1)),        # the large config's layer, strided, at reduced batch
+    (2, 8, 15, 17, 12, 1, 1, (2, 2), (0, 0)),          # 1 x 1 filter: three of the four phase images are never read
+    (1, 5, 7, 30, 9, 3, 3, (1, 2), (1, 1)),
+    (2, 6, 33, 33, 10, 7, 7, (2, 2), (3, 3)),          # odd extent: phase images of different true size
+    (1, 3, 20, 20, 4, 4, 4, (4, 4), (0, 0)),           # stride = filter size: every phase holds exactly one tap
+    (2, 70, 12, 300, 130, 3, 3, (2, 2), (1, 1)),       # wide rows, two channel blocks of the image, > 128 output channels
+]
+
+
+@pytest.mark.parametrize("geom", STRIDED)
+@pytest.mark.parametrize("lowering", ["implicit", "explicit"])
+def test_strided_forward_both_lowerings(be, orc, rng, geom, lowering):
+    """Strided forward convolutions run the implicit kernel too: the image planes are written as stride_h x
+    stride_w phase images, which turns every filter tap into a stride-1 window of one of them.  Same bounds as
+    the stride-1 path, against the oracle and float64, for both that kernel and the gathered-patch lowering."""
+    n, c, h, w, co, kh, kw, stride, padding = geom
+    mode = 0 if lowering == "implicit" else 0xFF00
+    xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wn = (rng.standard_normal((co, c, kh, kw)) * np.sqrt(2.0 / (c * kh * kw))).astype(np.float32)
+    bn = rng.standard_normal(co).astype(np.float32)
+    dev = lambda a: torch.from_numpy(a).to(be.device)
+    y = be.conv2d_fwd(dev(xn), dev(wn), dev(bn), stride, padding, f32_mode=mode)
+    be.sync()
+    ref = orc.conv2d(xn, wn, bn, stride, padding)
+    assert tuple(y.shape) == ref.shape
+    check_outputs("y", y.cpu().numpy(), ref, conv_f64.forward(xn, wn, bn, stride, padding),
+                  conv_f64.forward_norms(xn, wn, stride, padding), extra=np.abs(bn)[None, :, None, None])
+
+
 def test_implicit_conv_scales_every_image_on_its_own(be, orc, rng):
     """The default mode of the stride-1 kernels (two fp16 planes) scales each image by its own power of two:
     images 40 orders of magnitude apart and an all-zero image keep, per output, the accuracy of the plain case."""
