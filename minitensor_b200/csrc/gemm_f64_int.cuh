@@ -64,18 +64,18 @@ __device__ __forceinline__ void dmma_m8n8k4(double (&c)[2], double a, double b) 
       : "d"(a), "d"(b));
 }
 
-// Load a (rows i0.., k0..) tile of `rows` x 16 into registers, 8 per thread.
+// Load a (rows i0.., k0..) tile of `rows` x 16 into registers, ROWS * 16 / NT per thread.
 // The thread->element map follows whichever stride is 1 so reads coalesce.
-template <int ROWS>
+template <int ROWS, int NT>
 __device__ __forceinline__ void dgemm_fetch(const double* __restrict__ base, long long s_i,
                                             long long s_k, int i0, int k0, int imax, int kmax,
-                                            double (&r)[ROWS * D_BK / 256]) {
-  constexpr int PER = ROWS * D_BK / 256;
+                                            double (&r)[ROWS * D_BK / NT]) {
+  constexpr int PER = ROWS * D_BK / NT;
   const int tid = threadIdx.x;
   if (s_i == 1) {  // contiguous along i
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
-      const int idx = tid + e * 256;
+      const int idx = tid + e * NT;
       const int i = idx % ROWS, k = idx / ROWS;
       const bool ok = (i0 + i < imax) && (k0 + k < kmax);
       r[e] = ok ? base[(long long)(i0 + i) * s_i + (long long)(k0 + k) * s_k] : 0.0;
@@ -83,28 +83,37 @@ __device__ __forceinline__ void dgemm_fetch(const double* __restrict__ base, lon
   } else {  // contiguous (or at least closest) along k
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
-      const int idx = tid + e * 256;
+      const int idx = tid + e * NT;
       const int k = idx % D_BK, i = idx / D_BK;
       const bool ok = (i0 + i < imax) && (k0 + k < kmax);
       r[e] = ok ? base[(long long)(i0 + i) * s_i + (long long)(k0 + k) * s_k] : 0.0;
     }
   }
 }
-template <int ROWS>
+template <int ROWS, int NT>
 __device__ __forceinline__ void dgemm_stash(double* __restrict__ sm, long long s_i,
-                                            const double (&r)[ROWS * D_BK / 256]) {
-  constexpr int PER = ROWS * D_BK / 256;
+                                            const double (&r)[ROWS * D_BK / NT]) {
+  constexpr int PER = ROWS * D_BK / NT;
   const int tid = threadIdx.x;
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int idx = tid + e * 256;
+    const int idx = tid + e * NT;
     int i, k;
     if (s_i == 1) { i = idx % ROWS; k = idx / ROWS; } else { k = idx % D_BK; i = idx / D_BK; }
     sm[k * D_PITCH + i] = r[e];
   }
 }
 
-static __global__ void __launch_bounds__(256, 1) gemm_f64_dmma_kernel(const StridedGemmArgs g) {
+// WM x WN warps; each warp owns a (128 / WM) x (128 / WN) piece of the block tile.  2 x 4 (64 x 32 per warp, 256
+// threads) is what runs: it reads the least shared memory per MMA.  Measured at 4096^3 on B200: 2 x 4 27.4 TFLOP/s,
+// 4 x 4 (512 threads, four warps per scheduler) 26.5, and the same tile on mma.sync.m16n8k16 26.4 - the warp
+// layout and the MMA shape are not what holds the kernel at 0.74 of the 37.1 TFLOP/s an MMA-only loop reaches.
+template <int WM, int WN>
+static __global__ void __launch_bounds__(32 * WM * WN, 1) gemm_f64_dmma_kernel(const StridedGemmArgs g) {
+  constexpr int NT = 32 * WM * WN;
+  constexpr int TM = D_BM / WM, TN = D_BN / WN;     // warp tile
+  constexpr int FI = TM / 8, FJ = TN / 8;           // 8 x 8 MMA tiles per warp tile
+  constexpr int PER = D_BM * D_BK / NT;
   extern __shared__ __align__(16) uint8_t dsm_raw[];
   double* As = reinterpret_cast<double*>(dsm_raw);  // [2][D_BK][D_PITCH]
   double* Bs = As + 2 * D_BK * D_PITCH;             // [2][D_BK][D_PITCH]
@@ -118,58 +127,58 @@ static __global__ void __launch_bounds__(256, 1) gemm_f64_dmma_kernel(const Stri
   const double* AUX = g.aux ? static_cast<const double*>(g.aux) + b * g.c_sb : nullptr;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int wm = warp >> 2, wn = warp & 3;
+  const int wm = warp / WN, wn = warp % WN;
   const int fr = lane >> 2, fk = lane & 3;
 
-  double acc[8][4][2];
+  double acc[FI][FJ][2];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < FI; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+    for (int j = 0; j < FJ; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
   const int nkb = (g.K + D_BK - 1) / D_BK;
-  double ra[8], rb[8];
-  dgemm_fetch<D_BM>(A, g.a_si, g.a_sk, tm * D_BM, 0, g.M, g.K, ra);
-  dgemm_fetch<D_BN>(B, g.b_sj, g.b_sk, tn * D_BN, 0, g.N, g.K, rb);
-  dgemm_stash<D_BM>(As, g.a_si, ra);
-  dgemm_stash<D_BN>(Bs, g.b_sj, rb);
+  double ra[PER], rb[PER];
+  dgemm_fetch<D_BM, NT>(A, g.a_si, g.a_sk, tm * D_BM, 0, g.M, g.K, ra);
+  dgemm_fetch<D_BN, NT>(B, g.b_sj, g.b_sk, tn * D_BN, 0, g.N, g.K, rb);
+  dgemm_stash<D_BM, NT>(As, g.a_si, ra);
+  dgemm_stash<D_BN, NT>(Bs, g.b_sj, rb);
   __syncthreads();
 
   for (int kb = 0; kb < nkb; ++kb) {
     const int cur = kb & 1;
     if (kb + 1 < nkb) {
-      dgemm_fetch<D_BM>(A, g.a_si, g.a_sk, tm * D_BM, (kb + 1) * D_BK, g.M, g.K, ra);
-      dgemm_fetch<D_BN>(B, g.b_sj, g.b_sk, tn * D_BN, (kb + 1) * D_BK, g.N, g.K, rb);
+      dgemm_fetch<D_BM, NT>(A, g.a_si, g.a_sk, tm * D_BM, (kb + 1) * D_BK, g.M, g.K, ra);
+      dgemm_fetch<D_BN, NT>(B, g.b_sj, g.b_sk, tn * D_BN, (kb + 1) * D_BK, g.N, g.K, rb);
     }
     const double* as = As + cur * D_BK * D_PITCH;
     const double* bs = Bs + cur * D_BK * D_PITCH;
 #pragma unroll
     for (int k4 = 0; k4 < D_BK / 4; ++k4) {
-      double af[8], bf[4];
+      double af[FI], bf[FJ];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) af[i] = as[(k4 * 4 + fk) * D_PITCH + wm * 64 + i * 8 + fr];
+      for (int i = 0; i < FI; ++i) af[i] = as[(k4 * 4 + fk) * D_PITCH + wm * TM + i * 8 + fr];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) bf[j] = bs[(k4 * 4 + fk) * D_PITCH + wn * 32 + j * 8 + fr];
+      for (int j = 0; j < FJ; ++j) bf[j] = bs[(k4 * 4 + fk) * D_PITCH + wn * TN + j * 8 + fr];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < FI; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) dmma_m8n8k4(acc[i][j], af[i], bf[j]);
+        for (int j = 0; j < FJ; ++j) dmma_m8n8k4(acc[i][j], af[i], bf[j]);
     }
     if (kb + 1 < nkb) {
-      dgemm_stash<D_BM>(As + (cur ^ 1) * D_BK * D_PITCH, g.a_si, ra);
-      dgemm_stash<D_BN>(Bs + (cur ^ 1) * D_BK * D_PITCH, g.b_sj, rb);
+      dgemm_stash<D_BM, NT>(As + (cur ^ 1) * D_BK * D_PITCH, g.a_si, ra);
+      dgemm_stash<D_BN, NT>(Bs + (cur ^ 1) * D_BK * D_PITCH, g.b_sj, rb);
     }
     __syncthreads();
   }
 
   const double* bias = static_cast<const double*>(g.bias);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int row = tm * D_BM + wm * 64 + i * 8 + fr;
+  for (int i = 0; i < FI; ++i) {
+    const int row = tm * D_BM + wm * TM + i * 8 + fr;
     if (row >= g.M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int col = tn * D_BN + wn * 32 + j * 8 + fk * 2;
+    for (int j = 0; j < FJ; ++j) {
+      const int col = tn * D_BN + wn * TN + j * 8 + fk * 2;
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         if (col + e < g.N) {

@@ -12,6 +12,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <mutex>
 
 namespace mtb {
@@ -492,9 +493,9 @@ int32_t mtb200_gemm(mtb200_handle h, int32_t dtype, int32_t trans_a, int32_t tra
   ProfScope prof(h, dtype == MTB200_F64 ? PROF_GEMM_F64 : PROF_GEMM_INT, 2.0 * M * N * K * batch);
   if (dtype == MTB200_F64) {
     const int smem = 4 * D_BK * D_PITCH * int(sizeof(double));
-    if (int32_t rc_attr = grant_dynamic_smem(h, gemm_f64_dmma_kernel, int(smem))) return rc_attr;
     const long long tiles = ((M + D_BM - 1) / D_BM) * ((N + D_BN - 1) / D_BN);
-    gemm_f64_dmma_kernel<<<dim3(unsigned(tiles), unsigned(batch)), 256, smem, h->stream>>>(g);
+    if (int32_t rc_attr = grant_dynamic_smem(h, gemm_f64_dmma_kernel<2, 4>, int(smem))) return rc_attr;
+    gemm_f64_dmma_kernel<2, 4><<<dim3(unsigned(tiles), unsigned(batch)), 256, smem, h->stream>>>(g);
   } else if (dtype == MTB200_I32) {
     const long long tiles = ((M + 127) / 128) * ((N + 127) / 128);
     gemm_simt_kernel<uint32_t, 8, 8><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(g);
