@@ -426,57 +426,73 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     if (rc) return rc;
   }
 
-  // Pixels-on-M kernel (conv_pix_umma.cuh): the default.  Pick the output tile (tr x tc), the number of 128-position
-  // M blocks and whether the weights stay resident by a small cost model: per tile the tensor core needs
-  // mb * taps * cbs * 2 * products MMAs of width n_tile and the TMA engine one request per 64-byte halo-pixel piece
-  // (measured: about 4 ns each), whichever is longer bounds the tile.
+  // Pixels-on-M kernel (conv_pix_umma.cuh): the default.  Pick the channel block (64 or 32 channels per shared-memory
+  // row), the output tile (tr x tc), the number of 128-position M blocks and whether the weights stay resident by a
+  // small cost model.  Per tile the tensor core runs mb * taps * chan_p / 16 groups of MMAs, each MMA bounded either
+  // by its arithmetic (0.273 ns per accumulator column) or by fetching its operands from shared memory (measured:
+  // about 150 bytes per ns with 128-byte rows, two thirds of that with 64-byte rows); the TMA engine needs about 4 ns
+  // per shared-memory row it writes.  Whichever is longer bounds the tile.
   {
     const size_t smem_limit = 232448;
     const bool three = planes == 3;
     const int nsplit = gemm_mode == 1 ? 1 : ((gemm_mode == 3 || gemm_mode == 23) ? 2 : 3);
     const int products = split_pair_count(gemm_mode);
-    const int cbs = chan_p / 32;
-    const int tiles_n = (rows + 255) / 256;
-    const int n_tile = (((rows + tiles_n - 1) / tiles_n) + 15) / 16 * 16;
-    const size_t w_tile = size_t(n_tile) * 64;
-    struct Plan { double cost; int tr, tc, wp, mb, w_stages; bool resident; size_t img_plane; } best = {1e300, 0, 0, 0, 0, 0, false, 0};
-    const double t_mma = std::max(26.7, 0.273 * n_tile) * 1.35;   // ns per MMA under load
+    struct Plan { double cost; int bk, tr, tc, wp, mb, w_stages, n_tile, tiles_n; bool resident; size_t img_plane; } best =
+        {1e300, 0, 0, 0, 0, 0, 0, 0, 0, false, 0};
     // halo origin and reach of the taps, in (phase-)image coordinates relative to the output pixel
     auto fdiv = [](int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); };
     const int org_x = phases > 1 ? fdiv(-pad_w, sw) : w0 - (sgn < 0 ? kw - 1 : 0);
     const int org_y = phases > 1 ? fdiv(-pad_h, sh) : h0 - (sgn < 0 ? kh - 1 : 0);
     const int dxr = phases > 1 ? fdiv(kw - 1 - pad_w, sw) - org_x : kw - 1;    // halo columns beyond the tile's own
     const int dyr = phases > 1 ? fdiv(kh - 1 - pad_h, sh) - org_y : kh - 1;
-    for (int mb = 1; mb <= 4 && 2 * mb * n_tile <= 512; mb *= 2)
-      for (int sx = 1; sx <= 16; ++sx) {
-        const int tc = (out_w + sx - 1) / sx;
-        const int wp = tc + dxr;
-        if (wp > 256 || wp > 128 * mb) continue;
-        const int tr = std::min(out_h, (128 * mb) / wp);
-        if (tr < 1 || tr + dyr > 256 || phases * (tr + dyr) * wp * 64 > (1 << 20) - 1) continue;
-        const size_t img_plane = align_up(size_t((phases - 1) * (tr + dyr) * wp + mb * 128 + dyr * wp + dxr) * 64, 512);
-        const size_t fixed = three ? ConvPixCfg<3>::fixed_bytes(img_plane) : ConvPixCfg<2>::fixed_bytes(img_plane);
-        if (fixed >= smem_limit) continue;
-        const bool resident = tiles_n == 1 && fixed + size_t(taps) * cbs * planes * w_tile <= smem_limit;
-        int w_stages = taps * cbs;
-        if (!resident) {
-          w_stages = int(std::min<size_t>(ConvPixCfg<2>::MAX_W_STAGES, (smem_limit - fixed) / (planes * w_tile)));
-          if (w_stages < 3) continue;
+    auto mma_ns = [](int n, int bk) {
+      return std::max(0.273 * n, (128.0 + n) * 32.0 / (bk == 64 ? 150.0 : 100.0)) * 1.3;
+    };
+    for (int bk = 64; bk >= 32; bk /= 2)
+    for (int n_cap = 256; n_cap >= 64; n_cap /= 2) {    // narrower channel tiles leave room for more weight stages
+      const int row_bytes = 2 * bk, cbs = chan_p / bk;
+      const int tiles_n = (rows + n_cap - 1) / n_cap;
+      if (n_cap < 256 && tiles_n == (rows + 2 * n_cap - 1) / (2 * n_cap)) continue;   // same split as the wider cap
+      const int n_tile = (((rows + tiles_n - 1) / tiles_n) + 15) / 16 * 16;
+      const size_t w_tile = size_t(n_tile) * row_bytes;
+      const bool fold = gemm_mode == 23 && n_tile <= 128;     // hi x [hi; lo] in one MMA (conv_pix_umma.cuh)
+      const int acc_n = fold ? 2 * n_tile : n_tile;
+      const double group_ns = fold ? mma_ns(2 * n_tile, bk) + mma_ns(n_tile, bk) : products * mma_ns(n_tile, bk);
+      for (int mb = 1; mb <= 4 && 2 * mb * acc_n <= 512; mb *= 2)
+        for (int sx = 1; sx <= 16; ++sx) {
+          const int tc = (out_w + sx - 1) / sx;
+          const int wp = tc + dxr;
+          if (wp > 256 || wp > 128 * mb) continue;
+          const int tr = std::min(out_h, (128 * mb) / wp);
+          if (tr < 1 || tr + dyr > 256 || phases * (tr + dyr) * wp * row_bytes > (1 << 20) - 1) continue;
+          // a TMA destination must be 128-byte aligned, so every plane of the ring is
+          const size_t img_plane = align_up(size_t((phases - 1) * (tr + dyr) * wp + mb * 128 + dyr * wp + dxr) * row_bytes, 128);
+          const size_t fixed = conv_pix_fixed_bytes(planes, img_plane);
+          if (fixed >= smem_limit) continue;
+          const bool resident = tiles_n == 1 && fixed + size_t(taps) * cbs * planes * w_tile <= smem_limit;
+          int w_stages = taps * cbs;
+          if (!resident) {
+            w_stages = int(std::min<size_t>(CONV_PIX_MAX_W_STAGES, (smem_limit - fixed) / (planes * w_tile)));
+            if (w_stages < 3) continue;
+          }
+          const double tiles = double(tiles_n) * ((out_w + tc - 1) / tc) * ((out_h + tr - 1) / tr) * n;
+          const double tensor_ns = double(mb) * taps * (chan_p / 16) * group_ns;
+          const double tma_ns = (double(phases) * (tr + dyr) * wp * cbs * nsplit +
+                                 (resident ? 0.0 : double(taps) * cbs * nsplit * n_tile)) * 4.1;
+          const double cost = std::ceil(tiles / h->sm_count) * (std::max(tensor_ns, tma_ns) + 500.0);
+          if (cost < best.cost) best = {cost, bk, tr, tc, wp, mb, w_stages, n_tile, tiles_n, resident, img_plane};
         }
-        const double tiles = double(tiles_n) * ((out_w + tc - 1) / tc) * ((out_h + tr - 1) / tr) * n;
-        const double mma_ns = double(mb) * taps * cbs * 2 * products * t_mma;
-        const double tma_ns = (double(phases) * (tr + dyr) * wp * cbs * nsplit + (resident ? 0.0 : double(taps) * cbs * nsplit * n_tile)) * 4.1;
-        const double cost = std::ceil(tiles / h->sm_count) * (std::max(mma_ns, tma_ns) + 500.0);
-        if (cost < best.cost) best = {cost, tr, tc, wp, mb, w_stages, resident, img_plane};
-      }
+    }
     const int vbyte = (f32_mode >> 8) & 0xff;    // test hooks: 0xFB = the channels-on-M halo kernel, 0xFC = the per-tap kernel
-    if (best.tr >= 1 && taps <= ConvPixCfg<2>::MAX_TAPS && vbyte != 0xFB && vbyte != 0xFC) {
+    if (best.tr >= 1 && taps <= CONV_PIX_MAX_TAPS && vbyte != 0xFB && vbyte != 0xFC) {
+      const int bk = best.bk, n_tile = best.n_tile, tiles_n = best.tiles_n;
+      const size_t w_tile = size_t(n_tile) * 2 * bk;
       ConvPixArgs a = {};
       a.n_out = rows; a.out_h = out_h; a.out_w = out_w; a.batch = n;
       a.C = out; a.bias = bias; a.mode = gemm_mode; a.planes_per_mat = planes;
       a.exp_w = f16 ? ea : nullptr; a.exp_img = f16 ? eb : nullptr;
       a.tr = best.tr; a.tc = best.tc; a.wp = best.wp; a.hh = best.tr + dyr; a.mb = best.mb; a.n_tile = n_tile;
-      a.kh = kh; a.kw = kw; a.cbs = cbs; a.chan_p = chan_p;
+      a.kh = kh; a.kw = kw; a.cbs = chan_p / bk; a.chan_p = chan_p;
       a.flip = sgn < 0 ? 1 : 0;
       a.w_org = org_x;
       a.h_org = org_y;
@@ -484,38 +500,39 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
       a.img_plane_bytes = uint32_t(best.img_plane);
       a.w_tile_bytes = uint32_t(w_tile);
       a.w_stages = best.w_stages; a.w_resident = best.resident ? 1 : 0;
+      a.fold = (gemm_mode == 23 && n_tile <= 128) ? 1 : 0;
       a.status = h->status;
+      const CUtensorMapSwizzle swz = bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
       CUtensorMap tw, ti;
-      rc = make_split_tmap(&tw, p_w, Kp, rows, planes, 32, uint32_t(n_tile));
+      rc = make_split_tmap(&tw, p_w, Kp, rows, planes, bk, uint32_t(n_tile));
       if (rc) return rc;
       if (phases == 1) {
-        rc = image_plane_tmap(&ti, p_img, chan_p, img_w, img_h, n, planes, 32, uint32_t(a.wp), uint32_t(a.hh),
-                              CU_TENSOR_MAP_SWIZZLE_64B);
+        rc = image_plane_tmap(&ti, p_img, chan_p, img_w, img_h, n, planes, bk, uint32_t(a.wp), uint32_t(a.hh), swz);
       } else {   // {c, x, y, phase, image*planes + split} over the phase images
         EncodeTiledFn enc = get_encode_tiled();
         if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
         const cuuint64_t dims[5] = {cuuint64_t(chan_p), cuuint64_t(wq), cuuint64_t(hq), cuuint64_t(phases), cuuint64_t(planes) * n};
         const cuuint64_t strides[4] = {cuuint64_t(chan_p) * 2, cuuint64_t(wq) * chan_p * 2, cuuint64_t(hq) * wq * chan_p * 2,
                                        cuuint64_t(phases) * hq * wq * chan_p * 2};
-        const cuuint32_t box[5] = {32, cuuint32_t(a.wp), cuuint32_t(a.hh), cuuint32_t(phases), 1};
+        const cuuint32_t box[5] = {cuuint32_t(bk), cuuint32_t(a.wp), cuuint32_t(a.hh), cuuint32_t(phases), 1};
         const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
         CUresult r5 = enc(&ti, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, p_img, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         rc = r5 == CUDA_SUCCESS ? MTB200_OK : fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (phase images) failed (%d)", int(r5));
       }
       if (rc) return rc;
       const long long tiles = static_cast<long long>(tiles_n) * ((out_w + a.tc - 1) / a.tc) * ((out_h + a.tr - 1) / a.tr) * n;
       const int grid = int(std::min<long long>(tiles, h->sm_count));
-      const size_t smem = three ? ConvPixCfg<3>::smem_bytes(a.img_plane_bytes, w_tile, a.w_stages)
-                                : ConvPixCfg<2>::smem_bytes(a.img_plane_bytes, w_tile, a.w_stages);
+      const size_t smem = conv_pix_fixed_bytes(planes, a.img_plane_bytes) + size_t(a.w_stages) * planes * w_tile;
       ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
-      if (three) {
-        if (int32_t rc_attr = grant_dynamic_smem(h, conv_pix_umma_kernel<3>, int(int(smem)))) return rc_attr;
-        conv_pix_umma_kernel<3><<<grid, ConvPixCfg<3>::NUM_THREADS, smem, h->stream>>>(tw, ti, a);
-      } else {
-        if (int32_t rc_attr = grant_dynamic_smem(h, conv_pix_umma_kernel<2>, int(int(smem)))) return rc_attr;
-        conv_pix_umma_kernel<2><<<grid, ConvPixCfg<2>::NUM_THREADS, smem, h->stream>>>(tw, ti, a);
-      }
+      auto launch = [&](auto kernel) -> int32_t {
+        if (int32_t rc_attr = grant_dynamic_smem(h, kernel, int(smem))) return rc_attr;
+        kernel<<<grid, CONV_PIX_THREADS, smem, h->stream>>>(tw, ti, a);
+        return MTB200_OK;
+      };
+      if (three) rc = bk == 64 ? launch(conv_pix_umma_kernel<3, 64>) : launch(conv_pix_umma_kernel<3, 32>);
+      else rc = bk == 64 ? launch(conv_pix_umma_kernel<2, 64>) : launch(conv_pix_umma_kernel<2, 32>);
+      if (rc) return rc;
       MTB_CUDA(cudaGetLastError());
       return MTB200_OK;
     }

@@ -11,20 +11,30 @@
 // output pixel whatever the channel count, and N = the channel count (a multiple of 16 up to 256).
 //
 // Image operand (A).  The image lives in channels-last split planes {c, w, h, image*planes + split} (conv2d.cu).  An
-// output tile is tr rows x tc columns; per channel block of 32 the producer loads the halo box {32 channels,
-// wp = tc + kw - 1 columns, hh = tr + kh - 1 rows} with the hardware's zero fill standing in for the padding.  In
-// shared memory that box is a K-major operand whose rows are the halo pixels in raster order (64-byte rows, 64-byte
-// swizzle).  Output pixel (r, c) of the tile is "position" n = r * wp + c; its window under tap (fh, fw) is halo row
-// n + fh * wp + fw.  So the A operand of a tap is the tile's rows shifted by off = fh * wp + fw: the tile's
-// descriptor with the start address advanced by off rows (the swizzle is a function of the shared-memory address,
-// so a start that is not aligned to the swizzle repeat reads exactly the rows it names).  Positions with c >= tc,
-// and positions past the last row, are garbage that depends only on its own A row; they land in accumulator lanes
-// the epilogue skips.  A tile has mb blocks of 128 positions, each its own MMA and accumulator.  The image bytes
-// cross L2 -> shared memory once per (tile, channel block), not once per tap.
+// output tile is tr rows x tc columns; per channel block of BK channels (64, or 32 where 64 does not fit shared
+// memory) the producer loads the halo box {BK channels, wp = tc + kw - 1 columns, hh = tr + kh - 1 rows} with the
+// hardware's zero fill standing in for the padding.  In shared memory that box is a K-major operand whose rows are
+// the halo pixels in raster order (2 * BK bytes per row, swizzle of the same width).  Output pixel (r, c) of the
+// tile is "position" n = r * wp + c; its window under tap (fh, fw) is halo row n + fh * wp + fw.  So the A operand
+// of a tap is the tile's rows shifted by off = fh * wp + fw: the tile's descriptor with the start address advanced
+// by off rows.  The swizzle is a function of the shared-memory address, so a start - or a plane base - that is not
+// aligned to the swizzle repeat reads exactly the rows it names, and (measured) at the speed of an aligned one.
+// Positions with c >= tc, and positions past the last row, are garbage that depends only on its own A row; they
+// land in accumulator lanes the epilogue skips.  A tile has mb blocks of 128 positions, each its own MMA and
+// accumulator.  The image bytes cross L2 -> shared memory once per (tile, channel block), not once per tap.
 //
-// Weights (B).  One (channel block, tap) of the weights is a tile of n_tile rows x 32 channels per plane.  When all of
-// a layer's tiles fit beside the image ring they are loaded once per CTA and stay RESIDENT (the large conv config:
-// 2 x 9 tiles x 2 planes x 4 KB = 144 KB); otherwise they stream through a ring.
+// Weights (B).  One (channel block, tap) of the weights is a tile of n_tile rows x BK channels per plane.  When all
+// of a layer's tiles fit beside the image ring they are loaded once per CTA and stay RESIDENT (the large conv config:
+// 9 tiles x 2 planes x 8 KB = 144 KB); otherwise they stream through a ring.
+//
+// What bounds the MMAs here.  An MMA of 128 x N x 16 fetches (128 + N) x 32 bytes of operands from shared memory, at
+// about 150 bytes per ns measured (two thirds of that with 64-byte rows); below N = 128 that fetch, not the
+// arithmetic, sets its duration (N = 64: 27 ns against 17 ns of arithmetic).  With 64 output channels every MMA is
+// in that regime, so the fp16 mode FOLDS two of its three products: the hi and lo weight planes of a tile lie back
+// to back in shared memory and are multiplied as ONE operand of 2 * n_tile rows - image_hi x [w_hi; w_lo] - into an
+// accumulator of 2 * n_tile columns, then image_lo x w_hi goes onto its first n_tile columns.  The image rows are
+// fetched twice instead of three times, the issuing thread sends two MMAs instead of three, and the epilogue adds
+// the two column halves.
 //
 // Epilogue.  tcgen05.ld hands lane l of a warp the position 32 q + l of an M block and 32 consecutive output
 // channels.  For one channel the 32 lanes hold consecutive positions, i.e. consecutive pixels of an output row, so
@@ -55,9 +65,10 @@ struct ConvPixArgs {
   int tr, tc;              // output rows and columns per tile
   int wp, hh;              // halo pitch tc + kw - 1 and halo rows tr + kh - 1
   int mb;                  // blocks of 128 positions per tile: tr * wp <= 128 * mb
-  int n_tile;              // output channels per tile = MMA N (multiple of 16, <= 256, 2 * mb * n_tile <= 512)
+  int n_tile;              // output channels per tile = MMA N (multiple of 16, <= 256); two accumulator sets of
+                           // mb * n_tile columns (twice that when folded) must fit the 512 TMEM columns
   int kh, kw;
-  int cbs;                 // channel blocks of 32
+  int cbs;                 // channel blocks of BK
   int chan_p;              // padded channel count: the weights' K index is tap * chan_p + c
   int w_org, h_org;        // halo origin relative to the tile's first output pixel
   int flip;                // 0: tap (fh, fw) reads halo offset (fh, fw); 1: (kh-1-fh, kw-1-fw)  (data gradient)
@@ -66,34 +77,36 @@ struct ConvPixArgs {
   // (y + floor((fh - pad_h) / sh), x + floor((fw - pad_w) / sw)): a stride-1 window again.  The halo box then has
   // a phase dimension and w_org / h_org are in phase-image coordinates.  sh = sw = 1: one phase, as above.
   int sh, sw, pad_h, pad_w;
-  uint32_t img_plane_bytes;  // shared-memory bytes per image plane of a stage (multiple of 512)
-  uint32_t w_tile_bytes;     // shared-memory bytes per weight plane of one (channel block, tap): n_tile * 64
+  uint32_t img_plane_bytes;  // shared-memory bytes per image plane of a stage (multiple of 128: TMA destinations)
+  uint32_t w_tile_bytes;     // shared-memory bytes per weight plane of one (channel block, tap): n_tile rows
   int w_stages;            // weight tiles shared memory holds: the ring depth, or taps * cbs when resident
   int w_resident;          // 1: every (channel block, tap) tile is loaded once and kept (needs one channel tile)
   uint32_t* status;
+  int fold;                // fp16 mode: the two weight planes of a tile are multiplied as ONE operand of 2 * n_tile rows
 };
 
-template <int PLANES>
+constexpr int CONV_PIX_THREADS = 352;
+constexpr int CONV_PIX_MAX_W_STAGES = 16;      // bounds the streaming weight ring (barrier room)
+constexpr int CONV_PIX_IMG_STAGES = 2;
+constexpr int CONV_PIX_MAX_TAPS = 128;         // filter taps (kh * kw) the tap table has room for
+constexpr int CONV_PIX_BAR_BYTES = 384 + 4 * CONV_PIX_MAX_TAPS;   // barriers, TMEM slot, abort word; then the tap table
+// shared memory besides the weight tiles: alignment slack, the image ring, barriers and tap table
+constexpr size_t conv_pix_fixed_bytes(int planes, size_t img_plane_bytes) {
+  return 1024 + size_t(CONV_PIX_IMG_STAGES) * planes * img_plane_bytes + CONV_PIX_BAR_BYTES;
+}
+
+template <int PLANES, int BK_>
 struct ConvPixCfg {
-  static constexpr int BM = 128, BK = 32, ROW_BYTES = 64;
-  static constexpr int MAX_W_STAGES = 16, IMG_STAGES = 2;   // MAX_W_STAGES bounds the streaming ring (barrier room)
-  static constexpr int NUM_THREADS = 352;
+  static constexpr int BM = 128, BK = BK_, ROW_BYTES = 2 * BK_;
+  static constexpr int IMG_STAGES = CONV_PIX_IMG_STAGES;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int MAX_TAPS = 128;                     // filter taps (kh * kw) the tap table has room for
-  static constexpr int BAR_BYTES = 512 + 4 * MAX_TAPS;     // barriers, TMEM slot, abort word; then the tap table
-  static constexpr size_t fixed_bytes(size_t img_plane_bytes) {
-    return 1024 + size_t(IMG_STAGES) * PLANES * img_plane_bytes + BAR_BYTES;
-  }
-  static constexpr size_t smem_bytes(size_t img_plane_bytes, size_t w_tile_bytes, int w_stages) {
-    return fixed_bytes(img_plane_bytes) + size_t(w_stages) * PLANES * w_tile_bytes;
-  }
 };
 
-template <int PLANES>
-__global__ void __launch_bounds__(352, 1)
+template <int PLANES, int BK>
+__global__ void __launch_bounds__(CONV_PIX_THREADS, 1)
 conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constant__ CUtensorMap tmapImg,
                      const ConvPixArgs g) {
-  using Cfg = ConvPixCfg<PLANES>;
+  using Cfg = ConvPixCfg<PLANES, BK>;
   constexpr int IST = Cfg::IMG_STAGES;
   const int WST = g.w_resident ? 1 : g.w_stages;     // barrier pairs of the weight tiles
   const uint32_t w_stage = PLANES * g.w_tile_bytes;
@@ -114,7 +127,7 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
   volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(smem_raw + (abort_addr - raw));
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
   // tap_off16[tap]: the halo row offset of the tap's window, in 16-byte units of shared-memory address
-  uint32_t* tap_off16 = reinterpret_cast<uint32_t*>(smem_raw + (bars + 512u - raw));
+  uint32_t* tap_off16 = reinterpret_cast<uint32_t*>(smem_raw + (bars + 384u - raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_x = (g.out_w + g.tc - 1) / g.tc;
@@ -163,7 +176,8 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  const int acc_cols = g.mb * g.n_tile;              // TMEM columns of one accumulator set
+  const int acc_n = g.fold ? 2 * g.n_tile : g.n_tile;  // TMEM columns of one M block's accumulator
+  const int acc_cols = g.mb * acc_n;                 // TMEM columns of one accumulator set
 
   if (warp == 0) {
     // ------------------------------------------------------------ weight producer
@@ -240,6 +254,7 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
       // tap offsets come from the table in shared memory, the descriptors' constant high words are built once, and
       // each MMA costs a few 32-bit adds on the low words (start address field, 16-byte units).
       const uint32_t idesc = make_idesc(Cfg::BM, g.n_tile, g.mode == 23 ? 0u : 1u, /*f32*/ 1u);
+      const uint32_t idesc_fold = make_idesc(Cfg::BM, 2 * g.n_tile, 0u, /*f32*/ 1u);
       const uint32_t w_tile16 = g.w_tile_bytes >> 4, w_stage16 = w_stage >> 4;
       const uint32_t img_plane16 = g.img_plane_bytes >> 4, img_stage16 = img_stage >> 4;
       const uint64_t dproto = make_kmajor_desc<Cfg::ROW_BYTES>(0);
@@ -297,7 +312,17 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
               }
               for (int j = 0; j < g.mb; ++j) {
                 const uint32_t a_lo = i_lo_tap + j * mblock16;
-                const uint32_t dj = d_tmem + j * g.n_tile;
+                const uint32_t dj = d_tmem + j * acc_n;
+                if (NPAIRS == 3 && PLANES == 2 && g.fold) {
+                  // hi x [hi; lo] as one MMA of 2 * n_tile columns, then lo x hi onto the first n_tile columns: the
+                  // image rows are fetched twice instead of three times and the thread issues two MMAs, not three
+#pragma unroll
+                  for (int kk = 0; kk < Cfg::BK / 16; ++kk) {
+                    umma_f16_lohi(dj, a_lo + kk * 2, d_hi, w_lo_tap + kk * 2, d_hi, idesc_fold, kk == 0 ? accumulate : 1u);
+                    umma_f16_lohi(dj, a_lo + img_plane16 + kk * 2, d_hi, w_lo_tap + kk * 2, d_hi, idesc, 1u);
+                  }
+                  continue;
+                }
 #pragma unroll
                 for (int kk = 0; kk < Cfg::BK / 16; ++kk) {
 #pragma unroll
@@ -376,13 +401,27 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
           f1_own = __int_as_float((e1 + 127) << 23);
           f2_own = __int_as_float((e2 + 127) << 23);
         }
-        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * acc_cols + j * g.n_tile + c0;
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * acc_cols + j * acc_n + c0;
         uint32_t v[32];
         if (c0 + 32 <= g.n_tile) {
           tmem_ld_32x32(t_addr, v);
+          if (g.fold) {
+            uint32_t v2[32];
+            tmem_ld_32x32(t_addr + g.n_tile, v2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(v2[e]));
+          }
         } else {       // n_tile is a multiple of 16: the last chunk may be 16 wide
           uint32_t u[16];
           tmem_ld_32x16(t_addr, u);
+          if (g.fold) {
+            uint32_t u2[16];
+            tmem_ld_32x16(t_addr + g.n_tile, u2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) u[e] = __float_as_uint(__uint_as_float(u[e]) + __uint_as_float(u2[e]));
+          }
 #pragma unroll
           for (int e = 0; e < 16; ++e) { v[e] = u[e]; v[16 + e] = 0u; }
         }
