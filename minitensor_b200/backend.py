@@ -17,6 +17,10 @@ from . import _lib
 from ._lib import (EPI_GELU_ERF, EPI_GELU_TANH, EPI_NONE, EPI_RELU, EPI_RELU_BWD, F32, F64, I32,
                    I64, check)
 
+# the current stream's handle without building a torch.cuda.Stream object per call (a few microseconds on a path
+# whose whole host cost is about twenty); absent from a torch build, the public call serves
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
 _DTYPES = {torch.float32: F32, torch.float64: F64, torch.int32: I32, torch.int64: I64}
 
 
@@ -63,11 +67,16 @@ class Backend:
         check(self.lib.mtb200_create(device, C.byref(h)))
         self._h = h
         self.launches = 0  # kernels this backend enqueued (operand splits count)
+        self._dev_index = device
+        self._bound_stream = None
         self._bind_stream()
 
     def _bind_stream(self) -> None:
-        s = torch.cuda.current_stream(self.device).cuda_stream
-        check(self.lib.mtb200_set_stream(self._h, C.c_void_p(s)))
+        """Point the handle at torch's current stream; the C call is made only when that stream changed."""
+        s = _RAW_STREAM(self._dev_index) if _RAW_STREAM else torch.cuda.current_stream(self.device).cuda_stream
+        if s != self._bound_stream:
+            check(self.lib.mtb200_set_stream(self._h, C.c_void_p(s)))
+            self._bound_stream = s
 
     def close(self) -> None:
         if getattr(self, "_h", None):

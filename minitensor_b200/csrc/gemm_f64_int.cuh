@@ -17,6 +17,7 @@
 // / TT forms: element (i, k) of A is A[i*a_si + k*a_sk], element (k, j) of B
 // is B[k*b_sk + j*b_sj].
 #pragma once
+#include "ptx_sm100.cuh"
 #include <cstdint>
 #include <type_traits>
 
@@ -199,6 +200,7 @@ static __global__ void __launch_bounds__(32 * WM * WN, 1) gemm_f64_dmma_kernel(c
 template <typename T, int TM, int TN>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const StridedGemmArgs g) {
   constexpr int BM = 16 * TM, BN = 16 * TN, BK = 16;
+  grid_dependency_wait();        // the gate word is written by the kernels before this one
   if (g.gate && *g.gate != g.gate_value) return;
   constexpr int PA = BM + 4, PB = BN + 4;
   __shared__ T As[BK][PA];

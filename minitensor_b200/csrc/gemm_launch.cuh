@@ -98,22 +98,37 @@ inline int32_t make_split_tmap_mn(CUtensorMap* out, const void* base, uint64_t k
 }
 
 // allow_tail: the kernel walks K blocks of 64 and may split the tiles of a short last round (GemmArgs::tail_splits).
+// Launch with the programmatic-stream-serialization attribute: the kernel may start while the one before it in the
+// stream still runs and must call grid_dependency_wait() before it reads that kernel's results (ptx_sm100.cuh).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(mtb200_ctx* h, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = h->stream;
+  cfg.attrs = attr; cfg.numAttrs = h->pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 template <typename Kern>
 inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int threads, long long tiles,
                                   const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, double work,
                                   bool allow_tail = false, int prof_class = PROF_GEMM_UMMA) {
   if (int32_t rc_attr = grant_dynamic_smem(h, kern, int(smem_bytes))) return rc_attr;
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = h->stream;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 1;      // the occupancy query below takes the cluster shape only
   const int sms = (h->gemm_sm_limit > 0) ? std::min(h->gemm_sm_limit, h->sm_count) : h->sm_count;
   cfg.gridDim = dim3(2 * (sms / 2));
   // clusters of this kernel the device can hold at once: asked once per kernel and SM limit
@@ -164,12 +179,12 @@ inline int32_t launch_pair_kernel(mtb200_ctx* h, Kern kern, int smem_bytes, int 
     }
   }
   cfg.gridDim = dim3(2 * pairs);
+  cfg.numAttrs = h->pdl ? 2 : 1;
   ProfScope prof(h, prof_class, work);
   MTB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, g));
   if (g.tail_splits > 1) {
     const int tiles_m = (g.M + 255) / 256, tiles_n = (g.N + 255) / 256;
-    tail_fixup_kernel<<<dim3(unsigned(g.tail_tiles), 64), 256, 0, h->stream>>>(g, pairs, tiles_m, tiles_n);
-    MTB_CUDA(cudaGetLastError());
+    MTB_CUDA(launch_pdl(h, tail_fixup_kernel, dim3(unsigned(g.tail_tiles), 64), dim3(256), 0, g, pairs, tiles_m, tiles_n));
   }
   return MTB200_OK;
 }
@@ -213,9 +228,35 @@ inline int32_t launch_variant2(mtb200_ctx* h, const SplitOperand& a, const Split
                             Cfg::NUM_THREADS, tiles, ta, tb, g, work, tail && BK == 64);
 }
 
+// One-CTA kernel on the fp16 two-plane operands, 128 x 128 tiles, K block 64: for outputs of so few pair tiles that
+// the two-CTA kernel would leave most SMs idle or cut every tile along K and pay the fix-up pass (1024^3 is 16 pair
+// tiles but 64 of these).
+template <bool A_MN, bool B_MN>
+inline int32_t launch_small_f16(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp, GemmArgs g, int K) {
+  using Cfg = GemmCfg<128, 64, 3, 2>;
+  auto kern = gemm_split_umma_kernel<128, 64, 3, false, 2, A_MN, B_MN>;
+  if (int32_t rc_attr = grant_dynamic_smem(h, kern, int(Cfg::SMEM_BYTES))) return rc_attr;
+  CUtensorMap ta, tb;
+  int32_t rc;
+  if (A_MN) rc = make_split_tmap_mn(&ta, a.base, a.rows, a.cols_p, uint64_t(2) * a.batch, 64, 2);
+  else      rc = make_split_tmap(&ta, a.base, Kp, a.rows, uint64_t(2) * a.batch, 64, 128);
+  if (rc) return rc;
+  if (B_MN) rc = make_split_tmap_mn(&tb, b.base, b.rows, b.cols_p, uint64_t(2) * b.batch, 64, 2);
+  else      rc = make_split_tmap(&tb, b.base, Kp, b.rows, uint64_t(2) * b.batch, 64, 128);
+  if (rc) return rc;
+  g.num_kb = (K + 63) / 64;
+  g.planes_per_mat = 2;
+  const long long tiles = static_cast<long long>((g.M + 127) / 128) * ((g.N + 127) / 128) * g.batch;
+  const int grid = int(std::min<long long>(tiles, h->sm_count));
+  ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.M * g.N * double(g.num_kb) * 64 * g.batch);
+  MTB_CUDA(launch_pdl(h, kern, dim3(grid), dim3(Cfg::NUM_THREADS), Cfg::SMEM_BYTES, ta, tb, g));
+  return MTB200_OK;
+}
+
 // C[b] = epilogue(A_split[b] * B_split[b]^T + bias) on prepared operands.
 // variant: 0 = choose by N; 1 = 128x256 tile, K block 32; 2 = 128x128, K block 64;
-// 3 = 128x64, K block 64; 4 = 128x128, K block 32; 5 / 6 = two-CTA 256x256 pair tile with K block 64 / 32.
+// 3 = 128x64, K block 64; 4 = 128x128, K block 32; 5 / 6 = two-CTA 256x256 pair tile with K block 64 / 32;
+// 7 = 5 without tail splitting; 8 = one-CTA 128x128 on fp16 planes (chosen for outputs of few pair tiles).
 inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitOperand& b, int Kp,
                               int batch, int M, int N, float* C, long long ldc, long long strideC,
                               const float* bias, int epilogue, const float* aux, int mode, int variant,
@@ -236,6 +277,17 @@ inline int32_t run_split_gemm(mtb200_ctx* h, const SplitOperand& a, const SplitO
   g.num_kb = num_kb_override;  // 0: the whole padded K
   // two-CTA pair tiles whenever the output is at least one pair tile tall and wide
   if (variant == 0) variant = (M > 128 && N > 128) ? 5 : ((N > 128) ? 1 : (N > 64 ? 2 : 3));
+  // fp16 mode, whole K, few pair tiles: the one-CTA kernel fills more SMs and needs no fix-up pass
+  if (variant == 5 && mode == 23 && num_kb_override == 0 && kb_batch_stride == 0 && a.nplanes == 2 && b.nplanes == 2 &&
+      static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * batch <= h->sm_count / 4)
+    variant = 8;
+  if (variant == 8) {
+    const int Kl = K > 0 ? K : Kp;
+    if (a.mn_major && b.mn_major) return launch_small_f16<true, true>(h, a, b, Kp, g, Kl);
+    if (a.mn_major) return launch_small_f16<true, false>(h, a, b, Kp, g, Kl);
+    if (b.mn_major) return launch_small_f16<false, true>(h, a, b, Kp, g, Kl);
+    return launch_small_f16<false, false>(h, a, b, Kp, g, Kl);
+  }
   if ((a.mn_major || b.mn_major || mode == 23) && variant != 5 && variant != 7)
     return fail(MTB200_ERR_INVALID, "MN-major planes and the fp16 mode need the two-CTA kernel (variant 5)");
   switch (variant) {
@@ -401,8 +453,7 @@ inline int32_t gemm_f32_split_f16(mtb200_ctx* h, bool trans_a, bool trans_b, int
   s.bias = bias; s.aux = aux; s.epilogue = epilogue;
   s.gate = nf_word; s.gate_value = epoch;
   const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
-  gemm_simt_kernel<float, 8, 8><<<dim3(unsigned(tiles), unsigned(batch)), 256, 0, h->stream>>>(s);
-  MTB_CUDA(cudaGetLastError());
+  MTB_CUDA(launch_pdl(h, gemm_simt_kernel<float, 8, 8>, dim3(unsigned(tiles), unsigned(batch)), dim3(256), 0, s));
   return MTB200_OK;
 }
 

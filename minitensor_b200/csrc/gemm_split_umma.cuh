@@ -20,6 +20,7 @@
 // Two accumulators live in TMEM so the epilogue of tile i overlaps the main
 // loop of tile i+1.
 #pragma once
+#include <climits>
 #include <type_traits>
 #include "ptx_sm100.cuh"
 #include "split_bf16.cuh"
@@ -156,15 +157,14 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmArgs& g, float* s
   float* cbase = g.C + b * g.strideC;
   const float* abase = g.aux ? g.aux + b * g.strideC : nullptr;
   const int cq = (lane % LPR) * 4, rsub = lane / LPR;
+  int ea_span = SCALED ? abs(ea_own) : 0;      // largest |row exponent| of this warp's 32 rows
+  if constexpr (SCALED) {
+#pragma unroll
+    for (int o2 = 16; o2; o2 >>= 1) ea_span = max(ea_span, __shfl_xor_sync(0xffffffffu, ea_span, o2));
+  }
 #pragma unroll 1
   for (int c0 = col_base; c0 < col_end; c0 += CW) {
-    uint32_t v[CW];
-    if constexpr (CW == 32) tmem_ld_32x32(t_row + (c0 - col_base), v);
-    else tmem_ld_32x16(t_row + (c0 - col_base), v);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < CW; ++j) stage[lane * PITCH + j] = __uint_as_float(v[j]);
-    __syncwarp();
+    // the column group's bias and exponents first: their latency hides behind the TMEM read and the staging
     const int col = c0 + cq;
     float cb[4];
     int ce[4];
@@ -174,6 +174,20 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmArgs& g, float* s
       cb[e] = (g.bias && !g.bias_per_row && ok) ? __ldg(g.bias + col + e) : 0.0f;
       ce[e] = (SCALED && ok) ? (g.exp_b_per_batch ? eb_all : __ldg(eb + col + e)) : 0;
     }
+    uint32_t v[CW];
+    if constexpr (CW == 32) tmem_ld_32x32(t_row + (c0 - col_base), v);
+    else tmem_ld_32x16(t_row + (c0 - col_base), v);
+    bool fast = false;
+    if constexpr (SCALED) {
+      int ce_span = max(max(abs(ce[0]), abs(ce[1])), max(abs(ce[2]), abs(ce[3])));
+#pragma unroll
+      for (int o2 = 16; o2; o2 >>= 1) ce_span = max(ce_span, __shfl_xor_sync(0xffffffffu, ce_span, o2));
+      fast = ea_span + ce_span <= 126;
+    }
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < CW; ++j) stage[lane * PITCH + j] = __uint_as_float(v[j]);
+    __syncwarp();
 #pragma unroll
     for (int it = 0; it < LPR; ++it) {
       const int r = it * RPI + rsub;
@@ -199,7 +213,11 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmArgs& g, float* s
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float x = stage[r * PITCH + cq + e];
-          if constexpr (SCALED) x = scale_pow2(x, ea_r + ce[e]);
+          if constexpr (SCALED) {
+            // fast: every exponent sum of this warp's rows and columns is a normal float's exponent
+            if (fast) x *= __int_as_float((ea_r + ce[e] + 127) << 23);
+            else x = scale_pow2(x, ea_r + ce[e]);
+          }
           if (g.bias) x += g.bias_per_row ? rb : cb[e];
           o[e] = apply_epilogue_t<EPI>(x, ax[e]);
         }
@@ -213,6 +231,23 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmArgs& g, float* s
       }
     }
     __syncwarp();  // the tile is rewritten by the next column group
+  }
+}
+
+// What an epilogue warp reads besides its accumulator - scale exponents of its rows and of the tile's columns, the
+// bias - does not depend on the MMAs: asking for those cache lines before the wait on the accumulator takes their
+// latency out of the tail of a tile (an output of one tile per CTA has nothing else to hide it behind).
+__device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int b, int row0, int col_base, int col_end, int lane) {
+  auto touch = [](const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); };
+  const int c = col_base + lane * 32;          // one 128-byte line of 4-byte entries per lane
+  if (g.exp_b) {
+    if (lane == 0 && row0 < g.M) touch(g.exp_a + (g.a_batched ? static_cast<long long>(b) * g.M : 0) + row0);
+    if (g.exp_b_per_batch) { if (lane == 0) touch(g.exp_b + b); }
+    else if (c < col_end) touch(g.exp_b + (g.b_batched ? static_cast<long long>(b) * g.N : 0) + c);
+  }
+  if (g.bias) {
+    if (g.bias_per_row) { if (lane == 0 && row0 < g.M) touch(g.bias + row0); }
+    else if (c < col_end) touch(g.bias + c);
   }
 }
 
@@ -246,10 +281,13 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = PLANES * A_TILE + PLANES * B_TILE;
   static constexpr int ACC_COLS = BN;                      // f32 columns per accumulator
   static constexpr int TMEM_COLS = 2 * BN;                 // two accumulators (power of two)
-  static constexpr int NUM_THREADS = 192;
-  // epilogue staging: 4 warps x [32][CW + 1] floats; 16-column groups where the ring leaves less room
+  // epilogue staging: one [32][CW + 1] float tile per epilogue warp; 16-column groups where the ring leaves less
+  // room.  Eight epilogue warps (two per TMEM lane quarter, half of the tile's columns each) where their staging
+  // fits: an output of one tile per CTA has nothing to overlap the epilogue with, so its latency counts.
+  static constexpr int EPI_WARPS = (STAGES * STAGE_BYTES + 1024 + 256 + 8 * 32 * 33 * 4 <= 232448 && BN % 64 == 0) ? 8 : 4;
+  static constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int EPI_CW = (STAGES * STAGE_BYTES + 1024 + 256 + 4 * 32 * 33 * 4 <= 232448) ? 32 : 16;
-  static constexpr int EPI_BYTES = 4 * 32 * (EPI_CW + 1) * 4;
+  static constexpr int EPI_BYTES = EPI_WARPS * 32 * (EPI_CW + 1) * 4;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
   static_assert(ROW_BYTES == 64 || ROW_BYTES == 128, "BK must be 32 or 64");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
@@ -272,12 +310,15 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = in_band / rows_in_band;
 }
 
-template <int BN, int BK, int STAGES, bool CONV = false, int PLANES = 3>
-__global__ void __launch_bounds__(192, 1)
+// A_MN / B_MN: that operand's planes are MN-major ([k][mn] row-major in global memory, loaded as chunks of 64 mn
+// elements x BK k rows; needs BK = 64), as the two-CTA kernel takes them (gemm_split_umma2.cuh).
+template <int BN, int BK, int STAGES, bool CONV = false, int PLANES = 3, bool A_MN = false, bool B_MN = false>
+__global__ void __launch_bounds__(GemmCfg<BN, BK, STAGES, PLANES>::NUM_THREADS, 1)
 gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
                        const __grid_constant__ CUtensorMap tmapB, const GemmArgs g) {
   using Cfg = GemmCfg<BN, BK, STAGES, PLANES>;
   constexpr int BM = Cfg::BM;
+  static_assert(!(A_MN || B_MN) || (BK == 64 && !CONV), "MN-major operands need BK = 64 and the plain GEMM");
   extern __shared__ uint8_t smem_raw[];
 
   const uint32_t raw = smem_u32(smem_raw);
@@ -312,7 +353,7 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full_bar(a), 1);
-      mbar_init(acc_empty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(acc_empty_bar(a), Cfg::EPI_WARPS);  // one arrival per epilogue warp
     }
     fence_mbar_init();
     prefetch_tmap(&tmapA);
@@ -326,6 +367,8 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  grid_dependency_wait();        // the operand planes and exponents come from the kernels before this one
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -349,8 +392,12 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
           mbar_expect_tx(full_bar(stage), stage_tx);
           const uint32_t sa = tiles + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + PLANES * Cfg::A_TILE;
-          for (int s = 0; s < nsplit; ++s)
-            tma_load_3d(sa + s * Cfg::A_TILE, &tmapA, full_bar(stage), (kb0 + kb) * BK, tm * BM, za + s);
+          for (int s = 0; s < nsplit; ++s) {
+            if constexpr (A_MN)
+              tma_load_4d(sa + s * Cfg::A_TILE, &tmapA, full_bar(stage), 0, (kb0 + kb) * BK, (tm * BM) >> 6, za + s);
+            else
+              tma_load_3d(sa + s * Cfg::A_TILE, &tmapA, full_bar(stage), (kb0 + kb) * BK, tm * BM, za + s);
+          }
           if constexpr (CONV) {
             const int tap = kb / g.cv_kb_per_tap, cb = kb - tap * g.cv_kb_per_tap;
             const int fh = tap / g.cv_kw, fw = tap - fh * g.cv_kw;
@@ -358,8 +405,12 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
             for (int s = 0; s < nsplit; ++s)
               tma_load_4d(sb + s * Cfg::B_TILE, &tmapB, full_bar(stage), cb * BK, w, hh, zb + s);
           } else {
-            for (int s = 0; s < nsplit; ++s)
-              tma_load_3d(sb + s * Cfg::B_TILE, &tmapB, full_bar(stage), (kb0 + kb) * BK, tn * BN, zb + s);
+            for (int s = 0; s < nsplit; ++s) {
+              if constexpr (B_MN)
+                tma_load_4d(sb + s * Cfg::B_TILE, &tmapB, full_bar(stage), 0, (kb0 + kb) * BK, (tn * BN) >> 6, zb + s);
+              else
+                tma_load_3d(sb + s * Cfg::B_TILE, &tmapB, full_bar(stage), (kb0 + kb) * BK, tn * BN, zb + s);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -369,11 +420,14 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // operand format: bf16 planes, or fp16 planes in the two-plane mode 23
-      const uint32_t idesc = make_idesc(BM, CONV ? g.cv_umma_n : BN, g.mode == 23 ? 0u : 1u, /*f32*/ 1u);
+      const uint32_t idesc = make_idesc(BM, CONV ? g.cv_umma_n : BN, g.mode == 23 ? 0u : 1u, /*f32*/ 1u,
+                                        A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       // The whole issue loop with the product schedule known at compile time: per product the
       // thread adds a constant to each operand's descriptor and issues the MMA.
       auto issue_all = [&](auto npairs_tag) {
         constexpr int NPAIRS = decltype(npairs_tag)::value;
+        // one MMA covers 16 k: 32 bytes along a K-major row, 16 rows of 128 bytes in an MN-major chunk
+        constexpr uint32_t A_KSTEP = A_MN ? 2048u : 32u, B_KSTEP = B_MN ? 2048u : 32u;
         int stage = 0, acc = 0;
         uint32_t phase = 0, acc_phase = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -396,15 +450,15 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
             const uint32_t sb = sa + PLANES * Cfg::A_TILE;
             // descriptors of plane 0, k = 0; the start address sits in the low 14 bits in units of
             // 16 bytes and shared memory ends below 2^18, so adding an offset never carries out
-            const uint64_t da0 = make_kmajor_desc<Cfg::ROW_BYTES>(sa);
-            const uint64_t db0 = make_kmajor_desc<Cfg::ROW_BYTES>(sb);
+            const uint64_t da0 = A_MN ? make_mnmajor_desc(sa, BK * 128) : make_kmajor_desc<Cfg::ROW_BYTES>(sa);
+            const uint64_t db0 = B_MN ? make_mnmajor_desc(sb, BK * 128) : make_kmajor_desc<Cfg::ROW_BYTES>(sb);
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk) {
 #pragma unroll
               for (int p = 0; p < NPAIRS; ++p) {
                 const int code = split_pair_at(NPAIRS, p);
-                const uint32_t offa = (code >> 2) * Cfg::A_TILE + kk * 32;
-                const uint32_t offb = (code & 3) * Cfg::B_TILE + kk * 32;
+                const uint32_t offa = (code >> 2) * Cfg::A_TILE + kk * A_KSTEP;
+                const uint32_t offb = (code & 3) * Cfg::B_TILE + kk * B_KSTEP;
                 umma_f16<1>(d_tmem, da0 + (offa >> 4), db0 + (offb >> 4), idesc, accumulate);
                 accumulate = 1;
               }
@@ -430,6 +484,8 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // with eight epilogue warps the second warp of a quarter takes the upper half of the tile's columns
+    const int half_cols = (Cfg::EPI_WARPS == 8) ? ((warp - 2) >> 2) * (BN / 2) : 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) && ((g.ldc & 3) == 0) &&
@@ -437,16 +493,18 @@ gemm_split_umma_kernel(const __grid_constant__ CUtensorMap tmapA,
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int b, tm, tn;
       tile_coords(t, tiles_m, tiles_n, b, tm, tn);
+      const int col_first = tn * n_tile + half_cols;
+      const int col_last = min(min(g.N, (tn + 1) * n_tile), (Cfg::EPI_WARPS == 8) ? col_first + BN / 2 : INT_MAX);
+      epilogue_prefetch(g, b, tm * BM + q * 32, col_first, col_last, lane);
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_word)) {
         *abort_word = 1;
         if (lane == 0) atomicMax(g.status, 0x300u | 1u);
         break;
       }
       tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::ACC_COLS;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::ACC_COLS + half_cols;
       float* stage = reinterpret_cast<float*>(smem_raw + (bars + 256u - raw)) + (warp - 2) * 32 * (Cfg::EPI_CW + 1);
-      epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row, b, tm * BM + q * 32, tn * n_tile,
-                                      min(g.N, (tn + 1) * n_tile), lane, vec_ok);
+      epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row, b, tm * BM + q * 32, col_first, col_last, lane, vec_ok);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));

@@ -155,6 +155,8 @@ __device__ __forceinline__ void tail_fixup_body(const GemmArgs& g, int num_pairs
 }
 static __global__ void __launch_bounds__(256)
 tail_fixup_kernel(const GemmArgs g, int num_pairs, int tiles_m, int tiles_n) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   if (g.gate && ((*g.gate == g.gate_value) != (g.gate_run_if_equal != 0))) return;  // the product itself did not run
   switch (g.epilogue) {
     case EPI_RELU: tail_fixup_body<EPI_RELU>(g, num_pairs, tiles_m, tiles_n); break;
@@ -244,6 +246,8 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
   cluster_sync_all();  // barriers of both CTAs initialised, TMEM allocated
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  grid_dependency_wait();        // the operand planes and exponents come from the kernels before this one
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)

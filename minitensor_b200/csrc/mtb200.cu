@@ -233,6 +233,7 @@ int32_t mtb200_create(int32_t device_ordinal, mtb200_handle* out) {
   mtb200_ctx* h = new mtb200_ctx();
   h->device = device_ordinal;
   h->sm_count = prop.multiProcessorCount;
+  if (const char* no_pdl = getenv("MTB200_NO_PDL")) h->pdl = !(no_pdl[0] && no_pdl[0] != '0');
   e = cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
@@ -279,7 +280,20 @@ int32_t mtb200_destroy(mtb200_handle h) {
 
 int32_t mtb200_set_stream(mtb200_handle h, void* cuda_stream) {
   MTB_CHECK_HANDLE(h);
-  h->stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaStream_t next = static_cast<cudaStream_t>(cuda_stream);
+  if (next != h->stream) {
+    // calls on one handle share its workspace and flag words: what is still queued on the old stream goes first
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    const bool plain = cudaStreamIsCapturing(h->stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone &&
+                       cudaStreamIsCapturing(next, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone;
+    cudaGetLastError();
+    if (plain) {
+      DeviceGuard guard(h->device);
+      MTB_CUDA(cudaEventRecord(h->ev_join, h->stream));
+      MTB_CUDA(cudaStreamWaitEvent(next, h->ev_join, 0));
+    }
+    h->stream = next;
+  }
   return MTB200_OK;
 }
 

@@ -63,6 +63,7 @@ struct mtb200_ctx {
   // optional per-launch timing (mtb200_profile_*): event pairs around kernels
   struct ProfRec { cudaEvent_t start, stop; double work; int cls; };
   bool profiling = false;
+  bool pdl = true;             // programmatic dependent launch between a call's kernels (MTB200_NO_PDL=1 turns it off)
   std::vector<ProfRec> prof;
   // per-kernel set-up that costs microseconds of host time and does not change: the largest dynamic shared-memory
   // size already granted to a kernel on this device, and the cluster occupancy of the pair-tile kernels
@@ -124,8 +125,21 @@ inline int32_t grant_dynamic_smem(mtb200_ctx* h, Fn fn, int bytes) {
 constexpr int MTB_FLAG_SLOTS = 64;
 constexpr uint32_t MTB_FLAG_SET = 1u;
 inline int32_t call_flag_begin(mtb200_ctx* h, uint32_t** word) {
-  uint32_t* w = h->status + 4 + (h->epoch++ % MTB_FLAG_SLOTS);
-  MTB_CUDA(cudaMemsetAsync(w, 0, sizeof(uint32_t), h->stream));
+  const uint32_t slot = h->epoch++ % MTB_FLAG_SLOTS;
+  uint32_t* w = h->status + 4 + slot;
+  // Outside stream capture the words are cleared half a ring at a time, just before the half is handed out again:
+  // its previous users are 32 to 64 calls back in the same stream, so their kernels have read them.  (A captured
+  // graph replayed in between may leave one of these words set; the call that gets it then repeats its product
+  // in the IEEE kernel - slower, still correct.)  Under capture every call clears its own word, because a replay
+  // must start from a clear word whatever ran before it.
+  constexpr uint32_t HALF = MTB_FLAG_SLOTS / 2;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(h->stream, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusActive; }
+  if (cap != cudaStreamCaptureStatusNone) {
+    MTB_CUDA(cudaMemsetAsync(w, 0, sizeof(uint32_t), h->stream));
+  } else if (slot % HALF == 0) {
+    MTB_CUDA(cudaMemsetAsync(w, 0, HALF * sizeof(uint32_t), h->stream));
+  }
   *word = w;
   return MTB200_OK;
 }

@@ -17,6 +17,7 @@
 #pragma once
 #include <cooperative_groups.h>
 
+#include "ptx_sm100.cuh"
 #include "split_f16.cuh"
 
 namespace mtb {
@@ -176,6 +177,7 @@ prep16_pair_kernel(const PrepOperand a, const PrepOperand b, uint32_t* __restric
   __shared__ uint32_t s_part[16][64];
   __shared__ uint32_t s_max[64];
   __shared__ int s_exp[64];
+  grid_launch_dependents();      // the product's kernel may set itself up while this one runs (it waits before it reads)
   const bool second = int(blockIdx.x) >= a.blocks;
   const PrepOperand& o = second ? b : a;
   const int bx = int(blockIdx.x) - (second ? a.blocks : 0);

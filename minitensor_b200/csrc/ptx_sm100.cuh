@@ -96,6 +96,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   return true;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream still runs; grid_dependency_wait() blocks until that predecessor has finished
+// and its writes are visible, so everything before it (barrier setup, TMEM allocation, descriptor prefetch) overlaps
+// the predecessor's tail.  grid_launch_dependents() lets the NEXT kernel of the stream start early in the same way.
+// In a kernel launched without the attribute both are no-ops.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
