@@ -82,11 +82,11 @@ __device__ __forceinline__ bool pair_work_item(const GemmArgs& g, int it, int pa
 // pair tile), through the same shared-memory transposition as the final epilogue so that stores are row segments.
 template <int CW>
 __device__ __forceinline__ void epilogue_warp_raw(float* stage, uint32_t t_row, float* __restrict__ dst, int row0,
-                                                  int lane) {
+                                                  int lane, int col_begin, int col_end) {
   constexpr int LPR = CW / 4, RPI = 32 / LPR, PITCH = CW + 1;
   const int cq = (lane % LPR) * 4, rsub = lane / LPR;
 #pragma unroll 1
-  for (int c0 = 0; c0 < 256; c0 += CW) {
+  for (int c0 = col_begin; c0 < col_end; c0 += CW) {
     uint32_t v[CW];
     if constexpr (CW == 32) tmem_ld_32x32(t_row + c0, v);
     else tmem_ld_32x16(t_row + c0, v);
@@ -177,9 +177,13 @@ struct Gemm2Cfg {
   static constexpr int B_TILE = BNH * ROW_BYTES;
   static constexpr int STAGE_BYTES = NP * (A_TILE + B_TILE);  // NP planes of each operand per stage
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
-  static constexpr int NUM_THREADS = 192;
+  // Eight epilogue warps per CTA: two per TMEM lane quarter, 128 of the tile's 256 columns each.  While tiles follow
+  // one another the epilogue hides behind the next tile's MMAs either way; in the last round of a product, and in
+  // products of a single round, its length is exposed and halves.
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int EPI_CW = 32;
-  static constexpr int EPI_BYTES = 4 * 32 * (EPI_CW + 1) * 4;  // epilogue staging, see epilogue_warp_tile
+  static constexpr int EPI_BYTES = EPI_WARPS * 32 * (EPI_CW + 1) * 4;  // epilogue staging, see epilogue_warp_tile
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_BYTES;
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
   static_assert(ROW_BYTES == 64 || ROW_BYTES == 128, "BK must be 32 or 64");
@@ -194,13 +198,16 @@ struct Gemm2Cfg {
 // tcgen05.mma.kind::i8 per 32 k with an s32 accumulator, and the epilogue moves the 32-bit results out unchanged
 // (no scaling, bias or activation: the float path of the epilogue only copies bits then).
 template <int BK, int STAGES, bool A_MN = false, bool B_MN = false, int NP = 3, bool I8 = false>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(Gemm2Cfg<BK, STAGES, NP>::NUM_THREADS, 1)
 gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                         const GemmArgs g) {
   using Cfg = Gemm2Cfg<BK, STAGES, NP>;
   static_assert(!(A_MN || B_MN) || BK == 64, "MN-major operands need BK = 64");
   static_assert(!I8 || (!A_MN && !B_MN && BK == 64), "the int8 product takes K-major byte planes");
-  if (g.gate && ((*g.gate == g.gate_value) != (g.gate_run_if_equal != 0))) return;  // every thread of both CTAs
+  if (g.gate) {
+    grid_dependency_wait();      // the gate word is written by the kernels before this one
+    if ((*g.gate == g.gate_value) != (g.gate_run_if_equal != 0)) return;  // every thread of both CTAs
+  }
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -232,7 +239,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full_bar(a), 1);
-      mbar_init(acc_empty_bar(a), 8);
+      mbar_init(acc_empty_bar(a), 2 * Cfg::EPI_WARPS);   // every epilogue warp of both CTAs
     }
     fence_mbar_init();
     prefetch_tmap(&tmapA);
@@ -360,6 +367,7 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
+    const int half_cols = ((warp - 2) >> 2) * (Cfg::TILE_N / 2);   // the quarter's second warp takes the upper columns
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) && ((g.ldc & 3) == 0) && ((g.strideC & 3) == 0);
@@ -367,6 +375,10 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
     for (int it = 0; pair_work_item(g, it, pair, num_pairs, num_tiles, t, kbeg, kend, part); ++it) {
       int b, tm, tn;
       tile_coords(t, tiles_m, tiles_n, b, tm, tn);
+      const int row_first = tm * Cfg::TILE_M + int(rank) * Cfg::BM + q * 32;
+      const int col_first = tn * Cfg::TILE_N + half_cols;
+      const int col_last = min(min(g.N, (tn + 1) * Cfg::TILE_N), col_first + Cfg::TILE_N / 2);
+      if (part < 0) epilogue_prefetch(g, b, row_first, col_first, col_last, lane);
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_word)) {
         *abort_word = 1;
         if (lane == 0) atomicMax(g.status, 0x300u | 2u);
@@ -378,10 +390,10 @@ gemm_split_umma2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_
       if (part >= 0) {
         // one K range of a tail tile: the raw accumulator goes to its slot, the fix-up kernel finishes the tile
         float* slot = g.partial + (static_cast<long long>(t - g.tail_rounds * num_pairs) * g.tail_splits + part) * 65536;
-        epilogue_warp_raw<Cfg::EPI_CW>(stage, t_row, slot, int(rank) * Cfg::BM + q * 32, lane);
+        epilogue_warp_raw<Cfg::EPI_CW>(stage, t_row, slot, int(rank) * Cfg::BM + q * 32, lane, half_cols,
+                                       half_cols + Cfg::TILE_N / 2);
       } else {
-        epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row, b, tm * Cfg::TILE_M + int(rank) * Cfg::BM + q * 32,
-                                        tn * Cfg::TILE_N, min(g.N, (tn + 1) * Cfg::TILE_N), lane, vec_ok);
+        epilogue_warp_tile<Cfg::EPI_CW>(g, stage, t_row + half_cols, b, row_first, col_first, col_last, lane, vec_ok);
       }
       tc_fence_before();
       __syncwarp();
