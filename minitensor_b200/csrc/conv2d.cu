@@ -22,6 +22,7 @@
 // gathered-patch (explicit) lowering below.
 #include "mtb200_core.cuh"
 #include "gemm_launch.cuh"
+#include "conv_wgrad_halo.cuh"
 #include "conv_wgrad_umma.cuh"
 #include "conv_halo_umma.cuh"
 #include "conv_pix_umma.cuh"
@@ -711,6 +712,49 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
   const bool f16 = a.mode == 23;
   a.planes = f16 ? 2 : 3;
   a.status = h->status;
+  // Halo kernel (conv_wgrad_halo.cuh) for the fp16 mode: one staged block of x serves every tap.  Rows per step:
+  // the tr that wastes least of the reduction (a block is padded to a multiple of 16 indices and carries kw - 1
+  // zero columns per row) among those whose two stages fit shared memory.  0xFC in the variant byte keeps the
+  // window-per-tap kernel (test hook).
+  WgradHaloArgs hw = {};
+  bool halo = false;
+  {
+    const int wp = g.ow + g.kw - 1;
+    const int pairs = (taps + 1) / 2;
+    int best_tr = 0;
+    double best_waste = 1e30;
+    size_t best_x = 0, best_dy = 0;
+    if (f16 && wp <= 256 && ((f32_mode >> 8) & 0xff) != 0xFC) {
+      for (int tr = 1; tr <= std::min(g.oh, 256 - (g.kh - 1)); ++tr) {
+        const int kt = (tr * wp + 15) / 16 * 16;
+        const size_t xb = align_up(size_t(kt + (g.kh - 1) * wp + g.kw - 1) * 128, 1024);
+        const size_t db = align_up(size_t(kt) * 128, 1024);
+        if (WgradHaloCfg::smem_bytes(xb, db) > 232448) break;
+        if (size_t(2) * 128 * wp * (2 * tr + g.kh - 1) > (size_t(1) << 20) - 1) break;
+        // rows of the last, partly filled step of an image count as waste too
+        const double waste = double(kt) * ((g.oh + tr - 1) / tr) / (double(g.oh) * g.ow);
+        if (waste <= best_waste + 1e-12) { best_waste = waste; best_tr = tr; best_x = xb; best_dy = db; }
+      }
+    }
+    if (best_tr > 0) {
+      halo = true;
+      hw.c_out = g.c_out; hw.n_total = a.n_total; hw.cb_per_tap = a.cb_per_tap;
+      hw.kh = g.kh; hw.kw = g.kw; hw.pad_h = g.ph; hw.pad_w = g.pw; hw.oh = g.oh;
+      hw.tr = best_tr; hw.wp = wp; hw.ksteps = (best_tr * wp + 15) / 16;
+      hw.steps_per_image = (g.oh + best_tr - 1) / best_tr;
+      const long long steps = static_cast<long long>(g.n) * hw.steps_per_image;
+      hw.total_steps = int(steps);
+      hw.ocbs = cop / 64; hw.icbs = cip / 64;
+      hw.tgs = (pairs + WgradHaloCfg::MAX_UNITS - 1) / WgradHaloCfg::MAX_UNITS;
+      hw.taps_per_group = 2 * ((pairs + hw.tgs - 1) / hw.tgs);
+      const long long items = static_cast<long long>(hw.ocbs) * hw.icbs * hw.tgs;
+      hw.splits = int(std::max<long long>(1, std::min<long long>(steps, h->sm_count / std::max<long long>(1, items))));
+      hw.x_plane_bytes = uint32_t(best_x); hw.dy_plane_bytes = uint32_t(best_dy);
+      hw.status = h->status;
+      if (steps > INT32_MAX || items * hw.splits > INT32_MAX) halo = false;
+      else a.splits = hw.splits;
+    }
+  }
   const size_t bytes_dy = split_bytes(opix, cop, g.n), bytes_x = split_bytes(ipix, cip, g.n);   // room for three planes
   const size_t bytes_part = align_up(sizeof(float) * size_t(a.splits) * g.c_out * a.n_total, 1024);
   const size_t bytes_e = align_up(sizeof(int) * size_t(g.n), 1024);
@@ -757,6 +801,19 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     if (rc) return rc;
   }
   CUtensorMap tdy, tx;
+  if (halo) {
+    hw.part = a.part;
+    rc = image_plane_tmap(&tdy, p_dy, cop, g.ow, g.oh, g.n, 2, 64, uint32_t(hw.wp), uint32_t(hw.tr), CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, 2, 64, uint32_t(hw.wp), uint32_t(hw.tr + g.kh - 1),
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.c_out * double(opix) * taps * g.c_in * g.n);
+    const size_t smem = WgradHaloCfg::smem_bytes(hw.x_plane_bytes, hw.dy_plane_bytes);
+    if (int32_t rc_attr = grant_dynamic_smem(h, conv_wgrad_halo_kernel, int(smem))) return rc_attr;
+    conv_wgrad_halo_kernel<<<hw.ocbs * hw.icbs * hw.tgs * hw.splits, WgradHaloCfg::NUM_THREADS, smem, h->stream>>>(tdy, tx, hw);
+    MTB_CUDA(cudaGetLastError());
+  } else {
   rc = image_plane_tmap(&tdy, p_dy, cop, g.ow, g.oh, g.n, a.planes, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, a.planes, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -773,6 +830,7 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
       conv_wgrad_umma_kernel<3><<<a.splits * tiles, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, h->stream>>>(tdy, tx, a);
     }
     MTB_CUDA(cudaGetLastError());
+  }
   }
   const long long total = static_cast<long long>(g.c_out) * g.c_in * taps;
   wgrad_reduce_kernel<<<int(std::min<long long>((total + 255) / 256, 4096)), 256, 0, h->stream>>>(

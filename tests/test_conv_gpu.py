@@ -183,7 +183,10 @@ def test_both_lowerings_match_oracle(be, orc, rng, geom, lowering):
     block staged once per channel block as a halo tile: output pixels on the MMA's M side (default; two fp16 planes,
     or three bf16 planes when a bf16 mode is asked for) or output channels on the M side (variant byte 0xfb).
     Implicit GEMM that fetches the window of every tap (variant byte 0xfc; the last resort of the implicit path).
-    And the gathered-patch lowering (variant byte 0xff; taken by itself when a row is wider than 256)."""
+    And the gathered-patch lowering (variant byte 0xff; taken by itself when a row is wider than 256).
+    The weight gradient exists three times: implicit GEMM over one staged halo block of x per step with two taps
+    per MMA (default, fp16 planes), implicit GEMM with a window of x per tap (the bf16 modes, rows wider than 254,
+    and variant byte 0xfc), and the gathered-patch lowering."""
     n, c, h, w, co, kh, kw, stride, padding = geom
     mode = {"implicit": 0, "implicit_bf16x6": 6, "channels_on_m": 0xFB00, "channels_on_m_bf16x6": 0xFB06,
             "per_tap": 0xFC00, "explicit": 0xFF00}[lowering]
