@@ -25,6 +25,10 @@
 // tap pairs, range of steps) and writes its accumulators to part[range][oc][(tap, ic)]; wgrad_reduce_kernel adds
 // the ranges in order.
 //
+// (Tried and dropped: running x_hi*dy_hi and x_hi*dy_lo as one MMA of N = 128 whose dy operand takes its second
+// 64-channel chunk from the lo plane, as the forward kernel folds its weight planes.  With these MN-major operands
+// the kernel went from 146 to 216 us at the large conv config.)
+//
 // Roles: warp 0 producer, warp 1 TMEM owner and MMA issuer, warps 2..5 epilogue.  Every wait is bounded and reports
 // through the status word (role codes 0x1.. - 0x3.., site 6).
 #pragma once
