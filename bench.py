@@ -346,7 +346,9 @@ def config_table(be, torch, peaks, with_cpu: bool):
     del a, b, ad, bd, c
 
     # ---- square sweep, M = N = K in {256, 1024, 4096, 8192} x {f32, f64, i32}
-    cpu_budget_s = 16.0     # a single CPU timing predicted (from the previous size, x8) to exceed this is not run
+    # a single CPU timing predicted (from the previous size, by the cube of the size ratio) to exceed this is not
+    # run; the prediction is optimistic once the operands leave the caches, hence the margin
+    cpu_budget_s = 8.0
     for dt_name, tdt in (("f32", torch.float32), ("f64", torch.float64), ("i32", torch.int32)):
         last_cpu = None     # (size, ms) of the largest CPU run of this dtype
         for n in (256, 1024, 4096, 8192):

@@ -52,7 +52,8 @@ enum {
  * multiplies on the tensor cores with f32 accumulation; they differ in how an
  * f32 operand is represented. */
 enum {
-  MTB200_F32_DEFAULT = 0, /* F16X3 when the output is larger than 128 x 128, else BF16X6;
+  MTB200_F32_DEFAULT = 0, /* F16X3 when the output is larger than 128 x 128 (pair tiles, or
+                           * 128 x 128 tiles of one CTA when the pair tiles are few), else BF16X6;
                            * products with K <= 64 and at most 4e6 multiply-adds run as one
                            * launch of plain f32 multiply-add on the CUDA cores instead       */
   MTB200_F32_BF16X1 = 1,  /* single bf16 product: ~2^-8 relative, for experiments            */
@@ -67,7 +68,7 @@ enum {
 /* Second byte of f32_mode (f32_mode = mode | variant << 8), for tests and experiments: 0 = choose;
  * 1..6 = a fixed tile shape of the tensor kernels; 0xFE = the CUDA-core kernel (f32: IEEE multiply-add
  * in one launch; int32: the IMAD kernel); 0xFD = the integer tensor path regardless of size;
- * 0xFF (conv2d entries) = the gathered-patch lowering. */
+ * 0xFF / 0xFB / 0xFC (conv2d entries) = a fixed lowering, see there. */
 
 typedef struct mtb200_ctx* mtb200_handle;
 
@@ -343,10 +344,14 @@ int32_t mtb200_adam_step_counted(mtb200_handle h, int64_t n, float* param, const
  * else: engine/src/operations/conv.rs:85-93,202-204).
  * forward  = conv2d                     engine/src/operations/conv.rs:24-206
  * bwd_data / bwd_weight / bwd_bias = Conv2dBackward  engine/src/autograd/mod/shape.rs:57-197
- * f32_mode: MTB200_F32_DEFAULT = F16X3 for the stride-1 forward and data gradient (one power-of-two
- * scale per image and per weight row; Inf/NaN inputs give non-finite outputs in the windows they
- * touch) and BF16X6 for the weight gradient and for strided convolutions; the BF16 modes may be
- * asked for by value. */
+ * f32_mode: MTB200_F32_DEFAULT = F16X3 wherever the implicit kernels run - stride-1 forward, data
+ * gradient and weight gradient, and the strided forward (one power-of-two scale per image and per
+ * weight row; per tensor for the weight gradient, whose sums run over images) - and BF16X6 for the
+ * strided data and weight gradients, which go through gathered patches; the BF16 modes may be asked
+ * for by value.  Inf or NaN in an operand: the call recomputes its result with IEEE multiply-add in
+ * the reference's loop order, so non-finite values land where the reference puts them.
+ * Variant byte (f32_mode >> 8), for tests: 0xFF the gathered-patch lowering, 0xFB the
+ * channels-on-M halo kernel, 0xFC the kernels that load one window per filter tap. */
 int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t height, int64_t width,
                           int64_t c_out, int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w,
                           int64_t pad_h, int64_t pad_w, const float* x, const float* w,

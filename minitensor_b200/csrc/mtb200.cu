@@ -280,20 +280,12 @@ int32_t mtb200_destroy(mtb200_handle h) {
 
 int32_t mtb200_set_stream(mtb200_handle h, void* cuda_stream) {
   MTB_CHECK_HANDLE(h);
-  cudaStream_t next = static_cast<cudaStream_t>(cuda_stream);
-  if (next != h->stream) {
-    // calls on one handle share its workspace and flag words: what is still queued on the old stream goes first
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    const bool plain = cudaStreamIsCapturing(h->stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone &&
-                       cudaStreamIsCapturing(next, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone;
-    cudaGetLastError();
-    if (plain) {
-      DeviceGuard guard(h->device);
-      MTB_CUDA(cudaEventRecord(h->ev_join, h->stream));
-      MTB_CUDA(cudaStreamWaitEvent(next, h->ev_join, 0));
-    }
-    h->stream = next;
-  }
+  // No ordering is added between the old and the new stream: a host that moves a handle between streams (the
+  // data-parallel trainer runs Adam on a second stream while the backward pass continues on the first) orders them
+  // itself with events, and an implicit join here would serialise exactly the overlap it set up (measured at 8
+  // GPUs: 8.0 -> 8.7 ms per step).  Calls that share the handle's workspace or flag words must therefore be
+  // ordered by the caller when they are issued on different streams.
+  h->stream = static_cast<cudaStream_t>(cuda_stream);
   return MTB200_OK;
 }
 
