@@ -832,8 +832,8 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     MTB_CUDA(cudaGetLastError());
   }
   }
-  const long long total = static_cast<long long>(g.c_out) * g.c_in * taps;
-  wgrad_reduce_kernel<<<int(std::min<long long>((total + 255) / 256, 4096)), 256, 0, h->stream>>>(
+  const long long part_rows = static_cast<long long>(g.c_out) * a.n_total;
+  wgrad_reduce_kernel<<<int(std::min<long long>((part_rows + 31) / 32, 8192)), 256, 0, h->stream>>>(
       a.part, a.splits, g.c_out, g.c_in, cip, taps, dw, f16 ? e_dy : nullptr, f16 ? e_x : nullptr);
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;

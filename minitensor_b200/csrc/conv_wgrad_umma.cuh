@@ -231,21 +231,45 @@ conv_wgrad_umma_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
 
 // dw[oc][ic][tap] = 2^(e1 + e2) * sum_z part[z][oc][tap*cin_p + ic]   (fixed order: deterministic); e1 / e2 = the
 // operands' scale exponents in the fp16 mode (first entry of each vector), nullptr otherwise.
-__global__ void wgrad_reduce_kernel(const float* __restrict__ part, int splits, int c_out, int c_in, int cin_p,
-                                    int taps, float* __restrict__ dw, const int* __restrict__ e1,
-                                    const int* __restrict__ e2) {
+__global__ void __launch_bounds__(256)
+wgrad_reduce_kernel(const float* __restrict__ part, int splits, int c_out, int c_in, int cin_p,
+                    int taps, float* __restrict__ dw, const int* __restrict__ e1,
+                    const int* __restrict__ e2) {
+  // A block serves 32 consecutive entries of a partial's row (oc, (tap, ic)) - consecutive ic, so every load of a
+  // warp is one 128-byte line - with 8 threads per entry: thread zl adds the ranges zl, zl + 8, ... in ascending
+  // order and the eight sums are added in ascending zl, a fixed order whatever the launch.
+  __shared__ float red[8][33];
   const int e = e1 ? __ldg(e1) + __ldg(e2) : 0;
-  const long long total = static_cast<long long>(c_out) * c_in * taps;
   const long long n_total = static_cast<long long>(taps) * cin_p;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(i % taps);
-    const long long r = i / taps;
-    const int ic = static_cast<int>(r % c_in), oc = static_cast<int>(r / c_in);
-    const float* p = part + static_cast<long long>(oc) * n_total + static_cast<long long>(t) * cin_p + ic;
+  const long long rows = static_cast<long long>(c_out) * n_total;
+  const int lane = threadIdx.x & 31, zl = threadIdx.x >> 5;
+  for (long long base = static_cast<long long>(blockIdx.x) * 32; base < rows;
+       base += static_cast<long long>(gridDim.x) * 32) {
+    const long long j = base + lane;
     float s = 0.0f;
-    for (int z = 0; z < splits; ++z) s += p[static_cast<long long>(z) * c_out * n_total];
-    dw[i] = e1 ? scale_pow2(s, e) : s;
+    if (j < rows) {
+      const float* p = part + j;
+      int z = zl;
+      for (; z + 24 < splits; z += 32) {      // four loads in flight, added in ascending order
+        const float a0 = p[static_cast<long long>(z) * rows], a1 = p[static_cast<long long>(z + 8) * rows];
+        const float a2 = p[static_cast<long long>(z + 16) * rows], a3 = p[static_cast<long long>(z + 24) * rows];
+        s += a0; s += a1; s += a2; s += a3;
+      }
+      for (; z < splits; z += 8) s += p[static_cast<long long>(z) * rows];
+    }
+    red[zl][lane] = s;
+    __syncthreads();
+    if (zl == 0 && j < rows) {
+      float t = red[0][lane];
+#pragma unroll
+      for (int q = 1; q < 8; ++q) t += red[q][lane];
+      const int oc = static_cast<int>(j / n_total);
+      const int r = static_cast<int>(j - static_cast<long long>(oc) * n_total);
+      const int tap = r / cin_p, ic = r - tap * cin_p;
+      if (ic < c_in)
+        dw[(static_cast<long long>(oc) * c_in + ic) * taps + tap] = e1 ? scale_pow2(t, e) : t;
+    }
+    __syncthreads();
   }
 }
 
