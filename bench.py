@@ -746,6 +746,9 @@ def run_case(args):
         dw, db = torch.empty(4096, 4096, device=dev), torch.empty(4096, device=dev)
         fn = lambda: (be.dense_forward(x, w, b, 1, out=y, saved=saved),
                       be.dense_backward(x, w, dy, saved, dx=dx, dx_epilogue=4, dx_aux=x, dw=dw, db=db))
+    elif name == "gemm_f32_mid":        # plain products at 512, 1024 and 2048: the launch-bound middle of the range
+        mats = [(rnd(n, n), rnd(n, n), torch.empty(n, n, device=dev)) for n in (512, 1024, 2048)]
+        fn = lambda: [be.gemm(a, b, out=o) for (a, b, o) in mats]
     elif name == "gemm_f32_nt_tn":      # the two products of MatMulBackward at 2048
         a, b, dy = rnd(2048, 2048), rnd(2048, 2048), rnd(2048, 2048)
         fn = lambda: (be.gemm(dy, b, trans_b=True), be.gemm(a, dy, trans_a=True))
