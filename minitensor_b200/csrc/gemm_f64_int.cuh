@@ -109,6 +109,8 @@ __device__ __forceinline__ void dgemm_stash(double* __restrict__ sm, long long s
 // threads) is what runs: it reads the least shared memory per MMA.  Measured at 4096^3 on B200: 2 x 4 27.4 TFLOP/s,
 // 4 x 4 (512 threads, four warps per scheduler) 26.5, and the same tile on mma.sync.m16n8k16 26.4 - the warp
 // layout and the MMA shape are not what holds the kernel at 0.74 of the 37.1 TFLOP/s an MMA-only loop reaches.
+// Nor is the register staging: the same tile fed by three or four stages of 8-byte cp.async copies, with the
+// fragments of the next k step loaded while the current one multiplies, measured 24.9.
 template <int WM, int WN>
 static __global__ void __launch_bounds__(32 * WM * WN, 1) gemm_f64_dmma_kernel(const StridedGemmArgs g) {
   constexpr int NT = 32 * WM * WN;
