@@ -388,6 +388,9 @@ int32_t mtb200_conv2d_bwd_bias(mtb200_handle h, int64_t n, int64_t c_out, int64_
  * issue the same sequence of exchanges with the same n.  scale == 1 skips the multiply.  Asynchronous:
  * ordered after earlier work on that stream; synchronise the stream (or order another stream after it)
  * before reading buf. */
+/* A communicator is created with a budget of 16 CTAs for NCCL (through NCCL_MAX_CTAS, unless the host has set
+ * that variable itself; MTB200_COMM_CTAS=n changes the budget, 0 leaves NCCL alone): the collectives run beside
+ * persistent tensor kernels and must fit in the SMs those leave free. */
 typedef struct mtb200_comm_s* mtb200_comm;
 #define MTB200_COMM_ID_BYTES 128
 int32_t mtb200_comm_unique_id(void* id_out);

@@ -125,6 +125,18 @@ int32_t mtb200_comm_unique_id(void* id_out) {
   return MTB200_OK;
 }
 
+// The collectives of this library run BESIDE its persistent tensor kernels, which hold one CTA per SM for a whole
+// product: a collective with more CTAs than the SMs left free waits for, or displaces, CTAs of a product, and the
+// product's static tile deal turns one late CTA into a late product.  Measured on eight B200s (large MLP, steady
+// clocks, same box): no limit and 8 SMs free 8.67 ms per step, 16 CTAs / 16 SMs free 8.32, 24 / 24 8.33, 32 / 32 8.41.
+// NCCL takes its CTA budget from the environment when a communicator is created, so the default budget is set there
+// unless the host has chosen one (NCCL_MAX_CTAS) or opted out (MTB200_COMM_CTAS=0).
+static void apply_cta_budget() {
+  const char* own = getenv("MTB200_COMM_CTAS");
+  if (own && atoi(own) <= 0) return;
+  setenv("NCCL_MAX_CTAS", own ? own : "16", /*overwrite=*/0);
+}
+
 int32_t mtb200_comm_init_rank(int32_t world_size, int32_t rank, const void* id, int32_t device_ordinal,
                               mtb200_comm* out) {
   if (!out) return fail(MTB200_ERR_INVALID, "null output communicator");
@@ -139,6 +151,7 @@ int32_t mtb200_comm_init_rank(int32_t world_size, int32_t rank, const void* id, 
   NcclUniqueId uid;
   memcpy(&uid, id, sizeof uid);
   ncclComm_t c = nullptr;
+  apply_cta_budget();
   const int n = nccl().CommInitRank(&c, world_size, uid, rank);
   if (n) return nccl_fail("ncclCommInitRank", n);
   mtb200_comm_s* m = new mtb200_comm_s();
@@ -166,6 +179,7 @@ int32_t mtb200_comm_init(int32_t ndev, const int32_t* devs, mtb200_comm* out) {
   for (int d : list)
     if (d < 0 || d >= count) return fail(MTB200_ERR_INVALID, "device ordinal %d out of range [0,%d)", d, count);
   std::vector<ncclComm_t> comms(ndev, nullptr);
+  apply_cta_budget();
   const int n = nccl().CommInitAll(comms.data(), ndev, list.data());
   if (n) return nccl_fail("ncclCommInitAll", n);
   mtb200_comm_s* m = new mtb200_comm_s();

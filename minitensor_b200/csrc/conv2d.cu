@@ -323,24 +323,45 @@ static inline int direct_grid(const mtb200_ctx* h, long long items) {
   return int(std::max<long long>(1, std::min<long long>((items + 255) / 256, 8LL * h->sm_count)));
 }
 
-// dst[r][t][cp] (f32, zero for cp >= channels): the A operand of the implicit GEMM.
-//  mode 0 (forward):       r = oc, channel = ic : w[(r*chan + c)*taps + t]
-//  mode 1 (data gradient): r = ic, channel = oc : w[(c*rows + r)*taps + t]
+// A sub-filter: the taps (fh0 + a * fh_step, fw0 + b * fw_step), a < nfh, b < nfw, of a kh x kw filter.  The whole
+// filter is {0, 1, kh, 0, 1, kw}.  The strided data gradient computes dx one phase at a time, and a phase sees only
+// the taps whose offset matches its parity.
+struct TapSubset {
+  int fh0, fh_step, nfh, fw0, fw_step, nfw;
+};
+
+// dst[r][t][cp] (f32, zero for cp >= channels): the A operand of the implicit GEMM; t walks the sub-filter's taps.
+//  mode 0 (forward):       r = oc, channel = ic : w[(r*chan + c)*taps_full + tap]
+//  mode 1 (data gradient): r = ic, channel = oc : w[(c*rows + r)*taps_full + tap]
 __global__ void weight_taps_kernel(const float* __restrict__ w, float* __restrict__ dst, int rows, int chan,
-                                   int chan_p, int taps, int mode) {
+                                   int chan_p, int taps_full, int kw_full, TapSubset sub, int mode) {
+  const int taps = sub.nfh * sub.nfw;
   const long long total = static_cast<long long>(rows) * taps * chan_p;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int c = static_cast<int>(i % chan_p);
     const long long q = i / chan_p;
     const int t = static_cast<int>(q % taps), r = static_cast<int>(q / taps);
+    const int a = t / sub.nfw, b = t - a * sub.nfw;
+    const int tap = (sub.fh0 + a * sub.fh_step) * kw_full + sub.fw0 + b * sub.fw_step;
     float v = 0.0f;
     if (c < chan)
-      v = mode == 0 ? w[(static_cast<long long>(r) * chan + c) * taps + t]
-                    : w[(static_cast<long long>(c) * rows + r) * taps + t];
+      v = mode == 0 ? w[(static_cast<long long>(r) * chan + c) * taps_full + tap]
+                    : w[(static_cast<long long>(c) * rows + r) * taps_full + tap];
     dst[i] = v;
   }
 }
+
+// Extras of a call that computes one phase of a strided data gradient (implicit_conv below).
+struct ConvPhaseOut {
+  TapSubset sub;           // the phase's taps of the full kh_full x kw_full filter
+  int kh_full, kw_full;
+  bool image_ready;        // the image planes and exponents are in the workspace already (an earlier phase wrote them)
+  int out_sy, out_sx;      // pixel strides of the phase inside the full output image
+  int out_pitch;           // row pitch of the full output image
+  long long out_plane;     // pixels of the full output image
+  long long out_offset;    // first pixel of the phase inside it
+};
 
 static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, int img_w, int img_h, int n,
                                 int planes, uint32_t box_c, uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle sw);
@@ -351,13 +372,20 @@ static int32_t image_plane_tmap(CUtensorMap* out, const void* base, int chan_p, 
 static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, int img_h, int img_w,
                              const float* wsrc, int rows, int kh, int kw, int mode, int out_h, int out_w,
                              int w0, int h0, int sgn, const float* bias, float* out, int f32_mode,
-                             uint32_t* nf_word, int sh = 1, int sw = 1, int pad_h = 0, int pad_w = 0) {
+                             uint32_t* nf_word, int sh = 1, int sw = 1, int pad_h = 0, int pad_w = 0,
+                             const ConvPhaseOut* phase_out = nullptr) {
   // sh, sw > 1 (forward only, fp16 mode only - the caller checks): the image planes are written as sh * sw phase
   // images so that every tap reads a stride-1 window of one of them (conv_pix_umma.cuh).
   constexpr int BK = 32;
   using Cfg = GemmCfg<256, BK, 3>;
+  // with phase_out, kh x kw is the sub-filter; the workspace is laid out for the full filter so that every phase
+  // call finds the image planes of the first one where it left them
   const int chan_p = padded_k(chan), taps = kh * kw;
   const int Kp = taps * chan_p;
+  const int taps_full = phase_out ? phase_out->kh_full * phase_out->kw_full : taps;
+  const int Kp_full = taps_full * chan_p;
+  const TapSubset sub = phase_out ? phase_out->sub : TapSubset{0, 1, kh, 0, 1, kw};
+  const int kw_full = phase_out ? phase_out->kw_full : kw;
   const int phases = sh * sw;
   const int hq = (img_h + sh - 1) / sh, wq = (img_w + sw - 1) / sw;          // phase-image extent
   const int ipix = img_h * img_w, opix = out_h * out_w;
@@ -371,8 +399,8 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
   const bool f16 = gemm_mode == 23;
   const int planes = f16 ? 2 : 3;
   const size_t bytes_img = split_bytes(ppix, chan_p, n);      // sized for three planes; the fp16 mode uses two
-  const size_t bytes_w = split_bytes(rows, Kp, 1);
-  const size_t bytes_tmp = align_up(sizeof(float) * size_t(rows) * Kp, 1024);
+  const size_t bytes_w = split_bytes(rows, Kp_full, 1);
+  const size_t bytes_tmp = align_up(sizeof(float) * size_t(rows) * Kp_full, 1024);
   const size_t bytes_ea = align_up(sizeof(int) * size_t(rows), 1024), bytes_eb = align_up(sizeof(int) * size_t(n), 1024);
   void* ws = nullptr;
   int32_t rc = workspace_reserve(h, bytes_img + bytes_w + bytes_tmp + bytes_ea + 2 * bytes_eb, &ws);
@@ -386,8 +414,11 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
   uint32_t* amax = reinterpret_cast<uint32_t*>(wbase + bytes_img + bytes_w + bytes_tmp + bytes_ea + bytes_eb);
   const long long img_elems = static_cast<long long>(chan) * ipix;
   // channels-last planes: per image a [chan][pixels] -> [pixels][chan_p] turning split
-  if (f16) {
-    if (h->side_stream && !h->profiling) MTB_CUDA(cudaEventRecord(h->ev_fork, h->stream));   // the weights fork here
+  const bool image_ready = phase_out && phase_out->image_ready;
+  if (f16 && h->side_stream && !h->profiling) MTB_CUDA(cudaEventRecord(h->ev_fork, h->stream));   // the weights fork here
+  if (image_ready) {
+    // an earlier phase of the same call prepared the planes
+  } else if (f16) {
     ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (8.0 * chan + 4.0 * chan_p));
     MTB_CUDA(cudaMemsetAsync(amax, 0, sizeof(uint32_t) * size_t(n), h->stream));
     const int chunks = int(std::max<long long>(1, std::min<long long>((img_elems + 4095) / 4096,
@@ -411,7 +442,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     cudaStream_t sw = side ? h->side_stream : h->stream;
     if (side) MTB_CUDA(cudaStreamWaitEvent(sw, h->ev_fork, 0));
     weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, sw>>>(
-        wsrc, wtmp, rows, chan, chan_p, taps, mode);
+        wsrc, wtmp, rows, chan, chan_p, taps_full, kw_full, sub, mode);
     MTB_CUDA(cudaGetLastError());
     rc = launch_split16(h, wtmp, true, rows, Kp, 1, 0, reinterpret_cast<__half*>(p_w), ea, nf_word, MTB_FLAG_SET, sw);
     if (rc) return rc;
@@ -421,7 +452,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     }
   } else {
     weight_taps_kernel<<<int(std::min<long long>((wtotal + 255) / 256, 4096)), 256, 0, h->stream>>>(
-        wsrc, wtmp, rows, chan, chan_p, taps, mode);
+        wsrc, wtmp, rows, chan, chan_p, taps_full, kw_full, sub, mode);
     MTB_CUDA(cudaGetLastError());
     rc = launch_split(h, wtmp, false, rows, Kp, Kp, 1, 0, p_w, 3, nf_word, MTB_FLAG_SET);
     if (rc) return rc;
@@ -490,7 +521,11 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
       const size_t w_tile = size_t(n_tile) * 2 * bk;
       ConvPixArgs a = {};
       a.n_out = rows; a.out_h = out_h; a.out_w = out_w; a.batch = n;
-      a.C = out; a.bias = bias; a.mode = gemm_mode; a.planes_per_mat = planes;
+      a.C = out + (phase_out ? phase_out->out_offset : 0);
+      a.bias = bias; a.mode = gemm_mode; a.planes_per_mat = planes;
+      a.out_sy = phase_out ? phase_out->out_sy : 1; a.out_sx = phase_out ? phase_out->out_sx : 1;
+      a.out_pitch = phase_out ? phase_out->out_pitch : out_w;
+      a.out_plane = phase_out ? phase_out->out_plane : static_cast<long long>(opix);
       a.exp_w = f16 ? ea : nullptr; a.exp_img = f16 ? eb : nullptr;
       a.tr = best.tr; a.tc = best.tc; a.wp = best.wp; a.hh = best.tr + dyr; a.mb = best.mb; a.n_tile = n_tile;
       a.kh = kh; a.kw = kw; a.cbs = chan_p / bk; a.chan_p = chan_p;
@@ -539,7 +574,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     }
   }
 
-  if (phases > 1) return fail(MTB200_ERR_UNSUPPORTED, "strided implicit convolution: no tile plan fits");
+  if (phases > 1 || phase_out) return fail(MTB200_ERR_UNSUPPORTED, "strided implicit convolution: no tile plan fits");
   // Halo kernel (conv_halo_umma.cuh): the image block is staged once per (row block, channel block) and every tap
   // multiplies against it.  Geometry: halo row pitch wh (a multiple of 4), th output rows per tile with th * wh <= 256
   // MMA columns, and image stages that fit beside the weights - all of them resident when they fit, a ring otherwise.
@@ -718,19 +753,28 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
   // window-per-tap kernel (test hook).
   WgradHaloArgs hw = {};
   bool halo = false;
+  const int phases = g.sh * g.sw;
+  const int hq = (g.h + g.sh - 1) / g.sh, wq = (g.w + g.sw - 1) / g.sw;     // extent of a phase image of x
+  const int ppix = phases > 1 ? phases * hq * wq : ipix;                     // plane rows per image of x
   {
-    const int wp = g.ow + g.kw - 1;
+    // reach of the taps in (phase-)image coordinates relative to the output pixel
+    auto fdiv = [](int a_, int b_) { return (a_ >= 0) ? a_ / b_ : -((-a_ + b_ - 1) / b_); };
+    const int org_x = fdiv(-g.pw, g.sw), org_y = fdiv(-g.ph, g.sh);
+    const int dxr = fdiv(g.kw - 1 - g.pw, g.sw) - org_x, dyr = fdiv(g.kh - 1 - g.ph, g.sh) - org_y;
+    const int wp = g.ow + dxr;
     const int pairs = (taps + 1) / 2;
     int best_tr = 0;
     double best_waste = 1e30;
     size_t best_x = 0, best_dy = 0;
-    if (f16 && wp <= 256 && ((f32_mode >> 8) & 0xff) != 0xFC) {
-      for (int tr = 1; tr <= std::min(g.oh, 256 - (g.kh - 1)); ++tr) {
+    if (f16 && wp <= 256 && g.sh <= 8 && g.sw <= 8 && ((f32_mode >> 8) & 0xff) != 0xFC) {
+      for (int tr = 1; tr <= std::min(g.oh, 256 - dyr); ++tr) {
         const int kt = (tr * wp + 15) / 16 * 16;
-        const size_t xb = align_up(size_t(kt + (g.kh - 1) * wp + g.kw - 1) * 128, 1024);
+        const int hh = tr + dyr;
+        // rows the MMAs may touch: the last tap's shift plus a block of kt indices
+        const size_t xb = align_up(size_t((phases - 1) * hh * wp + dyr * wp + dxr + kt) * 128, 1024);
         const size_t db = align_up(size_t(kt) * 128, 1024);
         if (WgradHaloCfg::smem_bytes(xb, db) > 232448) break;
-        if (size_t(2) * 128 * wp * (2 * tr + g.kh - 1) > (size_t(1) << 20) - 1) break;
+        if (size_t(2) * 128 * wp * (phases * hh + tr) > (size_t(1) << 20) - 1) break;
         // rows of the last, partly filled step of an image count as waste too
         const double waste = double(kt) * ((g.oh + tr - 1) / tr) / (double(g.oh) * g.ow);
         if (waste <= best_waste + 1e-12) { best_waste = waste; best_tr = tr; best_x = xb; best_dy = db; }
@@ -740,6 +784,7 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
       halo = true;
       hw.c_out = g.c_out; hw.n_total = a.n_total; hw.cb_per_tap = a.cb_per_tap;
       hw.kh = g.kh; hw.kw = g.kw; hw.pad_h = g.ph; hw.pad_w = g.pw; hw.oh = g.oh;
+      hw.sh = g.sh; hw.sw = g.sw; hw.org_x = org_x; hw.org_y = org_y; hw.hh = best_tr + dyr;
       hw.tr = best_tr; hw.wp = wp; hw.ksteps = (best_tr * wp + 15) / 16;
       hw.steps_per_image = (g.oh + best_tr - 1) / best_tr;
       const long long steps = static_cast<long long>(g.n) * hw.steps_per_image;
@@ -755,7 +800,9 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
       else a.splits = hw.splits;
     }
   }
-  const size_t bytes_dy = split_bytes(opix, cop, g.n), bytes_x = split_bytes(ipix, cip, g.n);   // room for three planes
+  if (phases > 1 && !halo)
+    return fail(MTB200_ERR_UNSUPPORTED, "strided weight gradient: no step of the halo kernel fits shared memory");
+  const size_t bytes_dy = split_bytes(opix, cop, g.n), bytes_x = split_bytes(ppix, cip, g.n);   // room for three planes
   const size_t bytes_part = align_up(sizeof(float) * size_t(a.splits) * g.c_out * a.n_total, 1024);
   const size_t bytes_e = align_up(sizeof(int) * size_t(g.n), 1024);
   void* ws = nullptr;
@@ -786,8 +833,11 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     split16_turn_batch_kernel<<<dim3((opix + 63) / 64, cop / 64, g.n), 256, 0, h->stream>>>(
         dy, opix, dy_img, reinterpret_cast<__half*>(p_dy), amax, 0, e_dy, opix, g.c_out, cop);
     finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, sx>>>(x, 0, x_img * g.n, amax + 1, nf_word, MTB_FLAG_SET);
+    if (phases > 1 && ppix != ipix)   // phase images have rows / columns no pixel maps to: they must read as zero
+      MTB_CUDA(cudaMemsetAsync(p_x, 0, size_t(2) * g.n * ppix * cip * sizeof(__half), sx));
     split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, cip / 64, g.n), 256, 0, sx>>>(
-        x, ipix, x_img, reinterpret_cast<__half*>(p_x), amax + 1, 0, e_x, ipix, g.c_in, cip);
+        x, ipix, x_img, reinterpret_cast<__half*>(p_x), amax + 1, 0, e_x, ipix, g.c_in, cip,
+        RowPhases{g.w, g.sh, g.sw, hq, wq});
     MTB_CUDA(cudaGetLastError());
     if (side) {
       MTB_CUDA(cudaEventRecord(h->ev_join, sx));
@@ -805,8 +855,20 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     hw.part = a.part;
     rc = image_plane_tmap(&tdy, p_dy, cop, g.ow, g.oh, g.n, 2, 64, uint32_t(hw.wp), uint32_t(hw.tr), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, 2, 64, uint32_t(hw.wp), uint32_t(hw.tr + g.kh - 1),
-                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (phases == 1) {
+      rc = image_plane_tmap(&tx, p_x, cip, g.w, g.h, g.n, 2, 64, uint32_t(hw.wp), uint32_t(hw.hh), CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {   // {c, x, y, phase, image*planes + split} over the phase images
+      EncodeTiledFn enc = get_encode_tiled();
+      if (!enc) return fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+      const cuuint64_t dims[5] = {cuuint64_t(cip), cuuint64_t(wq), cuuint64_t(hq), cuuint64_t(phases), cuuint64_t(2) * g.n};
+      const cuuint64_t strides[4] = {cuuint64_t(cip) * 2, cuuint64_t(wq) * cip * 2, cuuint64_t(hq) * wq * cip * 2,
+                                     cuuint64_t(phases) * hq * wq * cip * 2};
+      const cuuint32_t box[5] = {64, cuuint32_t(hw.wp), cuuint32_t(hw.hh), cuuint32_t(phases), 1};
+      const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+      CUresult r5 = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, p_x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      rc = r5 == CUDA_SUCCESS ? MTB200_OK : fail(MTB200_ERR_CUDA, "cuTensorMapEncodeTiled (phase images) failed (%d)", int(r5));
+    }
     if (rc) return rc;
     ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.c_out * double(opix) * taps * g.c_in * g.n);
     const size_t smem = WgradHaloCfg::smem_bytes(hw.x_plane_bytes, hw.dy_plane_bytes);
@@ -956,6 +1018,39 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
                        nullptr, dx, f32_mode, nf_word);
     return rc ? rc : redo();
   }
+  // Strided data gradient, one output phase at a time.  Input pixel iy = sh * y' + py receives, from filter row fh,
+  // dy row (iy + ph - fh) / sh - only where that division is exact, i.e. for fh = fh0 + a * sh with
+  // fh0 = (py + ph) mod sh - so phase (py, px) of dx is a STRIDE-1 data gradient of dy under the sub-filter
+  // {fh0 + a * sh} x {fw0 + b * sw}: dy row y' + (py + ph - fh0) / sh - a.  The dy planes are prepared once; every
+  // phase gathers its sub-filter and runs the pixel kernel, which scatters its outputs with the strides.
+  if ((g.sh > 1 || g.sw > 1) && (f32_mode & 0xff) == 0 && !force_explicit && g.sh <= 8 && g.sw <= 8 && g.ow <= 4096) {
+    bool uncovered = false;     // a phase no tap reaches stays zero
+    for (int py = 0; py < g.sh && py < g.h; ++py)
+      for (int px = 0; px < g.sw && px < g.w; ++px)
+        if ((py + g.ph) % g.sh >= g.kh || (px + g.pw) % g.sw >= g.kw) uncovered = true;
+    if (uncovered) MTB_CUDA(cudaMemsetAsync(dx, 0, sizeof(float) * size_t(g.n) * g.c_in * ipix, h->stream));
+    bool first = true, fell_back = false;
+    for (int py = 0; py < g.sh && py < g.h && !fell_back; ++py)
+      for (int px = 0; px < g.sw && px < g.w; ++px) {
+        const int fh0 = (py + g.ph) % g.sh, fw0 = (px + g.pw) % g.sw;
+        if (fh0 >= g.kh || fw0 >= g.kw) continue;
+        const int nfh = (g.kh - 1 - fh0) / g.sh + 1, nfw = (g.kw - 1 - fw0) / g.sw + 1;
+        ConvPhaseOut po = {};
+        po.sub = TapSubset{fh0, g.sh, nfh, fw0, g.sw, nfw};
+        po.kh_full = g.kh; po.kw_full = g.kw;
+        po.image_ready = !first;
+        po.out_sy = g.sh; po.out_sx = g.sw; po.out_pitch = g.w;
+        po.out_plane = ipix;
+        po.out_offset = static_cast<long long>(py) * g.w + px;
+        rc = implicit_conv(h, dy, g.n, g.c_out, g.oh, g.ow, w, g.c_in, nfh, nfw, 1, (g.h - py + g.sh - 1) / g.sh,
+                           (g.w - px + g.sw - 1) / g.sw, (px + g.pw - fw0) / g.sw, (py + g.ph - fh0) / g.sh, -1, nullptr,
+                           dx, f32_mode, nf_word, 1, 1, 0, 0, &po);
+        if (rc == MTB200_ERR_UNSUPPORTED) { fell_back = true; break; }   // the gathered-patch lowering below writes all of dx
+        if (rc) return rc;
+        first = false;
+      }
+    if (!fell_back) return redo();
+  }
   const int Kp = padded_k(K);
   const size_t bytes_w = split_bytes(g.c_in, Kp, 1), bytes_p = split_bytes(ipix, Kp, g.n);
   const size_t bytes_perm = align_up(sizeof(float) * size_t(g.c_in) * K, 1024);
@@ -1007,9 +1102,11 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
     MTB_CUDA(cudaGetLastError());
     return MTB200_OK;
   };
-  if (g.sh == 1 && g.sw == 1 && ((f32_mode >> 8) & 0xff) != 0xff) {
+  const bool strided = g.sh > 1 || g.sw > 1;
+  if (((f32_mode >> 8) & 0xff) != 0xff && (!strided || (f32_mode & 0xff) == 0)) {
     rc = implicit_wgrad(h, g, dy, x, dw, f32_mode, nf_word);
-    return rc ? rc : redo();
+    if (!(strided && rc == MTB200_ERR_UNSUPPORTED)) return rc ? rc : redo();
+    // a strided layer the halo kernel has no step for: the gathered-patch lowering below
   }
   // split K: enough chunks to occupy the machine, each a whole number of 64-wide K blocks
   const long long kblocks = (Ktot + 63) / 64;

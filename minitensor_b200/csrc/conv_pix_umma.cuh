@@ -77,6 +77,11 @@ struct ConvPixArgs {
   // (y + floor((fh - pad_h) / sh), x + floor((fw - pad_w) / sw)): a stride-1 window again.  The halo box then has
   // a phase dimension and w_org / h_org are in phase-image coordinates.  sh = sw = 1: one phase, as above.
   int sh, sw, pad_h, pad_w;
+  // Where output pixel (y, x) of channel oc goes: C[image][oc * out_plane + y * out_sy * out_pitch + x * out_sx].
+  // A plain call has out_sy = out_sx = 1, out_pitch = out_w, out_plane = out_h * out_w; the strided data gradient
+  // computes one phase of dx per launch and scatters it with the convolution's strides.
+  int out_sy, out_sx, out_pitch;
+  long long out_plane;
   uint32_t img_plane_bytes;  // shared-memory bytes per image plane of a stage (multiple of 128: TMA destinations)
   uint32_t w_tile_bytes;     // shared-memory bytes per weight plane of one (channel block, tap): n_tile rows
   int w_stages;            // weight tiles shared memory holds: the ring depth, or taps * cbs when resident
@@ -364,7 +369,7 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
     // ------------------------------------------------------------ epilogue (warps 3..10)
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int half = (warp - 3) >> 2;    // which of the quarter's two warps
-    const long long opix = static_cast<long long>(g.out_h) * g.out_w;
+    const long long opix = g.out_plane;
     const int chunks = (g.n_tile + 31) / 32;             // 32-channel chunks of an M block
     const int items = g.mb * chunks;
     int acc = 0;
@@ -381,14 +386,15 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
       const int y0 = ty * g.tr, x0 = tx * g.tc;
       const int rows_here = min(g.tr, g.out_h - y0), cols_here = min(g.tc, g.out_w - x0);
       const int eb = g.exp_img ? __ldg(g.exp_img + b) : 0;
-      float* cimg = g.C + static_cast<long long>(b) * g.n_out * opix + static_cast<long long>(y0) * g.out_w + x0;
+      float* cimg = g.C + static_cast<long long>(b) * g.n_out * opix +
+                    static_cast<long long>(y0) * g.out_sy * g.out_pitch + static_cast<long long>(x0) * g.out_sx;
       for (int it = half; it < items; it += 2) {
         const int j = it / chunks, c0 = (it - j * chunks) * 32;
         // this lane's output pixel in M block j
         const int n = j * Cfg::BM + q * 32 + lane;
         const int r = n / g.wp, c = n - r * g.wp;
         const bool pix_ok = r < rows_here && c < cols_here;
-        const long long pix = static_cast<long long>(r) * g.out_w + c;
+        const long long pix = static_cast<long long>(r) * g.out_sy * g.out_pitch + static_cast<long long>(c) * g.out_sx;
         // lane e prepares channel c0 + e: bias and the two exact power-of-two factors that undo the operand scalings
         const int oc_own = tn * g.n_tile + c0 + lane;
         const bool oc_ok = oc_own < g.n_out && c0 + lane < g.n_tile;

@@ -25,6 +25,12 @@
 // tap pairs, range of steps) and writes its accumulators to part[range][oc][(tap, ic)]; wgrad_reduce_kernel adds
 // the ranges in order.
 //
+// Strides.  For a strided convolution the x planes are stored as sh * sw phase images (split_f16.cuh, RowPhases):
+// output pixel (oy, ox) under tap (fh, fw) reads phase ((fh - pad_h) mod sh, (fw - pad_w) mod sw) at
+// (oy + floor((fh - pad_h) / sh), ox + floor((fw - pad_w) / sw)) - a stride-1 window again.  The halo block then has
+// a phase dimension (one 5-D load), and a tap's row shift is phase * (rows of one phase's block) + the shift inside
+// it; nothing else changes.  Stride 1 is the one-phase case of the same formulas.
+//
 // (Tried and dropped: running x_hi*dy_hi and x_hi*dy_lo as one MMA of N = 128 whose dy operand takes its second
 // 64-channel chunk from the lo plane, as the forward kernel folds its weight planes.  With these MN-major operands
 // the kernel went from 146 to 216 us at the large conv config.)
@@ -41,8 +47,11 @@ struct WgradHaloArgs {
   int c_out, n_total;        // output channels; row length of a partial = taps * cin_p
   int cb_per_tap;            // cin_p / 64
   int kh, kw, pad_h, pad_w;
+  int sh, sw;                // strides (1, 1: one phase)
+  int org_x, org_y;          // halo origin relative to the step's first output pixel, in phase-image coordinates
+  int hh;                    // rows of one phase's halo block: tr + reach of the taps
   int oh;                    // output rows per image
-  int tr, wp;                // output rows per step; pitch ow + kw - 1
+  int tr, wp;                // output rows per step; pitch = output width + reach of the taps
   int ksteps;                // ceil(tr * wp / 16): MMAs of 16 reduction indices per (step, tap pair, product)
   int steps_per_image;       // ceil(oh / tr)
   int total_steps;           // images * steps_per_image
@@ -82,6 +91,7 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
   // unit_lo[u]: what tap pair u adds to the low word of the x descriptor - the first tap's row shift in the start
   // address field (16-byte units) and the distance to the second tap's rows in the leading-offset field
   uint32_t* unit_lo = reinterpret_cast<uint32_t*>(smem_raw + (bars + 128u - raw));
+  uint32_t* unit_swap = unit_lo + Cfg::MAX_UNITS;   // 1: lanes 0..63 of the pair hold its SECOND tap
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x / g.splits, z = blockIdx.x - item * g.splits;
@@ -100,9 +110,22 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
     const uint32_t n16 = (Cfg::STAGES * stage_bytes) >> 4;
     for (uint32_t i = threadIdx.x; i < n16; i += blockDim.x) p[i] = make_uint4(0u, 0u, 0u, 0u);
   }
+  const int phases = g.sh * g.sw;
   if (threadIdx.x < units) {
+    auto shift_of = [&](int tap) {       // halo row of the tap's window for the step's first output pixel
+      const int fh = tap / g.kw, fw = tap - fh * g.kw;
+      const int ay = fh - g.pad_h, ax = fw - g.pad_w;
+      const int py = ((ay % g.sh) + g.sh) % g.sh, px = ((ax % g.sw) + g.sw) % g.sw;
+      const int dy = (ay - py) / g.sh - g.org_y, dx = (ax - px) / g.sw - g.org_x;      // exact divisions
+      return (py * g.sw + px) * (g.hh * g.wp) + dy * g.wp + dx;
+    };
     const int ta = tap0 + 2 * threadIdx.x, tb = min(ta + 1, tap_end - 1);
-    const int off_a = (ta / g.kw) * g.wp + ta % g.kw, off_b = (tb / g.kw) * g.wp + tb % g.kw;
+    int off_a = shift_of(ta), off_b = shift_of(tb);
+    // with phases the second tap's rows may lie before the first's; the leading offset is kept non-negative by
+    // letting the pair's lanes swap roles (the epilogue reads the flag)
+    const bool swap = off_b < off_a;
+    if (swap) { const int t = off_a; off_a = off_b; off_b = t; }
+    unit_swap[threadIdx.x] = swap ? 1u : 0u;
     unit_lo[threadIdx.x] = (static_cast<uint32_t>(off_b - off_a) * 8u) << 16 | static_cast<uint32_t>(off_a) * 8u;
   }
   if (threadIdx.x == 0) {
@@ -131,7 +154,7 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
     if (lane == 0 && has_work) {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t tx = 2u * static_cast<uint32_t>(g.wp) * 128u * static_cast<uint32_t>(2 * g.tr + g.kh - 1);
+      const uint32_t tx = 2u * static_cast<uint32_t>(g.wp) * 128u * static_cast<uint32_t>(phases * g.hh + g.tr);
       for (int st = step_begin; st < step_end; ++st) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word)) {
           *abort_word = 1;
@@ -144,7 +167,10 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
         const uint32_t sx = ring + stage * stage_bytes;
         const uint32_t sd = sx + 2 * g.x_plane_bytes;
         for (int s = 0; s < 2; ++s) {
-          tma_load_4d(sx + s * g.x_plane_bytes, &tmapX, full_bar(stage), icb * 64, -g.pad_w, y0 - g.pad_h, img * 2 + s);
+          if (phases == 1)
+            tma_load_4d(sx + s * g.x_plane_bytes, &tmapX, full_bar(stage), icb * 64, g.org_x, y0 + g.org_y, img * 2 + s);
+          else   // {c, x, y, phase, plane}: every phase image's halo block in one request
+            tma_load_5d(sx + s * g.x_plane_bytes, &tmapX, full_bar(stage), icb * 64, g.org_x, y0 + g.org_y, 0, img * 2 + s);
           tma_load_4d(sd + s * g.dy_plane_bytes, &tmapDy, full_bar(stage), ocb * 64, 0, y0, img * 2 + s);
         }
         if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -203,7 +229,7 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const int oc_here = min(64, g.c_out - ocb * 64);
     for (int u = 0; u < units; ++u) {
-      const int tap = tap0 + 2 * u + slot;
+      const int tap = tap0 + 2 * u + (slot ^ int(unit_swap[u]));
       for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t v[32];
         if (ready) {

@@ -83,8 +83,9 @@ class MLPTrainer:
         if self.fused_dense and f32_mode != 0:
             raise ValueError("fused_dense uses the default f32 mode")
         self.overlap_comm = (self.world_size > 1) if overlap_comm is None else bool(overlap_comm)
-        # SMs left to the collectives that overlap the backward products (MTB200_COMM_SMS, default 8 when world > 1)
-        self.comm_sms = int(os.environ.get("MTB200_COMM_SMS", "8")) if self.world_size > 1 else 0
+        # SMs left to the collectives that overlap the backward products (MTB200_COMM_SMS, default 16 when world > 1:
+        # the library's communicator asks NCCL for at most 16 CTAs, so the collectives fit beside the products)
+        self.comm_sms = int(os.environ.get("MTB200_COMM_SMS", "16")) if self.world_size > 1 else 0
         self.be: Backend = get_backend(device)
         dev = self.be.device
         self.w_off, self.b_off, total = mlp_layout(self.dims)

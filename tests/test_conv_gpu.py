@@ -224,10 +224,12 @@ STRIDED = [  # n, c, h, w, co, kh, kw, stride, padding
 
 @pytest.mark.parametrize("geom", STRIDED)
 @pytest.mark.parametrize("lowering", ["implicit", "explicit"])
-def test_strided_forward_both_lowerings(be, orc, rng, geom, lowering):
-    """Strided forward convolutions run the implicit kernel too: the image planes are written as stride_h x
-    stride_w phase images, which turns every filter tap into a stride-1 window of one of them.  Same bounds as
-    the stride-1 path, against the oracle and float64, for both that kernel and the gathered-patch lowering."""
+def test_strided_both_lowerings(be, orc, rng, geom, lowering):
+    """Strided convolutions run the implicit kernels too.  Forward: the image planes are written as stride_h x
+    stride_w phase images, which turns every filter tap into a stride-1 window of one of them.  Data gradient: one
+    phase of dx at a time, each a stride-1 data gradient of dy under the sub-filter of taps with that phase's
+    parity, scattered with the strides (phases no tap reaches stay zero).  Same bounds as the stride-1 path, against
+    the oracle and float64, for both those kernels and the gathered-patch lowering."""
     n, c, h, w, co, kh, kw, stride, padding = geom
     mode = 0 if lowering == "implicit" else 0xFF00
     xn = rng.standard_normal((n, c, h, w)).astype(np.float32)
@@ -240,6 +242,15 @@ def test_strided_forward_both_lowerings(be, orc, rng, geom, lowering):
     assert tuple(y.shape) == ref.shape
     check_outputs("y", y.cpu().numpy(), ref, conv_f64.forward(xn, wn, bn, stride, padding),
                   conv_f64.forward_norms(xn, wn, stride, padding), extra=np.abs(bn)[None, :, None, None])
+    go = rng.standard_normal(ref.shape).astype(np.float32)
+    dx = be.conv2d_bwd_data(dev(go), dev(wn), xn.shape, stride, padding, f32_mode=mode)
+    dw = be.conv2d_bwd_weight(dev(go), dev(xn), wn.shape, stride, padding, f32_mode=mode)
+    be.sync()
+    gx, gw, _ = orc.conv2d_backward(xn, wn, go, stride, padding, need_b=False)
+    check_outputs("dx", dx.cpu().numpy(), gx, conv_f64.grad_input(go, wn, xn.shape, stride, padding),
+                  conv_f64.grad_input_norms(go, wn, xn.shape, stride, padding))
+    check_outputs("dw", dw.cpu().numpy(), gw, conv_f64.grad_weight(go, xn, wn.shape, stride, padding),
+                  conv_f64.grad_weight_norms(go, xn, wn.shape, stride, padding))
 
 
 def test_implicit_conv_scales_every_image_on_its_own(be, orc, rng):
