@@ -344,11 +344,11 @@ int32_t mtb200_adam_step_counted(mtb200_handle h, int64_t n, float* param, const
  * else: engine/src/operations/conv.rs:85-93,202-204).
  * forward  = conv2d                     engine/src/operations/conv.rs:24-206
  * bwd_data / bwd_weight / bwd_bias = Conv2dBackward  engine/src/autograd/mod/shape.rs:57-197
- * f32_mode: MTB200_F32_DEFAULT = F16X3 wherever the implicit kernels run - stride-1 forward, data
- * gradient and weight gradient, and the strided forward (one power-of-two scale per image and per
- * weight row; per tensor for the weight gradient, whose sums run over images) - and BF16X6 for the
- * strided data and weight gradients, which go through gathered patches; the BF16 modes may be asked
- * for by value.  Inf or NaN in an operand: the call recomputes its result with IEEE multiply-add in
+ * f32_mode: MTB200_F32_DEFAULT = F16X3 wherever the implicit kernels run - forward, data gradient
+ * and weight gradient, stride 1 or strided up to 8 (one power-of-two scale per image and per weight
+ * row; per tensor for the weight gradient, whose sums run over images) - and BF16X6 where a layer
+ * goes through gathered patches (rows wider than 254 pixels, larger strides); the BF16 modes may be
+ * asked for by value.  Inf or NaN in an operand: the call recomputes its result with IEEE multiply-add in
  * the reference's loop order, so non-finite values land where the reference puts them.
  * Variant byte (f32_mode >> 8), for tests: 0xFF the gathered-patch lowering, 0xFB the
  * channels-on-M halo kernel, 0xFC the kernels that load one window per filter tap. */
