@@ -1,25 +1,23 @@
-// conv2d (NCHW / OIHW, f32) lowered to the split-plane tensor-core GEMM (fp16 two-plane mode for the implicit
-// forward and data gradient, bf16 planes elsewhere).
+// conv2d (NCHW / OIHW, f32) on the split-plane tensor-core kernels: host side, preparation kernels, lowerings.
 //
-// The reference computes the convolution with direct loops
-// (engine/src/operations/conv.rs:111-157) and its backward with three more
-// (engine/src/autograd/mod/shape.rs:57-197).  Here each of the four results is
-// a GEMM whose operands are gathered straight into the split planes the
-// GEMM kernel consumes, with the image as the batch entry so the output lands
-// in NCHW without a transpose:
-//   forward   y[n]  [C_out][OH*OW] = W [C_out][C_in*kH*kW]   * patches(x[n])^T  (+ bias per row)
-//   bwd data  dx[n] [C_in][H*W]    = W'[C_in][C_out*kH*kW]   * patches'(dy[n])^T
-//   bwd weight dW [C_out][C_in*kH*kW] = sum over K chunks of dy[C_out][(n,oh,ow)] * patchesT(x)
-//   bwd bias  db[oc] = sum_{n,oh,ow} dy
+// The reference computes the convolution with direct loops (engine/src/operations/conv.rs:111-157) and its
+// backward with three more (engine/src/autograd/mod/shape.rs:57-197).  Here each result is a GEMM:
+//   forward    y[n]  [C_out][OH*OW] = W [C_out][C_in*kH*kW] * windows(x[n])^T  (+ bias per channel)
+//   bwd data   dx[n] [C_in][H*W]    = W'[C_in][C_out*kH*kW] * windows'(dy[n])^T
+//   bwd weight dW [C_out][C_in*kH*kW] = sum over (image, pixel) of dy[.][C_out] * windows(x)[.][C_in*kH*kW]
+//   bwd bias   db[oc] = sum_{n,oh,ow} dy
 //
-// Stride-1 forward and data gradient run as an IMPLICIT GEMM: the image is
-// split once into channels-last planes [image*planes+split][h][w][c] (two fp16
-// planes scaled per image by default, three bf16 planes otherwise) and the
-// GEMM kernel's TMA producer reads, for every (filter tap, channel block), the
-// shifted window {c block, full rows} of those planes with out-of-range
-// coordinates zero-filled by the hardware: the padding and the im2col matrix
-// never exist in memory.  Other strides and the weight gradient use the
-// gathered-patch (explicit) lowering below.
+// IMPLICIT lowering (default).  The image operand is split once into channels-last planes
+// [image*planes+split][h][w][c] (two fp16 planes scaled by a power of two per image - per tensor for the weight
+// gradient - or three bf16 planes in the bf16 modes; stride_h x stride_w phase images for strided layers) and the
+// kernels' TMA producers read halo blocks of those planes with out-of-range coordinates zero-filled by the hardware:
+// the padding and the im2col matrix never exist in memory.  Kernels: conv_pix_umma.cuh (forward and data gradient,
+// also strided: the data gradient one output phase at a time), conv_wgrad_halo.cuh (weight gradient, also strided),
+// and the earlier conv_halo_umma.cuh / per-tap kernels as fallbacks and test cross-checks.
+// EXPLICIT lowering (rows wider than the implicit kernels take, strides above 8, bf16 modes of strided layers, and
+// variant byte 0xFF): patches are gathered straight into the split planes of the plain GEMM.
+// Inf / NaN in an operand: every lowering ends with a gated direct kernel that recomputes the result in the
+// reference's loop order when the call's flag word was raised during preparation.
 #include "mtb200_core.cuh"
 #include "gemm_launch.cuh"
 #include "conv_wgrad_halo.cuh"
