@@ -526,6 +526,12 @@ def _run_ours(args, saved_stdout):
             print(json.dumps({"error": f"--gpus {args.gpus} needs torchrun with {args.gpus} processes"}), flush=True)
             return 2
     torch.cuda.set_device(local)
+    host_numa = None
+    if world > 1:
+        # host batches next to the GPU that reads them: with every rank copying at once, buffers on the far socket
+        # make the socket interconnect the bound (hostmem.py); N = 1 keeps all cores for the CPU baseline
+        from minitensor_b200.hostmem import bind_host_to_gpu
+        host_numa = bind_host_to_gpu(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
@@ -677,7 +683,8 @@ def _run_ours(args, saved_stdout):
                 "d2h_bytes_per_step": 4, "note": "next batch's host->device copy overlaps the current step",
                 "h2d_gbs_per_rank_needed": h2d / (ms_per_step * 1e6),
                 "h2d_gbs_per_rank_bare_copy_all_ranks_at_once": h2d_ceiling_gbs,
-                "floor_ms_per_step_from_host_link": copy_ms},
+                "floor_ms_per_step_from_host_link": copy_ms,
+                "host_cpus_bound_to_gpu_numa_node": host_numa},
         "gpu_launches": gpu_launches,
         "roofline": {
             "kernel": "gemm_split_umma2_kernel", "bound": "tensor", "achieved": achieved, "peak": peak_f32,

@@ -542,6 +542,33 @@ def test_gemm_sm_limit_changes_nothing_but_the_grid(be, rng):
         be.set_gemm_sm_limit(-1)
 
 
+def test_dependent_launch_changes_no_bit(be, rng, monkeypatch):
+    """The kernels of a call are launched with programmatic stream serialization and wait for their predecessors
+    inside the kernel; a handle created with MTB200_NO_PDL=1 launches them the plain way.  Same bits either way, for
+    the one-launch preparation + one-CTA kernel (small), the pair-tile kernel with cut tail tiles and fix-up (mid)
+    and an Inf operand that takes the gated redo."""
+    from minitensor_b200.backend import Backend
+    monkeypatch.setenv("MTB200_NO_PDL", "1")
+    plain = Backend(be.device.index or 0)
+    monkeypatch.delenv("MTB200_NO_PDL")
+    try:
+        for (m, k, n) in ((512, 512, 512), (768, 1024, 640), (1024, 1024, 1024), (2048, 512, 2304)):
+            a = dev(be, rng.standard_normal((m, k)).astype(np.float32))
+            b = dev(be, rng.standard_normal((k, n)).astype(np.float32))
+            for _ in range(3):                       # back to back: every kernel's set-up overlaps a predecessor's tail
+                got = be.gemm(a, b)
+            ref = plain.gemm(a, b)
+            be.sync(); plain.sync()
+            assert torch.equal(got, ref), (m, k, n)
+        a[3, 5] = float("inf")
+        got, ref = be.gemm(a, b), plain.gemm(a, b)
+        be.sync(); plain.sync()
+        assert torch.equal(torch.nan_to_num(got, nan=7.0), torch.nan_to_num(ref, nan=7.0))
+        assert bool(torch.isinf(got[3]).all())
+    finally:
+        plain.close()
+
+
 def test_plain_gemm_replays_from_a_cuda_graph(be, rng):
     """A mid-size f32 product (operands prepared on two streams, tail tiles cut, fix-up kernel) recorded into a
     CUDA graph after one eager call and replayed on new operand contents: same bits as the eager call."""

@@ -110,3 +110,38 @@ def test_two_rank_gradient_average_equals_full_batch():
     _, full = oracle.mlp_train_step(dims, x, labels, p, np.zeros_like(p), np.zeros_like(p), 0.0, 0.9, 0.999, 1e-8, 1,
                                     want_grads=True)
     np.testing.assert_allclose(got, full, rtol=1e-5, atol=1e-6)
+
+
+def test_host_binding_follows_nvml_and_never_raises(monkeypatch):
+    """hostmem.bind_host_to_gpu: with no NVML answer it returns None and leaves the affinity alone; with an NVML that
+    names a subset of the allowed CPUs as local to the GPU (a fake module here) the process is bound to that subset."""
+    import os
+    import sys
+    import types
+    from minitensor_b200 import hostmem
+    before = os.sched_getaffinity(0)
+    try:
+        assert hostmem.bind_host_to_gpu(0) is None or isinstance(hostmem.bind_host_to_gpu(0), dict)
+        os.sched_setaffinity(0, before)
+        if len(before) < 2:
+            return
+        want = sorted(before)[: len(before) // 2]
+        words = [0] * ((max(before) // 64) + 1)
+        for c in want:
+            words[c // 64] |= 1 << (c % 64)
+        fake = types.SimpleNamespace(
+            nvmlInit=lambda: None, nvmlShutdown=lambda: None,
+            nvmlDeviceGetCpuAffinity=lambda handle, n: (words + [0] * n)[:max(n, len(words))])
+        monkeypatch.setitem(sys.modules, "pynvml", fake)
+        monkeypatch.setattr(hostmem, "_nvml_handle", lambda nvml, index: object())
+        info = hostmem.bind_host_to_gpu(0)
+        assert info == {"cpus": len(want), "first": want[0], "last": want[-1]}
+        assert os.sched_getaffinity(0) == set(want)
+        # a mask that names every allowed CPU (one node) changes nothing
+        os.sched_setaffinity(0, before)
+        for c in before:
+            words[c // 64] |= 1 << (c % 64)
+        assert hostmem.bind_host_to_gpu(0) is None
+        assert os.sched_getaffinity(0) == before
+    finally:
+        os.sched_setaffinity(0, before)
