@@ -291,6 +291,18 @@ int32_t mtb200_sumsq(mtb200_handle h, int32_t dtype, int64_t n, const void* x, d
 int32_t mtb200_scale(mtb200_handle h, int32_t dtype, int64_t n, void* x, double coef);
 int32_t mtb200_clamp(mtb200_handle h, int32_t dtype, int64_t n, void* x, double lo, double hi);
 
+/* ---- the tape's own elementwise and layout operations
+ * add_inplace: y[i] += x[i], f32 / f64 / i32 / i64 (integers wrap): gradient accumulation,
+ *   arithmetic::add_inplace (engine/src/operations/arithmetic/elementwise.rs:102-160) as called by
+ *   accumulate_grad (engine/src/autograd/mod/core.rs:168, engine/src/autograd/graph.rs:266).
+ * swap_dims: materialised transpose (engine/src/operations/linalg/diagonal.rs:8-108).  x is read as
+ *   [outer][d0][mid][d1][inner] and written as [outer][d1][mid][d0][inner]; elements are moved, not
+ *   interpreted (elem_bytes 4 or 8).  transpose(dim0, dim1) of a tensor is outer = product of the
+ *   dimensions before dim0, mid = of those between, inner = of those after dim1.  Not in place. */
+int32_t mtb200_add_inplace(mtb200_handle h, int32_t dtype, int64_t n, void* y, const void* x);
+int32_t mtb200_swap_dims(mtb200_handle h, int32_t elem_bytes, int64_t outer, int64_t d0, int64_t mid,
+                         int64_t d1, int64_t inner, const void* x, void* y);
+
 /* ---- batch normalisation (f32 / f64) on x[N][C][S], S = product of the dimensions after the channel
  * batch_norm (engine/src/operations/normalization.rs:64-187; layers engine/src/nn/normalization.rs).
  * forward: statistics per channel over N and S (biased variance) when `training` or when a running

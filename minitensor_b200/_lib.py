@@ -60,6 +60,8 @@ SIGNATURES = {
     "mtb200_rmsprop_step": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64]),
     "mtb200_sumsq": (_i32, [_vp, _i32, _i64, _vp, _vp, _i32]),
     "mtb200_scale": (_i32, [_vp, _i32, _i64, _vp, _f64]),
+    "mtb200_add_inplace": (_i32, [_vp, _i32, _i64, _vp, _vp]),
+    "mtb200_swap_dims": (_i32, [_vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     "mtb200_clamp": (_i32, [_vp, _i32, _i64, _vp, _f64, _f64]),
     "mtb200_adam_step": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _f64, _f64, _f64, _f64, _f64, _i32,
                                 _i64, _f32]),

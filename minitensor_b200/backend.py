@@ -11,6 +11,7 @@ from __future__ import annotations
 import ctypes as C
 from typing import Optional
 
+import numpy as np
 import torch
 
 from . import _lib
@@ -229,6 +230,39 @@ class Backend:
         check(self.lib.mtb200_colsum(self._h, dtype_code(x), m, n, _ptr(x), _ptr(out)))
         self.launches += 2
         return out
+
+    def add_inplace(self, y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """``y += x`` on the device (gradient accumulation); shapes and dtypes must agree, as the reference demands."""
+        if tuple(y.shape) != tuple(x.shape):
+            raise ValueError(f"shape mismatch: {tuple(y.shape)} vs {tuple(x.shape)}")
+        _same_dtype("add_inplace", y, x)
+        self._bind_stream()
+        check(self.lib.mtb200_add_inplace(self._h, dtype_code(y), y.numel(), _ptr(y), _ptr(x)))
+        self.launches += 1
+        return y
+
+    def swap_dims(self, x: torch.Tensor, dim0: int, dim1: int) -> torch.Tensor:
+        """Materialised ``x.transpose(dim0, dim1)`` of a dense tensor, written by the library's kernel."""
+        nd = x.dim()
+        d0, d1 = (dim0 + nd if dim0 < 0 else dim0), (dim1 + nd if dim1 < 0 else dim1)
+        if not (0 <= d0 < nd and 0 <= d1 < nd):
+            raise IndexError(f"dimension out of range for a tensor of {nd} dimensions")
+        if d0 == d1:
+            return x.clone()
+        if d0 > d1:
+            d0, d1 = d1, d0
+        if x.element_size() not in (4, 8):
+            raise TypeError(f"unsupported dtype {x.dtype}")
+        shape = list(x.shape)
+        prod = lambda xs: int(np.prod(xs, dtype=np.int64)) if len(xs) else 1
+        outer, mid, inner = prod(shape[:d0]), prod(shape[d0 + 1:d1]), prod(shape[d1 + 1:])
+        shape[d0], shape[d1] = shape[d1], shape[d0]
+        y = torch.empty(shape, dtype=x.dtype, device=x.device)
+        self._bind_stream()
+        check(self.lib.mtb200_swap_dims(self._h, x.element_size(), outer, x.shape[d0], mid, x.shape[d1], inner, _ptr(x),
+                                        _ptr(y)))
+        self.launches += 1
+        return y
 
     def bias_act(self, x: torch.Tensor, bias: Optional[torch.Tensor], act: int = 0) -> torch.Tensor:
         """``act(x + bias)`` with ``bias`` broadcast over the rows of the 2-D view of ``x``."""

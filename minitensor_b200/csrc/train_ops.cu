@@ -523,6 +523,49 @@ using namespace mtb;
   DeviceGuard guard__((h)->device);                                 \
   if (!guard__.ok) return fail(MTB200_ERR_CUDA, "cannot make device %d current", (h)->device)
 
+// y[i] += x[i]: gradient accumulation (add_inplace, engine/src/operations/arithmetic/elementwise.rs:102-160).
+// Integers wrap, as the reference's wrapping_add does.
+template <typename T>
+static __global__ void add_inplace_kernel(T* __restrict__ y, const T* __restrict__ x, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    y[i] = y[i] + x[i];
+}
+
+// Materialised swap of two dimensions (transpose, engine/src/operations/linalg/diagonal.rs:8-108): x viewed as
+// [outer][d0][mid][d1][inner] becomes y [outer][d1][mid][d0][inner].
+//  * inner == 1 and mid == 1 (the matrix transpose of the last two of the swapped dimensions): 32 x 32 tiles through
+//    shared memory, so both the reads and the writes are whole lines;
+//  * otherwise runs of `inner` elements move together and a thread per output element is coalesced as it stands.
+template <typename T>
+static __global__ void __launch_bounds__(256) transpose_tiles_kernel(const T* __restrict__ x, T* __restrict__ y, int d0,
+                                                                      int d1) {
+  __shared__ T tile[32][33];
+  const long long plane = static_cast<long long>(d0) * d1;
+  const T* xs = x + blockIdx.z * plane;
+  T* ys = y + blockIdx.z * plane;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8)
+    if (r0 + r < d0 && c0 + tx < d1) tile[r][tx] = xs[static_cast<long long>(r0 + r) * d1 + c0 + tx];
+  __syncthreads();
+  for (int c = ty; c < 32; c += 8)
+    if (c0 + c < d1 && r0 + tx < d0) ys[static_cast<long long>(c0 + c) * d0 + r0 + tx] = tile[tx][c];
+}
+template <typename T>
+static __global__ void swap_dims_kernel(const T* __restrict__ x, T* __restrict__ y, long long total, long long d0,
+                                        long long mid, long long d1, long long inner) {
+  for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < total;
+       o += static_cast<long long>(gridDim.x) * blockDim.x) {
+    long long r = o;
+    const long long i = r % inner; r /= inner;
+    const long long a0 = r % d0; r /= d0;       // output layout [outer][d1][mid][d0][inner]
+    const long long m = r % mid; r /= mid;
+    const long long a1 = r % d1; r /= d1;
+    y[o] = x[(((r * d0 + a0) * mid + m) * d1 + a1) * inner + i];
+  }
+}
+
 static int32_t check_float_dtype(int32_t dtype, const char* what) {
   if (dtype != MTB200_F32 && dtype != MTB200_F64)
     return fail(MTB200_ERR_UNSUPPORTED, "%s only supports float32/float64 tensors (dtype %d)", what, dtype);
@@ -856,6 +899,54 @@ int32_t mtb200_dropout_apply(mtb200_handle h, int32_t dtype, int64_t n, int64_t 
   else
     dropout_apply_kernel<double><<<grid, 256, 0, h->stream>>>(static_cast<const double*>(x), n, inner, 1.0 - p, seed,
                                                               offset, static_cast<double*>(y));
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+int32_t mtb200_add_inplace(mtb200_handle h, int32_t dtype, int64_t n, void* y, const void* x) {
+  MTB_CHECK_HANDLE(h);
+  if (n < 0) return fail(MTB200_ERR_INVALID, "negative length");
+  if (n == 0) return MTB200_OK;
+  if (!x || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  const int grid = ew_grid(n, h->sm_count);
+  switch (dtype) {
+    case MTB200_F32: add_inplace_kernel<float><<<grid, 256, 0, h->stream>>>(static_cast<float*>(y), static_cast<const float*>(x), n); break;
+    case MTB200_F64: add_inplace_kernel<double><<<grid, 256, 0, h->stream>>>(static_cast<double*>(y), static_cast<const double*>(x), n); break;
+    case MTB200_I32: add_inplace_kernel<uint32_t><<<grid, 256, 0, h->stream>>>(static_cast<uint32_t*>(y), static_cast<const uint32_t*>(x), n); break;
+    case MTB200_I64: add_inplace_kernel<unsigned long long><<<grid, 256, 0, h->stream>>>(static_cast<unsigned long long*>(y), static_cast<const unsigned long long*>(x), n); break;
+    default: return fail(MTB200_ERR_UNSUPPORTED, "add_inplace: unsupported dtype %d", dtype);
+  }
+  MTB_CUDA(cudaGetLastError());
+  return MTB200_OK;
+}
+
+int32_t mtb200_swap_dims(mtb200_handle h, int32_t elem_bytes, int64_t outer, int64_t d0, int64_t mid, int64_t d1,
+                         int64_t inner, const void* x, void* y) {
+  MTB_CHECK_HANDLE(h);
+  if (elem_bytes != 4 && elem_bytes != 8) return fail(MTB200_ERR_UNSUPPORTED, "swap_dims moves 4- or 8-byte elements");
+  if (outer < 0 || d0 < 0 || mid < 0 || d1 < 0 || inner < 0) return fail(MTB200_ERR_INVALID, "negative dimension");
+  const long double total_ld = static_cast<long double>(outer) * d0 * mid * d1 * inner;
+  if (total_ld > 9.0e18L) return fail(MTB200_ERR_INVALID, "swap_dims: too many elements");
+  const long long total = outer * d0 * mid * d1 * inner;
+  if (total == 0) return MTB200_OK;
+  if (!x || !y) return fail(MTB200_ERR_INVALID, "null pointer");
+  if (x == y) return fail(MTB200_ERR_INVALID, "swap_dims does not work in place");
+  if (inner == 1 && mid == 1 && d0 <= INT32_MAX && d1 <= INT32_MAX && outer <= 65535 &&
+      (d0 + 31) / 32 <= 65535) {
+    const dim3 grid(unsigned((d1 + 31) / 32), unsigned((d0 + 31) / 32), unsigned(outer));
+    if (elem_bytes == 4)
+      transpose_tiles_kernel<uint32_t><<<grid, 256, 0, h->stream>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(y), int(d0), int(d1));
+    else
+      transpose_tiles_kernel<unsigned long long><<<grid, 256, 0, h->stream>>>(static_cast<const unsigned long long*>(x),
+                                                                             static_cast<unsigned long long*>(y), int(d0), int(d1));
+  } else {
+    const int grid = ew_grid(total, h->sm_count);
+    if (elem_bytes == 4)
+      swap_dims_kernel<uint32_t><<<grid, 256, 0, h->stream>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(y), total, d0, mid, d1, inner);
+    else
+      swap_dims_kernel<unsigned long long><<<grid, 256, 0, h->stream>>>(static_cast<const unsigned long long*>(x),
+                                                                       static_cast<unsigned long long*>(y), total, d0, mid, d1, inner);
+  }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;
 }

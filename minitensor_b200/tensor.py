@@ -33,6 +33,32 @@ def _be() -> _bk.Backend:
     return _bk.get_backend(torch.cuda.current_device())
 
 
+def _sum_leading(g: torch.Tensor, extra: int) -> torch.Tensor:
+    """Sum of ``g`` over its first ``extra`` dimensions."""
+    kept = g.shape[extra:]
+    rows = 1
+    for d in g.shape[:extra]:
+        rows *= d
+    cols = g.numel() // max(rows, 1)
+    if g.dtype not in (torch.float32, torch.float64):
+        raise TypeError("broadcast gradients are provided for float32/float64 tensors")
+    return _be().colsum(g.reshape(rows, cols)).reshape(kept)
+
+
+def _sum_dim_keep(g: torch.Tensor, dim: int) -> torch.Tensor:
+    """Sum of ``g`` over dimension ``dim``, kept with extent 1."""
+    outer = 1
+    for d in g.shape[:dim]:
+        outer *= d
+    n = g.shape[dim]
+    inner = g.numel() // max(outer * n, 1)
+    view = g.reshape(outer, n, inner)
+    out = torch.empty(outer, inner, dtype=g.dtype, device=g.device)
+    for o in range(outer):
+        _be().colsum(view[o], out=out[o])
+    return out.reshape(g.shape[:dim] + (1,) + g.shape[dim + 1:])
+
+
 class Tensor:
     """Device tensor with the reference's matmul-path methods."""
 
@@ -107,20 +133,23 @@ class Tensor:
 
     def transpose(self, dim0: int, dim1: int) -> "Tensor":
         """Materialised transpose (``engine/src/operations/linalg/diagonal.rs:8-108``)."""
-        buf = self._buf.transpose(dim0, dim1).contiguous()
-        return self._result(buf, (self,), lambda g: (g.transpose(dim0, dim1).contiguous(),))
+        be = _be()
+        buf = be.swap_dims(self._buf, dim0, dim1)
+        return self._result(buf, (self,), lambda g: (be.swap_dims(g.contiguous(), dim0, dim1),))
 
     def _expand_to(self, shape: Tuple[int, ...]) -> "Tensor":
         old = self.shape
         buf = self._buf.expand(shape).contiguous()
 
         def bw(g):
+            # the gradient of a broadcast is the sum over the broadcast dimensions: the library's column sum over
+            # the rows of a [rows, kept] view, slice by slice where the summed dimension is not the leading one
             extra = len(shape) - len(old)
             if extra:
-                g = g.sum(dim=tuple(range(extra)))
+                g = _sum_leading(g.contiguous(), extra)
             for i, d in enumerate(old):
                 if d == 1 and g.shape[i] != 1:
-                    g = g.sum(dim=i, keepdim=True)
+                    g = _sum_dim_keep(g.contiguous(), i)
             return (g.contiguous(),)
 
         return self._result(buf, (self,), bw)
@@ -148,7 +177,9 @@ class Tensor:
 
     def sum(self) -> "Tensor":
         shape = self.shape
-        buf = self._buf.sum().reshape(())
+        if self._buf.dtype not in (torch.float32, torch.float64):
+            raise TypeError("sum over all elements is provided for float32/float64 tensors")
+        buf = _be().colsum(self._buf.contiguous().reshape(-1, 1)).reshape(())     # one column: the sum of all rows
         return self._result(buf, (self,), lambda g: (g.reshape(()).expand(shape).contiguous(),))
 
     # ------------------------------------------------------------------ autograd
@@ -182,12 +213,19 @@ class Tensor:
             if g is None:
                 continue
             if node._backward_fn is None:  # leaf
-                node.grad = Tensor(None, _buf=g if node.grad is None else node.grad._buf + g)
+                if node.grad is None:
+                    node.grad = Tensor(None, _buf=g.clone())    # its own buffer: later contributions add in place
+                else:   # accumulate into the existing gradient (add_inplace, engine/src/autograd/mod/core.rs:168)
+                    _be().add_inplace(node.grad._buf, g.contiguous())
                 continue
             for p, pg in zip(node._parents, node._backward_fn(g)):
                 if pg is None or not p.requires_grad:
                     continue
-                grads[id(p)] = pg if id(p) not in grads else grads[id(p)] + pg  # accumulate_grad
+                if id(p) not in grads:
+                    grads[id(p)] = pg
+                else:   # accumulate_grad: a fresh buffer, the first contribution may alias a saved tensor
+                    acc = grads[id(p)].clone()
+                    grads[id(p)] = _be().add_inplace(acc, pg.contiguous())
 
 
 def _np_dtype(name: str):
@@ -265,7 +303,7 @@ def add(x: Tensor, y: Tensor) -> Tensor:
         raise TypeError(f"type mismatch: {x.dtype} vs {y.dtype}")
     be = _be()
     if x.shape == y.shape:
-        return x._result(x._buf + y._buf, (x, y), lambda g: (g, g))
+        return x._result(be.add_inplace(x._buf.clone(), y._buf.contiguous()), (x, y), lambda g: (g, g))
     if y.ndim == 1 and x.ndim >= 2 and x.shape[-1] == y.shape[0]:
         out = be.bias_act(x._buf, y._buf, 0)
         n = y.shape[0]

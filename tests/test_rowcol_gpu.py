@@ -178,3 +178,77 @@ def test_expired_wait_is_reported_and_the_context_survives(be, rng):
     assert (np.abs(c.cpu().numpy() - ref) / scale).max() <= 4e-6
     with pytest.raises(ValueError):
         check(be.lib.mtb200_selftest_wait_expiry(be._h, 0))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.int32, np.int64])
+def test_add_inplace_is_the_elementwise_sum(be, rng, dtype):
+    """mtb200_add_inplace: y += x, bit-exact with the host sum for floats, wrapping for integers; shapes and dtypes
+    must agree (arithmetic::add_inplace refuses both mismatches)."""
+    n = 100_003
+    if np.issubdtype(dtype, np.integer):
+        info = np.iinfo(dtype)
+        x = rng.integers(info.min, info.max, n, dtype=dtype, endpoint=True)
+        y = rng.integers(info.min, info.max, n, dtype=dtype, endpoint=True)
+        with np.errstate(over="ignore"):
+            want = (x.astype(np.uint64) + y.astype(np.uint64)).astype(np.uint32 if dtype == np.int32 else np.uint64).view(dtype)
+    else:
+        x, y = rng.standard_normal(n).astype(dtype), rng.standard_normal(n).astype(dtype)
+        want = y + x
+    yd = dev(be, y)
+    out = be.add_inplace(yd, dev(be, x))
+    be.sync()
+    assert out.data_ptr() == yd.data_ptr()
+    assert np.array_equal(out.cpu().numpy(), want)
+    with pytest.raises(ValueError):
+        be.add_inplace(yd, dev(be, x[:-1]))
+    with pytest.raises(TypeError):
+        be.add_inplace(yd, dev(be, x.astype(np.float64 if dtype != np.float64 else np.float32)))
+
+
+@pytest.mark.parametrize("shape,dims", [((5, 7), (0, 1)), ((300, 1000), (0, 1)), ((33, 65), (-1, -2)), ((4, 37, 129), (1, 2)),
+                                        ((6, 5, 4, 3), (0, 2)), ((2, 3, 4, 5), (1, 3)), ((3, 1, 8), (0, 2)), ((7, 9), (1, 1)),
+                                        ((2, 70000, 3), (0, 1))])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.int32])
+def test_swap_dims_is_the_materialised_transpose(be, rng, shape, dims, dtype):
+    """mtb200_swap_dims against numpy's swapaxes for matrix transposes (tiled kernel), batched ones and swaps of
+    dimensions with others between and after them (element kernel)."""
+    x = (rng.standard_normal(shape) * 100).astype(dtype)
+    got = be.swap_dims(dev(be, x), *dims)
+    be.sync()
+    want = np.ascontiguousarray(np.swapaxes(x, *dims))
+    assert tuple(got.shape) == want.shape and got.is_contiguous()
+    assert np.array_equal(got.cpu().numpy(), want)
+    with pytest.raises(IndexError):
+        be.swap_dims(dev(be, x), 0, len(shape))
+
+
+def test_tape_arithmetic_runs_on_the_library(be, rng, monkeypatch):
+    """Tensor.sum, transpose, equal-shape add, broadcast gradients and gradient accumulation of the tape go through
+    the library's kernels: the results match numpy, and the launch counter moves where torch arithmetic would not
+    move it."""
+    import minitensor_b200.tensor as mt
+    a = rng.standard_normal((6, 5)).astype(np.float32)
+    b = rng.standard_normal((5, 4)).astype(np.float32)
+    x, w = mt.Tensor(a, requires_grad=True), mt.Tensor(b, requires_grad=True)
+    before = be.launches
+    y = (x @ w).transpose(0, 1)                  # [4, 6]
+    z = y + y                                    # equal shapes; the same tensor feeds both operands
+    loss = z.sum()
+    assert be.launches - before >= 5
+    loss.backward()
+    assert abs(float(loss.numpy()) - 2.0 * float((a.astype(np.float64) @ b).sum())) <= 1e-4 * np.abs(a).sum() * np.abs(b).max()
+    # d loss / d x = 2 * ones[6,4] @ w^T, accumulated from the two uses of y
+    gx = 2.0 * np.ones((6, 4)) @ b.T.astype(np.float64)
+    gw = 2.0 * a.T.astype(np.float64) @ np.ones((6, 4))
+    assert np.allclose(x.grad.numpy(), gx, rtol=1e-5, atol=1e-5)
+    assert np.allclose(w.grad.numpy(), gw, rtol=1e-5, atol=1e-5)
+    # a second backward pass accumulates into the leaves' gradients in place
+    gptr = x.grad._buf.data_ptr()
+    ((x @ w).sum()).backward()
+    assert x.grad._buf.data_ptr() == gptr
+    assert np.allclose(x.grad.numpy(), gx * 1.5, rtol=1e-5, atol=1e-5)
+    # broadcast over a leading batch dimension: the gradient of the 2-D operand is the sum over the batch
+    l3 = mt.Tensor(rng.standard_normal((3, 6, 5)).astype(np.float32), requires_grad=True)
+    w2 = mt.Tensor(b, requires_grad=True)
+    (l3 @ w2).sum().backward()
+    assert np.allclose(w2.grad.numpy(), l3.numpy().astype(np.float64).sum(0).T @ np.ones((6, 4)), rtol=1e-5, atol=1e-4)
