@@ -101,14 +101,19 @@ inline int32_t make_split_tmap_mn(CUtensorMap* out, const void* base, uint64_t k
 // Launch with the programmatic-stream-serialization attribute: the kernel may start while the one before it in the
 // stream still runs and must call grid_dependency_wait() before it reads that kernel's results (ptx_sm100.cuh).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(mtb200_ctx* h, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+inline cudaError_t launch_pdl_on(mtb200_ctx* h, cudaStream_t stream, void (*kern)(KArgs...), dim3 grid, dim3 block,
+                                 size_t smem, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = h->stream;
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cfg.attrs = attr; cfg.numAttrs = h->pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(mtb200_ctx* h, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+  return launch_pdl_on(h, h->stream, kern, grid, block, smem, std::forward<Args>(args)...);
 }
 
 template <typename Kern>
@@ -333,11 +338,12 @@ inline int32_t launch_split16(mtb200_ctx* h, const float* src, bool k_major, int
     const int rows_per_band = (K + bands - 1) / bands;
     colabsmax_kernel<<<dim3((mn + 255) / 256, (K + rows_per_band - 1) / rows_per_band, batch), 256, 0, stream>>>(
         src, mn, bstride, K, mn, rows_per_band, reinterpret_cast<uint32_t*>(expo), nf_word, epoch);
-    exponent_from_amax_kernel<<<(batch * mn + 255) / 256, 256, 0, stream>>>(reinterpret_cast<uint32_t*>(expo), expo,
-                                                                          batch * mn);
+    MTB_CUDA(launch_pdl_on(h, stream, exponent_from_amax_kernel, dim3((batch * mn + 255) / 256), dim3(256), 0,
+                           reinterpret_cast<const uint32_t*>(expo), expo, batch * mn));
     const long long total = static_cast<long long>(K) * (cp / 8);
     const int blocks = int(std::min<long long>((total + 255) / 256, (long long)h->sm_count * 32));
-    split16_cols_scaled_kernel<<<dim3(blocks, 1, batch), 256, 0, stream>>>(src, mn, bstride, planes, expo, K, mn, cp);
+    MTB_CUDA(launch_pdl_on(h, stream, split16_cols_scaled_kernel, dim3(blocks, 1, batch), dim3(256), 0, src,
+                           static_cast<long long>(mn), bstride, planes, static_cast<const int*>(expo), K, mn, cp));
   }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;

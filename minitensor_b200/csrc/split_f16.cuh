@@ -17,6 +17,7 @@
 //   K-major planes (rows = M/N index):   one scale per ROW   -> split16_rows_kernel
 //   MN-major planes (rows = K index):    one scale per COLUMN -> colabsmax_kernel + split16_cols_scaled_kernel
 #pragma once
+#include "ptx_sm100.cuh"
 #include <cuda_fp16.h>
 #include <cstdint>
 
@@ -192,6 +193,7 @@ split16_rows_reg_kernel(const float* __restrict__ src, long long ld, long long b
 static __global__ void __launch_bounds__(256)
 colabsmax_kernel(const float* __restrict__ src, long long ld, long long bstride, int R, int Cc, int rows_per_band,
                  uint32_t* __restrict__ amax_bits, uint32_t* __restrict__ nf_word, uint32_t nf_epoch) {
+  grid_launch_dependents();      // the two small kernels after this one wait inside (programmatic dependent launch)
   const int b = blockIdx.z;
   const int c = blockIdx.x * 256 + threadIdx.x;
   if (c >= Cc) return;
@@ -210,6 +212,8 @@ colabsmax_kernel(const float* __restrict__ src, long long ld, long long bstride,
 
 // expo[i] = scale exponent of the magnitude whose bits are amax_bits[i] (in place is fine).
 static __global__ void exponent_from_amax_kernel(const uint32_t* __restrict__ amax_bits, int* __restrict__ expo, int n) {
+  grid_dependency_wait();        // the maxima come from the kernel before this one
+  grid_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) expo[i] = scale_exponent(__uint_as_float(amax_bits[i]));
 }
@@ -218,6 +222,7 @@ static __global__ void exponent_from_amax_kernel(const uint32_t* __restrict__ am
 static __global__ void __launch_bounds__(256)
 split16_cols_scaled_kernel(const float* __restrict__ src, long long ld, long long bstride, __half* __restrict__ dst,
                            const int* __restrict__ expo, int R, int Cc, int Cp) {
+  grid_dependency_wait();        // the exponents come from the kernel before this one
   const int b = blockIdx.z;
   const int chunks = Cp >> 3;
   const long long total = static_cast<long long>(R) * chunks;
