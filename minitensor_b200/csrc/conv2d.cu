@@ -223,6 +223,7 @@ __global__ void __launch_bounds__(256) conv_direct_fwd_kernel(ConvGeom g, const 
                                                               const float* __restrict__ w,
                                                               const float* __restrict__ bias, float* __restrict__ y,
                                                               const uint32_t* __restrict__ gate) {
+  grid_dependency_wait();        // the flag word is raised by the kernels before this one
   if (*gate != MTB_FLAG_SET) return;
   const long long total = static_cast<long long>(g.n) * g.c_out * g.oh * g.ow;
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
@@ -254,6 +255,7 @@ __global__ void __launch_bounds__(256) conv_direct_fwd_kernel(ConvGeom g, const 
 __global__ void __launch_bounds__(256) conv_direct_dgrad_kernel(ConvGeom g, const float* __restrict__ dy,
                                                                 const float* __restrict__ w, float* __restrict__ dx,
                                                                 const uint32_t* __restrict__ gate) {
+  grid_dependency_wait();        // the flag word is raised by the kernels before this one
   if (*gate != MTB_FLAG_SET) return;
   const long long total = static_cast<long long>(g.n) * g.c_in * g.h * g.w;
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
@@ -284,6 +286,7 @@ __global__ void __launch_bounds__(256) conv_direct_dgrad_kernel(ConvGeom g, cons
 __global__ void __launch_bounds__(256) conv_direct_wgrad_kernel(ConvGeom g, const float* __restrict__ dy,
                                                                 const float* __restrict__ x, float* __restrict__ dw,
                                                                 const uint32_t* __restrict__ gate) {
+  grid_dependency_wait();        // the flag word is raised by the kernels before this one
   if (*gate != MTB_FLAG_SET) return;
   __shared__ float red[256];
   const long long outputs = static_cast<long long>(g.c_out) * g.c_in * g.kh * g.kw;
@@ -424,10 +427,9 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
     finite_absmax_kernel<<<dim3(chunks, n), 256, 0, h->stream>>>(img, img_elems, img_elems, amax, nf_word, MTB_FLAG_SET);
     if (phases > 1 && ppix != ipix)   // phase images have rows / columns no pixel maps to: they must read as zero
       MTB_CUDA(cudaMemsetAsync(p_img, 0, size_t(2) * n * ppix * chan_p * sizeof(__half), h->stream));
-    split16_turn_batch_kernel<<<dim3((ipix + 63) / 64, chan_p / 64, n), 256, 0, h->stream>>>(
-        img, ipix, img_elems, reinterpret_cast<__half*>(p_img), amax, 1, eb, ipix, chan, chan_p,
-        RowPhases{img_w, sh, sw, hq, wq});
-    MTB_CUDA(cudaGetLastError());
+    MTB_CUDA(launch_pdl(h, split16_turn_batch_kernel, dim3((ipix + 63) / 64, chan_p / 64, n), dim3(256), 0, img,
+                        static_cast<long long>(ipix), img_elems, reinterpret_cast<__half*>(p_img),
+                        static_cast<const uint32_t*>(amax), 1, eb, ipix, chan, chan_p, RowPhases{img_w, sh, sw, hq, wq}));
   } else {
     ProfScope prof(h, PROF_CONV_GATHER, double(n) * ipix * (4.0 * chan + 6.0 * chan_p));
     rc = launch_split(h, img, true, ipix, chan, chan_p, n, img_elems, p_img, 3, nf_word, MTB_FLAG_SET);
@@ -561,7 +563,7 @@ static int32_t implicit_conv(mtb200_ctx* h, const float* img, int n, int chan, i
       ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * rows * double(opix) * taps * chan * n);
       auto launch = [&](auto kernel) -> int32_t {
         if (int32_t rc_attr = grant_dynamic_smem(h, kernel, int(smem))) return rc_attr;
-        kernel<<<grid, CONV_PIX_THREADS, smem, h->stream>>>(tw, ti, a);
+        MTB_CUDA(launch_pdl(h, kernel, dim3(grid), dim3(CONV_PIX_THREADS), smem, tw, ti, a));
         return MTB200_OK;
       };
       if (three) rc = bk == 64 ? launch(conv_pix_umma_kernel<3, 64>) : launch(conv_pix_umma_kernel<3, 32>);
@@ -828,8 +830,9 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
       MTB_CUDA(cudaStreamWaitEvent(sx, h->ev_fork, 0));
     }
     finite_absmax_kernel<<<dim3(chunks_of(dy_img * g.n), 1), 256, 0, h->stream>>>(dy, 0, dy_img * g.n, amax, nf_word, MTB_FLAG_SET);
-    split16_turn_batch_kernel<<<dim3((opix + 63) / 64, cop / 64, g.n), 256, 0, h->stream>>>(
-        dy, opix, dy_img, reinterpret_cast<__half*>(p_dy), amax, 0, e_dy, opix, g.c_out, cop);
+    MTB_CUDA(launch_pdl(h, split16_turn_batch_kernel, dim3((opix + 63) / 64, cop / 64, g.n), dim3(256), 0, dy,
+                        static_cast<long long>(opix), dy_img, reinterpret_cast<__half*>(p_dy),
+                        static_cast<const uint32_t*>(amax), 0, e_dy, opix, g.c_out, cop, RowPhases{0, 1, 1, 0, 0}));
     finite_absmax_kernel<<<dim3(chunks_of(x_img * g.n), 1), 256, 0, sx>>>(x, 0, x_img * g.n, amax + 1, nf_word, MTB_FLAG_SET);
     if (phases > 1 && ppix != ipix)   // phase images have rows / columns no pixel maps to: they must read as zero
       MTB_CUDA(cudaMemsetAsync(p_x, 0, size_t(2) * g.n * ppix * cip * sizeof(__half), sx));
@@ -871,8 +874,8 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
     ProfScope prof(h, PROF_GEMM_UMMA, 2.0 * g.c_out * double(opix) * taps * g.c_in * g.n);
     const size_t smem = WgradHaloCfg::smem_bytes(hw.x_plane_bytes, hw.dy_plane_bytes);
     if (int32_t rc_attr = grant_dynamic_smem(h, conv_wgrad_halo_kernel, int(smem))) return rc_attr;
-    conv_wgrad_halo_kernel<<<hw.ocbs * hw.icbs * hw.tgs * hw.splits, WgradHaloCfg::NUM_THREADS, smem, h->stream>>>(tdy, tx, hw);
-    MTB_CUDA(cudaGetLastError());
+    MTB_CUDA(launch_pdl(h, conv_wgrad_halo_kernel, dim3(hw.ocbs * hw.icbs * hw.tgs * hw.splits),
+                        dim3(WgradHaloCfg::NUM_THREADS), smem, tdy, tx, hw));
   } else {
   rc = image_plane_tmap(&tdy, p_dy, cop, g.ow, g.oh, g.n, a.planes, 64, a.tw, a.th, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
@@ -893,9 +896,9 @@ static int32_t implicit_wgrad(mtb200_ctx* h, const ConvGeom& g, const float* dy,
   }
   }
   const long long part_rows = static_cast<long long>(g.c_out) * a.n_total;
-  wgrad_reduce_kernel<<<int(std::min<long long>((part_rows + 31) / 32, 8192)), 256, 0, h->stream>>>(
-      a.part, a.splits, g.c_out, g.c_in, cip, taps, dw, f16 ? e_dy : nullptr, f16 ? e_x : nullptr);
-  MTB_CUDA(cudaGetLastError());
+  MTB_CUDA(launch_pdl(h, wgrad_reduce_kernel, dim3(unsigned(std::min<long long>((part_rows + 31) / 32, 8192))), dim3(256), 0,
+                      static_cast<const float*>(a.part), a.splits, g.c_out, g.c_in, cip, taps, dw,
+                      static_cast<const int*>(f16 ? e_dy : nullptr), static_cast<const int*>(f16 ? e_x : nullptr)));
   return MTB200_OK;
 }
 
@@ -946,9 +949,8 @@ int32_t mtb200_conv2d_fwd(mtb200_handle h, int64_t n, int64_t c_in, int64_t heig
   rc = call_flag_begin(h, &nf_word);
   if (rc) return rc;
   auto redo = [&]() -> int32_t {   // returns at once unless the operands held Inf / NaN
-    conv_direct_fwd_kernel<<<direct_grid(h, static_cast<long long>(g.n) * g.c_out * opix), 256, 0, h->stream>>>(
-        g, x, w, bias, y, nf_word);
-    MTB_CUDA(cudaGetLastError());
+    MTB_CUDA(launch_pdl(h, conv_direct_fwd_kernel, dim3(direct_grid(h, static_cast<long long>(g.n) * g.c_out * opix)),
+                        dim3(256), 0, g, x, w, bias, y, static_cast<const uint32_t*>(nf_word)));
     return MTB200_OK;
   };
   if (g.sh == 1 && g.sw == 1 && g.ow <= 256 && !force_explicit) {
@@ -1006,9 +1008,8 @@ int32_t mtb200_conv2d_bwd_data(mtb200_handle h, int64_t n, int64_t c_in, int64_t
   rc = call_flag_begin(h, &nf_word);
   if (rc) return rc;
   auto redo = [&]() -> int32_t {
-    conv_direct_dgrad_kernel<<<direct_grid(h, static_cast<long long>(g.n) * g.c_in * ipix), 256, 0, h->stream>>>(
-        g, dy, w, dx, nf_word);
-    MTB_CUDA(cudaGetLastError());
+    MTB_CUDA(launch_pdl(h, conv_direct_dgrad_kernel, dim3(direct_grid(h, static_cast<long long>(g.n) * g.c_in * ipix)),
+                        dim3(256), 0, g, dy, w, dx, static_cast<const uint32_t*>(nf_word)));
     return MTB200_OK;
   };
   if (g.sh == 1 && g.sw == 1 && g.w <= 256 && !force_explicit) {
@@ -1095,9 +1096,8 @@ int32_t mtb200_conv2d_bwd_weight(mtb200_handle h, int64_t n, int64_t c_in, int64
   rc = call_flag_begin(h, &nf_word);
   if (rc) return rc;
   auto redo = [&]() -> int32_t {
-    conv_direct_wgrad_kernel<<<int(std::min<size_t>(out_elems, size_t(16) * h->sm_count)), 256, 0, h->stream>>>(
-        g, dy, x, dw, nf_word);
-    MTB_CUDA(cudaGetLastError());
+    MTB_CUDA(launch_pdl(h, conv_direct_wgrad_kernel, dim3(unsigned(std::min<size_t>(out_elems, size_t(16) * h->sm_count))),
+                        dim3(256), 0, g, dy, x, dw, static_cast<const uint32_t*>(nf_word)));
     return MTB200_OK;
   };
   const bool strided = g.sh > 1 || g.sw > 1;

@@ -181,6 +181,8 @@ conv_pix_umma_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  grid_dependency_wait();        // planes and exponents come from the kernels before this one
+  grid_launch_dependents();
   const int acc_n = g.fold ? 2 * g.n_tile : g.n_tile;  // TMEM columns of one M block's accumulator
   const int acc_cols = g.mb * acc_n;                 // TMEM columns of one accumulator set
 

@@ -148,6 +148,8 @@ conv_wgrad_halo_kernel(const __grid_constant__ CUtensorMap tmapDy, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  grid_dependency_wait();        // the planes come from the kernels before this one
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer: one x halo block and one dy block per step

@@ -239,7 +239,9 @@ wgrad_reduce_kernel(const float* __restrict__ part, int splits, int c_out, int c
   // warp is one 128-byte line - with 8 threads per entry: thread zl adds the ranges zl, zl + 8, ... in ascending
   // order and the eight sums are added in ascending zl, a fixed order whatever the launch.
   __shared__ float red[8][33];
-  const int e = e1 ? __ldg(e1) + __ldg(e2) : 0;
+  grid_dependency_wait();        // partials and exponents come from the kernels before this one
+  grid_launch_dependents();
+  const int e = e1 ? __ldcg(e1) + __ldcg(e2) : 0;
   const long long n_total = static_cast<long long>(taps) * cin_p;
   const long long rows = static_cast<long long>(c_out) * n_total;
   const int lane = threadIdx.x & 31, zl = threadIdx.x >> 5;

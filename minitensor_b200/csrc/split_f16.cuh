@@ -260,6 +260,7 @@ static __global__ void __launch_bounds__(256)
 finite_absmax_kernel(const float* __restrict__ src, long long bstride, long long count, uint32_t* __restrict__ amax_bits,
                      uint32_t* __restrict__ nf_word = nullptr, uint32_t nf_value = 0) {
   __shared__ float red[8];
+  grid_launch_dependents();      // the split that follows waits inside (programmatic dependent launch)
   const float* p = src + blockIdx.y * bstride;
   float amax = 0.0f;
   bool nf = false;
@@ -315,7 +316,9 @@ split16_turn_batch_kernel(const float* __restrict__ src, long long ld, long long
   const int b = blockIdx.z;
   const int r0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
   const float* s = src + b * bstride;
-  const int e = scale_exponent(__uint_as_float(__ldg(amax_bits + static_cast<long long>(b) * amax_stride)));
+  grid_dependency_wait();        // the maximum comes from the kernel before this one
+  grid_launch_dependents();
+  const int e = scale_exponent(__uint_as_float(__ldcg(amax_bits + static_cast<long long>(b) * amax_stride)));
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) expo[b] = e;
   const int tx = threadIdx.x & 63, kg = threadIdx.x >> 6;
   const int r = r0 + tx;

@@ -322,3 +322,30 @@ def test_nonfinite_operands_give_the_reference_results(be, orc, rng, stride):
     y2 = be.conv2d_fwd(dev(xc), dev(wc), None, stride, p1).cpu().numpy()
     check_outputs("y after a non-finite call", y2, orc.conv2d(xc, wc, None, stride, p1),
                   conv_f64.forward(xc, wc, None, stride, p1), conv_f64.forward_norms(xc, wc, stride, p1))
+
+
+def test_dependent_launch_changes_no_bit_of_a_convolution(be, rng, monkeypatch):
+    """The kernels of a conv2d call are chained by programmatic dependent launch (each waits for its predecessor
+    inside the kernel); a handle created with MTB200_NO_PDL=1 launches them the plain way.  Forward, data gradient
+    and weight gradient give the same bits either way, stride 1 and strided, calls issued back to back."""
+    from minitensor_b200.backend import Backend
+    monkeypatch.setenv("MTB200_NO_PDL", "1")
+    plain = Backend(be.device.index or 0)
+    monkeypatch.delenv("MTB200_NO_PDL")
+    try:
+        for (n, c, h, w, co, k, stride, pad) in ((8, 64, 28, 28, 64, 3, (1, 1), (1, 1)), (4, 16, 14, 14, 32, 3, (2, 2), (1, 1))):
+            x = torch.from_numpy(rng.standard_normal((n, c, h, w)).astype(np.float32)).to(be.device)
+            wt = torch.from_numpy((rng.standard_normal((co, c, k, k)) * 0.05).astype(np.float32)).to(be.device)
+            bias = torch.from_numpy(rng.standard_normal(co).astype(np.float32)).to(be.device)
+            for _ in range(2):
+                y = be.conv2d_fwd(x, wt, bias, stride, pad)
+                dy = torch.ones_like(y) * 0.5 + y * 0.01
+                dx = be.conv2d_bwd_data(dy, wt, x.shape, stride, pad)
+                dw = be.conv2d_bwd_weight(dy, x, wt.shape, stride, pad)
+            y0 = plain.conv2d_fwd(x, wt, bias, stride, pad)
+            dx0 = plain.conv2d_bwd_data(dy, wt, x.shape, stride, pad)
+            dw0 = plain.conv2d_bwd_weight(dy, x, wt.shape, stride, pad)
+            be.sync(); plain.sync()
+            assert torch.equal(y, y0) and torch.equal(dx, dx0) and torch.equal(dw, dw0), (n, c, h, w, stride)
+    finally:
+        plain.close()
