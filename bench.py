@@ -47,9 +47,22 @@ def _traffic(key: str):
 
 def record_traffic(csv_path: str, key: str, kernel_regex: str, command: str):
     """Fold an ncu raw CSV (--page raw --csv, or --csv --log-file) into profiles/dram_traffic.json: mean of
-    dram__bytes_read.sum + dram__bytes_write.sum over the captured launches whose kernel name matches."""
+    dram__bytes_read.sum + dram__bytes_write.sum over the captured launches whose kernel name matches.  Several
+    expressions joined by " + " record the SUM of their means (a call made of a tensor kernel and its fix-up)."""
     import csv
     import re
+    if " + " in kernel_regex:
+        total, launches = 0.0, 0
+        for part in kernel_regex.split(" + "):
+            rec = record_traffic(csv_path, key, part.strip(), command)
+            total += rec["dram_bytes_per_launch"]
+            launches += rec["launches_captured"]
+        p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+        data = json.load(open(p))
+        data[key].update(dram_bytes_per_launch=total, launches_captured=launches, kernels=kernel_regex)
+        json.dump(data, open(p, "w"), indent=2)
+        print(json.dumps({key: data[key]}))
+        return data[key]
     rows = list(csv.reader(open(csv_path, errors="replace")))
     hdr_i = next(i for i, r in enumerate(rows) if "Kernel Name" in r)
     hdr = rows[hdr_i]
@@ -84,6 +97,7 @@ def record_traffic(csv_path: str, key: str, kernel_regex: str, command: str):
     data[key] = rec
     json.dump(data, open(p, "w"), indent=2)
     print(json.dumps({key: rec}))
+    return rec
 
 
 def _peaks():
