@@ -1,6 +1,9 @@
 // Handle, error reporting, scratch memory and tensor-map helpers shared by the
 // C-ABI translation units.
 #pragma once
+#include <utility>
+#include <mutex>
+#include <map>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdarg>
@@ -67,7 +70,6 @@ struct mtb200_ctx {
   std::vector<ProfRec> prof;
   // per-kernel set-up that costs microseconds of host time and does not change: the largest dynamic shared-memory
   // size already granted to a kernel on this device, and the cluster occupancy of the pair-tile kernels
-  std::unordered_map<const void*, int> smem_granted;
   std::unordered_map<const void*, int> cluster_occupancy;
 };
 
@@ -108,14 +110,19 @@ int32_t make_split_tmap(CUtensorMap* out, const void* base, uint64_t Kp, uint64_
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize for `fn` on the handle's device, raised only when a launch needs more
-// than an earlier one asked for (the attribute is per device and per function; the handle is per device).
+// than any earlier one asked for.  The attribute belongs to the (device, function) pair, not to a handle: a second
+// handle on the same device that asked for less would LOWER it and make the first handle's next launch fail, so the
+// record of what has been granted is shared by all handles of the process.
 template <typename Fn>
 inline int32_t grant_dynamic_smem(mtb200_ctx* h, Fn fn, int bytes) {
-  const void* key = reinterpret_cast<const void*>(fn);
-  auto it = h->smem_granted.find(key);
-  if (it != h->smem_granted.end() && it->second >= bytes) return MTB200_OK;
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> granted;
+  const std::pair<int, const void*> key(h->device, reinterpret_cast<const void*>(fn));
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = granted.find(key);
+  if (it != granted.end() && it->second >= bytes) return MTB200_OK;
   MTB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  h->smem_granted[key] = bytes;
+  granted[key] = bytes;
   return MTB200_OK;
 }
 

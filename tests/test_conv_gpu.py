@@ -346,6 +346,35 @@ def test_dependent_launch_changes_no_bit_of_a_convolution(be, rng, monkeypatch):
             dx0 = plain.conv2d_bwd_data(dy, wt, x.shape, stride, pad)
             dw0 = plain.conv2d_bwd_weight(dy, x, wt.shape, stride, pad)
             be.sync(); plain.sync()
-            assert torch.equal(y, y0) and torch.equal(dx, dx0) and torch.equal(dw, dw0), (n, c, h, w, stride)
+            for name, got, ref in (("y", y, y0), ("dx", dx, dx0), ("dw", dw, dw0)):
+                diff = (got - ref).abs()
+                assert torch.equal(got, ref), (name, (n, c, h, w, stride), float(diff.max()), int((diff > 0).sum()),
+                                               float(ref.abs().max()))
     finally:
         plain.close()
+
+
+def test_a_second_handle_does_not_shrink_what_the_first_may_launch(be, rng):
+    """The opt-in shared-memory size of a kernel belongs to the device, not to a handle: a second handle whose
+    layer needs less must not lower it under the first handle's feet (the launch would fail with 'invalid
+    argument').  First handle: a layer with a large step; second handle: a small layer; first handle again."""
+    from minitensor_b200.backend import Backend
+    other = Backend(be.device.index or 0)
+    try:
+        big = (4, 64, 30, 120, 64, 3)
+        small = (2, 3, 8, 9, 5, 3)
+        mk = lambda n, c, h, w, co, k: (torch.from_numpy(rng.standard_normal((n, c, h, w)).astype(np.float32)).to(be.device),
+                                        torch.from_numpy(rng.standard_normal((n, co, h, w)).astype(np.float32)).to(be.device),
+                                        (co, c, k, k))
+        xb, dyb, wsb = mk(*big)
+        xs, dys, wss = mk(*small)
+        first = be.conv2d_bwd_weight(dyb, xb, wsb, (1, 1), (1, 1))
+        y1 = be.conv2d_fwd(xb, torch.ones(wsb, device=be.device), None, (1, 1), (1, 1))
+        other.conv2d_bwd_weight(dys, xs, wss, (1, 1), (1, 1))
+        other.conv2d_fwd(xs, torch.ones(wss, device=be.device), None, (1, 1), (1, 1))
+        again = be.conv2d_bwd_weight(dyb, xb, wsb, (1, 1), (1, 1))
+        y2 = be.conv2d_fwd(xb, torch.ones(wsb, device=be.device), None, (1, 1), (1, 1))
+        be.sync(); other.sync()
+        assert torch.equal(first, again) and torch.equal(y1, y2)
+    finally:
+        other.close()
