@@ -8,7 +8,15 @@
  * DEVICE pointers owned by the caller (from mtb200_alloc or any other CUDA
  * allocator on the handle's device); matrices are dense row-major.  Work is
  * enqueued on the handle's stream and is asynchronous until mtb200_sync.
- * A handle is used from one host thread at a time.
+ * A handle is used from one host thread at a time; calls on one handle that are issued on
+ * different streams (mtb200_set_stream) share its scratch memory and must be ordered by the
+ * caller.  Several handles may live on one device.
+ *
+ * Environment (read when a handle or a communicator is created):
+ *   MTB200_NO_PDL=1     launch every kernel the plain way (default: the kernels of a call are chained
+ *                       by programmatic dependent launch; results are bit-identical either way)
+ *   MTB200_NCCL_LIB     path of the NCCL library to open when none is loaded in the process
+ *   MTB200_COMM_CTAS=n  CTA budget asked of NCCL for a communicator (default 16, 0 = leave NCCL alone)
  *
  * File/line references name the minitensor source each entry point stands in
  * for (paths relative to the minitensor repository root).
