@@ -83,6 +83,11 @@ class MLPTrainer:
         if self.fused_dense and f32_mode != 0:
             raise ValueError("fused_dense uses the default f32 mode")
         self.overlap_comm = (self.world_size > 1) if overlap_comm is None else bool(overlap_comm)
+        # MTB200_COMM_BUCKET=1: no overlap at all - the whole flat gradient is reduced once, after the backward pass,
+        # with every SM free for it (a measurement aid: what the overlapped schedule has to beat)
+        self.single_bucket = self.world_size > 1 and os.environ.get("MTB200_COMM_BUCKET", "0") == "1"
+        if self.single_bucket:
+            self.overlap_comm = False
         # SMs left to the collectives that overlap the backward products (MTB200_COMM_SMS, default 16 when world > 1:
         # the library's communicator asks NCCL for at most 16 CTAs, so the collectives fit beside the products)
         self.comm_sms = int(os.environ.get("MTB200_COMM_SMS", "16")) if self.world_size > 1 else 0
@@ -233,13 +238,33 @@ class MLPTrainer:
             else:
                 be.colsum(g, out=self.db[l])
                 be.gemm(g, a_in, trans_a=True, out=self.dW[l], f32_mode=self.f32_mode)      # dW = g^T a
-            if self.world_size > 1:
+            if self.world_size > 1 and not self.single_bucket:
                 lo = self.w_off[l]
                 hi = self.b_off[l] + self.dims[l + 1]
                 self._all_reduce(lo, hi)
             if l > 0 and not self.fused_dense:
                 be.gemm(g, self.W[l], epilogue=EPI_RELU_BWD, aux=self.h[l - 1], out=self.g[l - 1],
                         f32_mode=self.f32_mode)                                            # (g W) * relu'
+        if self.single_bucket and not self._counted:
+            # the backward pass is done: reduce layer by layer on the communication stream and update each layer on
+            # the side stream as soon as its slice has landed, so the (HBM-bound) update of layer l hides behind the
+            # reduction of layer l + 1 and nothing runs beside the products
+            main = torch.cuda.current_stream(be.device)
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=be.device)
+            side = self._side_stream
+            for l in range(self.nl):
+                lo, hi = self.w_off[l], self.b_off[l] + self.dims[l + 1]
+                self._all_reduce(lo, hi)
+                side.wait_stream(self._comm_stream)
+                with torch.cuda.stream(side):
+                    be.adam_step(self.params[lo:hi], self.grads[lo:hi], self.m[lo:hi], self.v[lo:hi], lr=self.lr,
+                                 beta1=self.beta1, beta2=self.beta2, eps=self.eps, step=self.step_count,
+                                 grad_scale=1.0 / self.world_size)
+            main.wait_stream(side)
+            return loss
+        if self.single_bucket:
+            self._all_reduce(0, self.n_params)
         if self.world_size > 1:
             torch.cuda.current_stream(be.device).wait_stream(self._comm_stream)
         if self._counted:
