@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(256) conv_bias_partial_kernel(const float* __r
                                                                 int opix, int imgs_per_chunk,
                                                                 float* __restrict__ partial) {
   __shared__ float red[8];
+  grid_launch_dependents();      // the second stage waits inside
   const int oc = blockIdx.x, chunk = blockIdx.y;
   const int n0 = chunk * imgs_per_chunk, n1 = min(n, n0 + imgs_per_chunk);
   const bool vec = ((opix & 3) == 0) && ((reinterpret_cast<uintptr_t>(dy) & 15) == 0);
@@ -1164,8 +1165,9 @@ int32_t mtb200_conv2d_bwd_bias(mtb200_handle h, int64_t n, int64_t c_out, int64_
   float* part = static_cast<float*>(ws);
   conv_bias_partial_kernel<<<dim3(unsigned(c_out), unsigned(chunks)), 256, 0, h->stream>>>(dy, int(n), int(c_out), opix,
                                                                                          per, part);
-  colsum_stage2_kernel<float><<<int((c_out + 255) / 256), 256, 0, h->stream>>>(part, chunks, int(c_out), db);
   MTB_CUDA(cudaGetLastError());
+  MTB_CUDA(launch_pdl(h, colsum_stage2_kernel<float>, dim3(unsigned((c_out + 255) / 256)), dim3(256), 0,
+                      static_cast<const float*>(part), chunks, int(c_out), db));
   return MTB200_OK;
 }
 

@@ -540,13 +540,13 @@ int32_t mtb200_colsum(mtb200_handle h, int32_t dtype, int64_t M, int64_t N, cons
   if (dtype == MTB200_F32) {
     colsum_stage1_kernel<float><<<dim3(col_blocks, bands), 256, 0, h->stream>>>(
         static_cast<const float*>(X), N, int(M), int(N), rows_per_band, static_cast<float*>(ws));
-    colsum_stage2_kernel<float><<<int((N + 255) / 256), 256, 0, h->stream>>>(
-        static_cast<const float*>(ws), bands, int(N), static_cast<float*>(out));
+    MTB_CUDA(launch_pdl(h, colsum_stage2_kernel<float>, dim3(unsigned((N + 255) / 256)), dim3(256), 0,
+                        static_cast<const float*>(ws), bands, int(N), static_cast<float*>(out)));
   } else {
     colsum_stage1_kernel<double><<<dim3(col_blocks, bands), 256, 0, h->stream>>>(
         static_cast<const double*>(X), N, int(M), int(N), rows_per_band, static_cast<double*>(ws));
-    colsum_stage2_kernel<double><<<int((N + 255) / 256), 256, 0, h->stream>>>(
-        static_cast<const double*>(ws), bands, int(N), static_cast<double*>(out));
+    MTB_CUDA(launch_pdl(h, colsum_stage2_kernel<double>, dim3(unsigned((N + 255) / 256)), dim3(256), 0,
+                        static_cast<const double*>(ws), bands, int(N), static_cast<double*>(out)));
   }
   MTB_CUDA(cudaGetLastError());
   return MTB200_OK;

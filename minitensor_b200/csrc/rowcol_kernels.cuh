@@ -1,6 +1,7 @@
 // HBM-bound kernels either side of the GEMMs in a training step: bias-gradient
 // column sum, activation forward/backward, fused cross-entropy, Adam.
 #pragma once
+#include "ptx_sm100.cuh"
 #include <cstdint>
 #include <cuda_runtime.h>
 
@@ -21,6 +22,7 @@ __global__ void __launch_bounds__(256) colsum_stage1_kernel(const T* __restrict_
   constexpr int V = 16 / sizeof(T);  // elements per 16-byte vector
   constexpr int COLS = 8 * V;        // columns per block
   __shared__ T red[8][COLS];
+  grid_launch_dependents();          // stage 2 may set itself up meanwhile; it waits before it reads
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int rl = lane >> 3, cg = lane & 7;
   const int col = blockIdx.x * COLS + cg * V;
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(256) colsum_stage1_kernel(const T* __restrict_
 template <typename T>
 __global__ void colsum_stage2_kernel(const T* __restrict__ partial, int bands, int N,
                                      T* __restrict__ out) {
+  grid_dependency_wait();        // the partials come from the kernel before this one (no-op in a plain launch)
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= N) return;
   T s = T(0);
