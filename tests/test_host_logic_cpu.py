@@ -145,3 +145,34 @@ def test_host_binding_follows_nvml_and_never_raises(monkeypatch):
         assert os.sched_getaffinity(0) == before
     finally:
         os.sched_setaffinity(0, before)
+
+
+def test_traffic_records_are_folded_from_ncu_csv(tmp_path, monkeypatch):
+    """bench.record_traffic: the long CSV form ncu writes with --csv --log-file (one row per launch and metric,
+    units in their own column) becomes a per-launch mean in profiles/dram_traffic.json; expressions joined by
+    ' + ' record the sum of their means (a call made of a tensor kernel and its fix-up)."""
+    import json
+    import bench
+    (tmp_path / "profiles").mkdir()
+    monkeypatch.setattr(bench, "ROOT", str(tmp_path))
+    rows = ['"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size",'
+            '"Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"']
+    def add(i, kernel, name, unit, value):
+        rows.append(f'"{i}","1","python","box","{kernel}","1","7","(256, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","{name}","{unit}","{value}"')
+    add(0, "void mtb::gemm_split_umma2_kernel<64, 3>(A)", "dram__bytes_read.sum", "Mbyte", "300")
+    add(0, "void mtb::gemm_split_umma2_kernel<64, 3>(A)", "dram__bytes_write.sum", "Mbyte", "40")
+    add(0, "void mtb::gemm_split_umma2_kernel<64, 3>(A)", "gpu__time_duration.sum", "us", "270")
+    add(1, "mtb::tail_fixup_kernel(G)", "dram__bytes_read.sum", "Kbyte", "9,000")
+    add(1, "mtb::tail_fixup_kernel(G)", "dram__bytes_write.sum", "byte", "11000000")
+    add(2, "void mtb::gemm_split_umma2_kernel<64, 3>(A)", "dram__bytes_read.sum", "Mbyte", "320")
+    add(2, "void mtb::gemm_split_umma2_kernel<64, 3>(A)", "dram__bytes_write.sum", "Mbyte", "40")
+    csv_path = tmp_path / "list.csv"
+    csv_path.write_text("==PROF== banner line\n" + "\n".join(rows) + "\n")
+    rec = bench.record_traffic(str(csv_path), "k.only", "gemm_split_umma2", "ncu ... cmd")
+    assert rec["launches_captured"] == 2 and abs(rec["dram_bytes_per_launch"] - 350e6) < 1
+    rec = bench.record_traffic(str(csv_path), "k.call", "gemm_split_umma2 + tail_fixup", "ncu ... cmd")
+    assert abs(rec["dram_bytes_per_launch"] - (350e6 + 20e6)) < 1 and rec["launches_captured"] == 3
+    data = json.load(open(tmp_path / "profiles" / "dram_traffic.json"))
+    assert set(data) == {"k.only", "k.call"} and data["k.call"]["command"] == "ncu ... cmd"
+    with pytest.raises(SystemExit):
+        bench.record_traffic(str(csv_path), "k.none", "no_such_kernel", "cmd")
